@@ -1,0 +1,231 @@
+/* C ABI of the B200 implementation of vkllama's Llama-2 token loop.
+ *
+ * Every entry point is plain C: opaque handles, pointers, sizes. Functions
+ * return a status code (0 = OK; the other values are absl::StatusCode numbers,
+ * which is what the reference's ops return) and leave a message retrievable
+ * with vkl_last_error() on the calling thread. Nothing throws across this
+ * boundary. Citations name the reference interface each group replaces, by its
+ * path inside the vkllama tree.
+ *
+ * Execution model (reference: src/core/command.h:26-483): ops only enqueue
+ * work on their command's CUDA stream between vkl_command_begin() and
+ * vkl_command_end(); results and host copies are valid after
+ * vkl_command_wait(). Callers are single-threaded per command, as in the
+ * reference. A CUDA device is required: there is no CPU fallback.
+ */
+#ifndef VKLLAMA_B200_H_
+#define VKLLAMA_B200_H_
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct vkl_device vkl_device;
+typedef struct vkl_tensor vkl_tensor;
+typedef struct vkl_command vkl_command;
+typedef struct vkl_op vkl_op;
+typedef struct vkl_model vkl_model;
+
+/* src/core/common.h:15-22 (enum DType), same numeric values. */
+enum vkl_dtype { VKL_FP32 = 0, VKL_FP16 = 1, VKL_UINT32 = 2, VKL_INT8 = 3, VKL_Q8_0 = 4 };
+
+/* absl::StatusCode values used by the reference's ops. */
+enum vkl_status {
+  VKL_OK = 0,
+  VKL_INVALID_ARGUMENT = 3,
+  VKL_RESOURCE_EXHAUSTED = 8,
+  VKL_FAILED_PRECONDITION = 9,
+  VKL_OUT_OF_RANGE = 11,
+  VKL_UNIMPLEMENTED = 12,
+  VKL_INTERNAL = 13
+};
+
+const char *vkl_last_error(void);
+/* Number of kernels this library has launched in the calling process. */
+uint64_t vkl_kernel_launches(void);
+
+/* ---- device: GPUDevice, src/core/gpu_device.h:13-62 ---------------------- */
+int vkl_device_create(int ordinal, vkl_device **out);
+int vkl_device_destroy(vkl_device *dev);
+/* name: at least 256 bytes. */
+int vkl_device_info(vkl_device *dev, char *name, int *sm_count, size_t *total_mem);
+
+/* ---- tensor: Tensor, src/core/tensor.h:16-90 ------------------------------
+ * Shape [c,h,w], row-major, strides in bytes (tensor.cpp:248-258). A handle is
+ * reference counted (tensor.cpp:38-84, 355-366); views share the buffer and
+ * keep the parent's strides (tensor.cpp:294-302). Q8_0 tensors are uploaded
+ * and downloaded as GGUF blocks (fp16 scale + 32 int8 = 34 bytes,
+ * src/shaders/common.h:8-10); their device layout is private. */
+int vkl_tensor_create(vkl_device *dev, int c, int h, int w, int dtype, vkl_tensor **out);
+int vkl_tensor_retain(vkl_tensor *t);
+int vkl_tensor_release(vkl_tensor *t);
+int vkl_tensor_view(vkl_tensor *t, size_t c, size_t h, size_t w, vkl_tensor **out);
+int vkl_tensor_reshape(vkl_tensor *t, size_t c, size_t h, size_t w);
+/* out6: c, h, w, cs, hs, ws (ShapeConstant, common.h:24-27). */
+int vkl_tensor_shape(vkl_tensor *t, uint32_t out6[6]);
+int vkl_tensor_dtype(vkl_tensor *t, int *dtype);
+/* Bytes a host copy of the tensor takes (Q8_0: 34 per block). */
+int vkl_tensor_bytes(vkl_tensor *t, size_t *bytes);
+/* Raw device pointer of element (0,0,0); for interop with a caller's CUDA code. */
+int vkl_tensor_device_ptr(vkl_tensor *t, void **ptr);
+
+/* ---- command: Command, src/core/command.h:26-483 ------------------------- */
+int vkl_command_create(vkl_device *dev, vkl_command **out);
+int vkl_command_destroy(vkl_command *cmd);
+int vkl_command_begin(vkl_command *cmd);
+int vkl_command_end(vkl_command *cmd);
+int vkl_command_submit(vkl_command *cmd);
+int vkl_command_wait(vkl_command *cmd);
+int vkl_command_submit_and_wait(vkl_command *cmd);
+/* upload_bytes / download (command.h:141-260): host memory is copied through
+ * pinned staging; a download lands in `host` when vkl_command_wait returns. */
+int vkl_command_upload(vkl_command *cmd, const void *host, size_t bytes, vkl_tensor *to);
+int vkl_command_download(vkl_command *cmd, vkl_tensor *from, void *host, size_t bytes);
+
+/* ---- ops: class Op, src/ops/op.h:14-25 ------------------------------------
+ * create = constructor, vkl_op_init = Op::init(), run = operator(), vkl_op_time
+ * = Op::time() (device microseconds of the op's last run, valid after wait).
+ * Output tensors are owned by the op and reused while the shape is unchanged
+ * (e.g. mat_mul.cpp:189-194); *out is a borrowed handle, valid until the op
+ * runs with another shape or is destroyed (retain it to keep it longer). */
+int vkl_op_init(vkl_op *op);
+int vkl_op_time(vkl_op *op, uint64_t *usec);
+int vkl_op_destroy(vkl_op *op);
+
+/* MatMul, src/ops/mat_mul.h:12-27. weight may be NULL (two-operand form). */
+int vkl_matmul_create(vkl_device *dev, vkl_command *cmd, vkl_tensor *weight, float scale,
+                      float bias, int act, int broadcast_type, int transpose_b, int a_dtype,
+                      int b_dtype, vkl_op **out);
+int vkl_matmul_run(vkl_op *op, vkl_tensor *a, vkl_tensor *b, vkl_tensor **out);
+
+/* FeedForward, src/ops/feed_forward.h:17-22 (w1 = gate, w2 = down, w3 = up). */
+int vkl_feed_forward_create(vkl_device *dev, vkl_command *cmd, vkl_tensor *w1, vkl_tensor *w2,
+                            vkl_tensor *w3, int transposed_weight, int dtype, vkl_op **out);
+int vkl_feed_forward_run(vkl_op *op, vkl_tensor *x, vkl_tensor **out);
+
+/* MultiHeadAttentionV2, src/ops/multiheadattention_v2.h:25-35. */
+int vkl_mha_create(vkl_device *dev, vkl_command *cmd, vkl_tensor *wk, vkl_tensor *wq,
+                   vkl_tensor *wv, vkl_tensor *wo, int maxlen, int dim, int transposed_weight,
+                   int dtype, int use_kvcache, int clip_output, vkl_op **out);
+int vkl_mha_run(vkl_op *op, vkl_tensor *x, size_t offset, vkl_tensor **out);
+/* The op's caches [heads, maxlen, dim] (kcache_/vcache_ members); borrowed. */
+int vkl_mha_caches(vkl_op *op, vkl_tensor **kcache, vkl_tensor **vcache);
+
+/* UpdateKVCache, src/ops/update_kv_cache.h:13-18. */
+int vkl_update_kvcache_create(vkl_device *dev, vkl_command *cmd, int dtype, vkl_op **out);
+int vkl_update_kvcache_run(vkl_op *op, vkl_tensor *cache, vkl_tensor *kv, uint32_t offset);
+
+/* RMSNorm, src/ops/rms_norm.h:12-16 (weight must be FP32, rms_norm.cpp:33). */
+int vkl_rms_norm_create(vkl_device *dev, vkl_command *cmd, vkl_tensor *weight, float eps,
+                        int dtype, vkl_op **out);
+int vkl_rms_norm_run(vkl_op *op, vkl_tensor *x, vkl_tensor **out);
+
+/* Rope, src/ops/rope.h:15-21: rotates `q` in place and returns it. */
+int vkl_rope_create(vkl_device *dev, vkl_command *cmd, int maxlen, int dim, int dtype,
+                    vkl_op **out);
+int vkl_rope_run(vkl_op *op, vkl_tensor *q, size_t offset, vkl_tensor **out);
+
+/* Softmax, src/ops/softmax.h:14-18 (temp is stored and unused, as in the reference). */
+int vkl_softmax_create(vkl_device *dev, vkl_command *cmd, int seq_mask, float temp, int dtype,
+                       vkl_op **out);
+int vkl_softmax_run(vkl_op *op, vkl_tensor *a, size_t offset, vkl_tensor **out);
+
+/* ArgOp<op_type>, src/ops/argop.h:13-156 (0 = ArgMax, 1 = ArgMin); output UINT32 [c,h,1]. */
+int vkl_argop_create(vkl_device *dev, vkl_command *cmd, int op_type, int dtype, vkl_op **out);
+int vkl_argop_run(vkl_op *op, vkl_tensor *in, vkl_tensor **out);
+
+/* Embedding, src/ops/embedding.h:13-18; indices UINT32 [1,H,W] -> FP16 [H,W,VW]. */
+int vkl_embedding_create(vkl_device *dev, vkl_command *cmd, vkl_tensor *vocab, uint32_t unk,
+                         int dtype, vkl_op **out);
+int vkl_embedding_run(vkl_op *op, vkl_tensor *indices, vkl_tensor **out);
+
+/* ElementWise, src/ops/elementwise.h:16-21: y <- x (type) y, type 0 add, 1 sub,
+ * 2 mul, 3 div; written into and returning the second operand. */
+int vkl_elementwise_create(vkl_device *dev, vkl_command *cmd, int type, int dtype, vkl_op **out);
+int vkl_elementwise_run(vkl_op *op, vkl_tensor *x, vkl_tensor *y, vkl_tensor **out);
+
+/* Transpose (type 0: [C,H,W] -> [H,C,W]), src/ops/transpose.h:14-19. */
+int vkl_transpose_create(vkl_device *dev, vkl_command *cmd, int type, int dtype, vkl_op **out);
+int vkl_transpose_run(vkl_op *op, vkl_tensor *in, vkl_tensor **out);
+
+/* Slice, src/ops/slice.h:13-18. */
+int vkl_slice_create(vkl_device *dev, vkl_command *cmd, int dtype, vkl_op **out);
+int vkl_slice_run(vkl_op *op, vkl_tensor *in, const uint32_t starts[3],
+                  const uint32_t extents[3], vkl_tensor **out);
+
+/* Cast, src/ops/cast.h:15-20 (FP16 -> FP32 and FP32 -> FP16). */
+int vkl_cast_create(vkl_device *dev, vkl_command *cmd, int from, int to, vkl_op **out);
+int vkl_cast_run(vkl_op *op, vkl_tensor *in, vkl_tensor **out);
+
+/* ---- host Q8_0 quantizer: src/core/quants.h:37-176 ------------------------
+ * blocks34: GGUF/device layout [fp16 scale][32 x int8]; blocks36: the
+ * reference's host layout [fp32 scale][32 x int8] (quants.cpp:14). The fp16
+ * scale is the fp32 scale rounded to nearest even. */
+int vkl_q8_0_quantize(const float *src, void *blocks34, size_t h, size_t w);
+int vkl_q8_0_quantize36(const float *src, void *blocks36, size_t h, size_t w);
+int vkl_q8_0_dequantize(const void *blocks34, float *dst, size_t h, size_t w);
+int vkl_q8_0_blocks36_to_34(const void *blocks36, void *blocks34, size_t n_blocks);
+/* Same quantizer on the device: FP32 [1,h,w] tensor -> Q8_0 [1,h,w] tensor. */
+int vkl_q8_0_quantize_device(vkl_command *cmd, vkl_tensor *src_fp32, vkl_tensor *dst_q8_0);
+
+/* Seeded synthetic tensor contents (stand-ins for checkpoints, which this
+ * library never ships): N(mean, std) for FP32/FP16/Q8_0 tensors, generated on
+ * the device, bit-identical to the host generator of the test oracle. */
+int vkl_tensor_fill_synthetic(vkl_command *cmd, vkl_tensor *t, uint64_t seed, uint64_t tensor_id,
+                              float mean, float stdv);
+
+/* ---- model: vkllama::Model, models/llama2.h:322-854 ------------------------ */
+typedef struct vkl_model_config {
+  uint32_t dim, heads, ffn, vocab, layers, maxlen;
+  float eps;          /* llama.attention.layer_norm_rms_epsilon (llama2.h:369) */
+  float final_eps;    /* the reference hard-codes 1e-6 for the output norm (llama2.h:268) */
+  int weight_dtype;   /* VKL_Q8_0 or VKL_FP16 */
+  int tp_rank, tp_size; /* tensor-parallel shard of this process (1 = single GPU) */
+} vkl_model_config;
+
+int vkl_model_create(vkl_device *dev, const vkl_model_config *cfg, vkl_model **out);
+int vkl_model_destroy(vkl_model *m);
+/* Model::init's per-tensor upload (llama2.h:401-677). `name` is the GGUF tensor
+ * name the reference looks up: token_embd.weight, output.weight,
+ * output_norm.weight, blk.N.{attn_norm,attn_q,attn_k,attn_v,attn_output,
+ * ffn_norm,ffn_gate,ffn_up,ffn_down}.weight. Data is the raw GGUF payload of
+ * the FULL tensor; a tensor-parallel rank keeps only its shard. */
+int vkl_model_set_weight(vkl_model *m, const char *name, int dtype, const void *data,
+                         size_t bytes);
+/* Fill every weight with the seeded synthetic model (N(0,wstd) matrices,
+ * 1+N(0,nstd) norm weights) without touching the host. */
+int vkl_model_synth_weights(vkl_model *m, uint64_t seed, float wstd, float nstd);
+/* Model::operator()(toks, offset) (llama2.h:683-843): host token ids in, fp32
+ * logits of the last token out (vocab floats), synchronous. */
+int vkl_model_forward(vkl_model *m, const uint32_t *toks, size_t n, size_t offset,
+                      float *logits_out);
+/* llama2_infer's loop (app/llama2_infer.cpp:141-210) with the greedy pick kept
+ * on the device: prefill `prompt`, then n_gen - 1 one-token steps, each step one
+ * replay of a captured CUDA graph. out_ids receives n_gen ids. If
+ * device_ms is not NULL it receives the device time of the decode steps only. */
+int vkl_model_generate(vkl_model *m, const uint32_t *prompt, size_t n_prompt, size_t n_gen,
+                       uint32_t *out_ids, float *prefill_ms, float *decode_ms);
+/* Copy one layer's caches [heads_local, maxlen, head_dim] fp16 to / from the host. */
+int vkl_model_read_kv(vkl_model *m, uint32_t layer, void *kcache, void *vcache);
+int vkl_model_write_kv(vkl_model *m, uint32_t layer, const void *kcache, const void *vcache);
+/* One decoder block on host hidden states (Llama2Block::operator(), llama2.h:160-213):
+ * x fp16 [T, dim] -> out fp16 [T, dim] (all rows; the reference's last block keeps the last). */
+int vkl_model_block_forward(vkl_model *m, uint32_t layer, const void *x_fp16, size_t T,
+                            size_t offset, void *out_fp16);
+/* Op::time() for the model path (models/llama2.h:816-841 prints per-op costs): one
+ * decode step run kernel by kernel with an event after each launch. out_us[8]:
+ * device microseconds summed over layers of 0 embedding, 1 RMSNorm+QKV,
+ * 2 RoPE+append+attention, 3 o_proj+residual, 4 RMSNorm+gate/up+SwiGLU,
+ * 5 down+residual, 6 RMSNorm+lm head, 7 arg-max. Appends to the KV cache at `offset`. */
+int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[8]);
+/* Tensor-parallel set-up: peer device pointers of every rank's exchange buffer
+ * (obtained by the caller through CUDA IPC), indexed by rank. */
+int vkl_model_tp_buffer(vkl_model *m, void **local_ptr, size_t *bytes);
+int vkl_model_tp_connect(vkl_model *m, void *const *peer_ptrs, int n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VKLLAMA_B200_H_ */

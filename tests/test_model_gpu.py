@@ -1,0 +1,172 @@
+"""Block- and model-level parity of the CUDA token loop against the CPU oracle:
+one Llama-2-7B-shaped block at position 511, a small model end to end (logits
+and greedy ids through prefill + decode), and the full 7B greedy ids against
+the committed oracle fixture (tests/golden/make_golden_7b.py)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+import vkllama_b200 as vk
+from util import LOGITS_MAX_ABS, assert_close, load_from_oracle
+
+pytestmark = pytest.mark.gpu
+
+SMALL = dict(dim=256, heads=4, ffn=512, vocab=1000, layers=3, maxlen=128)
+
+
+def small_pair(dev, seed=5, **over):
+    cfg = dict(SMALL, **over)
+    om = O.Model(seed=seed, **cfg)
+    dm = vk.Model(dev, cfg["dim"], cfg["heads"], cfg["ffn"], cfg["vocab"], cfg["layers"], cfg["maxlen"])
+    load_from_oracle(dm, om)
+    return om, dm, cfg
+
+
+def test_block_7b_shape_decode_at_position_511(dev):
+    """One decoder block with Llama-2-7B shapes, one decode step at position 511,
+    fp16 KV cache prefilled with N(0,1) for 511 positions."""
+    cfg = dict(dim=4096, heads=32, ffn=11008, vocab=64, layers=1, maxlen=512)
+    om = O.Model(seed=20240602, **cfg)
+    dm = vk.Model(dev, cfg["dim"], cfg["heads"], cfg["ffn"], cfg["vocab"], cfg["layers"], cfg["maxlen"])
+    load_from_oracle(dm, om)
+    k0 = O.synth_f16(20240602, 900, 32 * 512 * 128).reshape(32, 512, 128)
+    v0 = O.synth_f16(20240602, 901, 32 * 512 * 128).reshape(32, 512, 128)
+    om.kcache(0)[:] = k0
+    om.vcache(0)[:] = v0
+    dm.write_kv(0, k0, v0)
+    x = O.synth_f16(20240602, 902, 4096).reshape(1, 4096)
+    want = om.block(0, x, 1, 511)
+    got = dm.block_forward(0, x, 511)
+    assert_close(got, want, what="7B block @511")
+    gk, gv = dm.read_kv(0)
+    assert_close(gk[:, 511], om.kcache(0)[:, 511], tol=2e-3, what="appended k")
+    assert np.array_equal(gv[:, 511], om.vcache(0)[:, 511])
+    assert np.array_equal(gk[:, :511], k0[:, :511])
+
+
+@pytest.mark.parametrize("T,offset", [(1, 0), (9, 0), (64, 0), (70, 0)])
+def test_block_multi_token(dev, T, offset):
+    om, dm, cfg = small_pair(dev, seed=6)
+    x = O.synth_f16(6, 700 + T, T * cfg["dim"]).reshape(T, cfg["dim"])
+    want = om.block(1, x, T, offset)
+    got = dm.block_forward(1, x, offset)
+    assert_close(got, want, what="block T=%d" % T)
+
+
+def test_small_model_logits_prefill_then_decode(dev):
+    om, dm, cfg = small_pair(dev, seed=7)
+    prompt = O.synth_tokens(7, 1000, 12, cfg["vocab"])
+    want = om.forward(prompt, 0)
+    got = dm(prompt, 0)
+    assert np.abs(got - want).max() <= LOGITS_MAX_ABS
+    tok = np.array([int(np.argmax(want))], np.uint32)
+    for i in range(5):
+        want = om.forward(tok, 12 + i)
+        got = dm(tok, 12 + i)
+        assert np.abs(got - want).max() <= LOGITS_MAX_ABS, "decode step %d" % i
+        tok = np.array([int(np.argmax(want))], np.uint32)
+    for l in range(cfg["layers"]):
+        gk, gv = dm.read_kv(l)
+        assert_close(gk[:, :17], om.kcache(l)[:, :17], tol=5e-3, what="kcache layer %d" % l)
+        assert_close(gv[:, :17], om.vcache(l)[:, :17], tol=5e-3, what="vcache layer %d" % l)
+
+
+@pytest.mark.parametrize("seed,P,n_gen", [(8, 9, 40), (9, 1, 20), (10, 33, 64)])
+def test_small_model_greedy_ids_match_oracle(dev, seed, P, n_gen):
+    om, dm, cfg = small_pair(dev, seed=seed)
+    prompt = O.synth_tokens(seed, 1000, P, cfg["vocab"])
+    want, gap = om.generate(prompt, n_gen)
+    got, pre_ms, dec_ms = dm.generate(prompt, n_gen)
+    bad = np.nonzero(got != want)[0]
+    assert bad.size == 0, "first mismatch at step %d (oracle top-2 gap there %.4f)" % (bad[0], gap[bad[0]])
+    # the generate loop and the host-driven loop (Model::operator() per token) agree
+    logits = dm(prompt, 0)
+    assert int(np.argmax(logits)) == int(got[0])
+
+
+def test_generate_matches_host_driven_loop(dev):
+    om, dm, cfg = small_pair(dev, seed=11)
+    prompt = O.synth_tokens(11, 1000, 7, cfg["vocab"])
+    ids, _, _ = dm.generate(prompt, 12)
+    logits = dm(prompt, 0)
+    tok = int(np.argmax(logits))
+    host = [tok]
+    for i in range(1, 12):
+        logits = dm(np.array([tok], np.uint32), 7 + i - 1)
+        tok = int(np.argmax(logits))
+        host.append(tok)
+    assert host == ids.tolist()
+
+
+def test_device_synth_weights_equal_uploaded_oracle_weights(dev):
+    om, dm, cfg = small_pair(dev, seed=12)
+    dm2 = vk.Model(dev, cfg["dim"], cfg["heads"], cfg["ffn"], cfg["vocab"], cfg["layers"], cfg["maxlen"])
+    dm2.synth_weights(12)
+    prompt = O.synth_tokens(12, 1000, 10, cfg["vocab"])
+    a = dm(prompt, 0)
+    b = dm2(prompt, 0)
+    assert np.array_equal(a, b)
+
+
+def test_model_errors(dev):
+    dm = vk.Model(dev, 256, 4, 512, 1000, 1, 32)
+    with pytest.raises(vk.VklError) as e:  # weights not set
+        dm(np.array([1], np.uint32), 0)
+    assert e.value.code == 9
+    with pytest.raises(vk.VklError) as e:
+        dm.set_weight("blk.7.attn_q.weight", vk.Q8_0, np.zeros(34, np.uint8))
+    assert e.value.code == 3
+    with pytest.raises(vk.VklError) as e:  # wrong byte count
+        dm.set_weight("blk.0.attn_q.weight", vk.Q8_0, np.zeros(34, np.uint8))
+    assert e.value.code == 3
+    dm.synth_weights(1)
+    with pytest.raises(vk.VklError) as e:  # beyond the context length
+        dm(np.zeros(33, np.uint32), 0)
+    assert e.value.code == 11
+
+
+GOLD7B = os.path.join(os.path.dirname(__file__), "golden", "llama2_7b_q8_0_greedy.npz")
+
+
+@pytest.fixture(scope="module")
+def model7b(dev):
+    if not os.path.exists(GOLD7B):
+        pytest.skip("7B oracle fixture not generated")
+    g = np.load(GOLD7B)
+    dm = vk.Model(dev, 4096, 32, 11008, 32000, 32, 4096)
+    dm.synth_weights(int(g["seed"]))
+    yield g, dm
+    dm.close()
+
+
+def test_llama2_7b_q8_0_greedy_ids_match_oracle_fixture(model7b):
+    """Full Llama-2-7B shape, Q8_0, 32-token prompt, 64 free-running greedy tokens
+    against ids computed by the CPU oracle (prompt selected so that the oracle's own
+    top-2 gap stays >= 2 fp16 ulps; see tests/golden/make_golden_7b.py)."""
+    g, dm = model7b
+    prompt = g["sel_prompt"]
+    logits = dm(prompt, 0)
+    assert np.abs(logits - g["sel_prefill_logits"]).max() <= LOGITS_MAX_ABS
+    n = len(g["sel_ids"])
+    got, pre_ms, dec_ms = dm.generate(prompt, n)
+    bad = np.nonzero(got != g["sel_ids"])[0]
+    assert bad.size == 0, "first mismatch at step %d (oracle top-2 gap there %.4f)" % (bad[0], g["sel_gap"][bad[0]])
+
+
+def test_llama2_7b_q8_0_teacher_forced_steps(model7b):
+    """Unselected base prompt, teacher-forced with the oracle's ids: every step whose
+    oracle top-2 gap exceeds 2 fp16 ulps must pick the oracle's id."""
+    g, dm = model7b
+    prompt, ids, gap = g["base_prompt"], g["base_ids"], g["base_gap"]
+    logits = dm(prompt, 0)
+    assert np.abs(logits - g["base_prefill_logits"]).max() <= LOGITS_MAX_ABS
+    picks = [int(np.argmax(logits))]
+    for i in range(1, len(ids)):
+        logits = dm(np.array([ids[i - 1]], np.uint32), len(prompt) + i - 1)
+        picks.append(int(np.argmax(logits)))
+    picks = np.array(picks)
+    decided = gap > 2.0 / 128.0
+    assert np.array_equal(picks[decided], ids[decided])
+    assert (picks == ids).mean() >= 0.9

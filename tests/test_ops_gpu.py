@@ -1,0 +1,445 @@
+"""Per-op parity of the CUDA ops (through the C ABI) against the CPU oracle, at
+the reference's own test shapes (tests/test_*.cpp of vkllama) and at the
+Llama-2-7B shapes. Tolerance: max |a-b| / max |b| <= 1e-2 on fp16 outputs;
+Q8_0 codes and scales, indices and copies are compared bit for bit."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+import vkllama_b200 as vk
+from util import assert_close, up
+
+pytestmark = pytest.mark.gpu
+
+
+def run(cmd, fn):
+    cmd.begin()
+    res = fn()
+    cmd.end()
+    cmd.submit_and_wait()
+    return res
+
+
+# ---- Q8_0 layout / quantizer ------------------------------------------------
+@pytest.mark.parametrize("N,K", [(1, 32), (17, 256), (16, 95), (33, 4096), (4096, 4096)])
+def test_q8_0_upload_download_round_trip_is_bit_exact(dev, N, K):
+    w = O.synth_q8_0(3, 7, N, K)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    t = up(cmd, dev, w, vk.Q8_0, 1, N, K)
+    back = cmd.download(t)
+    cmd.end()
+    cmd.submit_and_wait()
+    assert np.array_equal(back, w)
+
+
+@pytest.mark.parametrize("N,K", [(3, 95), (64, 4096), (8, 11008)])
+def test_device_quantizer_is_bit_exact_with_reference_quantizer(dev, N, K):
+    x = O.synth_f32(21, 4, N * K, 0.0, 0.02).reshape(N, K)
+    want = O.quantize34(x)  # pinned to the reference's quants.h by the CPU tests
+    cmd = vk.Command(dev)
+    cmd.begin()
+    src = up(cmd, dev, x, vk.FP32, 1, N, K)
+    dst = vk.Tensor(1, N, K, dev, vk.Q8_0)
+    cmd.q8_0_quantize(src, dst)
+    got = cmd.download(dst)
+    cmd.end()
+    cmd.submit_and_wait()
+    assert np.array_equal(got, want)
+
+
+def test_device_synthetic_generator_matches_host_generator(dev):
+    cmd = vk.Command(dev)
+    cmd.begin()
+    a = vk.Tensor(1, 7, 333, dev, vk.FP32)
+    b = vk.Tensor(1, 5, 96, dev, vk.FP16)
+    c = vk.Tensor(1, 48, 4096, dev, vk.Q8_0)
+    cmd.fill_synthetic(a, 5, 1, 1.0, 0.01)
+    cmd.fill_synthetic(b, 5, 2, 0.0, 1.0)
+    cmd.fill_synthetic(c, 5, 3, 0.0, 0.02)
+    ga, gb, gc = cmd.download(a), cmd.download(b), cmd.download(c)
+    cmd.end()
+    cmd.submit_and_wait()
+    assert np.array_equal(ga.ravel(), O.synth_f32(5, 1, 7 * 333, 1.0, 0.01))
+    assert np.array_equal(gb.ravel(), O.synth_f16(5, 2, 5 * 96, 0.0, 1.0))
+    assert np.array_equal(gc, O.synth_q8_0(5, 3, 48, 4096, 0.0, 0.02))
+
+
+# ---- MatMul with a Q8_0 weight (tests/test_matmul.cpp Q8_0 cases; 7B shapes) --
+@pytest.mark.parametrize("M,N,K,act", [
+    (1, 4096, 4096, 0), (1, 11008, 4096, 0), (1, 4096, 11008, 0), (1, 32000, 4096, 0),
+    (2, 4096, 4096, 0), (8, 4096, 4096, 1), (9, 17, 256, 0), (16, 4096, 4096, 0), (33, 1000, 4096, 0),
+    (64, 4096, 4096, 0), (100, 256, 11008, 0), (5, 16, 32, 0), (3, 50, 96, 1)])
+def test_matmul_q8_0(dev, M, N, K, act):
+    w = O.synth_q8_0(31, 1, N, K)
+    x = O.synth_f16(31, 2, M * K).reshape(M, K)
+    want = O.matmul_q8_0(x, w, M, N, K, 1.0, 0.0, act)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tw = up(cmd, dev, w, vk.Q8_0, 1, N, K)
+    tx = up(cmd, dev, x, vk.FP16, 1, M, K)
+    op = vk.MatMul(dev, cmd, tw, 1.0, 0.0, act, 0, True, vk.FP16, vk.Q8_0).init()
+    got = cmd.download(op(tx))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert got.shape == (1, M, N)
+    assert_close(got, want, what="matmul_q8_0 %s" % ((M, N, K),))
+    assert op.time() >= 0
+
+
+def test_matmul_q8_0_k_not_multiple_of_32(dev):
+    M, N, K = 3, 20, 95  # tail block padded with zero codes (quants.h:79-84)
+    xf = O.synth_f32(8, 1, N * K, 0.0, 0.02).reshape(N, K)
+    w = O.quantize34(xf)
+    x = O.synth_f16(8, 2, M * K).reshape(M, K)
+    want = O.matmul_q8_0(x, w, M, N, K)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tw = up(cmd, dev, w, vk.Q8_0, 1, N, K)
+    tx = up(cmd, dev, x, vk.FP16, 1, M, K)
+    op = vk.MatMul(dev, cmd, tw, 1.0, 0.0, 0, 0, True, vk.FP16, vk.Q8_0).init()
+    got = cmd.download(op(tx))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert_close(got, want, what="matmul_q8_0 ragged K")
+
+
+# ---- MatMul fp16 x fp16 (tests/test_matmul.cpp:191: C1 M9 N9 K128, transpose_b) --
+@pytest.mark.parametrize("C,M,N,K,tb", [(1, 9, 9, 128, True), (32, 1, 512, 128, True), (32, 1, 128, 512, False),
+                                          (3, 5, 7, 100, False), (2, 4, 6, 70, True)])
+def test_matmul_fp16_pair(dev, C, M, N, K, tb):
+    a = O.synth_f16(41, 1, C * M * K).reshape(C, M, K)
+    bshape = (C, N, K) if tb else (C, K, N)
+    b = O.synth_f16(41, 2, C * N * K).reshape(bshape)
+    want = np.empty(C * M * N, np.uint16)
+    f = O.lib().orc_matmul_tb_f16 if tb else O.lib().orc_matmul_nn_f16
+    f(a, b, want, C, M, N, K, M * K, K, N * K, K if tb else N, M * N, N, 0.5, 0.0, 0)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    ta = up(cmd, dev, a, vk.FP16, C, M, K)
+    tb_ = up(cmd, dev, b, vk.FP16, *bshape)
+    op = vk.MatMul(dev, cmd, None, 0.5, 0.0, 0, 0, tb, vk.FP16, vk.FP16).init()
+    got = cmd.download(op(ta, tb_))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert_close(got, want, what="matmul fp16")
+
+
+def test_matmul_fp16_weight(dev):
+    M, N, K = 3, 100, 256
+    a = O.synth_f16(42, 1, M * K).reshape(1, M, K)
+    w = O.synth_f16(42, 2, N * K, 0.0, 0.02).reshape(1, N, K)
+    want = np.empty(M * N, np.uint16)
+    O.lib().orc_matmul_tb_f16(a, w, want, 1, M, N, K, M * K, K, N * K, K, M * N, N, 1.0, 0.0, 0)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    ta = up(cmd, dev, a, vk.FP16, 1, M, K)
+    tw = up(cmd, dev, w, vk.FP16, 1, N, K)
+    op = vk.MatMul(dev, cmd, tw, 1.0, 0.0, 0, 0, True, vk.FP16, vk.FP16).init()
+    got = cmd.download(op(ta))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert_close(got, want, what="matmul fp16 weight")
+
+
+# ---- FeedForward (tests/test_feedforward.cpp:143-148 Q8_0: dims 16,8,256,17; 7B) --
+@pytest.mark.parametrize("M,dim,hidden", [(64, 32, 256), (1, 4096, 11008), (4, 4096, 11008), (17, 64, 96)])
+def test_feed_forward_q8_0(dev, M, dim, hidden):
+    gate = O.synth_q8_0(51, 1, hidden, dim)
+    down = O.synth_q8_0(51, 2, dim, hidden)
+    upw = O.synth_q8_0(51, 3, hidden, dim)
+    x = O.synth_f16(51, 4, M * dim).reshape(M, dim)
+    want = np.empty(M * dim, np.uint16)
+    O.lib().orc_feed_forward_q8_0(x, gate, down, upw, want, M, dim, hidden)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    w1 = up(cmd, dev, gate, vk.Q8_0, 1, hidden, dim)
+    w2 = up(cmd, dev, down, vk.Q8_0, 1, dim, hidden)
+    w3 = up(cmd, dev, upw, vk.Q8_0, 1, hidden, dim)
+    tx = up(cmd, dev, x, vk.FP16, 1, M, dim)
+    op = vk.FeedForward(dev, cmd, w1, w2, w3, True, vk.Q8_0).init()
+    got = cmd.download(op(tx))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert_close(got, want, what="feed_forward")
+
+
+# ---- RMSNorm (tests/test_rmsnorm.cpp:100-105: [1,1,128]; 7B rows) -------------
+@pytest.mark.parametrize("rows,W,eps", [(1, 128, 1e-3), (1, 4096, 1e-5), (33, 4096, 1e-5), (5, 100, 1e-6)])
+def test_rms_norm(dev, rows, W, eps):
+    x = O.synth_f16(61, 1, rows * W).reshape(rows, W)
+    w = O.synth_f32(61, 2, W, 1.0, 0.01)
+    want = np.empty(rows * W, np.uint16)
+    O.lib().orc_rms_norm_f16(x, w, want, rows, W, eps)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tw = up(cmd, dev, w, vk.FP32, 1, 1, W)
+    tx = up(cmd, dev, x, vk.FP16, 1, rows, W)
+    op = vk.RMSNorm(dev, cmd, tw, eps, vk.FP16).init()
+    got = cmd.download(op(tx))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert_close(got, want, tol=2e-3, what="rms_norm")
+
+
+# ---- Rope (tests/test_rope.cpp:211-217: [32,{8,25,13},100], offsets 0/100/1020) --
+@pytest.mark.parametrize("C,H,W,maxlen,offset", [(32, 8, 100, 2048, 0), (32, 25, 100, 1024, 100),
+                                                  (32, 13, 100, 2048, 1020), (32, 1, 128, 4096, 511)])
+def test_rope(dev, C, H, W, maxlen, offset):
+    x = O.synth_f16(71, 1, C * H * W).reshape(C, H, W)
+    fc = np.empty(2 * maxlen * W // 2, np.float32)
+    fs = np.empty_like(fc)
+    O.lib().orc_rope_table(W, 2 * maxlen, fc, fs)
+    want = x.copy()
+    O.lib().orc_rope_f16(want, C, H, W, offset, fc, fs)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tx = up(cmd, dev, x, vk.FP16, C, H, W)
+    op = vk.Rope(dev, cmd, maxlen, W, vk.FP16).init()
+    out = op(tx, offset)
+    got = cmd.download(out)
+    got_in_place = cmd.download(tx)
+    cmd.end()
+    cmd.submit_and_wait()
+    assert_close(got, want, tol=1e-3, what="rope")
+    assert np.array_equal(got, got_in_place)
+
+
+# ---- Softmax (tests/test_softmax.cpp: [32,62,62], [1,1023,63], [3,1023,51]) ----
+@pytest.mark.parametrize("C,H,W,mask", [(32, 62, 62, False), (1, 1023, 63, False), (3, 1023, 51, False),
+                                          (32, 62, 62, True), (32, 1, 512, True), (4, 8, 40, True)])
+def test_softmax(dev, C, H, W, mask):
+    x = O.synth_f16(81, 1, C * H * W).reshape(C, H, W)
+    off = W - H if mask else 0
+    want = np.empty_like(x)
+    O.lib().orc_softmax_f16(x, want, C, H, W, int(mask), off)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tx = up(cmd, dev, x, vk.FP16, C, H, W)
+    op = vk.Softmax(dev, cmd, mask, 1.0, vk.FP16).init()
+    got = cmd.download(op(tx, off))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert_close(got, want, what="softmax")
+    if mask:
+        assert np.array_equal(got == 0, want == 0)
+
+
+# ---- ArgMax / ArgMin (tests/test_argop.cpp: [1 or 3, 1023, 511]; vocab row) -----
+@pytest.mark.parametrize("C,H,W", [(1, 1023, 511), (3, 1023, 511), (1, 1, 32000), (1, 2, 5)])
+@pytest.mark.parametrize("op_type", [0, 1])
+def test_argop(dev, C, H, W, op_type):
+    x = O.synth_f16(91, 1, C * H * W).reshape(C, H, W)
+    xf = O.f16(x).reshape(C * H, W)
+    want = (np.argmax(xf, 1) if op_type == 0 else np.argmin(xf, 1)).astype(np.uint32)  # first index on ties
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tx = up(cmd, dev, x, vk.FP16, C, H, W)
+    op = vk.ArgOp(dev, cmd, op_type, vk.FP16).init()
+    got = cmd.download(op(tx))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert got.shape == (C, H, 1)
+    assert np.array_equal(got.ravel(), want)
+    if op_type == 0:
+        o = np.empty(C * H, np.uint32)
+        O.lib().orc_argmax_f16(x, o, C * H, W)
+        assert np.array_equal(o, want)
+
+
+def test_argmax_ties_pick_lowest_index(dev):
+    x = np.zeros((1, 3, 5000), np.float32)
+    x[0, 0, [4000, 77, 4999]] = 2.0
+    x[0, 1, :] = 1.0
+    x[0, 2, [1024, 1023]] = 3.0
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tx = up(cmd, dev, O.bits(x), vk.FP16, 1, 3, 5000)
+    op = vk.ArgMax(dev, cmd, vk.FP16).init()
+    got = cmd.download(op(tx))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert got.ravel().tolist() == [77, 0, 1023]
+
+
+# ---- Embedding (tests/test_embedding.cpp: ids [55x19],[123x128], vocab 20000x64) --
+@pytest.mark.parametrize("H,W,VH,VW,q8", [(55, 19, 20000, 64, True), (123, 128, 20000, 64, False),
+                                           (1, 1, 32000, 4096, True), (1, 32, 32000, 4096, True)])
+def test_embedding(dev, H, W, VH, VW, q8):
+    ids = O.synth_tokens(101, 1, H * W, VH + 50)  # some ids >= VH map to UNK
+    ids[0] = VH + 7
+    unk = 3
+    want = np.empty(H * W * VW, np.uint16)
+    if q8:
+        vocab = O.synth_q8_0(101, 2, VH, VW, 0.0, 1.0)
+        O.lib().orc_embedding_q8_0(vocab, ids, want, H * W, VH, VW, unk)
+    else:
+        vocab = O.synth_f16(101, 2, VH * VW)
+        O.lib().orc_embedding_f16(vocab, ids, want, H * W, VH, VW, unk)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tv = up(cmd, dev, vocab, vk.Q8_0 if q8 else vk.FP16, 1, VH, VW)
+    ti = up(cmd, dev, ids, vk.UINT32, 1, H, W)
+    op = vk.Embedding(dev, cmd, tv, unk, vk.Q8_0 if q8 else vk.FP16).init()
+    got = cmd.download(op(ti))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert got.shape == (H, W, VW)
+    assert np.array_equal(got.ravel(), want)  # a dequantised value is one exact product, one rounding
+
+
+# ---- UpdateKVCache (tests/test_update_kv_cache.cpp: heads 32, seq 25, maxlen 1024, dim 100, wrap) --
+@pytest.mark.parametrize("offset", [0, 500, 1022])
+def test_update_kvcache_with_wrap(dev, offset):
+    C, H, W, HO = 32, 25, 100, 1024
+    kv = O.synth_f16(111, 1, C * H * W).reshape(C, H, W)
+    cache0 = O.synth_f16(111, 2, C * HO * W).reshape(C, HO, W)
+    want = cache0.copy()
+    O.lib().orc_update_kvcache_f16(want, kv, C, H, W, HO, W, offset)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tc = up(cmd, dev, cache0, vk.FP16, C, HO, W)
+    tk = up(cmd, dev, kv, vk.FP16, C, H, W)
+    op = vk.UpdateKVCache(dev, cmd, vk.FP16).init()
+    op(tc, tk, offset)
+    got = cmd.download(tc)
+    cmd.end()
+    cmd.submit_and_wait()
+    assert np.array_equal(got, want)
+
+
+# ---- ElementWise add, Transpose, Slice, Cast ----------------------------------
+def test_elementwise_add_writes_into_second_operand(dev):
+    x = O.synth_f16(121, 1, 3 * 4096).reshape(1, 3, 4096)
+    y = O.synth_f16(121, 2, 3 * 4096).reshape(1, 3, 4096)
+    want = y.copy().ravel()
+    O.lib().orc_add_f16(x.ravel(), want, want.size)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tx, ty = up(cmd, dev, x, vk.FP16, 1, 3, 4096), up(cmd, dev, y, vk.FP16, 1, 3, 4096)
+    op = vk.ElementWise(dev, cmd, 0, vk.FP16).init()
+    out = op(tx, ty)
+    got, gy = cmd.download(out), cmd.download(ty)
+    cmd.end()
+    cmd.submit_and_wait()
+    assert np.array_equal(got.ravel(), want) and np.array_equal(gy.ravel(), want)
+
+
+def test_transpose_slice_cast(dev):
+    C, H, W = 5, 7, 33
+    x = O.synth_f16(131, 1, C * H * W).reshape(C, H, W)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tx = up(cmd, dev, x, vk.FP16, C, H, W)
+    tr = vk.Transpose(dev, cmd, 0, vk.FP16).init()
+    sl = vk.Slice(dev, cmd, vk.FP16).init()
+    ca = vk.Cast(dev, cmd, vk.FP16, vk.FP32).init()
+    cb = vk.Cast(dev, cmd, vk.FP32, vk.FP16).init()
+    g_t = cmd.download(tr(tx))
+    g_s = cmd.download(sl(tx, (1, 2, 3), (2, 4, 20)))
+    f32 = ca(tx)
+    g_c = cmd.download(f32)
+    g_b = cmd.download(cb(f32))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert np.array_equal(g_t, x.transpose(1, 0, 2))
+    assert np.array_equal(g_s, x[1:3, 2:6, 3:23])
+    assert np.array_equal(g_c, O.f16(x).reshape(C, H, W))
+    assert np.array_equal(g_b, x)
+
+
+# ---- MultiHeadAttentionV2 (no working test in the reference; oracle = its op chain) --
+@pytest.mark.parametrize("T,offset,clip", [(1, 0, False), (7, 0, False), (1, 7, False), (5, 8, False),
+                                            (6, 0, True), (1, 13, True)])
+def test_multiheadattention_q8_0_sequence(dev, T, offset, clip):
+    heads, dim, maxlen = 4, 64, 32
+    Wd = heads * dim
+    ws = [O.synth_q8_0(141, i, Wd, Wd, 0.0, 0.05) for i in range(4)]  # wk, wq, wv, wo
+    att = O.lib().orc_attn_create(heads, dim, maxlen)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tw = [up(cmd, dev, w, vk.Q8_0, 1, Wd, Wd) for w in ws]
+    op = vk.MultiHeadAttentionV2(dev, cmd, tw[0], tw[1], tw[2], tw[3], maxlen, dim, True, vk.FP16, True, clip).init()
+    cmd.end()
+    cmd.submit_and_wait()
+    # warm both sides with `offset` earlier tokens so the caches hold history
+    steps = ([(offset, 0)] if offset else []) + [(T, offset)]
+    for (t, off) in steps:
+        x = O.synth_f16(141, 10 + off, t * Wd).reshape(t, Wd)
+        want = np.empty((1 if clip else t) * Wd, np.uint16)
+        O.lib().orc_attn_forward_q8_0(att, x, ws[0], ws[1], ws[2], ws[3], t, off, int(clip), want)
+        cmd.begin()
+        tx = up(cmd, dev, x, vk.FP16, 1, t, Wd)
+        got = cmd.download(op(tx, off))
+        cmd.end()
+        cmd.submit_and_wait()
+    assert_close(got, want, what="mha T=%d offset=%d clip=%s" % (T, offset, clip))
+    kc, vc = op.caches()
+    cmd.begin()
+    gk, gv = cmd.download(kc), cmd.download(vc)
+    cmd.end()
+    cmd.submit_and_wait()
+    ok = np.ctypeslib.as_array(O.lib().orc_attn_kcache(att), shape=(heads, maxlen, dim))
+    ov = np.ctypeslib.as_array(O.lib().orc_attn_vcache(att), shape=(heads, maxlen, dim))
+    L = min(offset + T, maxlen)
+    assert_close(gk[:, :L], ok[:, :L], tol=2e-3, what="kcache")
+    assert np.array_equal(gv[:, :L], ov[:, :L])
+    O.lib().orc_attn_destroy(att)
+
+
+def test_multiheadattention_ring_wrap(dev):
+    heads, dim, maxlen = 2, 32, 8
+    Wd = heads * dim
+    ws = [O.synth_q8_0(151, i, Wd, Wd, 0.0, 0.05) for i in range(4)]
+    att = O.lib().orc_attn_create(heads, dim, maxlen)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tw = [up(cmd, dev, w, vk.Q8_0, 1, Wd, Wd) for w in ws]
+    op = vk.MultiHeadAttentionV2(dev, cmd, tw[0], tw[1], tw[2], tw[3], maxlen, dim, True, vk.FP16, True, False).init()
+    cmd.end()
+    cmd.submit_and_wait()
+    off = 0
+    for t in (6, 1, 1, 1, 1):  # positions 6..9 pass the end of the 8-row cache
+        x = O.synth_f16(151, 10 + off, t * Wd).reshape(t, Wd)
+        want = np.empty(t * Wd, np.uint16)
+        O.lib().orc_attn_forward_q8_0(att, x, ws[0], ws[1], ws[2], ws[3], t, off, 0, want)
+        cmd.begin()
+        tx = up(cmd, dev, x, vk.FP16, 1, t, Wd)
+        got = cmd.download(op(tx, off))
+        cmd.end()
+        cmd.submit_and_wait()
+        assert_close(got, want, what="mha wrap offset=%d" % off)
+        off += t
+    O.lib().orc_attn_destroy(att)
+
+
+# ---- argument checks keep the reference's status categories --------------------
+def test_op_errors(dev):
+    cmd = vk.Command(dev)
+    cmd.begin()
+    w32 = vk.Tensor(1, 1, 64, dev, vk.FP32)
+    w16 = vk.Tensor(1, 1, 64, dev, vk.FP16)
+    x32 = vk.Tensor(1, 2, 64, dev, vk.FP32)
+    with pytest.raises(vk.VklError) as e:  # rms_norm.cpp:33: weight must be FP32
+        vk.RMSNorm(dev, cmd, w16, 1e-5, vk.FP16).init()
+    assert e.value.code == 3
+    op = vk.RMSNorm(dev, cmd, w32, 1e-5, vk.FP16).init()
+    with pytest.raises(vk.VklError) as e:  # rms_norm.cpp:64: input dtype
+        op(x32)
+    assert e.value.code == 3
+    with pytest.raises(vk.VklError) as e:  # tensor.cpp:279: reshape size mismatch
+        x32.reshape(1, 3, 64)
+    assert e.value.code == 11
+    cache = vk.Tensor(2, 4, 8, dev, vk.FP16)
+    kv = vk.Tensor(2, 5, 8, dev, vk.FP16)
+    with pytest.raises(vk.VklError) as e:  # update_kv_cache.cpp:40: value larger than cache
+        vk.UpdateKVCache(dev, cmd, vk.FP16).init()(cache, kv, 0)
+    assert e.value.code == 11
+    with pytest.raises(vk.VklError) as e:  # mat_mul.cpp:130: unsupported dtype pair
+        vk.MatMul(dev, cmd, None, 1.0, 0.0, 0, 0, True, vk.FP32, vk.FP32).init()
+    assert e.value.code == 3
+    cmd.end()
+    cmd.submit_and_wait()
+    with pytest.raises(vk.VklError) as e:  # ops record only between begin() and end()
+        op(vk.Tensor(1, 2, 64, dev, vk.FP16))
+    assert e.value.code == 9

@@ -1,0 +1,108 @@
+// Host-callable launchers of every CUDA kernel in the library. All pointers are
+// device pointers; every launcher enqueues on `stream` and returns the CUDA
+// error of the launch (no synchronisation).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vkl {
+
+enum MvEpilogue { EPI_PLAIN = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+
+// Y = epilogue(X . W^T) for up to three Q8_0 (tiled planes) or FP16 (row-major)
+// weight matrices [N,K] sharing one input X [M,K].
+struct MvParams {
+  const uint8_t *codes[3];   // Q8_0: codes plane; FP16: row-major weights
+  const uint8_t *scales[3];  // Q8_0: scales plane; FP16: unused
+  __half *out[3];            // fp16 [M, out_ld] per matrix (SWIGLU: out[0] only)
+  float *out_f32;            // optional fp32 copy of out[0] (cast of the fp16 value)
+  const __half *x;           // [M, x_ld]
+  const __half *residual;    // EPI_ADD: [M, out_ld], may alias out[0]
+  const float *norm_w;       // fused RMSNorm weight [K] (decode path), or null
+  float eps;
+  uint32_t nmat;             // 1..3 matrices (SWIGLU: codes[0]=gate, codes[1]=up, nmat=1)
+  uint32_t N, K, M;
+  uint32_t x_ld, out_ld;
+  float scale, bias;
+  int act;                   // 1 = SiLU on the PLAIN epilogue
+  int fp16_weights;          // 0 = Q8_0 tiled planes, 1 = FP16 row-major
+  int use_pdl;               // programmatic dependent launch: prefetch weights before waiting
+};
+cudaError_t launch_matvec(const MvParams &p, int epilogue, bool fuse_norm_smem, cudaStream_t s);
+
+// 34-byte GGUF blocks <-> tiled planes (codes at dst, scales at dst + codes_bytes).
+cudaError_t launch_q8_repack(const uint8_t *blocks34, uint8_t *planes, uint32_t N, uint32_t K,
+                             cudaStream_t s);
+cudaError_t launch_q8_unpack(const uint8_t *planes, uint8_t *blocks34, uint32_t N, uint32_t K,
+                             cudaStream_t s);
+// fp32 [N,K] -> 34-byte blocks on the device (same arithmetic as the host quantizer).
+cudaError_t launch_q8_quantize(const float *src, uint8_t *blocks34, uint32_t N, uint32_t K,
+                               cudaStream_t s);
+// Seeded synthetic data, bit-identical to the host generator.
+cudaError_t launch_synth_f32(float *dst, uint64_t seed, uint64_t tensor, uint64_t first,
+                             uint64_t n, float mean, float stdv, cudaStream_t s);
+cudaError_t launch_synth_f16(__half *dst, uint64_t seed, uint64_t tensor, uint64_t first,
+                             uint64_t n, float mean, float stdv, cudaStream_t s);
+// Synthetic N(mean,std) matrix quantised straight into 34-byte blocks. The [N,K]
+// result is the window at (row0, col0) of a full matrix with `ld_full` columns
+// (element index = (row0+r)*ld_full + col0 + k), so a shard equals a slice.
+cudaError_t launch_synth_q8(uint8_t *blocks34, uint64_t seed, uint64_t tensor, uint32_t N,
+                            uint32_t K, float mean, float stdv, uint32_t row0, uint32_t col0,
+                            uint32_t ld_full, cudaStream_t s);
+
+cudaError_t launch_rms_norm(const __half *x, const float *w, __half *y, uint32_t rows,
+                            uint32_t W, float eps, cudaStream_t s);
+cudaError_t launch_add(const __half *x, __half *y, uint64_t n, int op, cudaStream_t s);
+cudaError_t launch_embedding(const uint8_t *vocab, int vocab_is_q8, const uint32_t *ids,
+                             __half *out, uint32_t T, uint32_t VH, uint32_t VW, uint32_t unk,
+                             cudaStream_t s);
+// Two-stage arg-max/min over rows of width W; partials needs rows*ceil(W/1024)*8 bytes.
+cudaError_t launch_argop(const __half *x, uint32_t *out, void *partials, uint32_t rows,
+                         uint32_t W, int op_type, cudaStream_t s);
+size_t argop_partials_bytes(uint32_t rows, uint32_t W);
+cudaError_t launch_softmax(const __half *in, __half *out, uint32_t C, uint32_t H, uint32_t W,
+                           int seq_mask, uint32_t offset, cudaStream_t s);
+cudaError_t launch_rope(__half *x, uint32_t C, uint32_t H, uint32_t W, uint64_t cs, uint64_t hs,
+                        const uint32_t *pos_dev, uint32_t offset, const float *freqc,
+                        const float *freqs, cudaStream_t s);
+cudaError_t launch_update_kvcache(__half *cache, const __half *kv, uint32_t C, uint32_t H,
+                                  uint32_t W, uint32_t HO, uint32_t WO, uint32_t offset,
+                                  cudaStream_t s);
+cudaError_t launch_transpose(const __half *in, __half *out, uint32_t C, uint32_t H, uint32_t W,
+                             cudaStream_t s);
+cudaError_t launch_slice(const __half *in, __half *out, uint32_t C, uint32_t H, uint32_t W,
+                         uint32_t c0, uint32_t h0, uint32_t w0, uint32_t EC, uint32_t EH,
+                         uint32_t EW, cudaStream_t s);
+cudaError_t launch_cast_f16_f32(const __half *in, float *out, uint64_t n, cudaStream_t s);
+cudaError_t launch_cast_f32_f16(const float *in, __half *out, uint64_t n, cudaStream_t s);
+// Batched fp16 x fp16 matmul with element strides; transpose_b selects A.B^T.
+cudaError_t launch_bmm_f16(const __half *a, const __half *b, __half *c, uint32_t C, uint32_t M,
+                           uint32_t N, uint32_t K, uint64_t a_cs, uint64_t a_hs, uint64_t b_cs,
+                           uint64_t b_hs, uint64_t c_cs, uint64_t c_hs, int transpose_b,
+                           float scale, float bias, int act, cudaStream_t s);
+
+// Fused attention core for the model path. q,k,v: [T, heads*dim] fresh projections.
+// Rotates q and k at positions pos+row, appends k,v to the caches [heads,maxlen,dim]
+// at (pos+row) % maxlen, then softmax(q.K^T/sqrt(dim)).V over the first
+// min(pos+T, maxlen) cache rows with the causal mask; out: [T, heads*dim].
+struct AttnParams {
+  __half *q;
+  const __half *k, *v;
+  __half *kcache, *vcache;
+  __half *out;
+  const float *freqc, *freqs;
+  const uint32_t *pos_dev;  // position of row 0, read on the device
+  float *scratch;           // splits*T*heads*(dim+2) floats
+  uint32_t *counters;       // T*heads, zero before first use (left zero after)
+  uint32_t T, heads, dim, maxlen, splits;
+  // clip: only the last row is computed and written to row 0 of `out`; its query is
+  // rotated at position pos (row 0), as the reference does after clipping Q
+  // (src/ops/multiheadattention_v2.cpp:223-253).
+  int clip;
+  int use_pdl;
+};
+cudaError_t launch_attention(const AttnParams &p, cudaStream_t s);
+size_t attention_scratch_bytes(uint32_t T, uint32_t heads, uint32_t dim, uint32_t splits);
+
+}  // namespace vkl

@@ -1,0 +1,647 @@
+// Llama-2 driver behind the C ABI: weight table, KV caches, the multi-token
+// (prefill) pass and the one-token decode step, which is captured once into a
+// CUDA graph and replayed per token with the position, the current token and
+// the output cursor living in device memory.
+//
+// Mirrors models/llama2.h of the reference: Model::init (348-681) becomes
+// vkl_model_set_weight per GGUF tensor, Model::operator() (683-843) becomes
+// vkl_model_forward, and the loop of app/llama2_infer.cpp:141-210 becomes
+// vkl_model_generate. Per layer the reference records 19 dispatches
+// (llama2.h:160-213, multiheadattention_v2.cpp:190-319); the decode step here
+// is 5 kernels per layer:
+//   RMSNorm+QKV mat-vec | RoPE+append+attention | o_proj+residual |
+//   RMSNorm+gate/up+SwiGLU | down+residual
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+
+#include "runtime.h"
+
+namespace vkl {
+int rope_tables(vkl_device *dev, cudaStream_t s, int dim, int rows, vkl_tensor **fc, vkl_tensor **fs);
+}
+using namespace vkl;
+
+namespace {
+struct Layer {
+  vkl_tensor *attn_norm = nullptr, *ffn_norm = nullptr;
+  vkl_tensor *wq = nullptr, *wk = nullptr, *wv = nullptr, *wo = nullptr;
+  vkl_tensor *gate = nullptr, *up = nullptr, *down = nullptr;
+  vkl_tensor *kcache = nullptr, *vcache = nullptr;
+};
+
+__global__ void set_u32(uint32_t *p, uint32_t v) { *p = v; }
+// After the arg-max: publish the picked id, feed it back, advance the position.
+__global__ void advance_kernel(const uint32_t *next, uint32_t *tok, uint32_t *pos, uint32_t *step,
+                               uint32_t *out_ids, uint32_t cap, uint32_t pos_inc) {
+  const uint32_t id = *next, s = *step;
+  if (s < cap) out_ids[s] = id;
+  *tok = id;
+  *pos += pos_inc;
+  *step = s + 1;
+}
+}  // namespace
+
+struct vkl_model {
+  vkl_device *dev = nullptr;
+  vkl_model_config cfg;
+  cudaStream_t stream = nullptr;
+  uint32_t head_dim = 0, heads_l = 0, dim_l = 0, ffn_l = 0, vocab_l = 0;
+  std::vector<Layer> L;
+  vkl_tensor *tok_embd = nullptr, *output_norm = nullptr, *output = nullptr;
+  vkl_tensor *fc = nullptr, *fs = nullptr;
+  // activations, sized for `cap_T` rows
+  uint32_t cap_T = 0;
+  vkl_tensor *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ao = nullptr, *t = nullptr;
+  vkl_tensor *logits16 = nullptr, *logits32 = nullptr;
+  vkl_tensor *toks = nullptr;  // [cap_T] device token ids; toks[0] is the decode token
+  vkl_tensor *state = nullptr; // uint32: [0] pos, [1] step, [2] next id
+  vkl_tensor *out_ids = nullptr;
+  vkl_tensor *argpart = nullptr, *attn_scratch = nullptr, *attn_counters = nullptr;
+  uint32_t splits = 8, out_cap = 0;
+  cudaGraphExec_t decode_graph = nullptr;
+  bool use_pdl = true;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
+  uint32_t *pos_dev() { return (uint32_t *)state->data(); }
+  uint32_t *step_dev() { return (uint32_t *)state->data() + 1; }
+  uint32_t *next_dev() { return (uint32_t *)state->data() + 2; }
+  ~vkl_model() {
+    if (decode_graph) cudaGraphExecDestroy(decode_graph);
+    for (auto &l : L)
+      for (vkl_tensor *p : {l.attn_norm, l.ffn_norm, l.wq, l.wk, l.wv, l.wo, l.gate, l.up, l.down, l.kcache, l.vcache}) vkl_tensor_release(p);
+    for (vkl_tensor *p : {tok_embd, output_norm, output, fc, fs, x, xn, q, k, v, ao, t, logits16, logits32, toks, state, out_ids, argpart, attn_scratch, attn_counters})
+      vkl_tensor_release(p);
+    if (ev0) cudaEventDestroy(ev0);
+    if (ev1) cudaEventDestroy(ev1);
+    if (ev2) cudaEventDestroy(ev2);
+    if (stream) cudaStreamDestroy(stream);
+  }
+};
+
+namespace {
+
+bool q8(const vkl_model *m) { return m->cfg.weight_dtype == VKL_Q8_0; }
+
+int ensure_rows(vkl_model *m, uint32_t T) {
+  if (T <= m->cap_T) return VKL_OK;
+  if (m->decode_graph) {  // the graph holds the old buffers
+    cudaGraphExecDestroy(m->decode_graph);
+    m->decode_graph = nullptr;
+  }
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  const size_t D = m->cfg.dim;
+  VKL_OKAY(ensure_tensor(m->dev, &m->x, 1, T, D, VKL_FP16));
+  VKL_OKAY(ensure_tensor(m->dev, &m->xn, 1, T, D, VKL_FP16));
+  VKL_OKAY(ensure_tensor(m->dev, &m->q, 1, T, m->dim_l, VKL_FP16));
+  VKL_OKAY(ensure_tensor(m->dev, &m->k, 1, T, m->dim_l, VKL_FP16));
+  VKL_OKAY(ensure_tensor(m->dev, &m->v, 1, T, m->dim_l, VKL_FP16));
+  VKL_OKAY(ensure_tensor(m->dev, &m->ao, 1, T, m->dim_l, VKL_FP16));
+  VKL_OKAY(ensure_tensor(m->dev, &m->t, 1, T, m->ffn_l, VKL_FP16));
+  VKL_OKAY(ensure_tensor(m->dev, &m->toks, 1, 1, T, VKL_UINT32));
+  const size_t sc = attention_scratch_bytes(1, m->heads_l, m->head_dim, m->splits);
+  VKL_OKAY(ensure_tensor(m->dev, &m->attn_scratch, 1, 1, sc / 4, VKL_FP32));
+  m->cap_T = T;
+  return VKL_OK;
+}
+
+MvParams mv(const vkl_model *m, const vkl_tensor *w, const __half *x, __half *out, uint32_t M) {
+  MvParams p = {};
+  p.codes[0] = w->data();
+  p.scales[0] = q8(m) ? w->scales() : nullptr;
+  p.out[0] = out;
+  p.x = x;
+  p.nmat = 1;
+  p.N = (uint32_t)w->h;
+  p.K = (uint32_t)w->w;
+  p.M = M;
+  p.x_ld = p.K;
+  p.out_ld = p.N;
+  p.scale = 1.f;
+  p.fp16_weights = !q8(m);
+  p.use_pdl = 0;
+  return p;
+}
+
+// Optional per-kernel timing of a pass: an event after every launch, tagged with
+// the kernel's class (0 embedding, 1 norm+QKV, 2 attention, 3 o_proj, 4 gate/up,
+// 5 down, 6 lm head, 7 arg-max).
+struct Marker {
+  std::vector<cudaEvent_t> ev;
+  std::vector<int> cls;
+  cudaStream_t s;
+  void mark(int c) {
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    cudaEventRecord(e, s);
+    ev.push_back(e);
+    cls.push_back(c);
+  }
+};
+#define MARK(c) do { if (mk) mk->mark(c); } while (0)
+
+// One pass over T tokens already in m->toks, first position in state[0].
+// Leaves the last token's fp16/fp32 logits and its arg-max in state[2].
+int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
+  cudaStream_t s = m->stream;
+  MARK(-1);
+  const uint32_t D = m->cfg.dim, nl = m->cfg.layers;
+  const bool dec = T == 1;
+  __half *x = (__half *)m->x->data(), *xn = (__half *)m->xn->data();
+  __half *qb = (__half *)m->q->data(), *kb = (__half *)m->k->data(), *vb = (__half *)m->v->data();
+  __half *ao = (__half *)m->ao->data(), *tb = (__half *)m->t->data();
+  VKL_LAUNCH(1, launch_embedding(m->tok_embd->data(), m->tok_embd->dtype == VKL_Q8_0, (const uint32_t *)m->toks->data(), x, T,
+                                 (uint32_t)m->tok_embd->h, D, 0, s));
+  MARK(0);
+  uint32_t rows = T;      // rows still alive (the last block keeps one: llama2.h:181-191)
+  __half *xr = x;         // first live row of the residual stream
+  for (uint32_t l = 0; l < nl; ++l) {
+    Layer &y = m->L[l];
+    const bool clip = (l == nl - 1) && T > 1;
+    // --- attention ---------------------------------------------------------
+    MvParams p = mv(m, y.wk, dec ? x : xn, kb, T);
+    p.codes[1] = y.wq->data(); p.codes[2] = y.wv->data();
+    if (q8(m)) { p.scales[1] = y.wq->scales(); p.scales[2] = y.wv->scales(); }
+    p.out[1] = qb; p.out[2] = vb;
+    p.nmat = 3;
+    if (dec) {
+      p.norm_w = (const float *)y.attn_norm->data();
+      p.eps = m->cfg.eps;
+      p.use_pdl = pdl;
+      VKL_LAUNCH(1, launch_matvec(p, EPI_PLAIN, true, s));
+    } else {
+      VKL_LAUNCH(1, launch_rms_norm(x, (const float *)y.attn_norm->data(), xn, T, D, m->cfg.eps, s));
+      VKL_LAUNCH((T + 63) / 64, launch_matvec(p, EPI_PLAIN, false, s));
+    }
+    MARK(1);
+    AttnParams a = {};
+    a.q = qb; a.k = kb; a.v = vb;
+    a.kcache = (__half *)y.kcache->data(); a.vcache = (__half *)y.vcache->data();
+    a.out = ao;
+    a.freqc = (const float *)m->fc->data(); a.freqs = (const float *)m->fs->data();
+    a.pos_dev = m->pos_dev();
+    a.scratch = (float *)m->attn_scratch->data(); a.counters = (uint32_t *)m->attn_counters->data();
+    a.T = T; a.heads = m->heads_l; a.dim = m->head_dim; a.maxlen = m->cfg.maxlen;
+    a.splits = dec ? m->splits : 1;
+    a.clip = clip;
+    a.use_pdl = dec && pdl;
+    VKL_LAUNCH(dec ? 1 : 2, launch_attention(a, s));
+    MARK(2);
+    if (clip) {
+      xr = x + (size_t)(T - 1) * D;
+      rows = 1;
+    }
+    // --- o_proj + residual (add_op_(attn, in): llama2.h:193-196) -------------
+    MvParams o = mv(m, y.wo, ao, xr, rows);
+    o.residual = xr;
+    o.use_pdl = dec && pdl;
+    VKL_LAUNCH((rows + 63) / 64, launch_matvec(o, EPI_ADD, false, s));
+    MARK(3);
+    // --- feed forward --------------------------------------------------------
+    MvParams f = mv(m, y.gate, dec || rows == 1 ? xr : xn, tb, rows);
+    f.codes[1] = y.up->data();
+    if (q8(m)) f.scales[1] = y.up->scales();
+    if (rows == 1) {
+      f.norm_w = (const float *)y.ffn_norm->data();
+      f.eps = m->cfg.eps;
+      f.use_pdl = dec && pdl;
+      VKL_LAUNCH(1, launch_matvec(f, EPI_SWIGLU, true, s));
+    } else {
+      VKL_LAUNCH(1, launch_rms_norm(xr, (const float *)y.ffn_norm->data(), xn, rows, D, m->cfg.eps, s));
+      VKL_LAUNCH((rows + 63) / 64, launch_matvec(f, EPI_SWIGLU, false, s));
+    }
+    MARK(4);
+    MvParams d = mv(m, y.down, tb, xr, rows);
+    d.residual = xr;
+    d.use_pdl = dec && pdl;
+    VKL_LAUNCH((rows + 63) / 64, launch_matvec(d, EPI_ADD, false, s));
+    MARK(5);
+  }
+  // --- output layer: RMSNorm(1e-6) -> lm head -> fp32 cast (llama2.h:283-298) --
+  if (T > 1 && nl == 0) xr = x + (size_t)(T - 1) * D;
+  MvParams h = mv(m, m->output, xr, (__half *)m->logits16->data(), 1);
+  h.norm_w = (const float *)m->output_norm->data();
+  h.eps = m->cfg.final_eps;
+  h.out_f32 = (float *)m->logits32->data();
+  h.use_pdl = dec && pdl;
+  VKL_LAUNCH(1, launch_matvec(h, EPI_PLAIN, true, s));
+  MARK(6);
+  VKL_LAUNCH(2, launch_argop((const __half *)m->logits16->data(), m->next_dev(), m->argpart->data(), 1, m->vocab_l, 0, s));
+  MARK(7);
+  return VKL_OK;
+}
+
+int launch_advance(vkl_model *m, uint32_t pos_inc) {
+  advance_kernel<<<1, 1, 0, m->stream>>>(m->next_dev(), (uint32_t *)m->toks->data(), m->pos_dev(), m->step_dev(),
+                                         (uint32_t *)m->out_ids->data(), m->out_cap, pos_inc);
+  VKL_LAUNCH(1, cudaGetLastError());
+  return VKL_OK;
+}
+
+int build_decode_graph(vkl_model *m) {
+  if (m->decode_graph) return VKL_OK;
+  VKL_OKAY(ensure_rows(m, 1));
+  cudaGraph_t g = nullptr;
+  VKL_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeRelaxed));
+  int st = run_tokens(m, 1, m->use_pdl);
+  if (st == VKL_OK) st = launch_advance(m, 1);
+  cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+  if (st != VKL_OK) {
+    if (g) cudaGraphDestroy(g);
+    return st;
+  }
+  if (e != cudaSuccess) return fail(VKL_INTERNAL, "decode graph capture failed: %s", cudaGetErrorString(e));
+  e = cudaGraphInstantiate(&m->decode_graph, g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) {
+    m->decode_graph = nullptr;
+    return fail(VKL_INTERNAL, "decode graph instantiation failed: %s", cudaGetErrorString(e));
+  }
+  return VKL_OK;
+}
+
+int check_ready(vkl_model *m) {
+  if (!m) return fail(VKL_INVALID_ARGUMENT, "model: null handle");
+  if (!m->tok_embd || !m->output || !m->output_norm) return fail(VKL_FAILED_PRECONDITION, "model: token_embd/output/output_norm weights are not set");
+  for (uint32_t l = 0; l < m->cfg.layers; ++l) {
+    Layer &y = m->L[l];
+    if (!y.attn_norm || !y.ffn_norm || !y.wq || !y.wk || !y.wv || !y.wo || !y.gate || !y.up || !y.down)
+      return fail(VKL_FAILED_PRECONDITION, "model: weights of block %u are incomplete", l);
+  }
+  return VKL_OK;
+}
+
+// Destination slot and shard geometry of a GGUF tensor name.
+struct Slot {
+  vkl_tensor **dst;
+  uint32_t rows, cols;        // full shape
+  uint32_t r0, nr, c0, nc;    // this rank's window
+  bool norm;
+  uint64_t synth_id;
+};
+
+int find_slot(vkl_model *m, const char *name, Slot *s) {
+  const vkl_model_config &c = m->cfg;
+  const uint32_t tp = c.tp_size, rk = c.tp_rank;
+  auto full = [&](vkl_tensor **d, uint32_t r, uint32_t k, uint64_t id) { *s = Slot{d, r, k, 0, r, 0, k, false, id}; };
+  auto rowsplit = [&](vkl_tensor **d, uint32_t r, uint32_t k, uint64_t id) { *s = Slot{d, r, k, rk * (r / tp), r / tp, 0, k, false, id}; };
+  auto colsplit = [&](vkl_tensor **d, uint32_t r, uint32_t k, uint64_t id) { *s = Slot{d, r, k, 0, r, rk * (k / tp), k / tp, false, id}; };
+  auto norm = [&](vkl_tensor **d, uint64_t id) { *s = Slot{d, 1, c.dim, 0, 1, 0, c.dim, true, id}; };
+  const uint64_t g = (uint64_t)c.layers * 16;
+  if (!strcmp(name, "token_embd.weight")) { full(&m->tok_embd, c.vocab, c.dim, g + 0); return VKL_OK; }
+  if (!strcmp(name, "output_norm.weight")) { norm(&m->output_norm, g + 1); return VKL_OK; }
+  if (!strcmp(name, "output.weight")) { rowsplit(&m->output, c.vocab, c.dim, g + 2); return VKL_OK; }
+  unsigned b = 0;
+  char kind[64];
+  if (sscanf(name, "blk.%u.%63s", &b, kind) == 2 && b < c.layers) {
+    Layer &y = m->L[b];
+    const uint64_t id = (uint64_t)b * 16;
+    if (!strcmp(kind, "attn_norm.weight")) { norm(&y.attn_norm, id + 0); return VKL_OK; }
+    if (!strcmp(kind, "attn_q.weight")) { rowsplit(&y.wq, c.dim, c.dim, id + 1); return VKL_OK; }
+    if (!strcmp(kind, "attn_k.weight")) { rowsplit(&y.wk, c.dim, c.dim, id + 2); return VKL_OK; }
+    if (!strcmp(kind, "attn_v.weight")) { rowsplit(&y.wv, c.dim, c.dim, id + 3); return VKL_OK; }
+    if (!strcmp(kind, "attn_output.weight")) { colsplit(&y.wo, c.dim, c.dim, id + 4); return VKL_OK; }
+    if (!strcmp(kind, "ffn_norm.weight")) { norm(&y.ffn_norm, id + 5); return VKL_OK; }
+    if (!strcmp(kind, "ffn_gate.weight")) { rowsplit(&y.gate, c.ffn, c.dim, id + 6); return VKL_OK; }
+    if (!strcmp(kind, "ffn_up.weight")) { rowsplit(&y.up, c.ffn, c.dim, id + 7); return VKL_OK; }
+    if (!strcmp(kind, "ffn_down.weight")) { colsplit(&y.down, c.dim, c.ffn, id + 8); return VKL_OK; }
+  }
+  return fail(VKL_INVALID_ARGUMENT, "model: tensor name '%s' is not part of a Llama-2 model with %u blocks", name, c.layers);
+}
+
+const char *kLayerNames[9] = {"attn_norm", "attn_q", "attn_k", "attn_v", "attn_output", "ffn_norm", "ffn_gate", "ffn_up", "ffn_down"};
+
+}  // namespace
+
+extern "C" {
+
+int vkl_model_create(vkl_device *dev, const vkl_model_config *cfg, vkl_model **out) {
+  if (!dev || !cfg || !out) return fail(VKL_INVALID_ARGUMENT, "model_create: null argument");
+  const vkl_model_config &c = *cfg;
+  if (!c.dim || !c.heads || !c.ffn || !c.vocab || !c.maxlen || c.dim % c.heads)
+    return fail(VKL_INVALID_ARGUMENT, "model_create: bad dimensions (dim %u, heads %u, ffn %u, vocab %u, maxlen %u)", c.dim, c.heads, c.ffn, c.vocab, c.maxlen);
+  if (c.weight_dtype != VKL_Q8_0 && c.weight_dtype != VKL_FP16) return fail(VKL_INVALID_ARGUMENT, "model_create: weight dtype %d is unsupported (Q8_0 or FP16)", c.weight_dtype);
+  const uint32_t hd = c.dim / c.heads;
+  if (hd > 128 || (hd & 7)) return fail(VKL_UNIMPLEMENTED, "model_create: head dim %u is unsupported (multiple of 8, at most 128)", hd);
+  const uint32_t tp = c.tp_size < 1 ? 1 : c.tp_size;
+  if (c.tp_rank < 0 || (uint32_t)c.tp_rank >= tp) return fail(VKL_INVALID_ARGUMENT, "model_create: tp_rank %d outside tp_size %u", c.tp_rank, tp);
+  if (c.heads % tp || (c.ffn / tp) % 32 || c.ffn % tp || (c.dim / tp) % 32 || c.vocab % tp)
+    return fail(VKL_INVALID_ARGUMENT, "model_create: tp_size %u does not divide heads/ffn/dim/vocab on 32-column boundaries", tp);
+  if (c.weight_dtype == VKL_FP16 && ((c.dim & 7) || (c.ffn & 7))) return fail(VKL_UNIMPLEMENTED, "model_create: FP16 weights need widths that are multiples of 8");
+  if (tp > 1) return fail(VKL_UNIMPLEMENTED, "model_create: tensor parallel execution is not built yet");
+  VKL_CUDA(cudaSetDevice(dev->ordinal));
+  vkl_model *m = new vkl_model();
+  m->dev = dev;
+  m->cfg = c;
+  m->cfg.tp_size = tp;
+  m->head_dim = hd;
+  m->heads_l = c.heads / tp;
+  m->dim_l = m->heads_l * hd;
+  m->ffn_l = c.ffn / tp;
+  m->vocab_l = c.vocab / tp;
+  m->L.resize(c.layers);
+  auto bail = [&](int st) {
+    delete m;
+    return st;
+  };
+  cudaError_t e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) return bail(fail(VKL_INTERNAL, "cudaStreamCreate: %s", cudaGetErrorString(e)));
+  cudaEventCreate(&m->ev0);
+  cudaEventCreate(&m->ev1);
+  cudaEventCreate(&m->ev2);
+  for (auto &l : m->L) {
+    if (int st = tensor_new(dev, m->heads_l, c.maxlen, hd, VKL_FP16, &l.kcache)) return bail(st);
+    if (int st = tensor_new(dev, m->heads_l, c.maxlen, hd, VKL_FP16, &l.vcache)) return bail(st);
+    cudaMemsetAsync(l.kcache->data(), 0, l.kcache->device_bytes(), m->stream);
+    cudaMemsetAsync(l.vcache->data(), 0, l.vcache->device_bytes(), m->stream);
+  }
+  // Positions up to 2*maxlen are valid, the size the reference gives its tables (rope.cpp:73-76).
+  if (int st = rope_tables(dev, m->stream, hd, 2 * c.maxlen, &m->fc, &m->fs)) return bail(st);
+  m->splits = 8;
+  m->out_cap = 2 * c.maxlen + 16;
+  int st = VKL_OK;
+  if ((st = tensor_new(dev, 1, 1, m->vocab_l, VKL_FP16, &m->logits16)) || (st = tensor_new(dev, 1, 1, m->vocab_l, VKL_FP32, &m->logits32)) ||
+      (st = tensor_new(dev, 1, 1, 4, VKL_UINT32, &m->state)) || (st = tensor_new(dev, 1, 1, m->out_cap, VKL_UINT32, &m->out_ids)) ||
+      (st = tensor_new(dev, 1, 1, argop_partials_bytes(1, m->vocab_l) / 4 + 2, VKL_FP32, &m->argpart)) ||
+      (st = tensor_new(dev, 1, 1, m->heads_l, VKL_UINT32, &m->attn_counters)))
+    return bail(st);
+  cudaMemsetAsync(m->state->data(), 0, 16, m->stream);
+  cudaMemsetAsync(m->attn_counters->data(), 0, m->attn_counters->device_bytes(), m->stream);
+  if ((st = ensure_rows(m, 1))) return bail(st);
+  e = cudaStreamSynchronize(m->stream);
+  if (e != cudaSuccess) return bail(fail(VKL_INTERNAL, "model_create: %s", cudaGetErrorString(e)));
+  *out = m;
+  return VKL_OK;
+}
+
+int vkl_model_destroy(vkl_model *m) {
+  if (!m) return VKL_OK;
+  cudaSetDevice(m->dev->ordinal);
+  cudaStreamSynchronize(m->stream);
+  delete m;
+  return VKL_OK;
+}
+
+int vkl_model_set_weight(vkl_model *m, const char *name, int dtype, const void *data, size_t bytes) {
+  if (!m || !name || !data) return fail(VKL_INVALID_ARGUMENT, "model_set_weight: null argument");
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  Slot s;
+  VKL_OKAY(find_slot(m, name, &s));
+  if (s.norm) {
+    if (dtype != VKL_FP32) return fail(VKL_INVALID_ARGUMENT, "model_set_weight: %s must be FP32 (rms_norm.cpp:33), got dtype %d", name, dtype);
+    if (bytes != (size_t)s.cols * 4) return fail(VKL_INVALID_ARGUMENT, "model_set_weight: %s takes %zu bytes, got %zu", name, (size_t)s.cols * 4, bytes);
+    VKL_OKAY(ensure_tensor(m->dev, s.dst, 1, 1, s.cols, VKL_FP32));
+    VKL_CUDA(cudaMemcpyAsync((*s.dst)->data(), data, bytes, cudaMemcpyHostToDevice, m->stream));
+    VKL_CUDA(cudaStreamSynchronize(m->stream));
+    return VKL_OK;
+  }
+  if (dtype != m->cfg.weight_dtype) return fail(VKL_INVALID_ARGUMENT, "model_set_weight: %s has dtype %d but the model was created for %d", name, dtype, m->cfg.weight_dtype);
+  const bool isq = dtype == VKL_Q8_0;
+  const size_t row_b = isq ? (size_t)(s.cols / 32) * 34 : (size_t)s.cols * 2;
+  if (isq && s.cols % 32) return fail(VKL_UNIMPLEMENTED, "model_set_weight: Q8_0 rows must be whole blocks");
+  if (bytes != row_b * s.rows) return fail(VKL_INVALID_ARGUMENT, "model_set_weight: %s takes %zu bytes, got %zu", name, row_b * s.rows, bytes);
+  // Cut this rank's window out of the full tensor on the host (block aligned).
+  const size_t win_row_b = isq ? (size_t)(s.nc / 32) * 34 : (size_t)s.nc * 2;
+  const size_t col_off = isq ? (size_t)(s.c0 / 32) * 34 : (size_t)s.c0 * 2;
+  const uint8_t *src = (const uint8_t *)data;
+  std::vector<uint8_t> win;
+  const uint8_t *up = src + (size_t)s.r0 * row_b;
+  if (s.nc != s.cols) {
+    win.resize(win_row_b * s.nr);
+    for (uint32_t r = 0; r < s.nr; ++r) memcpy(&win[r * win_row_b], src + (size_t)(s.r0 + r) * row_b + col_off, win_row_b);
+    up = win.data();
+  }
+  VKL_OKAY(ensure_tensor(m->dev, s.dst, 1, s.nr, s.nc, dtype));
+  if (isq) {
+    void *tmp = nullptr;
+    VKL_OKAY(m->dev->alloc(win_row_b * s.nr, &tmp));
+    cudaError_t e = cudaMemcpyAsync(tmp, up, win_row_b * s.nr, cudaMemcpyHostToDevice, m->stream);
+    if (e == cudaSuccess) e = launch_q8_repack((const uint8_t *)tmp, (*s.dst)->data(), s.nr, s.nc, m->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    m->dev->release(tmp, win_row_b * s.nr);
+    count_launches(1);
+    if (e != cudaSuccess) return fail(VKL_INTERNAL, "model_set_weight: %s", cudaGetErrorString(e));
+  } else {
+    VKL_CUDA(cudaMemcpyAsync((*s.dst)->data(), up, win_row_b * s.nr, cudaMemcpyHostToDevice, m->stream));
+    VKL_CUDA(cudaStreamSynchronize(m->stream));
+  }
+  return VKL_OK;
+}
+
+int vkl_model_synth_weights(vkl_model *m, uint64_t seed, float wstd, float nstd) {
+  if (!m) return fail(VKL_INVALID_ARGUMENT, "model_synth_weights: null model");
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  std::vector<std::string> names = {"token_embd.weight", "output_norm.weight", "output.weight"};
+  for (uint32_t l = 0; l < m->cfg.layers; ++l)
+    for (const char *k : kLayerNames) names.push_back("blk." + std::to_string(l) + "." + k + ".weight");
+  void *tmp = nullptr;
+  size_t tmp_b = 0;
+  for (auto &nm : names) {
+    Slot s;
+    VKL_OKAY(find_slot(m, nm.c_str(), &s));
+    if (s.norm) {
+      VKL_OKAY(ensure_tensor(m->dev, s.dst, 1, 1, s.cols, VKL_FP32));
+      VKL_LAUNCH(1, launch_synth_f32((float *)(*s.dst)->data(), seed, s.synth_id, 0, s.cols, 1.f, nstd, m->stream));
+      continue;
+    }
+    VKL_OKAY(ensure_tensor(m->dev, s.dst, 1, s.nr, s.nc, m->cfg.weight_dtype));
+    if (q8(m)) {
+      const size_t need = (size_t)s.nr * (s.nc / 32) * 34;
+      if (need > tmp_b) {
+        if (tmp) {
+          VKL_CUDA(cudaStreamSynchronize(m->stream));
+          m->dev->release(tmp, tmp_b);
+        }
+        VKL_OKAY(m->dev->alloc(need, &tmp));
+        tmp_b = need;
+      }
+      VKL_LAUNCH(1, launch_synth_q8((uint8_t *)tmp, seed, s.synth_id, s.nr, s.nc, 0.f, wstd, s.r0, s.c0, s.cols, m->stream));
+      VKL_LAUNCH(1, launch_q8_repack((const uint8_t *)tmp, (*s.dst)->data(), s.nr, s.nc, m->stream));
+    } else {
+      if (s.nc != s.cols) return fail(VKL_UNIMPLEMENTED, "model_synth_weights: column-split FP16 shards are not generated on the device");
+      VKL_LAUNCH(1, launch_synth_f16((__half *)(*s.dst)->data(), seed, s.synth_id, (uint64_t)s.r0 * s.cols, (uint64_t)s.nr * s.cols, 0.f, wstd, m->stream));
+    }
+  }
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  if (tmp) m->dev->release(tmp, tmp_b);
+  return VKL_OK;
+}
+
+int vkl_model_forward(vkl_model *m, const uint32_t *toks, size_t n, size_t offset, float *logits_out) {
+  VKL_OKAY(check_ready(m));
+  if (!toks || !logits_out) return fail(VKL_INVALID_ARGUMENT, "model_forward: null argument");
+  if (n == 0) return fail(VKL_INVALID_ARGUMENT, "model_forward: no tokens");
+  if (n > m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_forward: %zu tokens exceed the context length %u", n, m->cfg.maxlen);
+  if (offset + n > (size_t)2 * m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_forward: position %zu is beyond the RoPE table (2*maxlen)", offset + n);
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  VKL_OKAY(ensure_rows(m, (uint32_t)n));
+  if (n == 1) VKL_OKAY(build_decode_graph(m));
+  const uint32_t st[2] = {(uint32_t)offset, 0};
+  VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
+  VKL_CUDA(cudaMemcpyAsync(m->toks->data(), toks, n * 4, cudaMemcpyHostToDevice, m->stream));
+  if (n == 1) {
+    VKL_CUDA(cudaGraphLaunch(m->decode_graph, m->stream));
+    count_launches(5 * m->cfg.layers + 5);
+  } else {
+    VKL_OKAY(run_tokens(m, (uint32_t)n, false));
+  }
+  VKL_CUDA(cudaMemcpyAsync(logits_out, m->logits32->data(), (size_t)m->vocab_l * 4, cudaMemcpyDeviceToHost, m->stream));
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  return VKL_OK;
+}
+
+int vkl_model_generate(vkl_model *m, const uint32_t *prompt, size_t n_prompt, size_t n_gen, uint32_t *out_ids, float *prefill_ms,
+                       float *decode_ms) {
+  VKL_OKAY(check_ready(m));
+  if (!prompt || !out_ids) return fail(VKL_INVALID_ARGUMENT, "model_generate: null argument");
+  if (n_prompt == 0 || n_gen == 0) return fail(VKL_INVALID_ARGUMENT, "model_generate: empty prompt or nothing to generate");
+  if (n_prompt > m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_generate: prompt of %zu tokens exceeds the context length %u", n_prompt, m->cfg.maxlen);
+  if (n_prompt + n_gen > (size_t)2 * m->cfg.maxlen || n_gen > m->out_cap)
+    return fail(VKL_OUT_OF_RANGE, "model_generate: %zu + %zu tokens run past the RoPE table (2*maxlen)", n_prompt, n_gen);
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  VKL_OKAY(ensure_rows(m, (uint32_t)n_prompt));
+  VKL_OKAY(build_decode_graph(m));
+  const uint32_t st[2] = {0, 0};
+  VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
+  VKL_CUDA(cudaMemcpyAsync(m->toks->data(), prompt, n_prompt * 4, cudaMemcpyHostToDevice, m->stream));
+  VKL_CUDA(cudaEventRecord(m->ev0, m->stream));
+  if (n_prompt == 1) {
+    VKL_CUDA(cudaGraphLaunch(m->decode_graph, m->stream));
+    count_launches(5 * m->cfg.layers + 5);
+  } else {
+    VKL_OKAY(run_tokens(m, (uint32_t)n_prompt, false));
+    VKL_OKAY(launch_advance(m, (uint32_t)n_prompt));
+  }
+  VKL_CUDA(cudaEventRecord(m->ev1, m->stream));
+  for (size_t i = 1; i < n_gen; ++i) VKL_CUDA(cudaGraphLaunch(m->decode_graph, m->stream));
+  count_launches((n_gen - 1) * (5 * m->cfg.layers + 5));
+  VKL_CUDA(cudaEventRecord(m->ev2, m->stream));
+  VKL_CUDA(cudaMemcpyAsync(out_ids, m->out_ids->data(), n_gen * 4, cudaMemcpyDeviceToHost, m->stream));
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  float ms = 0.f;
+  if (prefill_ms) {
+    VKL_CUDA(cudaEventElapsedTime(&ms, m->ev0, m->ev1));
+    *prefill_ms = ms;
+  }
+  if (decode_ms) {
+    VKL_CUDA(cudaEventElapsedTime(&ms, m->ev1, m->ev2));
+    *decode_ms = ms;
+  }
+  return VKL_OK;
+}
+
+int vkl_model_read_kv(vkl_model *m, uint32_t layer, void *kcache, void *vcache) {
+  if (!m || layer >= m->cfg.layers) return fail(VKL_INVALID_ARGUMENT, "model_read_kv: bad model or layer");
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  Layer &y = m->L[layer];
+  if (kcache) VKL_CUDA(cudaMemcpyAsync(kcache, y.kcache->data(), y.kcache->device_bytes(), cudaMemcpyDeviceToHost, m->stream));
+  if (vcache) VKL_CUDA(cudaMemcpyAsync(vcache, y.vcache->data(), y.vcache->device_bytes(), cudaMemcpyDeviceToHost, m->stream));
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  return VKL_OK;
+}
+int vkl_model_write_kv(vkl_model *m, uint32_t layer, const void *kcache, const void *vcache) {
+  if (!m || layer >= m->cfg.layers) return fail(VKL_INVALID_ARGUMENT, "model_write_kv: bad model or layer");
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  Layer &y = m->L[layer];
+  if (kcache) VKL_CUDA(cudaMemcpyAsync(y.kcache->data(), kcache, y.kcache->device_bytes(), cudaMemcpyHostToDevice, m->stream));
+  if (vcache) VKL_CUDA(cudaMemcpyAsync(y.vcache->data(), vcache, y.vcache->device_bytes(), cudaMemcpyHostToDevice, m->stream));
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  return VKL_OK;
+}
+
+int vkl_model_block_forward(vkl_model *m, uint32_t layer, const void *x_fp16, size_t T, size_t offset, void *out_fp16) {
+  if (!m || layer >= m->cfg.layers || !x_fp16 || !out_fp16 || T == 0) return fail(VKL_INVALID_ARGUMENT, "model_block_forward: bad argument");
+  if (T > m->cfg.maxlen || offset + T > (size_t)2 * m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_block_forward: rows or position out of range");
+  Layer &y = m->L[layer];
+  if (!y.attn_norm || !y.ffn_norm || !y.wq || !y.wk || !y.wv || !y.wo || !y.gate || !y.up || !y.down)
+    return fail(VKL_FAILED_PRECONDITION, "model_block_forward: weights of block %u are incomplete", layer);
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  VKL_OKAY(ensure_rows(m, (uint32_t)T));
+  // Run the model path on a one-block view of this model.
+  const uint32_t st[2] = {(uint32_t)offset, 0};
+  VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
+  const size_t D = m->cfg.dim;
+  cudaStream_t s = m->stream;
+  __half *x = (__half *)m->x->data(), *xn = (__half *)m->xn->data();
+  VKL_CUDA(cudaMemcpyAsync(x, x_fp16, T * D * 2, cudaMemcpyHostToDevice, s));
+  const bool dec = T == 1;
+  MvParams p = mv(m, y.wk, dec ? x : xn, (__half *)m->k->data(), (uint32_t)T);
+  p.codes[1] = y.wq->data(); p.codes[2] = y.wv->data();
+  if (q8(m)) { p.scales[1] = y.wq->scales(); p.scales[2] = y.wv->scales(); }
+  p.out[1] = (__half *)m->q->data(); p.out[2] = (__half *)m->v->data();
+  p.nmat = 3;
+  if (dec) {
+    p.norm_w = (const float *)y.attn_norm->data();
+    p.eps = m->cfg.eps;
+    VKL_LAUNCH(1, launch_matvec(p, EPI_PLAIN, true, s));
+  } else {
+    VKL_LAUNCH(1, launch_rms_norm(x, (const float *)y.attn_norm->data(), xn, (uint32_t)T, (uint32_t)D, m->cfg.eps, s));
+    VKL_LAUNCH((T + 63) / 64, launch_matvec(p, EPI_PLAIN, false, s));
+  }
+  AttnParams a = {};
+  a.q = (__half *)m->q->data(); a.k = (const __half *)m->k->data(); a.v = (const __half *)m->v->data();
+  a.kcache = (__half *)y.kcache->data(); a.vcache = (__half *)y.vcache->data();
+  a.out = (__half *)m->ao->data();
+  a.freqc = (const float *)m->fc->data(); a.freqs = (const float *)m->fs->data();
+  a.pos_dev = m->pos_dev();
+  a.scratch = (float *)m->attn_scratch->data(); a.counters = (uint32_t *)m->attn_counters->data();
+  a.T = (uint32_t)T; a.heads = m->heads_l; a.dim = m->head_dim; a.maxlen = m->cfg.maxlen;
+  a.splits = dec ? m->splits : 1;
+  VKL_LAUNCH(dec ? 1 : 2, launch_attention(a, s));
+  MvParams o = mv(m, y.wo, (__half *)m->ao->data(), x, (uint32_t)T);
+  o.residual = x;
+  VKL_LAUNCH((T + 63) / 64, launch_matvec(o, EPI_ADD, false, s));
+  MvParams f = mv(m, y.gate, dec ? x : xn, (__half *)m->t->data(), (uint32_t)T);
+  f.codes[1] = y.up->data();
+  if (q8(m)) f.scales[1] = y.up->scales();
+  if (dec) {
+    f.norm_w = (const float *)y.ffn_norm->data();
+    f.eps = m->cfg.eps;
+    VKL_LAUNCH(1, launch_matvec(f, EPI_SWIGLU, true, s));
+  } else {
+    VKL_LAUNCH(1, launch_rms_norm(x, (const float *)y.ffn_norm->data(), xn, (uint32_t)T, (uint32_t)D, m->cfg.eps, s));
+    VKL_LAUNCH((T + 63) / 64, launch_matvec(f, EPI_SWIGLU, false, s));
+  }
+  MvParams d = mv(m, y.down, (__half *)m->t->data(), x, (uint32_t)T);
+  d.residual = x;
+  VKL_LAUNCH((T + 63) / 64, launch_matvec(d, EPI_ADD, false, s));
+  VKL_CUDA(cudaMemcpyAsync(out_fp16, x, T * D * 2, cudaMemcpyDeviceToHost, s));
+  VKL_CUDA(cudaStreamSynchronize(s));
+  return VKL_OK;
+}
+
+int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[8]) {
+  VKL_OKAY(check_ready(m));
+  if (!out_us) return fail(VKL_INVALID_ARGUMENT, "model_decode_profile: null output");
+  if (offset + 1 > (size_t)2 * m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_decode_profile: position out of range");
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  VKL_OKAY(ensure_rows(m, 1));
+  const uint32_t st[2] = {(uint32_t)offset, 0};
+  VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
+  VKL_CUDA(cudaMemcpyAsync(m->toks->data(), &token, 4, cudaMemcpyHostToDevice, m->stream));
+  Marker mk;
+  mk.s = m->stream;
+  int rc = run_tokens(m, 1, false, &mk);
+  cudaError_t e = cudaStreamSynchronize(m->stream);
+  for (int i = 0; i < 8; ++i) out_us[i] = 0.f;
+  for (size_t i = 1; i < mk.ev.size(); ++i) {
+    float ms = 0.f;
+    if (rc == VKL_OK && e == cudaSuccess && cudaEventElapsedTime(&ms, mk.ev[i - 1], mk.ev[i]) == cudaSuccess && mk.cls[i] >= 0)
+      out_us[mk.cls[i]] += ms * 1000.f;
+  }
+  for (cudaEvent_t ev : mk.ev) cudaEventDestroy(ev);
+  if (rc != VKL_OK) return rc;
+  if (e != cudaSuccess) return fail(VKL_INTERNAL, "model_decode_profile: %s", cudaGetErrorString(e));
+  return VKL_OK;
+}
+
+int vkl_model_tp_buffer(vkl_model *m, void **local_ptr, size_t *bytes) {
+  (void)m; (void)local_ptr; (void)bytes;
+  return fail(VKL_UNIMPLEMENTED, "tensor parallel execution is not built yet");
+}
+int vkl_model_tp_connect(vkl_model *m, void *const *peer_ptrs, int n) {
+  (void)m; (void)peer_ptrs; (void)n;
+  return fail(VKL_UNIMPLEMENTED, "tensor parallel execution is not built yet");
+}
+
+}  // extern "C"
