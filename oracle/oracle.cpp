@@ -503,9 +503,13 @@ static void attn_init(OrcAttn &a, uint32_t heads, uint32_t dim, uint32_t maxlen)
   a.width = heads * dim;
   a.kcache.assign((size_t)heads * maxlen * dim, 0);
   a.vcache.assign((size_t)heads * maxlen * dim, 0);
-  a.freqc.resize((size_t)maxlen * dim / 2);
-  a.freqs.resize((size_t)maxlen * dim / 2);
-  orc_rope_table(dim, maxlen, a.freqc.data(), a.freqs.data());
+  // The reference sizes its tables for 2*maxlen positions but uploads only the
+  // first maxlen rows (src/ops/rope.cpp:73-96: the byte count uses sizeof(fp16)
+  // on fp32 data), so positions >= maxlen read uninitialised memory there. Here
+  // all 2*maxlen rows are computed: defined behaviour where the reference has none.
+  a.freqc.resize((size_t)2 * maxlen * dim / 2);
+  a.freqs.resize((size_t)2 * maxlen * dim / 2);
+  orc_rope_table(dim, 2 * maxlen, a.freqc.data(), a.freqs.data());
 }
 
 // Everything after the KQV projection and before o_proj; k,q,v are [T, heads*dim].

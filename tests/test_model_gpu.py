@@ -42,7 +42,7 @@ def test_block_7b_shape_decode_at_position_511(dev):
     assert_close(got, want, what="7B block @511")
     gk, gv = dm.read_kv(0)
     assert_close(gk[:, 511], om.kcache(0)[:, 511], tol=2e-3, what="appended k")
-    assert np.array_equal(gv[:, 511], om.vcache(0)[:, 511])
+    assert_close(gv[:, 511], om.vcache(0)[:, 511], tol=2e-3, what="appended v")
     assert np.array_equal(gk[:, :511], k0[:, :511])
 
 

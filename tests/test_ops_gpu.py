@@ -383,7 +383,7 @@ def test_multiheadattention_q8_0_sequence(dev, T, offset, clip):
     ov = np.ctypeslib.as_array(O.lib().orc_attn_vcache(att), shape=(heads, maxlen, dim))
     L = min(offset + T, maxlen)
     assert_close(gk[:, :L], ok[:, :L], tol=2e-3, what="kcache")
-    assert np.array_equal(gv[:, :L], ov[:, :L])
+    assert_close(gv[:, :L], ov[:, :L], tol=2e-3, what="vcache")
     O.lib().orc_attn_destroy(att)
 
 

@@ -74,12 +74,10 @@ __device__ __forceinline__ void quantize_block_store(float x, bool valid, uint8_
   const float scale = amax / 127.0f;
   const float inv = scale > 0 ? 127.0f / amax : 0.f;
   const int8_t q = valid ? (int8_t)roundf(x * inv) : (int8_t)0;
+  // Blocks are 34 bytes: every block start is 2-byte aligned, so the scale is one
+  // 16-bit store.
+  if (lane == 0) *reinterpret_cast<__half *>(blk) = __float2half_rn(scale);
   blk[2 + lane] = (uint8_t)q;
-  if (lane == 0) {
-    const unsigned short hs = __half_as_ushort(__float2half_rn(scale));
-    blk[0] = hs & 0xff;
-    blk[1] = hs >> 8;
-  }
 }
 
 __global__ void q8_quantize_kernel(const float *__restrict__ src, uint8_t *__restrict__ dst,

@@ -57,7 +57,7 @@ int tensor_new(vkl_device *dev, size_t c, size_t h, size_t w, int dtype, vkl_ten
     delete t;
     return s;
   }
-  t->buf = std::make_shared<Buffer>(Buffer{dev, p, bytes ? bytes : 16});
+  t->buf = std::make_shared<Buffer>(dev, p, bytes ? bytes : 16);
   *out = t;
   return VKL_OK;
 }
@@ -147,7 +147,10 @@ int vkl_device_destroy(vkl_device *dev) {
   if (!dev) return VKL_OK;
   cudaSetDevice(dev->ordinal);
   cudaDeviceSynchronize();
-  delete dev;
+  // Tensors may outlive the handle (they are reference counted); the last
+  // buffer to go frees the device record.
+  dev->closed.store(true);
+  if (dev->live_buffers.load() == 0) delete dev;
   return VKL_OK;
 }
 int vkl_device_info(vkl_device *dev, char *name, int *sm_count, size_t *total_mem) {

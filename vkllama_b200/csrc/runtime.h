@@ -47,6 +47,8 @@ struct vkl_device {
   cudaDeviceProp prop;
   std::mutex mu;
   std::multimap<size_t, void *> pool;  // free blocks by size
+  std::atomic<int> live_buffers{0};    // tensors' buffers still referencing this device
+  std::atomic<bool> closed{false};     // destroy was requested; the last buffer frees the device
   int alloc(size_t bytes, void **out);
   void release(void *p, size_t bytes);
   ~vkl_device();
@@ -57,7 +59,12 @@ struct Buffer {
   vkl_device *dev;
   void *ptr;
   size_t bytes;
-  ~Buffer() { dev->release(ptr, bytes); }
+  Buffer(vkl_device *d, void *p, size_t b) : dev(d), ptr(p), bytes(b) { dev->live_buffers.fetch_add(1); }
+  Buffer(const Buffer &) = delete;
+  ~Buffer() {
+    dev->release(ptr, bytes);
+    if (dev->live_buffers.fetch_sub(1) == 1 && dev->closed.load()) delete dev;
+  }
 };
 size_t dtype_elem_bytes(int dtype);
 }  // namespace vkl
