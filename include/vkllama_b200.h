@@ -79,6 +79,9 @@ int vkl_command_end(vkl_command *cmd);
 int vkl_command_submit(vkl_command *cmd);
 int vkl_command_wait(vkl_command *cmd);
 int vkl_command_submit_and_wait(vkl_command *cmd);
+/* Device time between begin() and end() of the last recording, valid after wait();
+ * the per-command counterpart of the timestamp queries in command.h:353-370. */
+int vkl_command_elapsed_us(vkl_command *cmd, float *usec);
 /* upload_bytes / download (command.h:141-260): host memory is copied through
  * pinned staging; a download lands in `host` when vkl_command_wait returns. */
 int vkl_command_upload(vkl_command *cmd, const void *host, size_t bytes, vkl_tensor *to);

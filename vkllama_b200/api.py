@@ -55,7 +55,7 @@ def load_library():
         "vkl_tensor_device_ptr": [vp, pvp],
         "vkl_command_create": [vp, pvp], "vkl_command_destroy": [vp], "vkl_command_begin": [vp],
         "vkl_command_end": [vp], "vkl_command_submit": [vp], "vkl_command_wait": [vp],
-        "vkl_command_submit_and_wait": [vp], "vkl_command_upload": [vp, vp, sz, vp],
+        "vkl_command_submit_and_wait": [vp], "vkl_command_elapsed_us": [vp, C.POINTER(f32)], "vkl_command_upload": [vp, vp, sz, vp],
         "vkl_command_download": [vp, vp, vp, sz],
         "vkl_op_init": [vp], "vkl_op_time": [vp, C.POINTER(u64)], "vkl_op_destroy": [vp],
         "vkl_matmul_create": [vp, vp, vp, f32, f32, i32, i32, i32, i32, i32, pvp],
@@ -258,6 +258,11 @@ class Command:
     def submit_and_wait(self):
         _ck(self.L.vkl_command_submit_and_wait(self.h))
         self._keep.clear()
+
+    def elapsed_us(self):
+        t = f32()
+        _ck(self.L.vkl_command_elapsed_us(self.h, C.byref(t)))
+        return t.value
 
     def upload(self, arr, tensor):
         a = np.ascontiguousarray(arr)

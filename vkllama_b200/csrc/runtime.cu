@@ -266,6 +266,8 @@ int vkl_command_create(vkl_device *dev, vkl_command **out) {
     delete c;
     return fail(VKL_INTERNAL, "cudaStreamCreate: %s", cudaGetErrorString(e));
   }
+  cudaEventCreate(&c->ev0);
+  cudaEventCreate(&c->ev1);
   *out = c;
   return VKL_OK;
 }
@@ -274,6 +276,8 @@ int vkl_command_destroy(vkl_command *cmd) {
   cudaStreamSynchronize(cmd->stream);
   for (auto &f : cmd->deferred) f();
   cudaStreamDestroy(cmd->stream);
+  if (cmd->ev0) cudaEventDestroy(cmd->ev0);
+  if (cmd->ev1) cudaEventDestroy(cmd->ev1);
   delete cmd;
   return VKL_OK;
 }
@@ -283,12 +287,14 @@ int vkl_command_begin(vkl_command *cmd) {
   VKL_CUDA(cudaSetDevice(cmd->dev->ordinal));
   cmd->recording = true;
   cmd->submitted = false;
+  VKL_CUDA(cudaEventRecord(cmd->ev0, cmd->stream));
   return VKL_OK;
 }
 int vkl_command_end(vkl_command *cmd) {
   if (!cmd) return fail(VKL_INVALID_ARGUMENT, "command_end: null command");
   if (!cmd->recording) return fail(VKL_FAILED_PRECONDITION, "command_end: not recording");
   cmd->recording = false;
+  VKL_CUDA(cudaEventRecord(cmd->ev1, cmd->stream));
   return VKL_OK;
 }
 int vkl_command_submit(vkl_command *cmd) {
@@ -304,6 +310,17 @@ int vkl_command_wait(vkl_command *cmd) {
   cmd->deferred.clear();
   for (auto &f : tasks) f();
   if (e != cudaSuccess) return fail(VKL_INTERNAL, "command_wait: %s", cudaGetErrorString(e));
+  return VKL_OK;
+}
+int vkl_command_elapsed_us(vkl_command *cmd, float *usec) {
+  if (!cmd || !usec) return fail(VKL_INVALID_ARGUMENT, "command_elapsed_us: null argument");
+  float ms = 0.f;
+  cudaError_t e = cudaEventElapsedTime(&ms, cmd->ev0, cmd->ev1);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(VKL_FAILED_PRECONDITION, "command_elapsed_us: the command has not been recorded and waited on");
+  }
+  *usec = ms * 1000.f;
   return VKL_OK;
 }
 int vkl_command_submit_and_wait(vkl_command *cmd) {

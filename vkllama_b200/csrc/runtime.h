@@ -93,6 +93,7 @@ struct vkl_command {
   cudaStream_t stream = nullptr;
   bool recording = false;
   bool submitted = false;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // recorded by begin() and end()
   std::vector<std::function<void()>> deferred;  // run by wait()
 };
 
