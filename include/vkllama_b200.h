@@ -218,11 +218,13 @@ int vkl_model_write_kv(vkl_model *m, uint32_t layer, const void *kcache, const v
 int vkl_model_block_forward(vkl_model *m, uint32_t layer, const void *x_fp16, size_t T,
                             size_t offset, void *out_fp16);
 /* Op::time() for the model path (models/llama2.h:816-841 prints per-op costs): one
- * decode step run kernel by kernel with an event after each launch. out_us[8]:
- * device microseconds summed over layers of 0 embedding, 1 RMSNorm+QKV,
- * 2 RoPE+append+attention, 3 o_proj+residual, 4 RMSNorm+gate/up+SwiGLU,
- * 5 down+residual, 6 RMSNorm+lm head, 7 arg-max. Appends to the KV cache at `offset`. */
-int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[8]);
+ * decode step with a time stamp after each op. out_us[0..7]: device microseconds
+ * summed over layers of 0 embedding, 1 RMSNorm+QKV, 2 RoPE+append+attention,
+ * 3 o_proj+residual, 4 RMSNorm+gate/up+SwiGLU, 5 down+residual, 6 RMSNorm+lm head,
+ * 7 arg-max; out_us[8..15]: the part of each spent waiting at the grid barrier (the
+ * persistent kernel, timeline of its first CTA; 0 on the multi-kernel path, which is
+ * timed with an event after every launch). Appends to the KV cache at `offset`. */
+int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[16]);
 /* Tensor-parallel set-up: peer device pointers of every rank's exchange buffer
  * (obtained by the caller through CUDA IPC), indexed by rank. */
 int vkl_model_tp_buffer(vkl_model *m, void **local_ptr, size_t *bytes);

@@ -573,7 +573,7 @@ class Model:
 
     def decode_profile(self, token, offset):
         """Per-kernel-class device microseconds of one decode step (see the header)."""
-        out = (f32 * 8)()
+        out = (f32 * 16)()
         _ck(self.L.vkl_model_decode_profile(self.h, token, offset, out))
         return list(out)
 

@@ -17,6 +17,11 @@ namespace vkl {
 //           block is 32 columns. lane = g*4 + t holds, biased by +128 to
 //           unsigned, the 8 codes of row 16*tile+g   at k = 32*b + 8*t..+7
 //           followed by the 8 codes of row 16*tile+g+8 at the same k.
+//           Inside every 32-bit word the four codes c0..c3 sit as bytes
+//           [c0, c2, c1, c3], so `w & 0x00ff00ff` and `(w >> 8) & 0x00ff00ff`
+//           are the code pairs (c0,c1) and (c2,c3) in the two 16-bit lanes:
+//           one logic op each turns them into fp16 pairs (byte permutes run on
+//           the slow conversion pipe of this GPU and are avoided).
 //           That is exactly the A fragment of two m16n8k16 MMAs, so one
 //           coalesced 128-bit load per lane feeds the tensor core.
 //   scales: [row_tile][group of 4 blocks][g 0..7][8 halves]: the fp16 scales
@@ -77,10 +82,22 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Two biased-unsigned codes (bytes `lo`,`lo+1` of w) -> packed fp16 pair, exact:
-// 0x6400 | u is the half 1024+u; subtracting 1152 leaves u-128.
+// Byte position of code i (0..7) inside the 8-byte run of one row (see Q8Layout).
+__host__ __device__ inline uint32_t q8_byte_pos(uint32_t i) {
+  const uint32_t k = i & 3;
+  return (i & 4) + (k == 1 ? 2 : k == 2 ? 1 : k);
+}
+
+// Code pair (c0,c1) [hi = false] or (c2,c3) [hi = true] of a layout word as the
+// fp16 pair (1024+u, 1024+u'): 0x6400 | u is the half 1024+u, exactly.
+__device__ __forceinline__ uint32_t codes_raw_h2(uint32_t w, bool hi) {
+  // one logic op for the low pair, one byte permute for the high pair
+  return hi ? __byte_perm(w, 0x64646464u, 0x4341) : ((w & 0x00ff00ffu) | 0x64006400u);
+}
+
+// Same pair with the +128 bias and the 1024 removed: the signed codes as fp16, exact.
 __device__ __forceinline__ uint32_t codes_to_h2(uint32_t w, bool hi) {
-  const uint32_t p = __byte_perm(w, 0x64646464u, hi ? 0x4342 : 0x4140);
+  const uint32_t p = codes_raw_h2(w, hi);
   const __half2 bias = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
   __half2 r = __hsub2(*reinterpret_cast<const __half2 *>(&p), bias);
   return *reinterpret_cast<uint32_t *>(&r);

@@ -1,0 +1,770 @@
+// One persistent kernel per decode token (Q8_0 weights, batch 1).
+//
+// The reference records 19 Vulkan dispatches per layer per token
+// (models/llama2.h:160-213, src/ops/multiheadattention_v2.cpp:190-319) and stalls
+// the weight stream at every one of them. Here the whole token is one
+// cooperative launch of one CTA per SM:
+//
+//   * a producer warp walks the static schedule of this CTA's weight tiles for
+//     ALL mat-vec ops of the token and streams them with bulk-copy TMA
+//     (cp.async.bulk + mbarrier) into a shared-memory ring. Weights never depend
+//     on activations, so the producer runs ahead across op boundaries and HBM
+//     stays busy while the consumers sit in a grid barrier, a norm or attention;
+//   * eight consumer warps take ring stages (8 groups of 4 Q8_0 blocks x 16 rows),
+//     convert codes to fp16 exactly, multiply on the tensor cores (m16n8k16, fp32
+//     accumulate), apply block scales in fp32, reduce across warps in fixed order
+//     and run the fused epilogue (RMSNorm prologue, residual add, SwiGLU, fp32
+//     logits, running arg-max);
+//   * ops are separated by a grid barrier (one atomic counter, bounded spin).
+//
+// Tiles of op i go to CTA (tile + rot_i) mod grid; rot_i advances by the op's
+// tile count so the uneven remainder rotates over the SMs.
+// Every wait is bounded; on a time-out the kernel raises *error, stops issuing
+// copies, drains the copies in flight and leaves through the normal path.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace vkl {
+namespace {
+
+constexpr int NCW = 15;                // consumer warps (+1 producer warp = 512 threads, 128 registers each)
+constexpr int CT = NCW * 32;           // consumer threads
+constexpr int THREADS = CT + 32;       // + producer warp
+constexpr int SG = 16;                 // 4-block groups per ring stage; owners rotate over the warps
+constexpr uint32_t STAGE_CODES = SG * 2048, STAGE_SCALES = SG * 128;
+constexpr uint32_t STAGE_BYTES = STAGE_CODES + STAGE_SCALES;  // 17408
+constexpr int NST = 5;                 // ring stages (170 KB)
+constexpr uint32_t WAIT_LIMIT = 1u << 21;
+constexpr int RED_SLOTS = 20;          // (tiles of one CTA) x (matrices) an op may have
+
+__device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t a, uint32_t n) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(a), "r"(n) : "memory");
+}
+__device__ __forceinline__ void mbar_expect(uint32_t a, uint32_t tx) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(tx) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t a) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(a) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try(uint32_t a, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(a), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(mbar)
+               : "memory");
+}
+__device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory"); }
+__device__ __forceinline__ uint64_t ld_acq_u64(const unsigned long long *p) {
+  uint64_t v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// The mat-vec multiplies the raw fp16 pairs (1024+u) and removes the bias afterwards
+// with the per-block sum of the input:
+//   sum_k (1152 + q_k) x_k = sum_k q_k x_k + 1152 * sum_k x_k.
+__device__ __forceinline__ bool getenv_prologue(const MegaParams &p) { return (p.timing_mode & 1u) != 0; }
+
+struct Ctx {
+  const MegaParams &p;
+  volatile uint32_t *abort_s;  // shared flag: some wait of this CTA timed out or *error was seen
+  __device__ __forceinline__ bool aborted() const { return *abort_s != 0; }
+  __device__ __forceinline__ void raise(uint32_t code) const {
+    *abort_s = 1;
+    atomicCAS(p.error, 0u, code);
+  }
+  // Bounded mbarrier wait; false (and the abort flag set) on time-out.
+  __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, uint32_t code) const {
+    if (aborted()) return false;
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+      if (mbar_try(bar, parity)) return true;
+      if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || aborted())) {
+        *abort_s = 1;
+        return false;
+      }
+    }
+    raise(code);
+    return false;
+  }
+};
+
+// First tile of this CTA for an op and the walk over (tile, matrix, stage).
+__device__ __forceinline__ uint32_t first_tile(const MegaOp &op, uint32_t cta, uint32_t G) {
+  return (cta + G - (op.rot % G)) % G;
+}
+
+// ------------------------------------------------------------------ producer
+// The producer warp walks this CTA's precomputed stage table (one entry per ring
+// stage of the whole token, in consumer order). Lane 0 keeps the shared-memory ring
+// full with bulk copies and, `l2_lookahead` stages further on, asks L2 for the codes
+// of later stages (cp.async.bulk.prefetch.L2): while the ring is full because the
+// consumers sit in a barrier, a norm or attention, HBM keeps streaming into L2 and the
+// ring is refilled from there afterwards. The other lanes only fetch table chunks.
+__device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint64_t *full, uint64_t *empty,
+                                         MegaStage *tabs /* [64] in shared memory */) {
+  const MegaParams &p = c.p;
+  const uint32_t lane = threadIdx.x & 31;
+  const MegaStage *table = p.stages + (size_t)blockIdx.x * p.stage_stride;
+  const uint32_t n = p.stage_count[blockIdx.x];
+  const uint32_t LA = min(p.l2_lookahead, 32u);
+  if (lane < min(n, 32u)) tabs[lane] = table[lane];
+  __syncwarp();
+  uint32_t it = 0;
+  bool stop = false;
+  for (uint32_t base = 0; base < n && !stop; base += 32) {
+    // chunk base/32 is in tabs[(base/32 % 2)*32 ..]; fetch the next one beside it
+    if (base + 32 + lane < n) tabs[((base / 32 + 1) & 1) * 32 + lane] = table[base + 32 + lane];
+    __syncwarp();
+    if (lane == 0) {
+      const uint32_t end = min(base + 32, n);
+      for (; it < end; ++it) {
+        if (LA && it + LA < n) {
+          const MegaStage &f = tabs[(it + LA) & 63];
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(f.codes)), "r"(f.ng * 2048u)
+                       : "memory");
+        }
+        const uint32_t slot = it % NST, ph = (it / NST) & 1u;
+        if (it >= NST && !c.wait(s32(&empty[slot]), ph ^ 1u, 2)) {
+          stop = true;
+          break;
+        }
+        const MegaStage &e = tabs[it & 63];
+        const uint32_t fb = s32(&full[slot]);
+        if (p.timing_mode & 2u) {  // diagnostic: consumer speed without the weight stream
+          mbar_arrive(fb);
+          continue;
+        }
+        mbar_expect(fb, e.ng * (2048u + 128u));
+        bulk_g2s(s32(ring + (size_t)slot * STAGE_BYTES), e.codes, e.ng * 2048u, fb);
+        bulk_g2s(s32(ring + (size_t)slot * STAGE_BYTES + STAGE_CODES), e.scales, e.ng * 128u, fb);
+      }
+    }
+    stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
+  }
+  it = __shfl_sync(0xffffffffu, it, 0);
+  // Nothing may still be landing in this CTA's shared memory when it exits.
+  if (lane == 0) {
+    const uint32_t lo = it > (uint32_t)NST ? it - NST : 0;
+    for (uint32_t j = lo; j < it; ++j) {
+      const uint32_t fb = s32(&full[j % NST]), ph = (j / NST) & 1u;
+      for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(fb, ph); ++i) {
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------ grid barrier
+__device__ __forceinline__ bool grid_barrier(const Ctx &c, uint64_t target) {
+  cons_sync();  // every consumer store of this op is issued
+  if (threadIdx.x == 0 && !c.aborted()) {
+    __threadfence();
+    atomicAdd(c.p.bar, 1ull);
+    bool ok = false;
+    for (uint32_t i = 0; i < WAIT_LIMIT * 8u; ++i) {
+      if (ld_acq_u64(c.p.bar) >= target) {
+        ok = true;
+        break;
+      }
+      if (i > 100000u) __nanosleep(64);
+      if ((i & 1023u) == 1023u && *(volatile uint32_t *)c.p.error != 0u) break;
+    }
+    if (!ok) c.raise(3);
+    __threadfence();
+  }
+  cons_sync();
+  return !c.aborted();
+}
+
+__device__ __forceinline__ float ldcg_h(const __half *p) {
+  return __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short *>(p))));
+}
+
+// ------------------------------------------------------------------ mat-vec
+struct Best {
+  float v;
+  uint32_t i;
+};
+__device__ __forceinline__ bool better(float v, uint32_t i, const Best &b) {
+  return b.i == 0xffffffffu || v > b.v || (v == b.v && i < b.i);
+}
+
+__device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global, uint32_t &it, unsigned char *ring, uint64_t *full,
+                          uint64_t *empty, __half *xs, float *red, float *ssum, float *xsum, const __half *zero16, Best &best,
+                          unsigned long long *tw) {
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const uint32_t G = gridDim.x, cta = blockIdx.x;
+  // Scalars in registers: the barriers' memory clobbers would otherwise make every use
+  // of a field a fresh global load inside the streaming loop.
+  struct {
+    uint32_t N, K, groups, nmat, tiles, epi, rot, track_argmax;
+    const float *norm_w;
+    float eps;
+    const __half *in;
+    __half *out[3];
+    float *out_f32;
+  } op;
+  op.N = op_global.N; op.K = op_global.K; op.groups = op_global.groups; op.nmat = op_global.nmat;
+  op.tiles = op_global.tiles; op.epi = op_global.epi; op.rot = op_global.rot; op.track_argmax = op_global.track_argmax;
+  op.norm_w = op_global.norm_w; op.eps = op_global.eps; op.in = op_global.in;
+  op.out[0] = op_global.out[0]; op.out[1] = op_global.out[1]; op.out[2] = op_global.out[2];
+  op.out_f32 = op_global.out_f32;
+  const uint32_t K = op.K, kpad = op.groups * 128;
+  // ---- input vector -> shared memory (RMSNorm fused, rounded to fp16 where the
+  // reference's RMSNorm op rounds: rms_norm_fp16.comp:70-77), plus 1152 * (sum of
+  // the 32 inputs of every block) for the bias removal. Norm weights and input are
+  // requested together: one memory round trip.
+  {
+    constexpr int MAXV = (2048 + CT - 1) / CT;  // 8-half vectors per thread: K <= 16384
+    uint4 v[MAXV];
+    const uint32_t nv = K / 8;
+    const bool norm = op.norm_w != nullptr;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const uint32_t i = tid + j * CT;
+      v[j] = make_uint4(0, 0, 0, 0);
+      if (i < nv) v[j] = __ldcg(reinterpret_cast<const uint4 *>(op.in) + i);
+    }
+    float alpha = 1.f;
+    if (norm) {
+      // the norm weights are not needed before alpha: start them towards L2/L1 now
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j) {
+        const uint32_t i = tid + j * CT;
+        if (i < nv) asm volatile("prefetch.global.L2 [%0];" ::"l"(op.norm_w + 8 * i));
+      }
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j) {
+        const __half2 *h = reinterpret_cast<const __half2 *>(&v[j]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(h[e]);
+          s += f.x * f.x + f.y * f.y;
+        }
+      }
+      s = warp_sum(s);
+      if (lane == 0) ssum[warp] = s;
+      cons_sync();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < NCW; ++w) tot += ssum[w];
+      alpha = 1.0f / sqrtf(tot / (float)K + op.eps);
+    }
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+      const uint32_t i = tid + j * CT;
+      float bs = 0.f;
+      if (i < nv) {
+        uint4 ov = v[j];
+        if (norm) {
+          const float4 w0 = __ldg(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i);
+          const float4 w1 = __ldg(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i + 1);
+          const __half2 *h = reinterpret_cast<const __half2 *>(&v[j]);
+          const float2 a = __half22float2(h[0]), b = __half22float2(h[1]), cc = __half22float2(h[2]), d = __half22float2(h[3]);
+          __half2 o[4];
+          o[0] = __halves2half2(__float2half_rn(a.x * w0.x * alpha), __float2half_rn(a.y * w0.y * alpha));
+          o[1] = __halves2half2(__float2half_rn(b.x * w0.z * alpha), __float2half_rn(b.y * w0.w * alpha));
+          o[2] = __halves2half2(__float2half_rn(cc.x * w1.x * alpha), __float2half_rn(cc.y * w1.y * alpha));
+          o[3] = __halves2half2(__float2half_rn(d.x * w1.z * alpha), __float2half_rn(d.y * w1.w * alpha));
+          ov = *reinterpret_cast<uint4 *>(o);
+        }
+        *reinterpret_cast<uint4 *>(xs + 8 * i) = ov;
+        const __half2 *h = reinterpret_cast<const __half2 *>(&ov);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(h[e]);
+          bs += f.x + f.y;
+        }
+      }
+      // a block of 32 inputs = 4 consecutive vectors = 4 consecutive lanes
+      bs += __shfl_xor_sync(0xffffffffu, bs, 1);
+      bs += __shfl_xor_sync(0xffffffffu, bs, 2);
+      if ((lane & 3) == 0 && i < nv) xsum[i >> 2] = 1152.0f * bs;
+    }
+    for (uint32_t i = K + tid; i < kpad; i += CT) xs[i] = __ushort_as_half(0);
+    for (uint32_t b = K / 32 + tid; b < kpad / 32; b += CT) xsum[b] = 0.f;
+    cons_sync();
+  }
+  if (tw) tw[1] = clock64();
+
+  // ---- stream this CTA's tiles. A warp owns one group (4 blocks x 16 rows) of every
+  // stage; its partial sums of a (tile, matrix) go to the warp's own slot in shared
+  // memory, so nothing synchronises until the op's single reduction at the end.
+  const uint32_t nstg = (op.groups + SG - 1) / SG;
+  const uint32_t groups = op.groups, nmat = op.nmat, tiles = op.tiles;
+  const uint32_t tile0 = (cta + G - (op.rot % G)) % G;
+  const uint32_t xstep = g == 0 ? 32u : 0u;  // token 0 is column 0 of B: other columns read zeros
+  uint32_t tl = 0;                           // local tile counter
+  for (uint32_t tile = tile0; tile < tiles; tile += G, ++tl) {
+    for (uint32_t m = 0; m < nmat; ++m) {
+      float a0 = 0.f, a1 = 0.f;
+      for (uint32_t s = 0; s < nstg; ++s, ++it) {
+        const uint32_t slot = it % NST, ph = (it / NST) & 1u;
+        unsigned long long w0 = 0, w1 = 0;
+        if (tw) w0 = clock64();
+        const bool ok = c.wait(s32(&full[slot]), ph, 1);
+        if (tw) {
+          w1 = clock64();
+          tw[0] += (w1 - w0) * 1000ull / 1965ull;  // SM cycles -> ns at the 1965 MHz boost clock
+        }
+        const uint32_t ng = min((uint32_t)SG, groups - s * SG);
+        const unsigned char *st = ring + (size_t)slot * STAGE_BYTES;
+        // Groups of a stage go to warps round-robin, starting one warp later every stage,
+        // so the warp that takes two of the 16 groups rotates.
+        uint32_t gi = (warp + NCW - (it % NCW)) % NCW;
+        for (;;) {
+          const bool have = ok && gi < ng;
+          const bool last = !(ok && gi + NCW < ng);
+          uint4 cw[4], sv;
+          if (have) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) cw[j] = *reinterpret_cast<const uint4 *>(st + (gi * 4 + j) * 512 + lane * 16);
+            sv = *reinterpret_cast<const uint4 *>(st + STAGE_CODES + gi * 128 + g * 16);
+          }
+          if (last) {  // this warp has read all it needs from the stage: release it
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(s32(&empty[slot]));
+          }
+          if (have && (c.p.timing_mode & 4u)) {  // diagnostic: ring traffic without arithmetic
+            a0 += __uint_as_float(cw[0].x ^ cw[1].y ^ cw[2].z ^ cw[3].w ^ sv.x);
+          } else if (have) {
+            const uint32_t blk0 = (s * SG + gi) * 4;
+            const __half *xp = g == 0 ? xs + blk0 * 32 + t * 8 : zero16;
+            const float2 da = __half22float2(*reinterpret_cast<const __half2 *>(&sv.x));
+            const float2 db = __half22float2(*reinterpret_cast<const __half2 *>(&sv.y));
+            const float2 ea = __half22float2(*reinterpret_cast<const __half2 *>(&sv.z));
+            const float2 eb = __half22float2(*reinterpret_cast<const __half2 *>(&sv.w));
+            const float dgs[4] = {da.x, da.y, db.x, db.y}, dg8s[4] = {ea.x, ea.y, eb.x, eb.y};
+            const float4 bias4 = *reinterpret_cast<const float4 *>(xsum + blk0);
+            const float biases[4] = {bias4.x, bias4.y, bias4.z, bias4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 X = *reinterpret_cast<const uint4 *>(xp + j * xstep);
+              float cacc[4] = {0.f, 0.f, 0.f, 0.f};
+              mma16816(cacc, codes_raw_h2(cw[j].x, false), codes_raw_h2(cw[j].z, false), codes_raw_h2(cw[j].x, true),
+                       codes_raw_h2(cw[j].z, true), X.x, X.y);
+              mma16816(cacc, codes_raw_h2(cw[j].y, false), codes_raw_h2(cw[j].w, false), codes_raw_h2(cw[j].y, true),
+                       codes_raw_h2(cw[j].w, true), X.z, X.w);
+              a0 = fmaf(cacc[0] - biases[j], dgs[j], a0);
+              a1 = fmaf(cacc[2] - biases[j], dg8s[j], a1);
+            }
+          }
+          if (last) break;
+          gi += NCW;
+        }
+      }
+      if (t == 0) {  // lanes t == 0 hold column 0 = token 0: rows g and g+8
+        float *slotp = red + ((size_t)(tl * nmat + m) * NCW + warp) * 16;
+        slotp[g] = a0;
+        slotp[g + 8] = a1;
+      }
+    }
+  }
+  // ---- one fixed-order reduction over the warps and the epilogue for all tiles
+  if (tw) tw[2] = clock64();
+  cons_sync();
+  for (uint32_t idx = tid; idx < tl * 16; idx += CT) {
+    const uint32_t lt = idx >> 4, r = idx & 15;
+    const uint32_t n = (tile0 + lt * G) * 16 + r;
+    float v[3] = {0.f, 0.f, 0.f};
+    for (uint32_t m = 0; m < nmat; ++m) {
+      const float *sp = red + ((size_t)(lt * nmat + m) * NCW) * 16 + r;
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < NCW; ++w) sum += sp[w * 16];
+      v[m] = sum;
+    }
+    if (n < op.N && !c.aborted()) {
+      if (op.epi == EPI_SWIGLU) {
+        const float gate = v[0], up = v[1];
+        op.out[0][n] = __float2half_rn(gate / (1.0f + expf(-gate)) * up);
+      } else if (op.epi == EPI_ADD) {
+        op.out[0][n] = __float2half_rn(round_h(v[0]) + ldcg_h(op.out[0] + n));
+      } else {
+        const __half h0 = __float2half_rn(v[0]);
+        op.out[0][n] = h0;
+        if (nmat > 1) op.out[1][n] = __float2half_rn(v[1]);
+        if (nmat > 2) op.out[2][n] = __float2half_rn(v[2]);
+        if (op.out_f32) op.out_f32[n] = __half2float(h0);
+        if (op.track_argmax && better(__half2float(h0), n, best)) {
+          best.v = __half2float(h0);
+          best.i = n;
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- attention
+__device__ __forceinline__ void rope_pair(float x0, float x1, float cs, float sn, __half &o0, __half &o1) {
+  o0 = __float2half_rn(x0 * cs - x1 * sn);
+  o1 = __float2half_rn(x0 * sn + x1 * cs);
+}
+
+// One (head, split) per CTA: RoPE(q), RoPE(k) + cache append by the split that
+// owns the new column, scores over its column range, partial softmax and P.V.
+// Same arithmetic as attention_kernel<true> (attention.cu).
+__device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, float *sm, uint32_t pos0, uint32_t S) {
+  const MegaParams &p = c.p;
+  const uint32_t cta = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (cta >= p.heads * S) return;
+  const uint32_t h = cta / S, split = cta % S, D = p.head_dim;
+  float *q_s = sm, *kn_s = sm + D, *red_s = sm + 2 * D, *s_s = sm + (2 + NCW / 2) * D + 2 * NCW + 32;
+  const uint32_t L = min(pos0 + 1, p.maxlen);
+  uint32_t chunk = (L + S - 1) / S;
+  chunk = (chunk + 31) & ~31u;
+  const uint32_t c0 = min(split * chunk, L), c1 = min(c0 + chunk, L);
+  const uint32_t jn = pos0 % p.maxlen;
+  const bool owns = jn >= c0 && jn < c1;
+  const size_t row = (size_t)h * D;
+  if (2 * tid < D) {
+    const size_t fi = (size_t)pos0 * (D / 2) + tid;
+    const float cs = p.freqc[fi], sn = p.freqs[fi];
+    __half r0, r1;
+    rope_pair(ldcg_h(p.q + row + 2 * tid), ldcg_h(p.q + row + 2 * tid + 1), cs, sn, r0, r1);
+    q_s[2 * tid] = __half2float(r0);
+    q_s[2 * tid + 1] = __half2float(r1);
+    if (owns) {
+      rope_pair(ldcg_h(p.k + row + 2 * tid), ldcg_h(p.k + row + 2 * tid + 1), cs, sn, r0, r1);
+      kn_s[2 * tid] = __half2float(r0);
+      kn_s[2 * tid + 1] = __half2float(r1);
+      const size_t dst = ((size_t)h * p.maxlen + jn) * D + 2 * tid;
+      op.kcache[dst] = r0;
+      op.kcache[dst + 1] = r1;
+      op.vcache[dst] = __ushort_as_half(__ldcg(reinterpret_cast<const unsigned short *>(p.v + row + 2 * tid)));
+      op.vcache[dst + 1] = __ushort_as_half(__ldcg(reinterpret_cast<const unsigned short *>(p.v + row + 2 * tid + 1)));
+    }
+  }
+  cons_sync();
+  const float scale = 1.0f / sqrtf((float)D);
+  const __half *kc = op.kcache + (size_t)h * p.maxlen * D;
+  float lmax = -INFINITY;
+  for (uint32_t j = c0 + tid; j < c1; j += CT) {
+    float a = 0.f;
+    if (owns && j == jn) {
+      for (uint32_t d = 0; d < D; ++d) a = fmaf(q_s[d], kn_s[d], a);
+    } else {
+      const uint4 *kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * D);
+#pragma unroll 8
+      for (uint32_t d8 = 0; d8 < D / 8; ++d8) {
+        const uint4 kv = __ldg(kr + d8);
+        const float4 qa = *reinterpret_cast<const float4 *>(q_s + d8 * 8);
+        const float4 qb = *reinterpret_cast<const float4 *>(q_s + d8 * 8 + 4);
+        const float2 k0 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.x));
+        const float2 k1 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.y));
+        const float2 k2 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.z));
+        const float2 k3 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.w));
+        a = fmaf(qa.x, k0.x, a); a = fmaf(qa.y, k0.y, a); a = fmaf(qa.z, k1.x, a); a = fmaf(qa.w, k1.y, a);
+        a = fmaf(qb.x, k2.x, a); a = fmaf(qb.y, k2.y, a); a = fmaf(qb.z, k3.x, a); a = fmaf(qb.w, k3.y, a);
+      }
+    }
+    const float sc = round_h(a * scale);
+    s_s[j - c0] = sc;
+    lmax = fmaxf(lmax, sc);
+  }
+  lmax = warp_max(lmax);
+  if (lane == 0) red_s[warp] = lmax;
+  cons_sync();
+  float mloc = red_s[0];
+#pragma unroll
+  for (int w = 1; w < NCW; ++w) mloc = fmaxf(mloc, red_s[w]);
+  cons_sync();
+  float lsum = 0.f;
+  for (uint32_t j = c0 + tid; j < c1; j += CT) {
+    const float pj = expf(s_s[j - c0] - mloc);
+    s_s[j - c0] = pj;
+    lsum += pj;
+  }
+  lsum = warp_sum(lsum);
+  if (lane == 0) red_s[NCW + warp] = lsum;
+  cons_sync();
+  float lloc = 0.f;
+#pragma unroll
+  for (int w = 0; w < NCW; ++w) lloc += red_s[NCW + w];
+  // P.V: CT/64 column groups x up to 64 dim pairs
+  const uint32_t npair = D / 2, grp = tid / 64, dp = tid % 64;
+  float2 acc = make_float2(0.f, 0.f);
+  if (dp < npair && grp < CT / 64) {
+    const __half *vc = op.vcache + (size_t)h * p.maxlen * D + 2 * dp;
+    constexpr uint32_t NG = CT / 64, UN = 4;  // threads beyond NG*64 sit this part out
+    for (uint32_t jb = c0 + grp; jb < c1; jb += NG * UN) {
+      uint32_t raw[UN];
+#pragma unroll
+      for (uint32_t u = 0; u < UN; ++u) {  // all loads of the batch in flight together
+        const uint32_t j = jb + u * NG;
+        raw[u] = 0;
+        if (j < c1)
+          raw[u] = (owns && j == jn) ? __ldcg(reinterpret_cast<const unsigned int *>(p.v + row + 2 * dp))
+                                     : __ldg(reinterpret_cast<const unsigned int *>(vc + (size_t)j * D));
+      }
+#pragma unroll
+      for (uint32_t u = 0; u < UN; ++u) {
+        const uint32_t j = jb + u * NG;
+        if (j < c1) {
+          const float2 vv = __half22float2(*reinterpret_cast<const __half2 *>(&raw[u]));
+          const float pj = s_s[j - c0];
+          acc.x = fmaf(pj, vv.x, acc.x);
+          acc.y = fmaf(pj, vv.y, acc.y);
+        }
+      }
+    }
+  }
+  cons_sync();
+  float *pv = red_s + 2 * NCW;  // [CT/64 groups][D]
+  if (dp < npair && grp < CT / 64) {
+    pv[grp * D + 2 * dp] = acc.x;
+    pv[grp * D + 2 * dp + 1] = acc.y;
+  }
+  cons_sync();
+  float *part = p.attn_scratch + ((size_t)h * p.splits + split) * (D + 2);
+  if (tid < D) {
+    float s = 0.f;
+#pragma unroll
+    for (int gq = 0; gq < CT / 64; ++gq) s += pv[gq * D + tid];
+    if (S == 1)
+      p.ao[row + tid] = __float2half_rn(s / lloc);  // whole row in this CTA: no combine phase
+    else
+      part[tid] = s;
+  }
+  if (tid == 0) {
+    part[D] = mloc;
+    part[D + 1] = lloc;
+  }
+}
+
+// One head per CTA: merge the split partials in split order.
+__device__ __forceinline__ void attn_combine_op(const Ctx &c, uint32_t) {
+  const MegaParams &p = c.p;
+  const uint32_t h = blockIdx.x, tid = threadIdx.x, D = p.head_dim;
+  if (h >= p.heads || tid >= D) return;
+  const float *base = p.attn_scratch + (size_t)h * p.splits * (D + 2);
+  float M = -INFINITY;
+  for (uint32_t s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(base + s * (D + 2) + D));
+  float den = 0.f, num = 0.f;
+  for (uint32_t s = 0; s < p.splits; ++s) {
+    const float ms = __ldcg(base + s * (D + 2) + D), ls = __ldcg(base + s * (D + 2) + D + 1);
+    if (ls > 0.f) {
+      const float w = expf(ms - M);
+      den += ls * w;
+      num += __ldcg(base + s * (D + 2) + tid) * w;
+    }
+  }
+  p.ao[(size_t)h * D + tid] = __float2half_rn(num / den);
+}
+
+// Embedding gather + dequantisation of the current token (embedding_q8_0.comp:39-85).
+__device__ __forceinline__ void embed_op(const Ctx &c, uint32_t tok) {
+  const MegaParams &p = c.p;
+  const uint32_t per = (p.dim + gridDim.x - 1) / gridDim.x;
+  const uint32_t k = blockIdx.x * per + threadIdx.x;
+  if (threadIdx.x >= per || k >= p.dim) return;
+  if (tok >= p.embd_rows) tok = 0;  // UNK = 0 (models/llama2.h:455-458)
+  const Q8Layout L = q8_layout(p.embd_rows, p.dim);
+  const uint32_t tile = tok >> 4, r = tok & 15, g = r & 7, half = r >> 3;
+  const uint32_t b = k >> 5, t = (k >> 3) & 3, i = k & 7;
+  const uint8_t cb = p.embd[(((size_t)tile * L.groups * 4 + b) * 32 + g * 4 + t) * 16 + half * 8 + q8_byte_pos(i)];
+  const uint16_t *sc = reinterpret_cast<const uint16_t *>(p.embd + L.codes_bytes());
+  const uint16_t d = sc[(((size_t)tile * L.groups + (b >> 2)) * 8 + g) * 8 + half * 4 + (b & 3)];
+  p.x[k] = __float2half_rn((float)((int)cb - 128) * __half2float(__ushort_as_half(d)));
+}
+
+// CTA 0: best of the per-CTA candidates (lowest index on ties), then publish the id,
+// feed it back and advance position, step and launch epoch.
+__device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_t pos0, uint64_t rounds_done) {
+  const MegaParams &p = c.p;
+  if (blockIdx.x != 0) return;
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  Best b = {0.f, 0xffffffffu};
+  for (uint32_t i = tid; i < gridDim.x; i += CT) {
+    const float v = __ldcg(p.arg_scratch + 2 * i);
+    const uint32_t ix = __float_as_uint(__ldcg(p.arg_scratch + 2 * i + 1));
+    if (ix != 0xffffffffu && better(v, ix, b)) {
+      b.v = v;
+      b.i = ix;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, b.v, o);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, b.i, o);
+    if (oi != 0xffffffffu && better(ov, oi, b)) {
+      b.v = ov;
+      b.i = oi;
+    }
+  }
+  uint32_t *si = reinterpret_cast<uint32_t *>(sm);
+  if (lane == 0) {
+    sm[32 + warp] = b.v;
+    si[warp] = b.i;
+  }
+  cons_sync();
+  if (tid == 0) {
+    for (int w = 1; w < NCW; ++w)
+      if (si[w] != 0xffffffffu && better(sm[32 + w], si[w], b)) {
+        b.v = sm[32 + w];
+        b.i = si[w];
+      }
+    if (!c.aborted()) {
+      const uint32_t step = p.state[1];
+      p.state[2] = b.i;
+      p.tok[0] = b.i;
+      if (step < p.out_cap) p.out_ids[step] = b.i;
+      p.state[1] = step + 1;
+      p.state[0] = pos0 + 1;
+      p.bar[1] = rounds_done;
+    }
+  }
+}
+
+template <bool TIMED>
+__global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char *ring = smem;
+  __half *xs = reinterpret_cast<__half *>(smem + (size_t)NST * STAGE_BYTES);
+  float *red = reinterpret_cast<float *>(smem + (size_t)NST * STAGE_BYTES + p.xs_bytes);
+  float *ssum = red + RED_SLOTS * NCW * 16;
+  float *xsum = ssum + 32;  // [512]
+  __half *zero16 = reinterpret_cast<__half *>(xsum + 512);  // 16 zero bytes
+  MegaStage *tabs = reinterpret_cast<MegaStage *>(xsum + 512 + 4);  // [64], 16-byte aligned
+  uint64_t *full = reinterpret_cast<uint64_t *>(tabs + 64);
+  uint64_t *empty = full + NST;
+  volatile uint32_t *abort_s = reinterpret_cast<volatile uint32_t *>(empty + NST);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < NST; ++i) {
+      mbar_init(s32(&full[i]), 1);
+      mbar_init(s32(&empty[i]), NCW);
+    }
+    *abort_s = 0;
+    *reinterpret_cast<uint4 *>(zero16) = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  const Ctx c{p, abort_s};
+
+  if (threadIdx.x >= CT) {  // producer warp
+    producer(c, ring, full, empty, tabs);
+    return;
+  }
+
+  const uint32_t G = gridDim.x;
+  const uint32_t pos0 = p.state[0], tok = p.tok[0];
+  const uint64_t base_rounds = p.bar[1];  // barrier rounds completed by earlier launches
+  uint64_t rounds = 0;
+  const uint32_t Lnow = min(pos0 + 1, p.maxlen);
+  const uint32_t S_eff = Lnow <= p.single_split_len ? 1u : p.splits;
+  uint32_t it = 0;
+  Best best = {0.f, 0xffffffffu};
+  const bool timed = TIMED && p.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+  unsigned long long t0 = 0, twait[3] = {0, 0, 0}, c0 = 0;
+  if (timed) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (uint32_t oi = 0; oi < p.nops; ++oi) {
+    const MegaOp &op = p.ops[oi];
+    if (op.kind == MK_ATTN_COMBINE && S_eff == 1) continue;  // nothing to merge, no barrier either
+    if (timed) c0 = clock64();
+    switch (op.kind) {
+      case MK_EMBED: embed_op(c, tok); break;
+      case MK_MATVEC: matvec_op(c, op, it, ring, full, empty, xs, red, ssum, xsum, zero16, best, (TIMED && timed) ? twait : nullptr); break;
+      case MK_ATTN_PART: attn_part_op(c, op, reinterpret_cast<float *>(xs), pos0, S_eff); break;
+      case MK_ATTN_COMBINE: attn_combine_op(c, pos0); break;
+      case MK_ARGMAX:
+        argmax_final_op(c, reinterpret_cast<float *>(xs), pos0, base_rounds + rounds);
+        break;
+    }
+    if (op.kind == MK_MATVEC && op.track_argmax) {
+      // per-CTA arg-max candidate: every epilogue thread holds the best of its rows
+      Best bb = best;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bb.v, o);
+        const uint32_t oi2 = __shfl_xor_sync(0xffffffffu, bb.i, o);
+        if (oi2 != 0xffffffffu && better(ov, oi2, bb)) {
+          bb.v = ov;
+          bb.i = oi2;
+        }
+      }
+      float *cand = ssum;  // [NCW] values, then [NCW] indices
+      cons_sync();
+      if ((threadIdx.x & 31) == 0) {
+        cand[threadIdx.x >> 5] = bb.v;
+        cand[NCW + (threadIdx.x >> 5)] = __uint_as_float(bb.i);
+      }
+      cons_sync();
+      if (threadIdx.x == 0) {
+        for (int w = 1; w < NCW; ++w) {
+          const uint32_t wi = __float_as_uint(cand[NCW + w]);
+          if (wi != 0xffffffffu && better(cand[w], wi, bb)) {
+            bb.v = cand[w];
+            bb.i = wi;
+          }
+        }
+        p.arg_scratch[2 * blockIdx.x] = bb.v;
+        p.arg_scratch[2 * blockIdx.x + 1] = __uint_as_float(bb.i);
+      }
+    }
+    unsigned long long t1 = 0, t2 = 0;
+    if (timed) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (oi + 1 < p.nops) {
+      ++rounds;
+      grid_barrier(c, (base_rounds + rounds) * G);
+    }
+    if (timed) {
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t2));
+      p.timing[2 * oi] = t1 - t0;
+      p.timing[2 * oi + 1] = t2 - t1;
+      const unsigned long long cend = clock64();
+      p.timing[2 * p.nops + oi] = (p.timing_mode & 8u) ? (twait[2] ? (cend - twait[2]) * 1000ull / 1965ull - (t2 - t1) : 0ull)
+                                  : getenv_prologue(p) ? (twait[1] > c0 ? (twait[1] - c0) * 1000ull / 1965ull : 0ull)
+                                                        : twait[0];
+      twait[2] = 0;
+      twait[0] = 0;
+      twait[1] = 0;
+      t0 = t2;
+    }
+  }
+}
+
+}  // namespace
+
+size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits) {
+  size_t x = (size_t)max_groups * 128 * 2;
+  uint32_t chunk = ((maxlen + splits - 1) / splits + 31) & ~31u;
+  size_t a = (size_t)((2 + NCW / 2) * head_dim + 2 * NCW + 32 + chunk + 32) * 4;
+  size_t b = x > a ? x : a;
+  return (b + 127) / 128 * 128;
+}
+size_t decode_mega_smem(size_t xs_bytes) {
+  return (size_t)NST * STAGE_BYTES + xs_bytes + (RED_SLOTS * NCW * 16 + 32 + 512 + 4) * 4 + 64 * sizeof(MegaStage) + 2 * NST * 8 + 64;
+}
+int decode_mega_max_k() { return 16384; }
+int decode_mega_red_slots() { return RED_SLOTS; }
+int decode_mega_stage_groups() { return SG; }
+
+cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s) {
+  const size_t smem = decode_mega_smem(p.xs_bytes);
+  auto kern = p.timing ? decode_mega_kernel<true> : decode_mega_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  void *args[] = {(void *)&p};
+  return cudaLaunchCooperativeKernel((void *)kern, dim3(grid), dim3(THREADS), args, smem, s);
+}
+
+cudaError_t decode_mega_occupancy(size_t xs_bytes, int *blocks_per_sm) {
+  const size_t smem = decode_mega_smem(xs_bytes);
+  cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, decode_mega_kernel<false>, THREADS, smem);
+}
+
+}  // namespace vkl

@@ -25,7 +25,7 @@ __global__ void q8_repack_kernel(const uint8_t *__restrict__ src, uint8_t *__res
       const bool ok = row < L.N && b < L.blocks;
       const uint8_t *blk = src + ((size_t)row * L.blocks + b) * 34 + 2 + t * 8;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v[half * 8 + k] = ok ? (uint8_t)(blk[k] ^ 0x80) : (uint8_t)0x80;
+      for (int k = 0; k < 8; ++k) v[half * 8 + q8_byte_pos(k)] = ok ? (uint8_t)(blk[k] ^ 0x80) : (uint8_t)0x80;
     }
     *reinterpret_cast<uint4 *>(dst + i * 16) = *reinterpret_cast<uint4 *>(v);
   } else if (i < nvec + nsc) {
@@ -61,7 +61,7 @@ __global__ void q8_unpack_kernel(const uint8_t *__restrict__ src, uint8_t *__res
   o[1] = d >> 8;
   for (uint32_t t = 0; t < 4; ++t) {
     const uint8_t *c = src + (((size_t)tile * L.groups * 4 + b) * 32 + g * 4 + t) * 16 + half * 8;
-    for (int k = 0; k < 8; ++k) o[2 + t * 8 + k] = c[k] ^ 0x80;
+    for (int k = 0; k < 8; ++k) o[2 + t * 8 + k] = c[q8_byte_pos(k)] ^ 0x80;
   }
 }
 
@@ -194,7 +194,7 @@ __global__ void embedding_q8_kernel(const uint8_t *__restrict__ planes,
   const uint16_t *sc = reinterpret_cast<const uint16_t *>(planes + L.codes_bytes());
   for (uint32_t k = threadIdx.x; k < L.K; k += blockDim.x) {
     const uint32_t b = k >> 5, t = (k >> 3) & 3, i = k & 7;
-    const uint8_t c = planes[(((size_t)tile * L.groups * 4 + b) * 32 + g * 4 + t) * 16 + half * 8 + i];
+    const uint8_t c = planes[(((size_t)tile * L.groups * 4 + b) * 32 + g * 4 + t) * 16 + half * 8 + q8_byte_pos(i)];
     const uint16_t d = sc[(((size_t)tile * L.groups + (b >> 2)) * 8 + g) * 8 + half * 4 + (b & 3)];
     const float q = (float)((int)c - 128);
     out[(size_t)blockIdx.x * L.K + k] = __float2half_rn(q * __half2float(__ushort_as_half(d)));

@@ -105,4 +105,59 @@ struct AttnParams {
 cudaError_t launch_attention(const AttnParams &p, cudaStream_t s);
 size_t attention_scratch_bytes(uint32_t T, uint32_t heads, uint32_t dim, uint32_t splits);
 
+// ---- persistent decode step (decode_mega.cu) --------------------------------
+enum MegaKind { MK_EMBED = 0, MK_MATVEC = 1, MK_ATTN_PART = 2, MK_ATTN_COMBINE = 3, MK_ARGMAX = 4 };
+struct MegaOp {
+  uint32_t kind, epi, nmat, rot;
+  uint32_t N, K, tiles, groups;
+  const uint8_t *codes[3];
+  const uint8_t *scales[3];
+  const float *norm_w;  // fused RMSNorm of the input, or null
+  float eps;
+  uint32_t track_argmax;  // lm head: keep a per-CTA (max, index) candidate
+  const __half *in;       // input vector [K]
+  __half *out[3];         // EPI_ADD: out[0] is also the residual
+  float *out_f32;
+  __half *kcache, *vcache;  // MK_ATTN_PART
+};
+// One ring stage of the persistent kernel: up to 16 groups of one (tile, matrix).
+struct MegaStage {
+  const uint8_t *codes;
+  const uint8_t *scales;
+  uint32_t ng, pad[3];
+};
+struct MegaParams {
+  const MegaOp *ops;
+  const MegaStage *stages;       // [grid][stage_stride]: every CTA's stages in consumer order
+  const uint32_t *stage_count;   // [grid]
+  uint32_t stage_stride;
+  uint32_t nops, nbarriers;
+  uint32_t *state;    // [0] position, [1] step, [2] picked id
+  uint32_t *tok;      // current token id
+  uint32_t *out_ids;
+  uint32_t out_cap;
+  const uint8_t *embd;  // token embedding, Q8_0 tiled planes
+  uint32_t embd_rows;
+  __half *x, *q, *k, *v, *ao;
+  const float *freqc, *freqs;
+  float *attn_scratch;      // heads*splits*(head_dim+2)
+  float *arg_scratch;       // grid*2
+  unsigned long long *bar;  // [0] arrivals, [1] completed launches
+  uint32_t *error;          // 0, or the code of the wait that timed out
+  uint32_t dim, heads, head_dim, maxlen, splits, vocab;
+  uint32_t xs_bytes;
+  uint32_t l2_lookahead;      // weight stages kept in flight towards L2 ahead of the ring
+  uint32_t single_split_len;  // KV lengths up to this use one CTA per head (no combine phase)
+  // Optional timeline of CTA 0: per op, nanoseconds of work and of barrier wait.
+  unsigned long long *timing;
+  uint32_t timing_mode;  // third column of the timeline: 0 = ring wait, 1 = op prologue
+};
+size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits);
+size_t decode_mega_smem(size_t xs_bytes);
+int decode_mega_max_k();
+int decode_mega_red_slots();
+int decode_mega_stage_groups();
+cudaError_t decode_mega_occupancy(size_t xs_bytes, int *blocks_per_sm);
+cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s);
+
 }  // namespace vkl

@@ -12,7 +12,10 @@
 //   RMSNorm+QKV mat-vec | RoPE+append+attention | o_proj+residual |
 //   RMSNorm+gate/up+SwiGLU | down+residual
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
+
+#include <algorithm>
 
 #include <string>
 
@@ -62,6 +65,12 @@ struct vkl_model {
   uint32_t splits = 8, out_cap = 0;
   cudaGraphExec_t decode_graph = nullptr;
   bool use_pdl = true;
+  // persistent single-kernel decode step (decode_mega.cu)
+  bool mega_ready = false, mega_tried = false;
+  int mega_grid = 0;
+  vkl_tensor *mega_ops = nullptr, *mega_sync = nullptr, *mega_arg = nullptr, *mega_attn = nullptr, *mega_stages = nullptr, *mega_counts = nullptr;
+  MegaParams mp;
+  uint32_t mega_launches_per_token = 1;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
   uint32_t *pos_dev() { return (uint32_t *)state->data(); }
   uint32_t *step_dev() { return (uint32_t *)state->data() + 1; }
@@ -70,7 +79,7 @@ struct vkl_model {
     if (decode_graph) cudaGraphExecDestroy(decode_graph);
     for (auto &l : L)
       for (vkl_tensor *p : {l.attn_norm, l.ffn_norm, l.wq, l.wk, l.wv, l.wo, l.gate, l.up, l.down, l.kcache, l.vcache}) vkl_tensor_release(p);
-    for (vkl_tensor *p : {tok_embd, output_norm, output, fc, fs, x, xn, q, k, v, ao, t, logits16, logits32, toks, state, out_ids, argpart, attn_scratch, attn_counters})
+    for (vkl_tensor *p : {tok_embd, output_norm, output, fc, fs, x, xn, q, k, v, ao, t, logits16, logits32, toks, state, out_ids, argpart, attn_scratch, attn_counters, mega_ops, mega_sync, mega_arg, mega_attn, mega_stages, mega_counts})
       vkl_tensor_release(p);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
@@ -90,6 +99,13 @@ int ensure_rows(vkl_model *m, uint32_t T) {
     m->decode_graph = nullptr;
   }
   VKL_CUDA(cudaStreamSynchronize(m->stream));
+  if (m->mega_tried) {  // the op table of the persistent kernel holds the old buffers too
+    for (vkl_tensor **t : {&m->mega_ops, &m->mega_sync, &m->mega_arg, &m->mega_attn, &m->mega_stages, &m->mega_counts}) {
+      vkl_tensor_release(*t);
+      *t = nullptr;
+    }
+    m->mega_ready = m->mega_tried = false;
+  }
   const size_t D = m->cfg.dim;
   VKL_OKAY(ensure_tensor(m->dev, &m->x, 1, T, D, VKL_FP16));
   VKL_OKAY(ensure_tensor(m->dev, &m->xn, 1, T, D, VKL_FP16));
@@ -235,6 +251,200 @@ int launch_advance(vkl_model *m, uint32_t pos_inc) {
   advance_kernel<<<1, 1, 0, m->stream>>>(m->next_dev(), (uint32_t *)m->toks->data(), m->pos_dev(), m->step_dev(),
                                          (uint32_t *)m->out_ids->data(), m->out_cap, pos_inc);
   VKL_LAUNCH(1, cudaGetLastError());
+  return VKL_OK;
+}
+
+// Builds the op table of the persistent decode kernel. Q8_0 weights, one GPU.
+// VKLLAMA_DECODE=graph keeps the multi-kernel CUDA-graph step instead.
+int build_mega(vkl_model *m) {
+  if (m->mega_tried) return VKL_OK;
+  m->mega_tried = true;
+  const char *env = getenv("VKLLAMA_DECODE");
+  if (env && !strcmp(env, "graph")) return VKL_OK;
+  if (!q8(m) || m->cfg.tp_size != 1 || m->tok_embd->dtype != VKL_Q8_0) return VKL_OK;
+  const vkl_model_config &c = m->cfg;
+  if ((int)c.dim > decode_mega_max_k() || (int)c.ffn > decode_mega_max_k() || (c.dim % 32) || (c.ffn % 32) || (m->head_dim & 1)) return VKL_OK;
+  int coop = 0;
+  VKL_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->dev->ordinal));
+  if (!coop) return VKL_OK;
+  const int G = m->dev->prop.multiProcessorCount;
+  uint32_t splits = (uint32_t)G / m->heads_l;
+  if (splits < 1) return VKL_OK;  // more heads than SMs: keep the graph path
+  if (splits > 8) splits = 8;
+  const uint32_t max_groups = (std::max(c.dim, c.ffn) / 32 + 3) / 4;
+  const size_t xs_bytes = decode_mega_xs_bytes(max_groups, m->head_dim, c.maxlen, splits);
+  if (decode_mega_smem(xs_bytes) > (size_t)m->dev->prop.sharedMemPerBlockOptin) return VKL_OK;
+  int occ = 0;
+  VKL_CUDA(decode_mega_occupancy(xs_bytes, &occ));
+  if (occ < 1) return VKL_OK;
+  {  // every op's (tiles per CTA) x (matrices) must fit the kernel's reduction slots
+    auto slots = [&](uint32_t rows, uint32_t nmat) { return (((rows + 15) / 16 + G - 1) / G) * nmat; };
+    const uint32_t need = std::max({slots(m->dim_l, 3), slots(c.dim, 1), slots(m->ffn_l, 2), slots(m->vocab_l, 1)});
+    if ((int)need > decode_mega_red_slots()) return VKL_OK;
+  }
+  VKL_OKAY(ensure_rows(m, 1));
+
+  std::vector<MegaOp> ops;
+  uint32_t rot = 0;
+  auto matvec = [&](std::initializer_list<const vkl_tensor *> ws, const float *norm, float eps, const __half *in, std::initializer_list<__half *> outs, int epi) {
+    MegaOp o = {};
+    o.kind = MK_MATVEC;
+    o.epi = epi;
+    const vkl_tensor *w0 = *ws.begin();
+    o.N = (uint32_t)w0->h;
+    o.K = (uint32_t)w0->w;
+    o.tiles = (o.N + 15) / 16;
+    o.groups = ((o.K + 31) / 32 + 3) / 4;
+    o.nmat = (uint32_t)ws.size();
+    int i = 0;
+    for (const vkl_tensor *w : ws) {
+      o.codes[i] = w->codes();
+      o.scales[i] = w->scales();
+      ++i;
+    }
+    i = 0;
+    for (__half *p : outs) o.out[i++] = p;
+    o.norm_w = norm;
+    o.eps = eps;
+    o.in = in;
+    o.rot = rot;
+    rot = (rot + o.tiles) % (uint32_t)G;
+    ops.push_back(o);
+  };
+  __half *x = (__half *)m->x->data(), *qb = (__half *)m->q->data(), *kb = (__half *)m->k->data(), *vb = (__half *)m->v->data();
+  __half *ao = (__half *)m->ao->data(), *tb = (__half *)m->t->data();
+  MegaOp e = {};
+  e.kind = MK_EMBED;
+  ops.push_back(e);
+  for (uint32_t l = 0; l < c.layers; ++l) {
+    Layer &y = m->L[l];
+    matvec({y.wk, y.wq, y.wv}, (const float *)y.attn_norm->data(), c.eps, x, {kb, qb, vb}, EPI_PLAIN);
+    MegaOp a = {};
+    a.kind = MK_ATTN_PART;
+    a.kcache = (__half *)y.kcache->data();
+    a.vcache = (__half *)y.vcache->data();
+    ops.push_back(a);
+    MegaOp cb = {};
+    cb.kind = MK_ATTN_COMBINE;
+    ops.push_back(cb);
+    matvec({y.wo}, nullptr, 0.f, ao, {x}, EPI_ADD);
+    matvec({y.gate, y.up}, (const float *)y.ffn_norm->data(), c.eps, x, {tb}, EPI_SWIGLU);
+    matvec({y.down}, nullptr, 0.f, tb, {x}, EPI_ADD);
+  }
+  matvec({m->output}, (const float *)m->output_norm->data(), c.final_eps, x, {(__half *)m->logits16->data()}, EPI_PLAIN);
+  ops.back().out_f32 = (float *)m->logits32->data();
+  ops.back().track_argmax = 1;
+  MegaOp am = {};
+  am.kind = MK_ARGMAX;
+  ops.push_back(am);
+
+  // Stage tables: every CTA's ring stages for one token, in the order its consumers walk them.
+  const uint32_t SGR = (uint32_t)decode_mega_stage_groups();
+  std::vector<std::vector<MegaStage>> per_cta(G);
+  for (const MegaOp &o : ops) {
+    if (o.kind != MK_MATVEC) continue;
+    const uint32_t nstg = (o.groups + SGR - 1) / SGR;
+    for (int cta = 0; cta < G; ++cta)
+      for (uint32_t tile = ((uint32_t)cta + G - (o.rot % G)) % G; tile < o.tiles; tile += G)
+        for (uint32_t mt = 0; mt < o.nmat; ++mt)
+          for (uint32_t st = 0; st < nstg; ++st) {
+            MegaStage e = {};
+            const size_t g0 = (size_t)tile * o.groups + (size_t)st * SGR;
+            e.codes = o.codes[mt] + g0 * 2048;
+            e.scales = o.scales[mt] + g0 * 128;
+            e.ng = std::min(SGR, o.groups - st * SGR);
+            per_cta[cta].push_back(e);
+          }
+  }
+  size_t stride = 0;
+  for (auto &v : per_cta) stride = std::max(stride, v.size());
+  std::vector<MegaStage> flat((size_t)G * stride);
+  std::vector<uint32_t> counts(G);
+  for (int cta = 0; cta < G; ++cta) {
+    counts[cta] = (uint32_t)per_cta[cta].size();
+    std::copy(per_cta[cta].begin(), per_cta[cta].end(), flat.begin() + (size_t)cta * stride);
+  }
+  VKL_OKAY(tensor_new(m->dev, 1, 1, flat.size() * sizeof(MegaStage) / 4, VKL_UINT32, &m->mega_stages));
+  VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)G, VKL_UINT32, &m->mega_counts));
+  VKL_CUDA(cudaMemcpyAsync(m->mega_stages->data(), flat.data(), flat.size() * sizeof(MegaStage), cudaMemcpyHostToDevice, m->stream));
+  VKL_CUDA(cudaMemcpyAsync(m->mega_counts->data(), counts.data(), (size_t)G * 4, cudaMemcpyHostToDevice, m->stream));
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+
+  const size_t ob = ops.size() * sizeof(MegaOp);
+  VKL_OKAY(tensor_new(m->dev, 1, 1, (ob + 3) / 4, VKL_UINT32, &m->mega_ops));
+  VKL_OKAY(tensor_new(m->dev, 1, 1, 16, VKL_UINT32, &m->mega_sync));  // [0..3] barrier words, [4] error
+  VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)G * 2, VKL_FP32, &m->mega_arg));
+  VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)m->heads_l * splits * (m->head_dim + 2), VKL_FP32, &m->mega_attn));
+  VKL_CUDA(cudaMemcpyAsync(m->mega_ops->data(), ops.data(), ob, cudaMemcpyHostToDevice, m->stream));
+  VKL_CUDA(cudaMemsetAsync(m->mega_sync->data(), 0, 64, m->stream));
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  MegaParams &p = m->mp;
+  p = MegaParams{};
+  p.ops = (const MegaOp *)m->mega_ops->data();
+  p.stages = (const MegaStage *)m->mega_stages->data();
+  p.stage_count = (const uint32_t *)m->mega_counts->data();
+  p.stage_stride = (uint32_t)stride;
+  p.nops = (uint32_t)ops.size();
+  p.nbarriers = p.nops - 1;
+  p.state = (uint32_t *)m->state->data();
+  p.tok = (uint32_t *)m->toks->data();
+  p.out_ids = (uint32_t *)m->out_ids->data();
+  p.out_cap = m->out_cap;
+  p.embd = m->tok_embd->data();
+  p.embd_rows = (uint32_t)m->tok_embd->h;
+  p.x = x; p.q = qb; p.k = kb; p.v = vb; p.ao = ao;
+  p.freqc = (const float *)m->fc->data();
+  p.freqs = (const float *)m->fs->data();
+  p.attn_scratch = (float *)m->mega_attn->data();
+  p.arg_scratch = (float *)m->mega_arg->data();
+  p.bar = (unsigned long long *)m->mega_sync->data();
+  p.error = (uint32_t *)m->mega_sync->data() + 4;
+  p.dim = c.dim; p.heads = m->heads_l; p.head_dim = m->head_dim; p.maxlen = c.maxlen; p.splits = splits; p.vocab = m->vocab_l;
+  p.xs_bytes = (uint32_t)xs_bytes;
+  {
+    const char *la = getenv("VKLLAMA_L2_LOOKAHEAD");
+    p.l2_lookahead = la ? (uint32_t)atoi(la) : 0u;
+    const uint32_t chunk_cap = ((c.maxlen + splits - 1) / splits + 31) & ~31u;
+    const char *ss = getenv("VKLLAMA_SINGLE_SPLIT_LEN");
+    p.single_split_len = std::min(ss ? (uint32_t)atoi(ss) : 0u, chunk_cap);
+  }
+  m->mega_grid = G;
+  m->mega_ready = true;
+  return VKL_OK;
+}
+
+// After a batch of decode launches: a wait that timed out inside the kernel is
+// reported as an error and the barrier words are reset.
+int check_mega(vkl_model *m) {
+  if (!m->mega_ready) return VKL_OK;
+  uint32_t err = 0;
+  VKL_CUDA(cudaMemcpyAsync(&err, m->mp.error, 4, cudaMemcpyDeviceToHost, m->stream));
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  if (err) {
+    cudaMemsetAsync(m->mega_sync->data(), 0, 64, m->stream);
+    cudaStreamSynchronize(m->stream);
+    return fail(VKL_INTERNAL, "decode kernel: a bounded wait ran out (code %u: 1 weight stage, 2 ring slot, 3 grid barrier)", err);
+  }
+  return VKL_OK;
+}
+
+int build_decode_graph(vkl_model *m);
+
+// Enqueue one decode step: the persistent kernel when available, else the graph.
+int decode_step(vkl_model *m) {
+  if (m->mega_ready) {
+    VKL_LAUNCH(1, launch_decode_mega(m->mp, m->mega_grid, m->stream));
+    return VKL_OK;
+  }
+  VKL_CUDA(cudaGraphLaunch(m->decode_graph, m->stream));
+  count_launches(5 * m->cfg.layers + 5);
+  return VKL_OK;
+}
+
+int prepare_decode(vkl_model *m) {
+  VKL_OKAY(ensure_rows(m, 1));
+  VKL_OKAY(build_mega(m));
+  if (!m->mega_ready) VKL_OKAY(build_decode_graph(m));
   return VKL_OK;
 }
 
@@ -475,18 +685,18 @@ int vkl_model_forward(vkl_model *m, const uint32_t *toks, size_t n, size_t offse
   if (offset + n > (size_t)2 * m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_forward: position %zu is beyond the RoPE table (2*maxlen)", offset + n);
   VKL_CUDA(cudaSetDevice(m->dev->ordinal));
   VKL_OKAY(ensure_rows(m, (uint32_t)n));
-  if (n == 1) VKL_OKAY(build_decode_graph(m));
+  if (n == 1) VKL_OKAY(prepare_decode(m));
   const uint32_t st[2] = {(uint32_t)offset, 0};
   VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaMemcpyAsync(m->toks->data(), toks, n * 4, cudaMemcpyHostToDevice, m->stream));
   if (n == 1) {
-    VKL_CUDA(cudaGraphLaunch(m->decode_graph, m->stream));
-    count_launches(5 * m->cfg.layers + 5);
+    VKL_OKAY(decode_step(m));
   } else {
     VKL_OKAY(run_tokens(m, (uint32_t)n, false));
   }
   VKL_CUDA(cudaMemcpyAsync(logits_out, m->logits32->data(), (size_t)m->vocab_l * 4, cudaMemcpyDeviceToHost, m->stream));
   VKL_CUDA(cudaStreamSynchronize(m->stream));
+  if (n == 1) VKL_OKAY(check_mega(m));
   return VKL_OK;
 }
 
@@ -500,21 +710,19 @@ int vkl_model_generate(vkl_model *m, const uint32_t *prompt, size_t n_prompt, si
     return fail(VKL_OUT_OF_RANGE, "model_generate: %zu + %zu tokens run past the RoPE table (2*maxlen)", n_prompt, n_gen);
   VKL_CUDA(cudaSetDevice(m->dev->ordinal));
   VKL_OKAY(ensure_rows(m, (uint32_t)n_prompt));
-  VKL_OKAY(build_decode_graph(m));
+  VKL_OKAY(prepare_decode(m));
   const uint32_t st[2] = {0, 0};
   VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaMemcpyAsync(m->toks->data(), prompt, n_prompt * 4, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaEventRecord(m->ev0, m->stream));
   if (n_prompt == 1) {
-    VKL_CUDA(cudaGraphLaunch(m->decode_graph, m->stream));
-    count_launches(5 * m->cfg.layers + 5);
+    VKL_OKAY(decode_step(m));
   } else {
     VKL_OKAY(run_tokens(m, (uint32_t)n_prompt, false));
     VKL_OKAY(launch_advance(m, (uint32_t)n_prompt));
   }
   VKL_CUDA(cudaEventRecord(m->ev1, m->stream));
-  for (size_t i = 1; i < n_gen; ++i) VKL_CUDA(cudaGraphLaunch(m->decode_graph, m->stream));
-  count_launches((n_gen - 1) * (5 * m->cfg.layers + 5));
+  for (size_t i = 1; i < n_gen; ++i) VKL_OKAY(decode_step(m));
   VKL_CUDA(cudaEventRecord(m->ev2, m->stream));
   VKL_CUDA(cudaMemcpyAsync(out_ids, m->out_ids->data(), n_gen * 4, cudaMemcpyDeviceToHost, m->stream));
   VKL_CUDA(cudaStreamSynchronize(m->stream));
@@ -527,7 +735,7 @@ int vkl_model_generate(vkl_model *m, const uint32_t *prompt, size_t n_prompt, si
     VKL_CUDA(cudaEventElapsedTime(&ms, m->ev1, m->ev2));
     *decode_ms = ms;
   }
-  return VKL_OK;
+  return check_mega(m);
 }
 
 int vkl_model_read_kv(vkl_model *m, uint32_t layer, void *kcache, void *vcache) {
@@ -610,20 +818,58 @@ int vkl_model_block_forward(vkl_model *m, uint32_t layer, const void *x_fp16, si
   return VKL_OK;
 }
 
-int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[8]) {
+int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[16]) {
   VKL_OKAY(check_ready(m));
   if (!out_us) return fail(VKL_INVALID_ARGUMENT, "model_decode_profile: null output");
   if (offset + 1 > (size_t)2 * m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_decode_profile: position out of range");
   VKL_CUDA(cudaSetDevice(m->dev->ordinal));
-  VKL_OKAY(ensure_rows(m, 1));
+  VKL_OKAY(prepare_decode(m));
   const uint32_t st[2] = {(uint32_t)offset, 0};
   VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaMemcpyAsync(m->toks->data(), &token, 4, cudaMemcpyHostToDevice, m->stream));
+  for (int i = 0; i < 16; ++i) out_us[i] = 0.f;
+  if (m->mega_ready) {
+    // Timeline of CTA 0 of the persistent kernel: per op, work and barrier wait.
+    const size_t n = m->mp.nops;
+    void *buf = nullptr;
+    VKL_OKAY(m->dev->alloc(n * 24, &buf));
+    MegaParams p = m->mp;
+    p.timing = (unsigned long long *)buf;
+    p.timing_mode = (getenv("VKLLAMA_DEBUG_PROLOGUE") ? 1 : 0) | (getenv("VKLLAMA_DEBUG_NOCOPY") ? 2 : 0) | (getenv("VKLLAMA_DEBUG_NOMATH") ? 4 : 0) | (getenv("VKLLAMA_DEBUG_EPILOGUE") ? 8 : 0);
+    std::vector<unsigned long long> tl(3 * n);
+    std::vector<MegaOp> ops(n);
+    cudaError_t e = cudaMemsetAsync(buf, 0, n * 24, m->stream);
+    if (e == cudaSuccess) e = launch_decode_mega(p, m->mega_grid, m->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(tl.data(), buf, n * 24, cudaMemcpyDeviceToHost, m->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(ops.data(), m->mp.ops, n * sizeof(MegaOp), cudaMemcpyDeviceToHost, m->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    m->dev->release(buf, n * 24);
+    count_launches(1);
+    if (e != cudaSuccess) return fail(VKL_INTERNAL, "model_decode_profile: %s", cudaGetErrorString(e));
+    int nmv = 0;
+    for (size_t i = 0; i < n; ++i) {
+      int cls = 0;
+      switch (ops[i].kind) {
+        case MK_EMBED: cls = 0; break;
+        case MK_ATTN_PART:
+        case MK_ATTN_COMBINE: cls = 2; break;
+        case MK_ARGMAX: cls = 7; break;
+        default: {
+          const int j = nmv++;
+          const int per = 4, layers = (int)m->cfg.layers;
+          cls = j >= per * layers ? 6 : (j % per == 0 ? 1 : j % per == 1 ? 3 : j % per == 2 ? 4 : 5);
+        }
+      }
+      out_us[cls] += (float)(tl[2 * i] + tl[2 * i + 1]) * 1e-3f;
+      out_us[8 + cls] += (float)tl[2 * i + 1] * 1e-3f;
+      if (getenv("VKLLAMA_DEBUG_RING")) out_us[8 + cls] = out_us[8 + cls] - (float)tl[2 * i + 1] * 1e-3f + (float)tl[2 * n + i] * 1e-3f;
+    }
+    return check_mega(m);
+  }
   Marker mk;
   mk.s = m->stream;
   int rc = run_tokens(m, 1, false, &mk);
   cudaError_t e = cudaStreamSynchronize(m->stream);
-  for (int i = 0; i < 8; ++i) out_us[i] = 0.f;
   for (size_t i = 1; i < mk.ev.size(); ++i) {
     float ms = 0.f;
     if (rc == VKL_OK && e == cudaSuccess && cudaEventElapsedTime(&ms, mk.ev[i - 1], mk.ev[i]) == cudaSuccess && mk.cls[i] >= 0)
