@@ -152,6 +152,9 @@ def run_reference(args, w, name):
     print(json.dumps(line))
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch from ncu (see profiles/), per workload
+TRAFFIC_NCU = {}
+
 MICRO_SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)]  # rows x K: qkvo, gate/up, down, lm head
 
 
@@ -306,14 +309,21 @@ def main():
     Ls = np.arange(w["prompt"] + 1, w["prompt"] + w["decode"] + 1)
     bytes_tok = float(np.mean([bytes_per_token(w, L, tp) for L in Ls]))
     step_gbs = bytes_tok / (ms_tok * 1e-3) / 1e9
-    prof = np.zeros(8)
+    prof = np.zeros(16)
     reps = 16
     for i in range(reps):
         prof += np.array(model.decode_profile(int(prompt[i % len(prompt)]), w["prompt"] + 100 + i))
     prof /= reps
-    gateup_bytes = 2 * q8_bytes(w["ffn"] // tp, w["dim"]) + w["dim"] * 2 + w["dim"] * 4 + (w["ffn"] // tp) * 2
-    gateup_us = prof[4] / w["layers"]
-    k_gbs = gateup_bytes / (gateup_us * 1e-6) / 1e9
+    persistent = os.environ.get("VKLLAMA_DECODE", "") != "graph" and prof[8:].sum() > 0
+    if persistent:
+        # one kernel launch per token: the dominant kernel is the whole decode step
+        kname = "decode_mega_kernel (persistent decode step: TMA weight ring + mma.sync consumers, all ops of a token)"
+        k_bytes, k_us = bytes_tok, ms_tok * 1e3
+    else:
+        kname = "mv_kernel (RMSNorm + gate/up Q8_0 mat-vec + SwiGLU)"
+        k_bytes = 2 * q8_bytes(w["ffn"] // tp, w["dim"]) + w["dim"] * 2 + w["dim"] * 4 + (w["ffn"] // tp) * 2
+        k_us = prof[4] / w["layers"]
+    k_gbs = k_bytes / (k_us * 1e-6) / 1e9
     line = {
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": job_ms, "higher_is_better": True,
@@ -324,14 +334,17 @@ def main():
                    "parallelism": "tp%d" % world, "l2": "inputs (%.1f GB of weights per token) larger than L2" % (bytes_tok / 1e9),
                    "step": "one job = prefill + %d decode tokens; value counts decode tokens over decode time" % w["decode"]},
         "ms_per_token": ms_tok, "prefill_ms": float(np.mean(pre_ms)),
-        "roofline": {"bound": "hbm", "kernel": "mv_kernel (RMSNorm + gate/up Q8_0 mat-vec + SwiGLU)", "achieved": k_gbs,
-                     "peak": peak, "unit": "GB/s", "frac": k_gbs / peak, "traffic": None, "peak_kind": peak_kind,
-                     "bytes_per_launch": gateup_bytes, "us_per_launch": gateup_us},
+        "roofline": {"bound": "hbm", "kernel": kname, "achieved": k_gbs,
+                     "peak": peak, "unit": "GB/s", "frac": k_gbs / peak, "traffic": TRAFFIC_NCU.get(name) if persistent else None,
+                     "peak_kind": peak_kind, "bytes_per_launch": k_bytes, "us_per_launch": k_us},
         "roofline_step": {"bound": "hbm", "what": "whole decode token: weights + norm weights + embedding row + KV", "achieved": step_gbs,
                           "peak": peak, "unit": "GB/s", "frac": step_gbs / peak, "frac_of_8TBs_nominal": step_gbs / 8000.0,
                           "bytes_per_token": bytes_tok, "peak_kind": peak_kind},
-        "kernel_us_per_token": dict(zip(["embedding", "norm_qkv", "attention", "o_proj_add", "norm_gateup_swiglu", "down_add",
-                                         "norm_lm_head", "argmax"], [float(x) for x in prof])),
+        "op_us_per_token": dict(zip(["embedding", "norm_qkv", "attention", "o_proj_add", "norm_gateup_swiglu", "down_add",
+                                     "norm_lm_head", "argmax"], [float(x) for x in prof[:8]])),
+        "op_barrier_wait_us_per_token": dict(zip(["embedding", "norm_qkv", "attention", "o_proj_add", "norm_gateup_swiglu", "down_add",
+                                                  "norm_lm_head", "argmax"], [float(x) for x in prof[8:]])),
+        "decode_path": "persistent kernel" if persistent else "cuda graph of 5 kernels per layer",
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 4 * (w["prompt"] + w["decode"]),
                 "d2h_bytes_per_step": 4 * (w["vocab"] // tp) * (w["decode"] + 1),
                 "what": "vkl_model_forward per token: host id in, fp32 logits out, host arg-max"},

@@ -52,7 +52,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t a) {
 __device__ __forceinline__ uint32_t mbar_try(uint32_t a, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
       : "=r"(ok)
       : "r"(a), "r"(parity)
       : "memory");
@@ -85,6 +85,7 @@ struct Ctx {
   }
   // Bounded mbarrier wait; false (and the abort flag set) on time-out.
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, uint32_t code) const {
+    if (mbar_try(bar, parity)) return !aborted();  // fast path: the phase is already complete
     if (aborted()) return false;
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
       if (mbar_try(bar, parity)) return true;
@@ -305,11 +306,11 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   const uint32_t tile0 = (cta + G - (op.rot % G)) % G;
   const uint32_t xstep = g == 0 ? 32u : 0u;  // token 0 is column 0 of B: other columns read zeros
   uint32_t tl = 0;                           // local tile counter
+  uint32_t slot = it % NST, ph = (it / NST) & 1u, rotc = it % NCW;  // kept incrementally
   for (uint32_t tile = tile0; tile < tiles; tile += G, ++tl) {
     for (uint32_t m = 0; m < nmat; ++m) {
       float a0 = 0.f, a1 = 0.f;
       for (uint32_t s = 0; s < nstg; ++s, ++it) {
-        const uint32_t slot = it % NST, ph = (it / NST) & 1u;
         unsigned long long w0 = 0, w1 = 0;
         if (tw) w0 = clock64();
         const bool ok = c.wait(s32(&full[slot]), ph, 1);
@@ -321,7 +322,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
         const unsigned char *st = ring + (size_t)slot * STAGE_BYTES;
         // Groups of a stage go to warps round-robin, starting one warp later every stage,
         // so the warp that takes two of the 16 groups rotates.
-        uint32_t gi = (warp + NCW - (it % NCW)) % NCW;
+        uint32_t gi = warp >= rotc ? warp - rotc : warp + NCW - rotc;
         for (;;) {
           const bool have = ok && gi < ng;
           const bool last = !(ok && gi + NCW < ng);
@@ -355,13 +356,21 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
                        codes_raw_h2(cw[j].z, true), X.x, X.y);
               mma16816(cacc, codes_raw_h2(cw[j].y, false), codes_raw_h2(cw[j].w, false), codes_raw_h2(cw[j].y, true),
                        codes_raw_h2(cw[j].w, true), X.z, X.w);
-              a0 = fmaf(cacc[0] - biases[j], dgs[j], a0);
-              a1 = fmaf(cacc[2] - biases[j], dg8s[j], a1);
+              a0 = fmaf(cacc[0], dgs[j], a0);
+              a1 = fmaf(cacc[2], dg8s[j], a1);
             }
+            // remove the +128 code bias of the four blocks: sum_j d_j * 1152 * sum(x_j)
+            a0 -= biases[0] * dgs[0] + biases[1] * dgs[1] + biases[2] * dgs[2] + biases[3] * dgs[3];
+            a1 -= biases[0] * dg8s[0] + biases[1] * dg8s[1] + biases[2] * dg8s[2] + biases[3] * dg8s[3];
           }
           if (last) break;
           gi += NCW;
         }
+        if (++slot == NST) {
+          slot = 0;
+          ph ^= 1u;
+        }
+        if (++rotc == NCW) rotc = 0;
       }
       if (t == 0) {  // lanes t == 0 hold column 0 = token 0: rows g and g+8
         float *slotp = red + ((size_t)(tl * nmat + m) * NCW + warp) * 16;
