@@ -70,9 +70,12 @@ __device__ __forceinline__ uint64_t ld_acq_u64(const unsigned long long *p) {
   return v;
 }
 
-// The mat-vec multiplies the raw fp16 pairs (1024+u) and removes the bias afterwards
-// with the per-block sum of the input:
-//   sum_k (1152 + q_k) x_k = sum_k q_k x_k + 1152 * sum_k x_k.
+// Default: codes are converted to signed fp16 exactly (one subtract per pair). The
+// optional "bias trick" multiplies the raw pairs (1024+u) and removes the bias afterwards
+// with the per-block sum of the input, sum_k (1152 + q_k) x_k = sum_k q_k x_k + 1152 *
+// sum_k x_k: 8 fewer instructions per block, but the large common term costs accumulator
+// precision (about 1e-5 relative per block) and the extra fp16 rounding flips were enough
+// to break greedy-id parity on the 7B model, so it is off unless asked for.
 __device__ __forceinline__ bool getenv_prologue(const MegaParams &p) { return (p.timing_mode & 1u) != 0; }
 
 struct Ctx {
@@ -199,6 +202,7 @@ __device__ __forceinline__ bool better(float v, uint32_t i, const Best &b) {
   return b.i == 0xffffffffu || v > b.v || (v == b.v && i < b.i);
 }
 
+template <bool EXACT>
 __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global, uint32_t &it, unsigned char *ring, uint64_t *full,
                           uint64_t *empty, __half *xs, float *red, float *ssum, float *xsum, const __half *zero16, Best &best,
                           unsigned long long *tw) {
@@ -352,16 +356,24 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
             for (int j = 0; j < 4; ++j) {
               const uint4 X = *reinterpret_cast<const uint4 *>(xp + j * xstep);
               float cacc[4] = {0.f, 0.f, 0.f, 0.f};
-              mma16816(cacc, codes_raw_h2(cw[j].x, false), codes_raw_h2(cw[j].z, false), codes_raw_h2(cw[j].x, true),
-                       codes_raw_h2(cw[j].z, true), X.x, X.y);
-              mma16816(cacc, codes_raw_h2(cw[j].y, false), codes_raw_h2(cw[j].w, false), codes_raw_h2(cw[j].y, true),
-                       codes_raw_h2(cw[j].w, true), X.z, X.w);
+              if (EXACT) {  // signed codes as fp16, exact products, fp32 accumulation
+                mma16816(cacc, codes_to_h2(cw[j].x, false), codes_to_h2(cw[j].z, false), codes_to_h2(cw[j].x, true),
+                         codes_to_h2(cw[j].z, true), X.x, X.y);
+                mma16816(cacc, codes_to_h2(cw[j].y, false), codes_to_h2(cw[j].w, false), codes_to_h2(cw[j].y, true),
+                         codes_to_h2(cw[j].w, true), X.z, X.w);
+              } else {
+                mma16816(cacc, codes_raw_h2(cw[j].x, false), codes_raw_h2(cw[j].z, false), codes_raw_h2(cw[j].x, true),
+                         codes_raw_h2(cw[j].z, true), X.x, X.y);
+                mma16816(cacc, codes_raw_h2(cw[j].y, false), codes_raw_h2(cw[j].w, false), codes_raw_h2(cw[j].y, true),
+                         codes_raw_h2(cw[j].w, true), X.z, X.w);
+              }
               a0 = fmaf(cacc[0], dgs[j], a0);
               a1 = fmaf(cacc[2], dg8s[j], a1);
             }
-            // remove the +128 code bias of the four blocks: sum_j d_j * 1152 * sum(x_j)
-            a0 -= biases[0] * dgs[0] + biases[1] * dgs[1] + biases[2] * dgs[2] + biases[3] * dgs[3];
-            a1 -= biases[0] * dg8s[0] + biases[1] * dg8s[1] + biases[2] * dg8s[2] + biases[3] * dg8s[3];
+            if (!EXACT) {  // remove the +128 code bias of the four blocks: sum_j d_j * 1152 * sum(x_j)
+              a0 -= biases[0] * dgs[0] + biases[1] * dgs[1] + biases[2] * dgs[2] + biases[3] * dgs[3];
+              a1 -= biases[0] * dg8s[0] + biases[1] * dg8s[1] + biases[2] * dg8s[2] + biases[3] * dg8s[3];
+            }
           }
           if (last) break;
           gi += NCW;
@@ -635,7 +647,7 @@ __device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_
   }
 }
 
-template <bool TIMED>
+template <bool TIMED, bool EXACT>
 __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char *ring = smem;
@@ -684,7 +696,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
     if (timed) c0 = clock64();
     switch (op.kind) {
       case MK_EMBED: embed_op(c, tok); break;
-      case MK_MATVEC: matvec_op(c, op, it, ring, full, empty, xs, red, ssum, xsum, zero16, best, (TIMED && timed) ? twait : nullptr); break;
+      case MK_MATVEC: matvec_op<EXACT>(c, op, it, ring, full, empty, xs, red, ssum, xsum, zero16, best, (TIMED && timed) ? twait : nullptr); break;
       case MK_ATTN_PART: attn_part_op(c, op, reinterpret_cast<float *>(xs), pos0, S_eff); break;
       case MK_ATTN_COMBINE: attn_combine_op(c, pos0); break;
       case MK_ARGMAX:
@@ -762,7 +774,8 @@ int decode_mega_stage_groups() { return SG; }
 
 cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s) {
   const size_t smem = decode_mega_smem(p.xs_bytes);
-  auto kern = p.timing ? decode_mega_kernel<true> : decode_mega_kernel<false>;
+  auto kern = p.timing ? (p.bias_trick ? decode_mega_kernel<true, false> : decode_mega_kernel<true, true>)
+                       : (p.bias_trick ? decode_mega_kernel<false, false> : decode_mega_kernel<false, true>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   void *args[] = {(void *)&p};
@@ -771,9 +784,9 @@ cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s) {
 
 cudaError_t decode_mega_occupancy(size_t xs_bytes, int *blocks_per_sm) {
   const size_t smem = decode_mega_smem(xs_bytes);
-  cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, decode_mega_kernel<false>, THREADS, smem);
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, decode_mega_kernel<false, true>, THREADS, smem);
 }
 
 }  // namespace vkl

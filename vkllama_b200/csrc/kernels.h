@@ -150,6 +150,7 @@ struct MegaParams {
   uint32_t single_split_len;  // KV lengths up to this use one CTA per head (no combine phase)
   // Optional timeline of CTA 0: per op, nanoseconds of work and of barrier wait.
   unsigned long long *timing;
+  uint32_t bias_trick;   // 1: raw code pairs + bias removal (faster, less exact); 0: exact codes
   uint32_t timing_mode;  // third column of the timeline: 0 = ring wait, 1 = op prologue
 };
 size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits);

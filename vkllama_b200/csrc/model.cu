@@ -402,6 +402,7 @@ int build_mega(vkl_model *m) {
   p.dim = c.dim; p.heads = m->heads_l; p.head_dim = m->head_dim; p.maxlen = c.maxlen; p.splits = splits; p.vocab = m->vocab_l;
   p.xs_bytes = (uint32_t)xs_bytes;
   {
+    p.bias_trick = getenv("VKLLAMA_DECODE_BIAS_TRICK") ? 1u : 0u;
     const char *la = getenv("VKLLAMA_L2_LOOKAHEAD");
     p.l2_lookahead = la ? (uint32_t)atoi(la) : 0u;
     const uint32_t chunk_cap = ((c.maxlen + splits - 1) / splits + 31) & ~31u;
