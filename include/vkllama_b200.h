@@ -84,6 +84,10 @@ int vkl_command_submit_and_wait(vkl_command *cmd);
 int vkl_command_elapsed_us(vkl_command *cmd, float *usec);
 /* upload_bytes / download (command.h:141-260): host memory is copied through
  * pinned staging; a download lands in `host` when vkl_command_wait returns. */
+/* The CUDA stream (cudaStream_t) the command enqueues on: the counterpart of the
+ * queue a Command submits to (command.h:42-44), for callers that mix their own CUDA
+ * work or the no-allocation entry point below with this library's ops. */
+int vkl_command_stream(vkl_command *cmd, void **cuda_stream);
 int vkl_command_upload(vkl_command *cmd, const void *host, size_t bytes, vkl_tensor *to);
 int vkl_command_download(vkl_command *cmd, vkl_tensor *from, void *host, size_t bytes);
 
@@ -161,6 +165,21 @@ int vkl_slice_run(vkl_op *op, vkl_tensor *in, const uint32_t starts[3],
 /* Cast, src/ops/cast.h:15-20 (FP16 -> FP32 and FP32 -> FP16). */
 int vkl_cast_create(vkl_device *dev, vkl_command *cmd, int from, int to, vkl_op **out);
 int vkl_cast_run(vkl_op *op, vkl_tensor *in, vkl_tensor **out);
+
+/* Row arg-max that allocates nothing. No counterpart in the reference.
+ * For callers that cannot allocate device memory where they need the greedy pick
+ * (a serving loop that gave its memory budget out at start-up, code inside a stream
+ * capture, a host runtime that forbids cudaMalloc after initialisation). x_fp16 is a
+ * device pointer to rows*width fp16 values, out_idx a device pointer to `rows`
+ * uint32; lowest index wins ties, as ArgMax. The scratch of the two-stage reduction
+ * is a fixed 64 KiB array inside the library, resident on every GPU that loads it:
+ * rows * ceil(width/1024) may not exceed 8192, larger inputs are refused with
+ * VKL_OUT_OF_RANGE. The first call on a device looks the array's device address up
+ * (with that device current); make that first call before any stream capture.
+ * All calls share the array: calls that overlap on the GPU race and must be
+ * serialised by the caller. Enqueues on cuda_stream (cudaStream_t, may be NULL) and
+ * does not synchronise. */
+int vkl_argmax_noalloc(const void *x_fp16, uint32_t rows, uint32_t width, uint32_t *out_idx, void *cuda_stream);
 
 /* ---- host Q8_0 quantizer: src/core/quants.h:37-176 ------------------------
  * blocks34: GGUF/device layout [fp16 scale][32 x int8]; blocks36: the

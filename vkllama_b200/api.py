@@ -55,7 +55,8 @@ def load_library():
         "vkl_tensor_device_ptr": [vp, pvp],
         "vkl_command_create": [vp, pvp], "vkl_command_destroy": [vp], "vkl_command_begin": [vp],
         "vkl_command_end": [vp], "vkl_command_submit": [vp], "vkl_command_wait": [vp],
-        "vkl_command_submit_and_wait": [vp], "vkl_command_elapsed_us": [vp, C.POINTER(f32)], "vkl_command_upload": [vp, vp, sz, vp],
+        "vkl_command_submit_and_wait": [vp], "vkl_command_elapsed_us": [vp, C.POINTER(f32)],
+        "vkl_command_stream": [vp, pvp], "vkl_argmax_noalloc": [vp, u32, u32, vp, vp], "vkl_command_upload": [vp, vp, sz, vp],
         "vkl_command_download": [vp, vp, vp, sz],
         "vkl_op_init": [vp], "vkl_op_time": [vp, C.POINTER(u64)], "vkl_op_destroy": [vp],
         "vkl_matmul_create": [vp, vp, vp, f32, f32, i32, i32, i32, i32, i32, pvp],
@@ -263,6 +264,12 @@ class Command:
         t = f32()
         _ck(self.L.vkl_command_elapsed_us(self.h, C.byref(t)))
         return t.value
+
+    def stream(self):
+        """The command's cudaStream_t as an integer."""
+        s = vp()
+        _ck(self.L.vkl_command_stream(self.h, C.byref(s)))
+        return s.value
 
     def upload(self, arr, tensor):
         a = np.ascontiguousarray(arr)

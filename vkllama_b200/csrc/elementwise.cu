@@ -2,8 +2,11 @@
 // quantizer, synthetic data, RMSNorm, residual add, embedding gather, arg-max,
 // softmax, RoPE, KV-cache append, transpose, slice, casts and the generic
 // batched fp16 mat-mul of the operator API.
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
+#include "runtime.h"
 
 namespace vkl {
 namespace {
@@ -516,3 +519,59 @@ cudaError_t launch_bmm_f16(const __half *a, const __half *b, __half *c, uint32_t
 }
 
 }  // namespace vkl
+
+// ---------------------------------------------------------------------------
+// Arg-max without any allocation.
+//
+// vkl_argmax_noalloc is for callers that may not allocate device memory at the
+// point where they need the greedy pick: a serving loop that handed its whole
+// memory budget out at start-up, code running while a stream is being captured, or
+// a host runtime that forbids cudaMalloc after initialisation (it synchronises the
+// device and can fail late). The two-stage arg-max needs a scratch buffer for the
+// per-chunk winners; here that buffer is a fixed array in the library's device
+// image instead of an allocation.
+//
+// The array below is resident on every GPU that loads this library, from load until
+// the process exits. It is shared by all calls and keeps whatever the previous call
+// left in it; the arg-max overwrites every entry it later reads, so nothing has to be
+// cleared between calls. Two calls that overlap on the GPU (different streams, or
+// different host threads without ordering) race on it and must be serialised by the
+// caller.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr size_t kNoAllocScratchBytes = 64 * 1024;  // 8192 (index, value) pairs
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+std::mutex g_noalloc_mu;
+void *g_noalloc_ptr[64] = {};  // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int vkl_argmax_noalloc(const void *x_fp16, uint32_t rows, uint32_t width, uint32_t *out_idx, void *cuda_stream) {
+  using namespace vkl;
+  if (!x_fp16 || !out_idx) return fail(VKL_INVALID_ARGUMENT, "argmax_noalloc: null input or output pointer");
+  if (rows == 0 || width == 0) return fail(VKL_INVALID_ARGUMENT, "argmax_noalloc: empty input (%u rows of %u)", rows, width);
+  const size_t need = argop_partials_bytes(rows, width);
+  if (need > kNoAllocScratchBytes)
+    return fail(VKL_OUT_OF_RANGE,
+                "argmax_noalloc: %u rows of %u values need %zu bytes of scratch, the built-in buffer holds %zu "
+                "(rows * ceil(width/1024) must not exceed %zu); use the ArgMax op for larger inputs",
+                rows, width, need, kNoAllocScratchBytes, kNoAllocScratchBytes / 8);
+  int dev = 0;
+  VKL_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(VKL_UNIMPLEMENTED, "argmax_noalloc: device ordinal %d is beyond the 64 this entry point tracks", dev);
+  void *scratch = nullptr;
+  {
+    // Set-up, once per device, with that device current: the array's name is only a
+    // host-side handle, the kernel needs the address the symbol has on this device.
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      void *p = nullptr;
+      VKL_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+      if (!p) return fail(VKL_INTERNAL, "argmax_noalloc: the scratch symbol has no address on device %d", dev);
+      g_noalloc_ptr[dev] = p;
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  VKL_LAUNCH(2, launch_argop(static_cast<const __half *>(x_fp16), out_idx, scratch, rows, width, 0, static_cast<cudaStream_t>(cuda_stream)));
+  return VKL_OK;
+}
+

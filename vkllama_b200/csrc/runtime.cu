@@ -323,6 +323,11 @@ int vkl_command_elapsed_us(vkl_command *cmd, float *usec) {
   *usec = ms * 1000.f;
   return VKL_OK;
 }
+int vkl_command_stream(vkl_command *cmd, void **cuda_stream) {
+  if (!cmd || !cuda_stream) return fail(VKL_INVALID_ARGUMENT, "command_stream: null argument");
+  *cuda_stream = cmd->stream;
+  return VKL_OK;
+}
 int vkl_command_submit_and_wait(vkl_command *cmd) {
   VKL_OKAY(vkl_command_submit(cmd));
   return vkl_command_wait(cmd);
