@@ -244,10 +244,19 @@ int vkl_model_block_forward(vkl_model *m, uint32_t layer, const void *x_fp16, si
  * persistent kernel, timeline of its first CTA; 0 on the multi-kernel path, which is
  * timed with an event after every launch). Appends to the KV cache at `offset`. */
 int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[16]);
-/* Tensor-parallel set-up: peer device pointers of every rank's exchange buffer
- * (obtained by the caller through CUDA IPC), indexed by rank. */
+/* Tensor-parallel set-up (no counterpart in the reference, which is single-device:
+ * gpu_device.cpp:14-21). One process per GPU creates its shard (tp_rank of tp_size);
+ * each exports its exchange buffer over CUDA IPC, the processes swap the 64-byte handles
+ * by any means (the Python layer uses torch.distributed), open the peers' handles and
+ * pass the mapped pointers, indexed by rank (own entry ignored), to vkl_model_tp_connect.
+ * The decode kernel then pushes row-split partial sums into every rank's buffer with
+ * plain peer stores and reduces them in rank order (one all-reduce after o_proj and one
+ * after down_proj per layer), and exchanges arg-max candidates of the vocabulary-split
+ * output layer. vkl_model_forward returns this rank's slice of the logits. */
 int vkl_model_tp_buffer(vkl_model *m, void **local_ptr, size_t *bytes);
 int vkl_model_tp_connect(vkl_model *m, void *const *peer_ptrs, int n);
+int vkl_ipc_export(void *device_ptr, unsigned char handle[64]);
+int vkl_ipc_open(vkl_device *dev, const unsigned char handle[64], void **device_ptr);
 
 #ifdef __cplusplus
 }

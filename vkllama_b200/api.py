@@ -88,6 +88,7 @@ def load_library():
         "vkl_model_block_forward": [vp, u32, vp, sz, sz, vp],
         "vkl_model_decode_profile": [vp, u32, sz, C.POINTER(f32)],
         "vkl_model_tp_buffer": [vp, pvp, C.POINTER(sz)], "vkl_model_tp_connect": [vp, pvp, i32],
+        "vkl_ipc_export": [vp, C.c_char_p], "vkl_ipc_open": [vp, C.c_char_p, pvp],
     }
     for name, args in sigs.items():
         f = getattr(L, name)
@@ -583,6 +584,25 @@ class Model:
         out = (f32 * 16)()
         _ck(self.L.vkl_model_decode_profile(self.h, token, offset, out))
         return list(out)
+
+    def tp_export(self):
+        """CUDA IPC handle (64 bytes) of this rank's exchange buffer."""
+        p, n = vp(), sz()
+        _ck(self.L.vkl_model_tp_buffer(self.h, C.byref(p), C.byref(n)))
+        h = C.create_string_buffer(64)
+        _ck(self.L.vkl_ipc_export(p, h))
+        return h.raw
+
+    def tp_connect(self, handles):
+        """handles[r] = IPC handle of rank r's exchange buffer (own entry ignored)."""
+        ptrs = (vp * len(handles))()
+        for r, hb in enumerate(handles):
+            if r == self.cfg.tp_rank:
+                continue
+            q = vp()
+            _ck(self.L.vkl_ipc_open(self.dev.h, C.create_string_buffer(hb, 64), C.byref(q)))
+            ptrs[r] = q
+        _ck(self.L.vkl_model_tp_connect(self.h, ptrs, len(handles)))
 
     def close(self):
         if self.h:

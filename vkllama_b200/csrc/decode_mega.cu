@@ -64,6 +64,15 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
                : "memory");
 }
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory"); }
+__device__ __forceinline__ uint32_t ld_acq_sys_u32(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_rel_sys_u32(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ uint64_t ld_acq_u64(const unsigned long long *p) {
   uint64_t v;
   asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -205,7 +214,7 @@ __device__ __forceinline__ bool better(float v, uint32_t i, const Best &b) {
 template <bool EXACT>
 __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global, uint32_t &it, unsigned char *ring, uint64_t *full,
                           uint64_t *empty, __half *xs, float *red, float *ssum, float *xsum, const __half *zero16, Best &best,
-                          unsigned long long *tw) {
+                          unsigned long long *tw, uint32_t ar_parity) {
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t G = gridDim.x, cta = blockIdx.x;
   // Scalars in registers: the barriers' memory clobbers would otherwise make every use
@@ -411,6 +420,13 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
         op.out[0][n] = __float2half_rn(gate / (1.0f + expf(-gate)) * up);
       } else if (op.epi == EPI_ADD) {
         op.out[0][n] = __float2half_rn(round_h(v[0]) + ldcg_h(op.out[0] + n));
+      } else if (op.epi == EPI_PARTIAL) {
+        // this rank's share of a row-split projection: the raw fp32 sum goes into slot
+        // [parity][my rank] of every rank's exchange buffer (plain peer stores over NVLink)
+        const MegaParams &pp = c.p;
+        for (uint32_t r = 0; r < pp.tp_size; ++r)
+          static_cast<float *>(pp.tp_peer[r])[((size_t)ar_parity * pp.tp_size + pp.tp_rank) * pp.dim + n] = v[0];
+        __threadfence_system();
       } else {
         const __half h0 = __float2half_rn(v[0]);
         op.out[0][n] = h0;
@@ -601,7 +617,7 @@ __device__ __forceinline__ void embed_op(const Ctx &c, uint32_t tok) {
 
 // CTA 0: best of the per-CTA candidates (lowest index on ties), then publish the id,
 // feed it back and advance position, step and launch epoch.
-__device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_t pos0, uint64_t rounds_done) {
+__device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_t pos0, uint64_t rounds_done, uint32_t ar_done) {
   const MegaParams &p = c.p;
   if (blockIdx.x != 0) return;
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -635,15 +651,94 @@ __device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_
         b.v = sm[32 + w];
         b.i = si[w];
       }
+    if (p.tp_size > 1 && !c.aborted()) {
+      // vocabulary-split lm head: exchange (value, global index) candidates with all ranks
+      const uint32_t tp = p.tp_size, aseq = p.state[4] + 1;
+      b.i += p.tp_rank * p.vocab;
+      for (uint32_t r = 0; r < tp; ++r) {
+        float *cand = static_cast<float *>(p.tp_peer[r]) + p.tp_flag_off + 32 + 2 * p.tp_rank;
+        cand[0] = b.v;
+        cand[1] = __uint_as_float(b.i);
+      }
+      __threadfence_system();
+      for (uint32_t r = 0; r < tp; ++r) st_rel_sys_u32(static_cast<uint32_t *>(p.tp_peer[r]) + p.tp_flag_off + 16 + p.tp_rank, aseq);
+      const uint32_t *mine = static_cast<const uint32_t *>(p.tp_peer[p.tp_rank]) + p.tp_flag_off;
+      for (uint32_t r = 0; r < tp && !c.aborted(); ++r) {
+        bool ok = false;
+        for (uint32_t i = 0; i < WAIT_LIMIT * 8u; ++i) {
+          if ((int32_t)(ld_acq_sys_u32(mine + 16 + r) - aseq) >= 0) {
+            ok = true;
+            break;
+          }
+          if (i > 100000u) __nanosleep(64);
+        }
+        if (!ok) c.raise(5);
+      }
+      Best gb = {0.f, 0xffffffffu};
+      for (uint32_t r = 0; r < tp; ++r) {
+        const float *cand = static_cast<const float *>(p.tp_peer[p.tp_rank]) + p.tp_flag_off + 32 + 2 * r;
+        const float v = __ldcg(cand);
+        const uint32_t ix = __float_as_uint(__ldcg(cand + 1));
+        if (better(v, ix, gb)) {
+          gb.v = v;
+          gb.i = ix;
+        }
+      }
+      b = gb;
+      p.state[4] = aseq;
+    }
     if (!c.aborted()) {
-      const uint32_t step = p.state[1];
+      const uint32_t step = p.state[1], n_forced = p.state[5];
       p.state[2] = b.i;
-      p.tok[0] = b.i;
-      if (step < p.out_cap) p.out_ids[step] = b.i;
-      p.state[1] = step + 1;
+      if (pos0 + 1 < n_forced) {
+        p.tok[0] = p.forced[pos0 + 1];  // still inside the prompt: feed the next prompt token
+      } else {
+        p.tok[0] = b.i;
+        if (step < p.out_cap) p.out_ids[step] = b.i;
+        p.state[1] = step + 1;
+      }
       p.state[0] = pos0 + 1;
+      p.state[3] = ar_done;
       p.bar[1] = rounds_done;
     }
+  }
+}
+
+// Tensor-parallel all-reduce, second half. The partial sums were pushed to every rank
+// by the preceding row-split projection and made visible by the grid barrier after it.
+// CTA 0 tells every rank "my partials for sequence `seq` are out"; every CTA waits
+// (bounded) until all ranks have said so, then reduces its slice of rows in rank order:
+// x <- fp16( fp16(sum_r partial_r) + x ), the same rounding as o_proj/down + residual add.
+__device__ __forceinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t seq) {
+  const MegaParams &p = c.p;
+  const uint32_t tid = threadIdx.x, tp = p.tp_size;
+  uint32_t *my_flags = static_cast<uint32_t *>(p.tp_peer[p.tp_rank]) + p.tp_flag_off;
+  if (tid == 0 && !c.aborted()) {
+    if (blockIdx.x == 0)
+      for (uint32_t r = 0; r < tp; ++r) st_rel_sys_u32(static_cast<uint32_t *>(p.tp_peer[r]) + p.tp_flag_off + p.tp_rank, seq);
+    for (uint32_t r = 0; r < tp && !c.aborted(); ++r) {
+      bool ok = false;
+      for (uint32_t i = 0; i < WAIT_LIMIT * 8u; ++i) {
+        if ((int32_t)(ld_acq_sys_u32(my_flags + r) - seq) >= 0) {
+          ok = true;
+          break;
+        }
+        if (i > 100000u) __nanosleep(64);
+        if ((i & 1023u) == 1023u && *(volatile uint32_t *)p.error != 0u) break;
+      }
+      if (!ok) c.raise(4);
+    }
+    __threadfence_system();
+  }
+  cons_sync();
+  if (c.aborted()) return;
+  const uint32_t per = (p.dim + gridDim.x - 1) / gridDim.x;
+  const uint32_t i = blockIdx.x * per + tid;
+  if (tid < per && i < p.dim) {
+    const float *part = static_cast<const float *>(p.tp_peer[p.tp_rank]) + (size_t)(seq & 1u) * tp * p.dim;
+    float s = 0.f;
+    for (uint32_t r = 0; r < tp; ++r) s += __ldcg(part + (size_t)r * p.dim + i);
+    op.out[0][i] = __float2half_rn(round_h(s) + ldcg_h(op.out[0] + i));
   }
 }
 
@@ -683,6 +778,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
   const uint32_t pos0 = p.state[0], tok = p.tok[0];
   const uint64_t base_rounds = p.bar[1];  // barrier rounds completed by earlier launches
   uint64_t rounds = 0;
+  const uint32_t seq0 = p.state[3];  // all-reduces completed by earlier launches
+  uint32_t ar_i = 0;
   const uint32_t Lnow = min(pos0 + 1, p.maxlen);
   const uint32_t S_eff = Lnow <= p.single_split_len ? 1u : p.splits;
   uint32_t it = 0;
@@ -696,11 +793,15 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
     if (timed) c0 = clock64();
     switch (op.kind) {
       case MK_EMBED: embed_op(c, tok); break;
-      case MK_MATVEC: matvec_op<EXACT>(c, op, it, ring, full, empty, xs, red, ssum, xsum, zero16, best, (TIMED && timed) ? twait : nullptr); break;
+      case MK_MATVEC: matvec_op<EXACT>(c, op, it, ring, full, empty, xs, red, ssum, xsum, zero16, best, (TIMED && timed) ? twait : nullptr, (seq0 + ar_i + 1) & 1u); break;
       case MK_ATTN_PART: attn_part_op(c, op, reinterpret_cast<float *>(xs), pos0, S_eff); break;
       case MK_ATTN_COMBINE: attn_combine_op(c, pos0); break;
+      case MK_ALLREDUCE:
+        ++ar_i;
+        allreduce_op(c, op, seq0 + ar_i);
+        break;
       case MK_ARGMAX:
-        argmax_final_op(c, reinterpret_cast<float *>(xs), pos0, base_rounds + rounds);
+        argmax_final_op(c, reinterpret_cast<float *>(xs), pos0, base_rounds + rounds, seq0 + ar_i);
         break;
     }
     if (op.kind == MK_MATVEC && op.track_argmax) {

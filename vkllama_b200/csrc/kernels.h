@@ -8,7 +8,9 @@
 
 namespace vkl {
 
-enum MvEpilogue { EPI_PLAIN = 0, EPI_ADD = 1, EPI_SWIGLU = 2 };
+// EPI_PARTIAL (persistent decode kernel only): raw fp32 partial sums of a row-split
+// projection, pushed into every tensor-parallel rank's exchange buffer.
+enum MvEpilogue { EPI_PLAIN = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
 
 // Y = epilogue(X . W^T) for up to three Q8_0 (tiled planes) or FP16 (row-major)
 // weight matrices [N,K] sharing one input X [M,K].
@@ -106,7 +108,7 @@ cudaError_t launch_attention(const AttnParams &p, cudaStream_t s);
 size_t attention_scratch_bytes(uint32_t T, uint32_t heads, uint32_t dim, uint32_t splits);
 
 // ---- persistent decode step (decode_mega.cu) --------------------------------
-enum MegaKind { MK_EMBED = 0, MK_MATVEC = 1, MK_ATTN_PART = 2, MK_ATTN_COMBINE = 3, MK_ARGMAX = 4 };
+enum MegaKind { MK_EMBED = 0, MK_MATVEC = 1, MK_ATTN_PART = 2, MK_ATTN_COMBINE = 3, MK_ARGMAX = 4, MK_ALLREDUCE = 5 };
 struct MegaOp {
   uint32_t kind, epi, nmat, rot;
   uint32_t N, K, tiles, groups;
@@ -132,7 +134,9 @@ struct MegaParams {
   const uint32_t *stage_count;   // [grid]
   uint32_t stage_stride;
   uint32_t nops, nbarriers;
-  uint32_t *state;    // [0] position, [1] step, [2] picked id
+  uint32_t *state;    // [0] position, [1] step, [2] picked id, [3] all-reduces done, [4] arg-max exchanges done,
+                      // [5] number of forced (prompt) tokens
+  const uint32_t *forced;  // prompt ids: while position+1 < state[5] the next input is forced[position+1]
   uint32_t *tok;      // current token id
   uint32_t *out_ids;
   uint32_t out_cap;
@@ -146,6 +150,12 @@ struct MegaParams {
   uint32_t *error;          // 0, or the code of the wait that timed out
   uint32_t dim, heads, head_dim, maxlen, splits, vocab;
   uint32_t xs_bytes;
+  // Tensor parallelism: every rank's exchange buffer (peer pointers, own included).
+  // Layout of one buffer, in 4-byte words: partial sums [2 parities][tp][dim] fp32, then
+  // at word tp_flag_off: flags[16] (all-reduce sequence per source rank), arg flags[16],
+  // arg candidates [16][2].
+  uint32_t tp_rank, tp_size, tp_flag_off;
+  void *tp_peer[8];
   uint32_t l2_lookahead;      // weight stages kept in flight towards L2 ahead of the ring
   uint32_t single_split_len;  // KV lengths up to this use one CTA per head (no combine phase)
   // Optional timeline of CTA 0: per op, nanoseconds of work and of barrier wait.

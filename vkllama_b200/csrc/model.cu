@@ -59,7 +59,15 @@ struct vkl_model {
   vkl_tensor *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ao = nullptr, *t = nullptr;
   vkl_tensor *logits16 = nullptr, *logits32 = nullptr;
   vkl_tensor *toks = nullptr;  // [cap_T] device token ids; toks[0] is the decode token
-  vkl_tensor *state = nullptr; // uint32: [0] pos, [1] step, [2] next id
+  vkl_tensor *state = nullptr; // uint32[8]: [0] pos, [1] step, [2] next id, [3] all-reduces, [4] arg exchanges, [5] forced tokens
+  vkl_tensor *forced = nullptr;  // prompt ids for token-by-token prefill
+  // tensor parallelism: this rank's exchange buffer (plain cudaMalloc so that it can be
+  // exported over CUDA IPC) and every rank's mapping of it
+  void *tp_buf = nullptr;
+  size_t tp_bytes = 0;
+  uint32_t tp_flag_off = 0;
+  void *tp_peer[8] = {};
+  bool tp_connected = false;
   vkl_tensor *out_ids = nullptr;
   vkl_tensor *argpart = nullptr, *attn_scratch = nullptr, *attn_counters = nullptr;
   uint32_t splits = 8, out_cap = 0;
@@ -77,9 +85,10 @@ struct vkl_model {
   uint32_t *next_dev() { return (uint32_t *)state->data() + 2; }
   ~vkl_model() {
     if (decode_graph) cudaGraphExecDestroy(decode_graph);
+    if (tp_buf) cudaFree(tp_buf);
     for (auto &l : L)
       for (vkl_tensor *p : {l.attn_norm, l.ffn_norm, l.wq, l.wk, l.wv, l.wo, l.gate, l.up, l.down, l.kcache, l.vcache}) vkl_tensor_release(p);
-    for (vkl_tensor *p : {tok_embd, output_norm, output, fc, fs, x, xn, q, k, v, ao, t, logits16, logits32, toks, state, out_ids, argpart, attn_scratch, attn_counters, mega_ops, mega_sync, mega_arg, mega_attn, mega_stages, mega_counts})
+    for (vkl_tensor *p : {tok_embd, output_norm, output, fc, fs, x, xn, q, k, v, ao, t, logits16, logits32, toks, state, out_ids, forced, argpart, attn_scratch, attn_counters, mega_ops, mega_sync, mega_arg, mega_attn, mega_stages, mega_counts})
       vkl_tensor_release(p);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
@@ -261,7 +270,9 @@ int build_mega(vkl_model *m) {
   m->mega_tried = true;
   const char *env = getenv("VKLLAMA_DECODE");
   if (env && !strcmp(env, "graph")) return VKL_OK;
-  if (!q8(m) || m->cfg.tp_size != 1 || m->tok_embd->dtype != VKL_Q8_0) return VKL_OK;
+  if (!q8(m) || m->tok_embd->dtype != VKL_Q8_0) return VKL_OK;
+  const uint32_t tp = m->cfg.tp_size;
+  if (tp > 1 && !m->tp_connected) return fail(VKL_FAILED_PRECONDITION, "model: tensor-parallel ranks are not connected (vkl_model_tp_connect)");
   const vkl_model_config &c = m->cfg;
   if ((int)c.dim > decode_mega_max_k() || (int)c.ffn > decode_mega_max_k() || (c.dim % 32) || (c.ffn % 32) || (m->head_dim & 1)) return VKL_OK;
   int coop = 0;
@@ -271,7 +282,7 @@ int build_mega(vkl_model *m) {
   uint32_t splits = (uint32_t)G / m->heads_l;
   if (splits < 1) return VKL_OK;  // more heads than SMs: keep the graph path
   if (splits > 8) splits = 8;
-  const uint32_t max_groups = (std::max(c.dim, c.ffn) / 32 + 3) / 4;
+  const uint32_t max_groups = (std::max(c.dim, m->ffn_l) / 32 + 3) / 4;
   const size_t xs_bytes = decode_mega_xs_bytes(max_groups, m->head_dim, c.maxlen, splits);
   if (decode_mega_smem(xs_bytes) > (size_t)m->dev->prop.sharedMemPerBlockOptin) return VKL_OK;
   int occ = 0;
@@ -327,9 +338,18 @@ int build_mega(vkl_model *m) {
     MegaOp cb = {};
     cb.kind = MK_ATTN_COMBINE;
     ops.push_back(cb);
-    matvec({y.wo}, nullptr, 0.f, ao, {x}, EPI_ADD);
+    auto allreduce = [&]() {
+      MegaOp r = {};
+      r.kind = MK_ALLREDUCE;
+      r.N = c.dim;
+      r.out[0] = x;
+      ops.push_back(r);
+    };
+    matvec({y.wo}, nullptr, 0.f, ao, {x}, tp > 1 ? EPI_PARTIAL : EPI_ADD);
+    if (tp > 1) allreduce();
     matvec({y.gate, y.up}, (const float *)y.ffn_norm->data(), c.eps, x, {tb}, EPI_SWIGLU);
-    matvec({y.down}, nullptr, 0.f, tb, {x}, EPI_ADD);
+    matvec({y.down}, nullptr, 0.f, tb, {x}, tp > 1 ? EPI_PARTIAL : EPI_ADD);
+    if (tp > 1) allreduce();
   }
   matvec({m->output}, (const float *)m->output_norm->data(), c.final_eps, x, {(__half *)m->logits16->data()}, EPI_PLAIN);
   ops.back().out_f32 = (float *)m->logits32->data();
@@ -387,6 +407,11 @@ int build_mega(vkl_model *m) {
   p.nops = (uint32_t)ops.size();
   p.nbarriers = p.nops - 1;
   p.state = (uint32_t *)m->state->data();
+  p.forced = (const uint32_t *)m->forced->data();
+  p.tp_rank = (uint32_t)c.tp_rank;
+  p.tp_size = tp;
+  p.tp_flag_off = m->tp_flag_off;
+  for (int i = 0; i < 8; ++i) p.tp_peer[i] = m->tp_peer[i];
   p.tok = (uint32_t *)m->toks->data();
   p.out_ids = (uint32_t *)m->out_ids->data();
   p.out_cap = m->out_cap;
@@ -539,7 +564,8 @@ int vkl_model_create(vkl_device *dev, const vkl_model_config *cfg, vkl_model **o
   if (c.heads % tp || (c.ffn / tp) % 32 || c.ffn % tp || (c.dim / tp) % 32 || c.vocab % tp)
     return fail(VKL_INVALID_ARGUMENT, "model_create: tp_size %u does not divide heads/ffn/dim/vocab on 32-column boundaries", tp);
   if (c.weight_dtype == VKL_FP16 && ((c.dim & 7) || (c.ffn & 7))) return fail(VKL_UNIMPLEMENTED, "model_create: FP16 weights need widths that are multiples of 8");
-  if (tp > 1) return fail(VKL_UNIMPLEMENTED, "model_create: tensor parallel execution is not built yet");
+  if (tp > 8) return fail(VKL_UNIMPLEMENTED, "model_create: at most 8 tensor-parallel ranks");
+  if (tp > 1 && c.weight_dtype != VKL_Q8_0) return fail(VKL_UNIMPLEMENTED, "model_create: tensor parallelism is built for Q8_0 weights");
   VKL_CUDA(cudaSetDevice(dev->ordinal));
   vkl_model *m = new vkl_model();
   m->dev = dev;
@@ -572,11 +598,18 @@ int vkl_model_create(vkl_device *dev, const vkl_model_config *cfg, vkl_model **o
   m->out_cap = 2 * c.maxlen + 16;
   int st = VKL_OK;
   if ((st = tensor_new(dev, 1, 1, m->vocab_l, VKL_FP16, &m->logits16)) || (st = tensor_new(dev, 1, 1, m->vocab_l, VKL_FP32, &m->logits32)) ||
-      (st = tensor_new(dev, 1, 1, 4, VKL_UINT32, &m->state)) || (st = tensor_new(dev, 1, 1, m->out_cap, VKL_UINT32, &m->out_ids)) ||
+      (st = tensor_new(dev, 1, 1, 8, VKL_UINT32, &m->state)) || (st = tensor_new(dev, 1, 1, c.maxlen, VKL_UINT32, &m->forced)) || (st = tensor_new(dev, 1, 1, m->out_cap, VKL_UINT32, &m->out_ids)) ||
       (st = tensor_new(dev, 1, 1, argop_partials_bytes(1, m->vocab_l) / 4 + 2, VKL_FP32, &m->argpart)) ||
       (st = tensor_new(dev, 1, 1, m->heads_l, VKL_UINT32, &m->attn_counters)))
     return bail(st);
-  cudaMemsetAsync(m->state->data(), 0, 16, m->stream);
+  cudaMemsetAsync(m->state->data(), 0, 32, m->stream);
+  if (tp > 1) {
+    m->tp_flag_off = 2 * tp * c.dim;
+    m->tp_bytes = ((size_t)m->tp_flag_off + 64) * 4;
+    if (cudaMalloc(&m->tp_buf, m->tp_bytes) != cudaSuccess) return bail(fail(VKL_RESOURCE_EXHAUSTED, "model_create: exchange buffer allocation failed"));
+    cudaMemsetAsync(m->tp_buf, 0, m->tp_bytes, m->stream);
+    m->tp_peer[c.tp_rank] = m->tp_buf;
+  }
   cudaMemsetAsync(m->attn_counters->data(), 0, m->attn_counters->device_bytes(), m->stream);
   if ((st = ensure_rows(m, 1))) return bail(st);
   e = cudaStreamSynchronize(m->stream);
@@ -684,9 +717,11 @@ int vkl_model_forward(vkl_model *m, const uint32_t *toks, size_t n, size_t offse
   if (n == 0) return fail(VKL_INVALID_ARGUMENT, "model_forward: no tokens");
   if (n > m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_forward: %zu tokens exceed the context length %u", n, m->cfg.maxlen);
   if (offset + n > (size_t)2 * m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_forward: position %zu is beyond the RoPE table (2*maxlen)", offset + n);
+  if (n > 1 && m->cfg.tp_size > 1) return fail(VKL_UNIMPLEMENTED, "model_forward: multi-token calls are not built for tensor-parallel models (vkl_model_generate prefills token by token)");
   VKL_CUDA(cudaSetDevice(m->dev->ordinal));
   VKL_OKAY(ensure_rows(m, (uint32_t)n));
   if (n == 1) VKL_OKAY(prepare_decode(m));
+  VKL_CUDA(cudaMemsetAsync((uint32_t *)m->state->data() + 5, 0, 4, m->stream));
   const uint32_t st[2] = {(uint32_t)offset, 0};
   VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaMemcpyAsync(m->toks->data(), toks, n * 4, cudaMemcpyHostToDevice, m->stream));
@@ -715,8 +750,19 @@ int vkl_model_generate(vkl_model *m, const uint32_t *prompt, size_t n_prompt, si
   const uint32_t st[2] = {0, 0};
   VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaMemcpyAsync(m->toks->data(), prompt, n_prompt * 4, cudaMemcpyHostToDevice, m->stream));
+  // Tensor-parallel models (and VKLLAMA_PREFILL=sequential) prefill token by token through
+  // the persistent decode kernel: while the position is inside the prompt the kernel feeds
+  // itself the next prompt id instead of its arg-max.
+  const char *pf = getenv("VKLLAMA_PREFILL");
+  const bool sequential = m->mega_ready && n_prompt > 1 && (m->cfg.tp_size > 1 || (pf && !strcmp(pf, "sequential")));
+  if (m->cfg.tp_size > 1 && !m->mega_ready) return fail(VKL_UNIMPLEMENTED, "model_generate: tensor-parallel models need the persistent decode kernel");
+  const uint32_t nf = sequential ? (uint32_t)n_prompt : 0u;
+  VKL_CUDA(cudaMemcpyAsync((uint32_t *)m->state->data() + 5, &nf, 4, cudaMemcpyHostToDevice, m->stream));
+  if (sequential) VKL_CUDA(cudaMemcpyAsync(m->forced->data(), prompt, n_prompt * 4, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaEventRecord(m->ev0, m->stream));
-  if (n_prompt == 1) {
+  if (sequential) {
+    for (size_t i = 0; i < n_prompt; ++i) VKL_OKAY(decode_step(m));
+  } else if (n_prompt == 1) {
     VKL_OKAY(decode_step(m));
   } else {
     VKL_OKAY(run_tokens(m, (uint32_t)n_prompt, false));
@@ -883,12 +929,38 @@ int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float 
 }
 
 int vkl_model_tp_buffer(vkl_model *m, void **local_ptr, size_t *bytes) {
-  (void)m; (void)local_ptr; (void)bytes;
-  return fail(VKL_UNIMPLEMENTED, "tensor parallel execution is not built yet");
+  if (!m || !local_ptr || !bytes) return fail(VKL_INVALID_ARGUMENT, "model_tp_buffer: null argument");
+  if (m->cfg.tp_size <= 1) return fail(VKL_FAILED_PRECONDITION, "model_tp_buffer: the model is not tensor parallel");
+  *local_ptr = m->tp_buf;
+  *bytes = m->tp_bytes;
+  return VKL_OK;
 }
 int vkl_model_tp_connect(vkl_model *m, void *const *peer_ptrs, int n) {
-  (void)m; (void)peer_ptrs; (void)n;
-  return fail(VKL_UNIMPLEMENTED, "tensor parallel execution is not built yet");
+  if (!m || !peer_ptrs) return fail(VKL_INVALID_ARGUMENT, "model_tp_connect: null argument");
+  if (n != m->cfg.tp_size) return fail(VKL_INVALID_ARGUMENT, "model_tp_connect: %d pointers for %d ranks", n, m->cfg.tp_size);
+  for (int i = 0; i < n; ++i) {
+    if (i == m->cfg.tp_rank) continue;
+    if (!peer_ptrs[i]) return fail(VKL_INVALID_ARGUMENT, "model_tp_connect: null pointer for rank %d", i);
+    m->tp_peer[i] = peer_ptrs[i];
+  }
+  m->tp_connected = true;
+  return VKL_OK;
+}
+int vkl_ipc_export(void *device_ptr, unsigned char handle[64]) {
+  if (!device_ptr || !handle) return fail(VKL_INVALID_ARGUMENT, "ipc_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  VKL_CUDA(cudaIpcGetMemHandle(&h, device_ptr));
+  memcpy(handle, &h, 64);
+  return VKL_OK;
+}
+int vkl_ipc_open(vkl_device *dev, const unsigned char handle[64], void **device_ptr) {
+  if (!dev || !handle || !device_ptr) return fail(VKL_INVALID_ARGUMENT, "ipc_open: null argument");
+  VKL_CUDA(cudaSetDevice(dev->ordinal));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  VKL_CUDA(cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return VKL_OK;
 }
 
 }  // extern "C"
