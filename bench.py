@@ -291,29 +291,36 @@ def main():
     e2e_jobs = min(args.steps, 2)
     e2e_t = 0.0
     for _ in range(e2e_jobs):
-        logits = model(prompt, 0)
-        tok = np.array([int(np.argmax(logits))], np.uint32)
+        if tp == 1:
+            logits = model(prompt, 0)
+            tok = np.array([int(np.argmax(logits))], np.uint32)
+        else:  # sharded models prefill inside generate; every rank gets the same first id
+            first, _, _ = model.generate(prompt, 1)
+            tok = np.array([int(first[0])], np.uint32)
         barrier()
         a = time.time()
         for i in range(w["decode"]):
-            logits = model(tok, w["prompt"] + i)
-            tok[0] = int(np.argmax(logits))
+            logits = model(tok, w["prompt"] + i)  # this rank's slice of the fp32 logits comes back to the host
+            tok[0] = int(np.argmax(logits)) if tp == 1 else model.last_token()
         barrier()
         e2e_t += time.time() - a
     e2e = e2e_jobs * w["decode"] / e2e_t
+    prof = np.zeros(16)
+    reps = 16
+    for i in range(reps):  # collective under tensor parallelism: every rank runs it
+        prof += np.array(model.decode_profile(int(prompt[i % len(prompt)]), w["prompt"] + 100 + i))
+    prof /= reps
 
     if rank != 0:
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
         return 0
     # ---- roofline: whole decode step and the dominant kernel (gate/up mat-vec), live
     peak, peak_kind = peak_hbm()
     Ls = np.arange(w["prompt"] + 1, w["prompt"] + w["decode"] + 1)
     bytes_tok = float(np.mean([bytes_per_token(w, L, tp) for L in Ls]))
     step_gbs = bytes_tok / (ms_tok * 1e-3) / 1e9
-    prof = np.zeros(16)
-    reps = 16
-    for i in range(reps):
-        prof += np.array(model.decode_profile(int(prompt[i % len(prompt)]), w["prompt"] + 100 + i))
-    prof /= reps
     persistent = os.environ.get("VKLLAMA_DECODE", "") != "graph" and prof[8:].sum() > 0
     if persistent:
         # one kernel launch per token: the dominant kernel is the whole decode step
@@ -354,6 +361,9 @@ def main():
         v, cores, sample = cpu_port_tokens_per_s(w)
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
     return 0
 
 

@@ -229,6 +229,10 @@ int vkl_model_forward(vkl_model *m, const uint32_t *toks, size_t n, size_t offse
  * device_ms is not NULL it receives the device time of the decode steps only. */
 int vkl_model_generate(vkl_model *m, const uint32_t *prompt, size_t n_prompt, size_t n_gen,
                        uint32_t *out_ids, float *prefill_ms, float *decode_ms);
+/* The id the device picked after the last forward/generate step (greedy arg-max over the
+ * whole vocabulary, also when the output layer is split over tensor-parallel ranks); the
+ * device-side counterpart of TopkSampler(1)::sample (models/samplers.cpp:37-64). */
+int vkl_model_last_token(vkl_model *m, uint32_t *id);
 /* Copy one layer's caches [heads_local, maxlen, head_dim] fp16 to / from the host. */
 int vkl_model_read_kv(vkl_model *m, uint32_t layer, void *kcache, void *vcache);
 int vkl_model_write_kv(vkl_model *m, uint32_t layer, const void *kcache, const void *vcache);

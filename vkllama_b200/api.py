@@ -84,7 +84,7 @@ def load_library():
         "vkl_model_synth_weights": [vp, u64, f32, f32],
         "vkl_model_forward": [vp, vp, sz, sz, vp],
         "vkl_model_generate": [vp, vp, sz, sz, vp, C.POINTER(f32), C.POINTER(f32)],
-        "vkl_model_read_kv": [vp, u32, vp, vp], "vkl_model_write_kv": [vp, u32, vp, vp],
+        "vkl_model_last_token": [vp, C.POINTER(u32)], "vkl_model_read_kv": [vp, u32, vp, vp], "vkl_model_write_kv": [vp, u32, vp, vp],
         "vkl_model_block_forward": [vp, u32, vp, sz, sz, vp],
         "vkl_model_decode_profile": [vp, u32, sz, C.POINTER(f32)],
         "vkl_model_tp_buffer": [vp, pvp, C.POINTER(sz)], "vkl_model_tp_connect": [vp, pvp, i32],
@@ -556,6 +556,11 @@ class Model:
         pre, dec = f32(), f32()
         _ck(self.L.vkl_model_generate(self.h, _ptr(p), p.size, n_gen, _ptr(ids), C.byref(pre), C.byref(dec)))
         return ids, pre.value, dec.value
+
+    def last_token(self):
+        t = u32()
+        _ck(self.L.vkl_model_last_token(self.h, C.byref(t)))
+        return t.value
 
     def kv_shape(self):
         c = self.cfg

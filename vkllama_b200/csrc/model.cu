@@ -785,6 +785,14 @@ int vkl_model_generate(vkl_model *m, const uint32_t *prompt, size_t n_prompt, si
   return check_mega(m);
 }
 
+int vkl_model_last_token(vkl_model *m, uint32_t *id) {
+  if (!m || !id) return fail(VKL_INVALID_ARGUMENT, "model_last_token: null argument");
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  VKL_CUDA(cudaMemcpyAsync(id, (uint32_t *)m->state->data() + 2, 4, cudaMemcpyDeviceToHost, m->stream));
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  return VKL_OK;
+}
+
 int vkl_model_read_kv(vkl_model *m, uint32_t layer, void *kcache, void *vcache) {
   if (!m || layer >= m->cfg.layers) return fail(VKL_INVALID_ARGUMENT, "model_read_kv: bad model or layer");
   VKL_CUDA(cudaSetDevice(m->dev->ordinal));
