@@ -180,8 +180,9 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
 __device__ __forceinline__ bool grid_barrier(const Ctx &c, uint64_t target) {
   cons_sync();  // every consumer store of this op is issued
   if (threadIdx.x == 0 && !c.aborted()) {
-    __threadfence();
-    atomicAdd(c.p.bar, 1ull);
+    // release-add without a return value: orders this CTA's stores (made visible to
+    // thread 0 by the bar.sync above) before the arrival, one L2 trip instead of two
+    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(c.p.bar), "l"(1ull) : "memory");
     bool ok = false;
     for (uint32_t i = 0; i < WAIT_LIMIT * 8u; ++i) {
       if (ld_acq_u64(c.p.bar) >= target) {
@@ -838,6 +839,25 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
     unsigned long long t1 = 0, t2 = 0;
     if (timed) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
     if (oi + 1 < p.nops) {
+      // While waiting for the other CTAs: start what the next op will need from DRAM and
+      // does not depend on this op's results (norm weights, this CTA's rows of the KV cache).
+      const MegaOp &nx = p.ops[oi + 1];
+      if (nx.kind == MK_MATVEC && nx.norm_w) {
+        for (uint32_t i = threadIdx.x * 32; i < nx.K; i += CT * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx.norm_w + i));
+      } else if (nx.kind == MK_ATTN_PART && blockIdx.x < p.heads * S_eff) {
+        const uint32_t h = blockIdx.x / S_eff, sp = blockIdx.x % S_eff;
+        uint32_t chunk = (Lnow + S_eff - 1) / S_eff;
+        chunk = (chunk + 31) & ~31u;
+        const uint32_t a0 = min(sp * chunk, Lnow), a1 = min(a0 + chunk, Lnow);
+        const size_t rowb = (size_t)p.head_dim * 2;
+        const char *kb = reinterpret_cast<const char *>(nx.kcache) + ((size_t)h * p.maxlen + a0) * rowb;
+        const char *vb = reinterpret_cast<const char *>(nx.vcache) + ((size_t)h * p.maxlen + a0) * rowb;
+        const size_t bytes = (size_t)(a1 - a0) * rowb;
+        for (size_t o = (size_t)threadIdx.x * 128; o < bytes; o += (size_t)CT * 128) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(kb + o));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(vb + o));
+        }
+      }
       ++rounds;
       grid_barrier(c, (base_rounds + rounds) * G);
     }
