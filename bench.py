@@ -32,6 +32,9 @@ WORKLOADS = {
                            prompt=32, decode=256, seed=20240602),
     "llama2-13b-q8_0": dict(dim=5120, heads=40, ffn=13824, vocab=32000, layers=40, maxlen=4096,
                             prompt=128, decode=512, seed=20240604),
+    # 4 of the 32 blocks of the 7B shape: the small case for multi-pass ncu captures (1.2 GB on the device)
+    "llama2-7b-q8_0-4blocks": dict(dim=4096, heads=32, ffn=11008, vocab=32000, layers=4, maxlen=4096,
+                                   prompt=32, decode=16, seed=20240602),
 }
 
 
@@ -153,7 +156,7 @@ def run_reference(args, w, name):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch from ncu (see profiles/), per workload
-TRAFFIC_NCU = {}
+TRAFFIC_NCU = {"llama2-7b-q8_0": 7.16e9}  # 1.008 x algorithmic, scaled from the 4-block capture (profiles/decode_mega_kernel_7b_shape_4blocks.md)
 
 MICRO_SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)]  # rows x K: qkvo, gate/up, down, lm head
 
