@@ -296,6 +296,44 @@ ORC_API void orc_matmul_tb_f16(const uint16_t *a, const uint16_t *b, uint16_t *c
       }
 }
 
+// One fp16 row dot with the 32-lane partition of the fp16 shaders: lane (ix, il) owns the
+// 16-element slice il of K blocks ix, ix+8, ...; lanes are summed in index order.
+static float f16_row_dot(const uint16_t *ar, const uint16_t *br, uint32_t K) {
+  const uint32_t nblk = (K + 63) / 64;
+  float lane[32];
+  for (int i = 0; i < 32; ++i) lane[i] = 0.f;
+  for (uint32_t bi = 0; bi < nblk; ++bi)
+    for (int il = 0; il < 4; ++il) {
+      float s = 0.f;
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t k = bi * 64 + il * 16 + i;
+        if (k < K) s += h2f(ar[k]) * h2f(br[k]);
+      }
+      lane[(bi & 7) * 4 + il] += s;
+    }
+  float v = 0.f;
+  for (int i = 0; i < 32; ++i) v += lane[i];
+  return v;
+}
+
+// FeedForward with FP16 weights: t = fp16(silu(gate.x) * (up.x)) on unrounded fp32 dots
+// (src/shaders/ffn_up_and_gate_fp16.comp:58-125), then the down MatMul
+// (src/ops/feed_forward.cpp:88-133). Weights are [out,in].
+ORC_API void orc_feed_forward_f16(const uint16_t *x, const uint16_t *w1_gate, const uint16_t *w2_down,
+                                  const uint16_t *w3_up, uint16_t *y, uint32_t M, uint32_t dim,
+                                  uint32_t hidden) {
+  std::vector<uint16_t> t((size_t)M * hidden);
+#pragma omp parallel for schedule(static)
+  for (int64_t n = 0; n < (int64_t)hidden; ++n)
+    for (uint32_t m = 0; m < M; ++m) {
+      const float up = f16_row_dot(x + (size_t)m * dim, w3_up + (size_t)n * dim, dim);
+      const float gate = f16_row_dot(x + (size_t)m * dim, w1_gate + (size_t)n * dim, dim);
+      t[(size_t)m * hidden + n] = f2h(gate / (1.0f + expf(-gate)) * up);
+    }
+  orc_matmul_tb_f16(t.data(), w2_down, y, 1, M, dim, hidden, (uint64_t)M * hidden, hidden,
+                    (uint64_t)dim * hidden, hidden, (uint64_t)M * dim, dim, 1.f, 0.f, 0);
+}
+
 // Batched A.B (B not transposed). src/shaders/matmul_broadcast0_fp16_v2.comp:
 // 37-105 with transpose_b = 0: lane i strides K by 32.
 ORC_API void orc_matmul_nn_f16(const uint16_t *a, const uint16_t *b, uint16_t *c, uint32_t C,
@@ -575,6 +613,7 @@ struct OrcModel {
   std::vector<OrcLayer> L;
   const uint8_t *tok_embd, *output;
   const float *output_norm;
+  bool fp16 = false;  // weights are dense fp16 [out,in] instead of Q8_0 blocks
   std::vector<std::vector<uint8_t>> owned8;
   std::vector<std::vector<float>> owned32;
 };
@@ -601,12 +640,16 @@ ORC_API void orc_model_destroy(void *h) { delete (OrcModel *)h; }
 enum { S_ATTN_NORM = 0, S_WQ, S_WK, S_WV, S_WO, S_FFN_NORM, S_GATE, S_UP, S_DOWN };
 enum { G_TOK_EMBD = 0, G_OUT_NORM, G_OUTPUT };
 
-// Weights N(0, wstd) -> Q8_0; norm weights 1 + N(0, nstd).
-ORC_API void orc_model_synth(void *h, uint64_t seed, float wstd, float nstd) {
-  OrcModel &m = *(OrcModel *)h;
+// Weights N(0, wstd) -> Q8_0 (or, for an fp16 model, rounded to fp16); norm weights 1 + N(0, nstd).
+static void model_synth(OrcModel &m, uint64_t seed, float wstd, float nstd) {
   auto q8 = [&](uint64_t id, uint32_t rows, uint32_t K) {
-    m.owned8.emplace_back((size_t)rows * ((K + 31) / 32) * 34);
-    orc_synth_q8_0(seed, id, rows, K, 0.f, wstd, m.owned8.back().data());
+    if (m.fp16) {
+      m.owned8.emplace_back((size_t)rows * K * 2);
+      orc_synth_normal_f16(seed, id, 0, (uint64_t)rows * K, 0.f, wstd, (uint16_t *)m.owned8.back().data());
+    } else {
+      m.owned8.emplace_back((size_t)rows * ((K + 31) / 32) * 34);
+      orc_synth_q8_0(seed, id, rows, K, 0.f, wstd, m.owned8.back().data());
+    }
     return (const uint8_t *)m.owned8.back().data();
   };
   auto nw = [&](uint64_t id, uint32_t n) {
@@ -632,11 +675,22 @@ ORC_API void orc_model_synth(void *h, uint64_t seed, float wstd, float nstd) {
   m.output_norm = nw(g + G_OUT_NORM, m.dim);
   m.output = q8(g + G_OUTPUT, m.vocab, m.dim);
 }
+ORC_API void orc_model_synth(void *h, uint64_t seed, float wstd, float nstd) {
+  OrcModel &m = *(OrcModel *)h;
+  m.fp16 = false;
+  model_synth(m, seed, wstd, nstd);
+}
+// The FP16-weights build of the model (models/llama2.h picks the dtype per GGUF tensor).
+ORC_API void orc_model_synth_f16(void *h, uint64_t seed, float wstd, float nstd) {
+  OrcModel &m = *(OrcModel *)h;
+  m.fp16 = true;
+  model_synth(m, seed, wstd, nstd);
+}
 
 // Raw 34-byte-block bytes of one weight, for upload to the device under test.
 ORC_API const void *orc_model_weight(void *h, uint32_t layer, uint32_t slot, uint64_t *bytes) {
   OrcModel &m = *(OrcModel *)h;
-  const size_t q = (size_t)(m.dim / 32) * 34, qf = (size_t)(m.ffn / 32) * 34;
+  const size_t q = m.fp16 ? (size_t)m.dim * 2 : (size_t)(m.dim / 32) * 34, qf = m.fp16 ? (size_t)m.ffn * 2 : (size_t)(m.ffn / 32) * 34;
   if (layer < m.layers) {
     OrcLayer &y = m.L[layer];
     switch (slot) {
@@ -670,19 +724,39 @@ ORC_API uint16_t *orc_model_vcache(void *h, uint32_t layer) {
 
 // One block on hidden states x [T, dim] -> out [To, dim], To = 1 when `clip`
 // (the last block keeps only the last token: models/llama2.h:181-191).
+// y[M,N] = x[M,K] . w[N,K]^T with dense fp16 weights (matmul_b0_tb_fp16_v2.comp).
+static void linear_f16(const uint16_t *x, const uint8_t *w, uint16_t *y, uint32_t M, uint32_t N, uint32_t K) {
+  orc_matmul_tb_f16(x, (const uint16_t *)w, y, 1, M, N, K, (uint64_t)M * K, K, (uint64_t)N * K, K, (uint64_t)M * N, N, 1.f, 0.f, 0);
+}
+
 static void block_forward(OrcModel &m, OrcLayer &y, const uint16_t *x, uint32_t T,
                           uint32_t offset, bool clip, uint16_t *out) {
   const uint32_t D = m.dim, To = clip ? 1 : T;
   std::vector<uint16_t> normed((size_t)T * D), added((size_t)To * D), normed2((size_t)To * D),
       feed((size_t)To * D), attn((size_t)To * D);
   orc_rms_norm_f16(x, y.attn_norm, normed.data(), T, D, m.eps);
-  orc_attn_forward_q8_0(&y.attn, normed.data(), y.wk, y.wq, y.wv, y.wo, T, offset, clip,
-                        attn.data());
+  if (m.fp16) {
+    // MultiHeadAttentionV2 with FP16 weights: three MatMuls, the shared core, o_proj
+    // (src/ops/multiheadattention_v2.cpp:186-300)
+    std::vector<uint16_t> k((size_t)T * D), q((size_t)T * D), v((size_t)T * D), cc((size_t)To * D);
+    linear_f16(normed.data(), y.wk, k.data(), T, D, D);
+    linear_f16(normed.data(), y.wq, q.data(), T, D, D);
+    linear_f16(normed.data(), y.wv, v.data(), T, D, D);
+    attn_core(y.attn, k.data(), q.data(), v.data(), T, offset, clip, cc.data());
+    linear_f16(cc.data(), y.wo, attn.data(), To, D, D);
+  } else {
+    orc_attn_forward_q8_0(&y.attn, normed.data(), y.wk, y.wq, y.wv, y.wo, T, offset, clip,
+                          attn.data());
+  }
   // add_op_(transformed, in): in <- fp16(transformed + in)   (llama2.h:193-196)
   memcpy(added.data(), clip ? x + (size_t)(T - 1) * D : x, (size_t)To * D * 2);
   orc_add_f16(attn.data(), added.data(), (size_t)To * D);
   orc_rms_norm_f16(added.data(), y.ffn_norm, normed2.data(), To, D, m.eps);
-  orc_feed_forward_q8_0(normed2.data(), y.gate, y.down, y.up, feed.data(), To, D, m.ffn);
+  if (m.fp16)
+    orc_feed_forward_f16(normed2.data(), (const uint16_t *)y.gate, (const uint16_t *)y.down, (const uint16_t *)y.up, feed.data(), To, D,
+                         m.ffn);
+  else
+    orc_feed_forward_q8_0(normed2.data(), y.gate, y.down, y.up, feed.data(), To, D, m.ffn);
   // add_op2_(feed, added): added <- fp16(feed + added)        (llama2.h:209)
   memcpy(out, added.data(), (size_t)To * D * 2);
   orc_add_f16(feed.data(), out, (size_t)To * D);
@@ -701,7 +775,10 @@ ORC_API void orc_model_forward(void *h, const uint32_t *toks, uint32_t T, uint32
   OrcModel &m = *(OrcModel *)h;
   const uint32_t D = m.dim;
   std::vector<uint16_t> x((size_t)T * D), nx((size_t)T * D);
-  orc_embedding_q8_0(m.tok_embd, toks, x.data(), T, m.vocab, D, 0);
+  if (m.fp16)
+    orc_embedding_f16((const uint16_t *)m.tok_embd, toks, x.data(), T, m.vocab, D, 0);
+  else
+    orc_embedding_q8_0(m.tok_embd, toks, x.data(), T, m.vocab, D, 0);
   for (uint32_t l = 0; l < m.layers; ++l) {
     const bool clip = l == m.layers - 1;
     block_forward(m, m.L[l], x.data(), T, offset, clip, nx.data());
@@ -710,7 +787,10 @@ ORC_API void orc_model_forward(void *h, const uint32_t *toks, uint32_t T, uint32
   if (hidden_out) memcpy(hidden_out, x.data(), (size_t)D * 2);
   std::vector<uint16_t> normed(D), lg(m.vocab);
   orc_rms_norm_f16(x.data(), m.output_norm, normed.data(), 1, D, m.final_eps);
-  orc_matmul_q8_0(normed.data(), m.output, lg.data(), 1, m.vocab, D, 1.f, 0.f, 0);
+  if (m.fp16)
+    linear_f16(normed.data(), m.output, lg.data(), 1, m.vocab, D);
+  else
+    orc_matmul_q8_0(normed.data(), m.output, lg.data(), 1, m.vocab, D, 1.f, 0.f, 0);
   for (uint32_t i = 0; i < m.vocab; ++i) logits[i] = h2f(lg[i]);  // Cast fp16->fp32
 }
 

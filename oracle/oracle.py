@@ -56,6 +56,7 @@ def lib():
     sig("orc_kqv_q8_0", None, u16p, u8p, u8p, u8p, u16p, u16p, u16p, u32, u32, u32)
     sig("orc_ffn_up_gate_q8_0", None, u16p, u8p, u8p, u16p, u32, u32, u32)
     sig("orc_feed_forward_q8_0", None, u16p, u8p, u8p, u8p, u16p, u32, u32, u32)
+    sig("orc_feed_forward_f16", None, u16p, u16p, u16p, u16p, u16p, u32, u32, u32)
     for n in ("orc_matmul_tb_f16", "orc_matmul_nn_f16"):
         sig(n, None, u16p, u16p, u16p, u32, u32, u32, u32, u64, u64, u64, u64, u64, u64, f32, f32, i32)
     sig("orc_softmax_f16", None, u16p, u16p, u32, u32, u32, i32, u32)
@@ -77,6 +78,7 @@ def lib():
     sig("orc_model_create", vp, u32, u32, u32, u32, u32, u32, f32, f32)
     sig("orc_model_destroy", None, vp)
     sig("orc_model_synth", None, vp, u64, f32, f32)
+    sig("orc_model_synth_f16", None, vp, u64, f32, f32)
     sig("orc_model_weight", vp, vp, u32, u32, C.POINTER(u64))
     sig("orc_model_kcache", C.POINTER(C.c_uint16), vp, u32)
     sig("orc_model_vcache", C.POINTER(C.c_uint16), vp, u32)
@@ -177,15 +179,16 @@ class Model:
     """Synthetic Llama-2-shaped model held by the oracle."""
 
     def __init__(self, dim, heads, ffn, vocab, layers, maxlen, eps=1e-5, final_eps=1e-6,
-                 seed=0, wstd=0.02, nstd=0.01):
+                 seed=0, wstd=0.02, nstd=0.01, fp16=False):
         self.cfg = dict(dim=dim, heads=heads, ffn=ffn, vocab=vocab, layers=layers,
                         maxlen=maxlen, eps=eps, final_eps=final_eps)
+        self.fp16 = fp16
         self.L = lib()
         self.h = self.L.orc_model_create(dim, heads, ffn, vocab, layers, maxlen, eps, final_eps)
-        self.L.orc_model_synth(self.h, seed, wstd, nstd)
+        (self.L.orc_model_synth_f16 if fp16 else self.L.orc_model_synth)(self.h, seed, wstd, nstd)
 
     def weight(self, layer, slot):
-        """Raw bytes (34-byte blocks, or fp32 for norms) as a numpy view."""
+        """Raw bytes (34-byte blocks or dense fp16; fp32 for norms) as a numpy view."""
         n = u64(0)
         p = self.L.orc_model_weight(self.h, layer, slot, C.byref(n))
         return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(n.value,))

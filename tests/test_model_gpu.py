@@ -24,6 +24,45 @@ def small_pair(dev, seed=5, **over):
     return om, dm, cfg
 
 
+def fp16_pair(dev, seed, **over):
+    cfg = dict(SMALL, **over)
+    om = O.Model(seed=seed, fp16=True, **cfg)
+    dm = vk.Model(dev, cfg["dim"], cfg["heads"], cfg["ffn"], cfg["vocab"], cfg["layers"], cfg["maxlen"], weight_dtype=vk.FP16)
+    load_from_oracle(dm, om)
+    return om, dm, cfg
+
+
+@pytest.mark.parametrize("P", [7, 48, 100, 128])
+def test_fp16_weights_model_prefill_then_decode(dev, P):
+    """FP16-weights model: prompts of 32 tokens and more prefill through the tcgen05 tensor-core
+    GEMM, shorter ones and the decode steps through the weight-streaming kernels."""
+    om, dm, cfg = fp16_pair(dev, seed=11)
+    prompt = O.synth_tokens(11, 1000 + P, P, cfg["vocab"])
+    want = om.forward(prompt, 0)
+    got = dm(prompt, 0)
+    assert np.abs(got - want).max() <= LOGITS_MAX_ABS
+    tok = np.array([int(np.argmax(want))], np.uint32)
+    for i in range(3):
+        want = om.forward(tok, P + i)
+        got = dm(tok, P + i)
+        assert np.abs(got - want).max() <= LOGITS_MAX_ABS, "decode step %d" % i
+        tok = np.array([int(np.argmax(want))], np.uint32)
+    for l in range(cfg["layers"]):
+        gk, gv = dm.read_kv(l)
+        n = min(P + 3, cfg["maxlen"])
+        assert_close(gk[:, :n], om.kcache(l)[:, :n], tol=5e-3, what="kcache layer %d" % l)
+        assert_close(gv[:, :n], om.vcache(l)[:, :n], tol=5e-3, what="vcache layer %d" % l)
+
+
+def test_fp16_weights_greedy_generate(dev):
+    om, dm, cfg = fp16_pair(dev, seed=12)
+    prompt = O.synth_tokens(12, 1000, 40, cfg["vocab"])
+    want, gap = om.generate(prompt, 16)
+    got = dm.generate(prompt, 16)[0]
+    bad = [i for i in range(16) if got[i] != want[i]]
+    assert not bad or gap[bad[0]] < UNDECIDED_GAP, (bad, gap)
+
+
 def test_block_7b_shape_decode_at_position_511(dev):
     """One decoder block with Llama-2-7B shapes, one decode step at position 511,
     fp16 KV cache prefilled with N(0,1) for 511 positions."""

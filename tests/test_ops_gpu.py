@@ -142,6 +142,48 @@ def test_matmul_fp16_weight(dev):
     assert_close(got, want, what="matmul fp16 weight")
 
 
+# Many rows with FP16 weights run on the tcgen05 tensor-core GEMM (one pass over the weights);
+# ragged M and N exercise the zero-filled tile edges, act/scale/bias the epilogue.
+@pytest.mark.parametrize("M,N,K,scale,bias,act", [(32, 128, 64, 1.0, 0.0, 0), (128, 128, 128, 1.0, 0.0, 0),
+                                                    (100, 136, 256, 0.5, 0.25, 1), (300, 344, 4096, 1.0, 0.0, 0),
+                                                    (512, 4096, 4096, 1.0, 0.0, 0), (129, 11008, 4096, 1.0, 0.0, 0)])
+def test_matmul_fp16_weight_many_rows(dev, M, N, K, scale, bias, act):
+    a = O.synth_f16(43, 1, M * K).reshape(1, M, K)
+    w = O.synth_f16(43, 2, N * K, 0.0, 0.02).reshape(1, N, K)
+    want = np.empty(M * N, np.uint16)
+    O.lib().orc_matmul_tb_f16(a, w, want, 1, M, N, K, M * K, K, N * K, K, M * N, N, scale, bias, act)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    ta = up(cmd, dev, a, vk.FP16, 1, M, K)
+    tw = up(cmd, dev, w, vk.FP16, 1, N, K)
+    op = vk.MatMul(dev, cmd, tw, scale, bias, act, 0, True, vk.FP16, vk.FP16).init()
+    got = cmd.download(op(ta))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert_close(got, want, what="matmul fp16 weight (tensor-core GEMM)")
+
+
+@pytest.mark.parametrize("M,dim,hidden", [(5, 64, 96), (64, 128, 256), (100, 4096, 11008)])
+def test_feed_forward_fp16(dev, M, dim, hidden):
+    gate = O.synth_f16(52, 1, hidden * dim, 0.0, 0.02)
+    down = O.synth_f16(52, 2, dim * hidden, 0.0, 0.02)
+    upw = O.synth_f16(52, 3, hidden * dim, 0.0, 0.02)
+    x = O.synth_f16(52, 4, M * dim).reshape(M, dim)
+    want = np.empty(M * dim, np.uint16)
+    O.lib().orc_feed_forward_f16(x, gate, down, upw, want, M, dim, hidden)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    w1 = up(cmd, dev, gate, vk.FP16, 1, hidden, dim)
+    w2 = up(cmd, dev, down, vk.FP16, 1, dim, hidden)
+    w3 = up(cmd, dev, upw, vk.FP16, 1, hidden, dim)
+    tx = up(cmd, dev, x, vk.FP16, 1, M, dim)
+    op = vk.FeedForward(dev, cmd, w1, w2, w3, True, vk.FP16).init()
+    got = cmd.download(op(tx))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert_close(got, want, what="feed_forward fp16")
+
+
 # ---- FeedForward (tests/test_feedforward.cpp:143-148 Q8_0: dims 16,8,256,17; 7B) --
 @pytest.mark.parametrize("M,dim,hidden", [(64, 32, 256), (1, 4096, 11008), (4, 4096, 11008), (17, 64, 96)])
 def test_feed_forward_q8_0(dev, M, dim, hidden):

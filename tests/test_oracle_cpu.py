@@ -102,3 +102,32 @@ def test_oracle_generate_is_self_consistent():
     logits = m2.forward(prompt, 0)
     assert int(np.argmax(logits)) == ids[0]
     assert gap[0] >= 0
+
+
+def test_oracle_fp16_feed_forward_against_numpy():
+    M, dim, hidden = 3, 128, 192
+    gate = O.synth_f16(31, 1, hidden * dim, 0.0, 0.05)
+    down = O.synth_f16(31, 2, dim * hidden, 0.0, 0.05)
+    upw = O.synth_f16(31, 3, hidden * dim, 0.0, 0.05)
+    x = O.synth_f16(31, 4, M * dim)
+    got = np.empty(M * dim, np.uint16)
+    O.lib().orc_feed_forward_f16(x, gate, down, upw, got, M, dim, hidden)
+    xf = O.f16(x).reshape(M, dim).astype(np.float64)
+    g = xf @ O.f16(gate).reshape(hidden, dim).astype(np.float64).T
+    u = xf @ O.f16(upw).reshape(hidden, dim).astype(np.float64).T
+    t = O.f16(O.bits(g / (1 + np.exp(-g)) * u)).astype(np.float64)
+    want = t @ O.f16(down).reshape(dim, hidden).astype(np.float64).T
+    err = np.abs(O.f16(got).reshape(M, dim) - want).max() / np.abs(want).max()
+    assert err < 2e-3
+
+
+def test_oracle_fp16_weights_model_runs_and_differs_from_q8_0():
+    cfg = dict(dim=128, heads=4, ffn=256, vocab=320, layers=2, maxlen=64, seed=9)
+    prompt = O.synth_tokens(9, 1000, 5, 320)
+    a = O.Model(fp16=True, **cfg).forward(prompt, 0)
+    b = O.Model(fp16=True, **cfg).forward(prompt, 0)
+    q = O.Model(**cfg).forward(prompt, 0)
+    assert np.isfinite(a).all() and np.array_equal(a, b)
+    assert not np.array_equal(a, q) and np.abs(a - q).max() < 0.5  # quantisation noise only
+    w = O.Model(fp16=True, **cfg).weight(0, O.SLOTS["wq"])
+    assert w.size == 128 * 128 * 2

@@ -40,16 +40,17 @@ def llama_names(layer=None):
 def load_from_oracle(model, om):
     """Upload every weight of an oracle model into a device model (raw GGUF bytes)."""
     L = om.cfg["layers"]
+    wdt = vk.FP16 if getattr(om, "fp16", False) else vk.Q8_0
     for l in range(L):
         for slot, name in llama_names(l).items():
             w = om.weight(l, O.SLOTS[slot])
             if slot.endswith("norm"):
                 model.set_weight(name, vk.FP32, w.view(np.float32))
             else:
-                model.set_weight(name, vk.Q8_0, w)
+                model.set_weight(name, wdt, w)
     for slot, name in llama_names().items():
         w = om.weight(L, O.GLOBALS[slot])
         if slot == "output_norm":
             model.set_weight(name, vk.FP32, w.view(np.float32))
         else:
-            model.set_weight(name, vk.Q8_0, w)
+            model.set_weight(name, wdt, w)

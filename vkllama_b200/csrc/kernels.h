@@ -171,4 +171,21 @@ int decode_mega_stage_groups();
 cudaError_t decode_mega_occupancy(size_t xs_bytes, int *blocks_per_sm);
 cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s);
 
+// ---- dense FP16 GEMM on tcgen05 tensor cores: C[M,N] = A[M,K] . W[N,K]^T (gemm_tcgen05.cu) ----
+struct GemmParams {
+  const __half *a;         // [M,K] row-major
+  const __half *w;         // [N,K] row-major (a transposed-weight matrix of the reference)
+  __half *c;               // [M,N] fp16 output, or nullptr when c_f32 is set
+  float *c_f32;            // raw fp32 output (for the fused SwiGLU step)
+  const __half *residual;  // optional [M,N]: c = fp16(fp16(acc) + residual)
+  uint32_t *error;         // device word raised when a bounded wait ran out
+  uint32_t M, N, K;
+  float scale, bias;       // MatMul's scale and bias (mat_mul.cpp:39-41)
+  int act;                 // 0 none, 1 SiLU
+};
+constexpr uint32_t GEMM_MIN_ROWS = 32;  // below this the weight-streaming mat-vec kernel is used
+bool gemm_tcgen05_supported(uint32_t M, uint32_t N, uint32_t K);
+cudaError_t launch_gemm_f16_tcgen05(const GemmParams &p, cudaStream_t s);
+cudaError_t launch_swiglu_f32(const float *gate, const float *up, __half *out, size_t n, cudaStream_t s);
+
 }  // namespace vkl

@@ -57,9 +57,11 @@ struct vkl_model {
   // activations, sized for `cap_T` rows
   uint32_t cap_T = 0;
   vkl_tensor *x = nullptr, *xn = nullptr, *q = nullptr, *k = nullptr, *v = nullptr, *ao = nullptr, *t = nullptr;
+  vkl_tensor *gu32 = nullptr;  // [2, cap_T, ffn] fp32 gate and up results of the FP16 prefill GEMMs
+  bool gemm_used = false;      // a tensor-core GEMM ran since the last check of state[6]
   vkl_tensor *logits16 = nullptr, *logits32 = nullptr;
   vkl_tensor *toks = nullptr;  // [cap_T] device token ids; toks[0] is the decode token
-  vkl_tensor *state = nullptr; // uint32[8]: [0] pos, [1] step, [2] next id, [3] all-reduces, [4] arg exchanges, [5] forced tokens
+  vkl_tensor *state = nullptr; // uint32[8]: [0] pos, [1] step, [2] next id, [3] all-reduces, [4] arg exchanges, [5] forced tokens, [6] GEMM wait error
   vkl_tensor *forced = nullptr;  // prompt ids for token-by-token prefill
   // tensor parallelism: this rank's exchange buffer (plain cudaMalloc so that it can be
   // exported over CUDA IPC) and every rank's mapping of it
@@ -88,7 +90,7 @@ struct vkl_model {
     if (tp_buf) cudaFree(tp_buf);
     for (auto &l : L)
       for (vkl_tensor *p : {l.attn_norm, l.ffn_norm, l.wq, l.wk, l.wv, l.wo, l.gate, l.up, l.down, l.kcache, l.vcache}) vkl_tensor_release(p);
-    for (vkl_tensor *p : {tok_embd, output_norm, output, fc, fs, x, xn, q, k, v, ao, t, logits16, logits32, toks, state, out_ids, forced, argpart, attn_scratch, attn_counters, mega_ops, mega_sync, mega_arg, mega_attn, mega_stages, mega_counts})
+    for (vkl_tensor *p : {tok_embd, output_norm, output, fc, fs, x, xn, q, k, v, ao, t, gu32, logits16, logits32, toks, state, out_ids, forced, argpart, attn_scratch, attn_counters, mega_ops, mega_sync, mega_arg, mega_attn, mega_stages, mega_counts})
       vkl_tensor_release(p);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
@@ -123,6 +125,7 @@ int ensure_rows(vkl_model *m, uint32_t T) {
   VKL_OKAY(ensure_tensor(m->dev, &m->v, 1, T, m->dim_l, VKL_FP16));
   VKL_OKAY(ensure_tensor(m->dev, &m->ao, 1, T, m->dim_l, VKL_FP16));
   VKL_OKAY(ensure_tensor(m->dev, &m->t, 1, T, m->ffn_l, VKL_FP16));
+  if (!q8(m) && T >= GEMM_MIN_ROWS) VKL_OKAY(ensure_tensor(m->dev, &m->gu32, 2, T, m->ffn_l, VKL_FP32));
   VKL_OKAY(ensure_tensor(m->dev, &m->toks, 1, 1, T, VKL_UINT32));
   const size_t sc = attention_scratch_bytes(1, m->heads_l, m->head_dim, m->splits);
   VKL_OKAY(ensure_tensor(m->dev, &m->attn_scratch, 1, 1, sc / 4, VKL_FP32));
@@ -146,6 +149,27 @@ MvParams mv(const vkl_model *m, const vkl_tensor *w, const __half *x, __half *ou
   p.fp16_weights = !q8(m);
   p.use_pdl = 0;
   return p;
+}
+
+// Many-row projection with FP16 weights on the tcgen05 tensor cores.
+GemmParams gemm(vkl_model *m, const vkl_tensor *w, const __half *a, __half *out, uint32_t M) {
+  GemmParams g = {};
+  g.a = a;
+  g.w = (const __half *)w->data();
+  g.c = out;
+  g.M = M;
+  g.N = (uint32_t)w->h;
+  g.K = (uint32_t)w->w;
+  g.scale = 1.f;
+  g.error = (uint32_t *)m->state->data() + 6;
+  m->gemm_used = true;
+  return g;
+}
+bool use_gemm(const vkl_model *m, uint32_t rows) {
+  static const bool off = [] { const char *e = getenv("VKLLAMA_PREFILL_GEMM"); return e && !strcmp(e, "0"); }();
+  return !off && !q8(m) && rows >= GEMM_MIN_ROWS && gemm_tcgen05_supported(rows, m->dim_l, m->cfg.dim) &&
+         gemm_tcgen05_supported(rows, m->cfg.dim, m->dim_l) && gemm_tcgen05_supported(rows, m->ffn_l, m->cfg.dim) &&
+         gemm_tcgen05_supported(rows, m->cfg.dim, m->ffn_l);
 }
 
 // Optional per-kernel timing of a pass: an event after every launch, tagged with
@@ -194,6 +218,11 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
       p.eps = m->cfg.eps;
       p.use_pdl = pdl;
       VKL_LAUNCH(1, launch_matvec(p, EPI_PLAIN, true, s));
+    } else if (use_gemm(m, T)) {
+      VKL_LAUNCH(1, launch_rms_norm(x, (const float *)y.attn_norm->data(), xn, T, D, m->cfg.eps, s));
+      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(gemm(m, y.wk, xn, kb, T), s));
+      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(gemm(m, y.wq, xn, qb, T), s));
+      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(gemm(m, y.wv, xn, vb, T), s));
     } else {
       VKL_LAUNCH(1, launch_rms_norm(x, (const float *)y.attn_norm->data(), xn, T, D, m->cfg.eps, s));
       VKL_LAUNCH((T + 63) / 64, launch_matvec(p, EPI_PLAIN, false, s));
@@ -217,10 +246,16 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
       rows = 1;
     }
     // --- o_proj + residual (add_op_(attn, in): llama2.h:193-196) -------------
-    MvParams o = mv(m, y.wo, ao, xr, rows);
-    o.residual = xr;
-    o.use_pdl = dec && pdl;
-    VKL_LAUNCH((rows + 63) / 64, launch_matvec(o, EPI_ADD, false, s));
+    if (use_gemm(m, rows)) {
+      GemmParams g = gemm(m, y.wo, ao, xr, rows);
+      g.residual = xr;
+      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, s));
+    } else {
+      MvParams o = mv(m, y.wo, ao, xr, rows);
+      o.residual = xr;
+      o.use_pdl = dec && pdl;
+      VKL_LAUNCH((rows + 63) / 64, launch_matvec(o, EPI_ADD, false, s));
+    }
     MARK(3);
     // --- feed forward --------------------------------------------------------
     MvParams f = mv(m, y.gate, dec || rows == 1 ? xr : xn, tb, rows);
@@ -231,15 +266,31 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
       f.eps = m->cfg.eps;
       f.use_pdl = dec && pdl;
       VKL_LAUNCH(1, launch_matvec(f, EPI_SWIGLU, true, s));
+    } else if (use_gemm(m, rows)) {
+      VKL_LAUNCH(1, launch_rms_norm(xr, (const float *)y.ffn_norm->data(), xn, rows, D, m->cfg.eps, s));
+      float *g32 = (float *)m->gu32->data(), *u32 = g32 + (size_t)rows * m->ffn_l;
+      GemmParams g = gemm(m, y.gate, xn, nullptr, rows);
+      g.c_f32 = g32;
+      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, s));
+      g.w = (const __half *)y.up->data();
+      g.c_f32 = u32;
+      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, s));
+      VKL_LAUNCH(1, launch_swiglu_f32(g32, u32, tb, (size_t)rows * m->ffn_l, s));
     } else {
       VKL_LAUNCH(1, launch_rms_norm(xr, (const float *)y.ffn_norm->data(), xn, rows, D, m->cfg.eps, s));
       VKL_LAUNCH((rows + 63) / 64, launch_matvec(f, EPI_SWIGLU, false, s));
     }
     MARK(4);
-    MvParams d = mv(m, y.down, tb, xr, rows);
-    d.residual = xr;
-    d.use_pdl = dec && pdl;
-    VKL_LAUNCH((rows + 63) / 64, launch_matvec(d, EPI_ADD, false, s));
+    if (use_gemm(m, rows)) {
+      GemmParams g = gemm(m, y.down, tb, xr, rows);
+      g.residual = xr;
+      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, s));
+    } else {
+      MvParams d = mv(m, y.down, tb, xr, rows);
+      d.residual = xr;
+      d.use_pdl = dec && pdl;
+      VKL_LAUNCH((rows + 63) / 64, launch_matvec(d, EPI_ADD, false, s));
+    }
     MARK(5);
   }
   // --- output layer: RMSNorm(1e-6) -> lm head -> fp32 cast (llama2.h:283-298) --
@@ -450,6 +501,19 @@ int check_mega(vkl_model *m) {
     cudaMemsetAsync(m->mega_sync->data(), 0, 64, m->stream);
     cudaStreamSynchronize(m->stream);
     return fail(VKL_INTERNAL, "decode kernel: a bounded wait ran out (code %u: 1 weight stage, 2 ring slot, 3 grid barrier)", err);
+  }
+  return VKL_OK;
+}
+
+// After a pass that ran tensor-core GEMMs (stream already synchronised): report a wait that ran out.
+int check_gemm(vkl_model *m) {
+  if (!m->gemm_used) return VKL_OK;
+  m->gemm_used = false;
+  uint32_t err = 0;
+  VKL_CUDA(cudaMemcpy(&err, (uint32_t *)m->state->data() + 6, 4, cudaMemcpyDeviceToHost));
+  if (err) {
+    cudaMemset((uint32_t *)m->state->data() + 6, 0, 4);
+    return fail(VKL_INTERNAL, "prefill GEMM: a bounded mbarrier wait ran out");
   }
   return VKL_OK;
 }
@@ -733,6 +797,7 @@ int vkl_model_forward(vkl_model *m, const uint32_t *toks, size_t n, size_t offse
   VKL_CUDA(cudaMemcpyAsync(logits_out, m->logits32->data(), (size_t)m->vocab_l * 4, cudaMemcpyDeviceToHost, m->stream));
   VKL_CUDA(cudaStreamSynchronize(m->stream));
   if (n == 1) VKL_OKAY(check_mega(m));
+  VKL_OKAY(check_gemm(m));
   return VKL_OK;
 }
 
@@ -782,6 +847,7 @@ int vkl_model_generate(vkl_model *m, const uint32_t *prompt, size_t n_prompt, si
     VKL_CUDA(cudaEventElapsedTime(&ms, m->ev1, m->ev2));
     *decode_ms = ms;
   }
+  VKL_OKAY(check_gemm(m));
   return check_mega(m);
 }
 

@@ -99,7 +99,15 @@ struct MatMulOp : vkl_op {
       p.x_ld = (uint32_t)K; p.out_ld = (uint32_t)N;
       p.scale = scale; p.bias = bias; p.act = act;
       p.fp16_weights = b_dtype == VKL_FP16;
-      if (p.fp16_weights && (K & 7)) {
+      if (p.fp16_weights && a->h >= GEMM_MIN_ROWS && gemm_tcgen05_supported((uint32_t)a->h, (uint32_t)N, (uint32_t)K)) {
+        // many rows: one pass over the weights on the tcgen05 tensor cores
+        GemmParams g = {};
+        g.a = (const __half *)a->data(); g.w = (const __half *)weight->data(); g.c = (__half *)out->data();
+        g.M = (uint32_t)a->h; g.N = (uint32_t)N; g.K = (uint32_t)K;
+        g.scale = scale; g.bias = bias; g.act = act;
+        VKL_OKAY(command_error_word(cmd, &g.error));
+        VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, cmd->stream));
+      } else if (p.fp16_weights && (K & 7)) {
         VKL_LAUNCH(1, launch_bmm_f16((const __half *)a->data(), (const __half *)weight->data(), (__half *)out->data(), 1,
                                      (uint32_t)a->h, (uint32_t)N, (uint32_t)K, 0, K, 0, K, 0, N, 1, scale, bias, act, cmd->stream));
       } else {
@@ -138,14 +146,14 @@ struct MatMulOp : vkl_op {
 struct FeedForwardOp : vkl_op {
   vkl_tensor *w1, *w2, *w3;  // gate, down, up
   int transposed_weight, dtype;
-  vkl_tensor *t0 = nullptr, *out = nullptr;
+  vkl_tensor *t0 = nullptr, *out = nullptr, *gu32 = nullptr;
   FeedForwardOp(vkl_device *d, vkl_command *c, vkl_tensor *a, vkl_tensor *b, vkl_tensor *e, int tw, int dt)
       : vkl_op(d, c), w1(a), w2(b), w3(e), transposed_weight(tw), dtype(dt) {
     vkl_tensor_retain(w1); vkl_tensor_retain(w2); vkl_tensor_retain(w3);
   }
   ~FeedForwardOp() override {
     vkl_tensor_release(w1); vkl_tensor_release(w2); vkl_tensor_release(w3);
-    vkl_tensor_release(t0); vkl_tensor_release(out);
+    vkl_tensor_release(t0); vkl_tensor_release(out); vkl_tensor_release(gu32);
   }
   // src/ops/feed_forward.cpp:24-68
   int init() override {
@@ -171,6 +179,29 @@ struct FeedForwardOp : vkl_op {
     VKL_OKAY(ensure_tensor(dev, &t0, x->c, x->h, w1->h, VKL_FP16));
     VKL_OKAY(ensure_tensor(dev, &out, x->c, x->h, w2->h, VKL_FP16));
     const bool q8 = dtype == VKL_Q8_0;
+    if (!q8 && x->h >= GEMM_MIN_ROWS && gemm_tcgen05_supported((uint32_t)x->h, (uint32_t)w1->h, (uint32_t)w1->w) &&
+        gemm_tcgen05_supported((uint32_t)x->h, (uint32_t)w2->h, (uint32_t)w2->w)) {
+      // many rows: gate and up as tensor-core GEMMs with raw fp32 results, SwiGLU on those
+      // (the rounding points of ffn_up_and_gate_fp16.comp), then the down GEMM
+      VKL_OKAY(ensure_tensor(dev, &gu32, 2, x->h, w1->h, VKL_FP32));
+      GemmParams g = {};
+      g.a = (const __half *)x->data(); g.w = (const __half *)w1->data(); g.c_f32 = (float *)gu32->data();
+      g.M = (uint32_t)x->h; g.N = (uint32_t)w1->h; g.K = (uint32_t)w1->w;
+      g.scale = 1.f;
+      VKL_OKAY(command_error_word(cmd, &g.error));
+      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, cmd->stream));
+      g.w = (const __half *)w3->data(); g.c_f32 += (size_t)x->h * w1->h;
+      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, cmd->stream));
+      VKL_LAUNCH(1, launch_swiglu_f32((const float *)gu32->data(), (const float *)gu32->data() + (size_t)x->h * w1->h, (__half *)t0->data(),
+                                      (size_t)x->h * w1->h, cmd->stream));
+      GemmParams d = {};
+      d.a = (const __half *)t0->data(); d.w = (const __half *)w2->data(); d.c = (__half *)out->data();
+      d.M = (uint32_t)x->h; d.N = (uint32_t)w2->h; d.K = (uint32_t)w2->w;
+      d.scale = 1.f; d.error = g.error;
+      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(d, cmd->stream));
+      *o = out;
+      return leave();
+    }
     MvParams p = {};
     p.codes[0] = w1->data(); p.codes[1] = w3->data();
     p.scales[0] = q8 ? w1->scales() : nullptr; p.scales[1] = q8 ? w3->scales() : nullptr;

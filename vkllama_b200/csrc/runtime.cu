@@ -188,6 +188,20 @@ bool vkl_tensor::dense() const {
   return hs == dhs && cs == h * dhs;
 }
 
+namespace vkl {
+int command_error_word(vkl_command *cmd, uint32_t **out) {
+  if (!cmd->err_word) {
+    void *p = nullptr;
+    VKL_OKAY(cmd->dev->alloc(256, &p));
+    VKL_CUDA(cudaMemsetAsync(p, 0, 256, cmd->stream));
+    cmd->err_word = (uint32_t *)p;
+  }
+  cmd->err_used = true;
+  *out = cmd->err_word;
+  return VKL_OK;
+}
+}  // namespace vkl
+
 extern "C" {
 
 int vkl_tensor_create(vkl_device *dev, int c, int h, int w, int dtype, vkl_tensor **out) {
@@ -275,6 +289,7 @@ int vkl_command_destroy(vkl_command *cmd) {
   if (!cmd) return VKL_OK;
   cudaStreamSynchronize(cmd->stream);
   for (auto &f : cmd->deferred) f();
+  if (cmd->err_word) cmd->dev->release(cmd->err_word, 256);
   cudaStreamDestroy(cmd->stream);
   if (cmd->ev0) cudaEventDestroy(cmd->ev0);
   if (cmd->ev1) cudaEventDestroy(cmd->ev1);
@@ -310,6 +325,15 @@ int vkl_command_wait(vkl_command *cmd) {
   cmd->deferred.clear();
   for (auto &f : tasks) f();
   if (e != cudaSuccess) return fail(VKL_INTERNAL, "command_wait: %s", cudaGetErrorString(e));
+  if (cmd->err_used) {
+    uint32_t err = 0;
+    cmd->err_used = false;
+    VKL_CUDA(cudaMemcpy(&err, cmd->err_word, 4, cudaMemcpyDeviceToHost));
+    if (err) {
+      cudaMemset(cmd->err_word, 0, 4);
+      return fail(VKL_INTERNAL, "command_wait: a bounded wait inside a kernel ran out (code %u)", err);
+    }
+  }
   return VKL_OK;
 }
 int vkl_command_elapsed_us(vkl_command *cmd, float *usec) {

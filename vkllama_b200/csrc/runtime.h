@@ -67,6 +67,8 @@ struct Buffer {
   }
 };
 size_t dtype_elem_bytes(int dtype);
+// The command's device error word (allocated and zeroed on first use); wait() reports it.
+int command_error_word(vkl_command *cmd, uint32_t **out);
 }  // namespace vkl
 
 struct vkl_tensor {
@@ -95,6 +97,8 @@ struct vkl_command {
   bool submitted = false;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // recorded by begin() and end()
   std::vector<std::function<void()>> deferred;  // run by wait()
+  uint32_t *err_word = nullptr;  // device word raised by a kernel whose bounded wait ran out; read by wait()
+  bool err_used = false;
 };
 
 namespace vkl {
