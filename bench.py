@@ -32,6 +32,9 @@ WORKLOADS = {
                            prompt=32, decode=256, seed=20240602),
     "llama2-13b-q8_0": dict(dim=5120, heads=40, ffn=13824, vocab=32000, layers=40, maxlen=4096,
                             prompt=128, decode=512, seed=20240604),
+    # FP16 weights, 512-token prompt: the prefill runs on the tcgen05 tensor-core GEMMs (a parity/profiling case, not the headline)
+    "llama2-7b-f16": dict(dim=4096, heads=32, ffn=11008, vocab=32000, layers=32, maxlen=4096,
+                          prompt=512, decode=256, seed=20240603, weights="f16"),
     # 4 of the 32 blocks of the 7B shape: the small case for multi-pass ncu captures (1.2 GB on the device)
     "llama2-7b-q8_0-4blocks": dict(dim=4096, heads=32, ffn=11008, vocab=32000, layers=4, maxlen=4096,
                                    prompt=32, decode=16, seed=20240602),
@@ -45,9 +48,10 @@ def q8_bytes(rows, cols):
 def bytes_per_token(w, L, tp=1):
     """Algorithmic HBM bytes of one decode token at KV length L (after append), per GPU."""
     d, f, v, nl = w["dim"], w["ffn"], w["vocab"], w["layers"]
-    mats = nl * (4 * q8_bytes(d, d) + 3 * q8_bytes(f, d)) + q8_bytes(v, d)
+    wb = (lambda r, c: r * c * 2) if w.get("weights") == "f16" else q8_bytes
+    mats = nl * (4 * wb(d, d) + 3 * wb(f, d)) + wb(v, d)
     norms = (2 * nl + 1) * d * 4
-    emb = q8_bytes(1, d)
+    emb = wb(1, d)
     kv = 2 * d * 2  # K and V, fp16, all heads, per cached position
     return mats / tp + norms + emb + kv * (L + 1) / tp
 
@@ -60,6 +64,16 @@ def peak_hbm():
         except Exception:
             pass
     return 6650.0, "fallback"
+
+
+def peak_tensor():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -212,10 +226,44 @@ def run_micro(args):
                       "gpu_launches": int(vk.kernel_launches() - launches0), "results": rows}))
 
 
+def run_gemm(args):
+    """FP16 prefill GEMM microbenchmark through the MatMul op (MxNxK, weights [N,K]): achieved
+    TFLOP/s of the tcgen05 kernel against the measured dense-GEMM peak."""
+    import vkllama_b200 as vk
+    M, N, K = (int(v) for v in args.gemm.split("x"))
+    tpeak, tkind = peak_tensor()
+    dev = vk.Device(0)
+    cmd = vk.Command(dev)
+    a, wt = vk.Tensor(1, M, K, dev, vk.FP16), vk.Tensor(1, N, K, dev, vk.FP16)
+    op = vk.MatMul(dev, cmd, wt, 1.0, 0.0, 0, 0, True, vk.FP16, vk.FP16).init()
+    cmd.begin()
+    cmd.fill_synthetic(a, 20240606, 1, 0.0, 1.0)
+    cmd.fill_synthetic(wt, 20240606, 2, 0.0, 0.02)
+    for _ in range(max(args.warmup, 3)):
+        op(a)
+    cmd.end()
+    cmd.submit_and_wait()
+    launches0 = vk.kernel_launches()
+    cmd.begin()
+    for _ in range(args.steps):
+        op(a)
+    cmd.end()
+    cmd.submit_and_wait()
+    us = cmd.elapsed_us() / args.steps
+    tf = 2.0 * M * N * K / (us * 1e-6) / 1e12
+    print(json.dumps({"metric": "prefill_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "us_per_launch": us, "dtype": "fp16 x fp16 -> fp32 accumulate -> fp16",
+                      "config": {"workload": "gemm %dx%dx%d (rows x weight rows x K)" % (M, N, K)},
+                      "roofline": {"bound": "tensor", "kernel": "gemm_f16_tcgen05_kernel", "achieved": tf, "peak": tpeak,
+                                   "unit": "TFLOP/s", "frac": tf / tpeak, "peak_kind": tkind},
+                      "gpu_launches": int(vk.kernel_launches() - launches0)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--micro", default=None, help="'all' or ROWSxK: Q8_0 mat-vec microbenchmark instead of the token loop")
     ap.add_argument("--micro-tokens", default="1,2,4,8,16,64")
+    ap.add_argument("--gemm", default=None, help="MxNxK: FP16 tensor-core prefill GEMM microbenchmark instead of the token loop")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
@@ -237,6 +285,10 @@ def main():
         if rank == 0:
             run_micro(args)
         return 0
+    if args.gemm:
+        if rank == 0:
+            run_gemm(args)
+        return 0
 
     import vkllama_b200 as vk
     from oracle import oracle as O  # seeded prompt generator and cpu_baseline leg only
@@ -249,7 +301,9 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     dev = vk.Device(local_rank)
-    model = vk.Model(dev, w["dim"], w["heads"], w["ffn"], w["vocab"], w["layers"], w["maxlen"], tp_rank=rank, tp_size=tp)
+    f16w = w.get("weights") == "f16"
+    model = vk.Model(dev, w["dim"], w["heads"], w["ffn"], w["vocab"], w["layers"], w["maxlen"],
+                     weight_dtype=vk.FP16 if f16w else vk.Q8_0, tp_rank=rank, tp_size=tp)
     model.synth_weights(w["seed"])
     if tp > 1:
         from vkllama_b200 import tp as vtp
@@ -330,15 +384,15 @@ def main():
         kname = "decode_mega_kernel (persistent decode step: TMA weight ring + mma.sync consumers, all ops of a token)"
         k_bytes, k_us = bytes_tok, ms_tok * 1e3
     else:
-        kname = "mv_kernel (RMSNorm + gate/up Q8_0 mat-vec + SwiGLU)"
-        k_bytes = 2 * q8_bytes(w["ffn"] // tp, w["dim"]) + w["dim"] * 2 + w["dim"] * 4 + (w["ffn"] // tp) * 2
+        kname = "mv_kernel (RMSNorm + gate/up %s mat-vec + SwiGLU)" % ("FP16" if f16w else "Q8_0")
+        k_bytes = 2 * (w["ffn"] // tp * w["dim"] * 2 if f16w else q8_bytes(w["ffn"] // tp, w["dim"])) + w["dim"] * 2 + w["dim"] * 4 + (w["ffn"] // tp) * 2
         k_us = prof[4] / w["layers"]
     k_gbs = k_bytes / (k_us * 1e-6) / 1e9
     line = {
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": job_ms, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
-        "dtype": "q8_0 weights, fp16 activations, fp32 accumulate", "data": "synthetic",
+        "dtype": "%s weights, fp16 activations, fp32 accumulate" % ("fp16" if f16w else "q8_0"), "data": "synthetic",
         "config": {"workload": name, "batch": 1, "prompt_tokens": w["prompt"], "decode_tokens": w["decode"],
                    "kv_len": "%d..%d" % (w["prompt"] + 1, w["prompt"] + w["decode"]),
                    "parallelism": "tp%d" % world, "l2": "inputs (%.1f GB of weights per token) larger than L2" % (bytes_tok / 1e9),
@@ -360,7 +414,16 @@ def main():
                 "what": "vkl_model_forward per token: host id in, fp32 logits out, host arg-max"},
         "gpu_launches": int(launches), "clocks": clocks, "wall_s": wall,
     }
-    if not args.no_cpu_baseline and world == 1:
+    if f16w:
+        # dense prefill on the tensor cores: 2 flops per weight per prompt token (attention and the 1-row lm head left out)
+        d, f, nl = w["dim"], w["ffn"], w["layers"]
+        flops = 2.0 * w["prompt"] * nl * (4 * d * d + 3 * f * d)
+        tf = flops / (float(np.mean(pre_ms)) * 1e-3) / 1e12
+        tpeak, tkind = peak_tensor()
+        line["roofline_prefill"] = {"bound": "tensor", "what": "whole prefill pass (GEMMs + attention + norms) over projection flops",
+                                    "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak, "peak_kind": tkind,
+                                    "prefill_tokens_per_s": w["prompt"] / (float(np.mean(pre_ms)) * 1e-3)}
+    if not args.no_cpu_baseline and world == 1 and not f16w:
         v, cores, sample = cpu_port_tokens_per_s(w)
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
     print(json.dumps(line))

@@ -4,25 +4,38 @@
 // Replaces, for FP16 weights and many rows, the reference's matmul_b0_tb_fp16_v2.comp
 // (src/ops/mat_mul.cpp:71-82), which re-reads the whole weight matrix for every input row.
 //
-// One CTA computes a 128 x 128 output tile. Per 64-wide K block the four warps copy the
-// A and W tiles into shared memory in the 128-byte-swizzled K-major layout that the
-// tensor core's shared-memory descriptors address, one elected thread issues four
-// tcgen05.mma (M128 N128 K16, kind::f16) that accumulate into 128 TMEM columns, and
-// tcgen05.commit arrives on an mbarrier when the MMAs have consumed the stage, so the copy
-// of the next K block overlaps the math (two stages). The epilogue reads the accumulator
-// back with tcgen05.ld (each warp its 32 lanes), applies the op's rounding and writes fp16
-// (optionally after a residual add) or raw fp32. Every mbarrier wait is bounded; on a
-// time-out the kernel raises the error word, still frees its TMEM and returns.
+// One CTA computes a 128 x BN output tile (BN = 128 or 256) with three kinds of warps:
+//   warp 0    producer: one lane issues TMA tensor copies (cp.async.bulk.tensor.2d, 128-byte
+//             swizzle) of the A and W tiles of each 64-wide K block into a ring of shared-
+//             memory stages; the copies complete on the stage's "full" mbarrier.
+//   warp 1    MMA: allocates the TMEM accumulator (BN columns); one lane waits for a full
+//             stage and issues four tcgen05.mma (M128 N{BN} K16, kind::f16) on shared-memory
+//             descriptors; tcgen05.commit arrives on the stage's "empty" mbarrier when the
+//             tensor core has read the stage, and on "acc_ready" after the last K block.
+//   warps 2-5 epilogue: each reads its 32 TMEM lanes (= 32 output rows) with tcgen05.ld,
+//             applies the op's rounding (scale, bias, SiLU, residual add) and stores fp16 or
+//             raw fp32 rows with 128-bit stores.
+// Every mbarrier wait is bounded; on a time-out the kernel raises the error word, lets
+// copies in flight land, frees its TMEM and returns.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
 namespace vkl {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int STAGES = 2;
-constexpr uint32_t TILE_BYTES = BM * BK * 2;  // 16 KB per operand tile
+constexpr int BM = 128, BK = 64;
+constexpr uint32_t A_TILE_BYTES = BM * BK * 2;  // 16 KB
 constexpr uint32_t GEMM_WAIT_LIMIT = 1u << 22;
+constexpr int GEMM_THREADS = 192;
+
+template <int BN> struct Cfg {
+  static constexpr uint32_t B_TILE_BYTES = BN * BK * 2;
+  static constexpr uint32_t STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int STAGES = BN == 128 ? 6 : 4;  // 192 KB of stages either way
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
+};
 
 __device__ __forceinline__ uint32_t sa(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -55,122 +68,166 @@ __host__ __device__ constexpr uint32_t instr_desc(uint32_t m, uint32_t n) {
   return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-// Copies rows [row0, row0+128) x columns [k0, k0+64) of a row-major fp16 matrix (ld = K) into
-// the swizzled tile: 16-byte chunk c of row r lands at r*128 + ((c ^ (r & 7)) * 16).
-__device__ __forceinline__ void load_tile(unsigned char *tile, const __half *src, uint32_t rows, uint32_t row0, uint32_t K,
-                                          uint32_t k0) {
-  for (uint32_t i = threadIdx.x; i < BM * 8; i += blockDim.x) {
-    const uint32_t r = i >> 3, c = i & 7;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row0 + r < rows) v = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)(row0 + r) * K + k0) + c);
-    *reinterpret_cast<uint4 *>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = v;
-  }
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+               : "memory");
 }
 
-__global__ void __launch_bounds__(128, 1) gemm_f16_tcgen05_kernel(const GemmParams p) {
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // 1024-byte alignment for the swizzle atoms
-  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char *a_tiles = smem;                         // [STAGES][16 KB]
-  unsigned char *b_tiles = smem + STAGES * TILE_BYTES;   // [STAGES][16 KB]
-  __shared__ __align__(8) uint64_t stage_free[STAGES];   // arrives when the MMAs have read the stage
+template <int COLS> __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"((uint32_t)COLS) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+        "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+        "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  // swizzle atoms are 1024 bytes: align the stage ring
+  unsigned char *stages = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full[C::STAGES];   // TMA bytes of the stage have landed
+  __shared__ __align__(8) uint64_t empty[C::STAGES];  // the MMAs have read the stage
   __shared__ __align__(8) uint64_t acc_ready;
   __shared__ uint32_t tmem_base_s;
-  __shared__ uint32_t failed_s;
+  __shared__ volatile uint32_t failed_s;
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const uint32_t m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const uint32_t nkb = p.K / BK;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&stage_free[s])) : "memory");
+    for (int s = 0; s < C::STAGES; ++s) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&full[s])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&empty[s])) : "memory");
+    }
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&acc_ready)) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     failed_s = 0;
   }
-  if (warp == 0) {  // one warp allocates 128 TMEM columns (the fp32 accumulator of the tile)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sa(&tmem_base_s)), "r"(128u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
+  if (warp == 1) tmem_alloc<BN>(sa(&tmem_base_s));
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_acc = tmem_base_s;
 
-  const uint32_t nkb = p.K / BK;
-  constexpr uint32_t idesc = instr_desc(BM, BN);
-  for (uint32_t kb = 0; kb < nkb; ++kb) {
-    const uint32_t s = kb % STAGES;
-    if (kb >= STAGES) {  // the MMAs of k-block kb-STAGES must have finished reading this stage
-      if (!failed_s && !mbar_wait_bounded(sa(&stage_free[s]), ((kb / STAGES) - 1) & 1u)) failed_s = 1;
-    }
-    load_tile(a_tiles + s * TILE_BYTES, p.a, p.M, m0, p.K, kb * BK);
-    load_tile(b_tiles + s * TILE_BYTES, p.w, p.N, n0, p.K, kb * BK);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> tensor-core reads
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (threadIdx.x == 0 && !failed_s) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a_addr = sa(a_tiles + s * TILE_BYTES), b_addr = sa(b_tiles + s * TILE_BYTES);
-#pragma unroll
-      for (uint32_t k = 0; k < BK / 16; ++k) {
-        const uint64_t da = smem_desc(a_addr + k * 32), db = smem_desc(b_addr + k * 32);
-        const uint32_t accumulate = (kb | k) ? 1u : 0u;
-        asm volatile(
-            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_acc),
-            "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-            : "memory");
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      for (uint32_t kb = 0; kb < nkb; ++kb) {
+        const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
+        if (use > 0 && !mbar_wait_bounded(sa(&empty[s]), (use - 1) & 1u)) {
+          failed_s = 1;
+          break;
+        }
+        if (failed_s) break;
+        const uint32_t bar = sa(&full[s]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(C::STAGE_BYTES) : "memory");
+        unsigned char *st = stages + (size_t)s * C::STAGE_BYTES;
+        tma_load_2d(sa(st), &map_a, kb * BK, m0, bar);
+        tma_load_2d(sa(st + A_TILE_BYTES), &map_w, kb * BK, n0, bar);
       }
-      // arrives on the barrier once every MMA issued so far has completed
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sa(&stage_free[s])) : "memory");
-      if (kb + 1 == nkb)
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sa(&acc_ready)) : "memory");
     }
-  }
-  __syncthreads();
-  if (!failed_s && nkb > 0 && !mbar_wait_bounded(sa(&acc_ready), 0)) failed_s = 1;
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-
-  if (!failed_s) {
-    // ---- epilogue: warp w owns TMEM lanes 32w..32w+31 = output rows m0 + 32w + lane
-    const uint32_t row = m0 + warp * 32 + lane;
-#pragma unroll 1
-    for (uint32_t cc = 0; cc < BN; cc += 32) {
-      uint32_t r[32];
-      const uint32_t taddr = tmem_acc + ((warp * 32u) << 16) + cc;
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-          "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-            "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-            "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-            "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-          : "r"(taddr)
-          : "memory");
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (row < p.M) {
+  } else if (warp == 1) {
+    // --------------------------------------------------------------------- MMA
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BM, BN);
+      for (uint32_t kb = 0; kb < nkb; ++kb) {
+        const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
+        if (!mbar_wait_bounded(sa(&full[s]), use & 1u)) {
+          failed_s = 2;
+          break;
+        }
+        if (failed_s) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = sa(stages + (size_t)s * C::STAGE_BYTES), b_addr = a_addr + A_TILE_BYTES;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const uint32_t n = n0 + cc + j;
-          if (n >= p.N) break;
-          float v = __uint_as_float(r[j]) * p.scale + p.bias;
-          if (p.act == 1) v = v / (1.0f + expf(-v));
-          const size_t o = (size_t)row * p.N + n;
-          if (p.c_f32) {
-            p.c_f32[o] = v;
-          } else if (p.residual) {
-            p.c[o] = __float2half_rn(round_h(v) + __half2float(p.residual[o]));
-          } else {
-            p.c[o] = __float2half_rn(v);
+        for (uint32_t k = 0; k < BK / 16; ++k) {
+          const uint64_t da = smem_desc(a_addr + k * 32), db = smem_desc(b_addr + k * 32);
+          const uint32_t accumulate = (kb | k) ? 1u : 0u;
+          asm volatile(
+              "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_acc),
+              "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+              : "memory");
+        }
+        // arrives once every MMA issued so far has completed (implies fence::before_thread_sync)
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sa(&empty[s])) : "memory");
+        if (kb + 1 == nkb)
+          asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sa(&acc_ready)) : "memory");
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    // a warp may only touch TMEM lanes 32*(warp % 4) .. +31
+    const uint32_t quad = warp & 3u;
+    const uint32_t row = m0 + quad * 32 + lane;
+    uint32_t ok = 1;
+    if (lane == 0) ok = mbar_wait_bounded(sa(&acc_ready), 0) ? 1u : 0u;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) {
+      if (lane == 0) failed_s = 3;
+    } else if (!failed_s) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+      for (uint32_t cc = 0; cc < (uint32_t)BN; cc += 32) {
+        if (n0 + cc >= p.N) break;  // uniform over the warp
+        uint32_t r[32];
+        tmem_ld32(tmem_acc + ((quad * 32u) << 16) + cc, r);
+        if (row < p.M) {
+          const size_t o = (size_t)row * p.N + n0 + cc;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (n0 + cc + j >= p.N) break;  // N is a multiple of 8
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              v[i] = __uint_as_float(r[j + i]) * p.scale + p.bias;
+              if (p.act == 1) v[i] = v[i] / (1.0f + expf(-v[i]));
+            }
+            if (p.c_f32) {
+              *reinterpret_cast<float4 *>(p.c_f32 + o + j) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4 *>(p.c_f32 + o + j + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+              union {
+                uint4 u;
+                __half h[8];
+              } out, res;
+              if (p.residual) {
+                res.u = *reinterpret_cast<const uint4 *>(p.residual + o + j);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) out.h[i] = __float2half_rn(round_h(v[i]) + __half2float(res.h[i]));
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) out.h[i] = __float2half_rn(v[i]);
+              }
+              *reinterpret_cast<uint4 *>(p.c + o + j) = out.u;
+            }
           }
         }
       }
     }
-  } else if (threadIdx.x == 0 && p.error) {
-    atomicExch(p.error, 1u);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(128u) : "memory");
+  if (failed_s) {
+    if (threadIdx.x == 0 && p.error) atomicExch(p.error, failed_s);
+    // let tensor copies that are still in flight land before the shared memory is given back
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+    __syncthreads();
+  }
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
 }
 
 // y <- fp16( silu(gate) * up ) on fp32 inputs: the epilogue of ffn_up_and_gate_fp16.comp.
@@ -181,17 +238,53 @@ __global__ void swiglu_f32_kernel(const float *__restrict__ gate, const float *_
   out[i] = __float2half_rn(g / (1.0f + expf(-g)) * up[i]);
 }
 
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                 const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = [] {
+    void *f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) f = nullptr;
+    return reinterpret_cast<EncodeTiled>(f);
+  }();
+  return fn;
+}
+
+// Tensor map over a row-major fp16 matrix [rows, K]: boxes of 64 columns x box_rows rows,
+// 128-byte swizzle, rows beyond the matrix read as zero.
+bool make_map(CUtensorMap *map, const __half *base, uint32_t rows, uint32_t K, uint32_t box_rows) {
+  EncodeTiled enc = encode_tiled();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {K, rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {BK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN> cudaError_t launch_bn(const GemmParams &p, cudaStream_t s) {
+  CUtensorMap ma, mw;
+  if (!make_map(&ma, p.a, p.M, p.K, BM) || !make_map(&mw, p.w, p.N, p.K, BN)) return cudaErrorInvalidValue;
+  cudaError_t e = cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::SMEM);
+  if (e != cudaSuccess) return e;
+  // x = row tile, so that the CTAs sharing one tile of W run together and W crosses HBM once
+  gemm_f16_tcgen05_kernel<BN><<<dim3((p.M + BM - 1) / BM, (p.N + BN - 1) / BN), GEMM_THREADS, Cfg<BN>::SMEM, s>>>(ma, mw, p);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 bool gemm_tcgen05_supported(uint32_t M, uint32_t N, uint32_t K) { return M >= 1 && K % BK == 0 && K >= BK && (N % 8) == 0; }
 
 cudaError_t launch_gemm_f16_tcgen05(const GemmParams &p, cudaStream_t s) {
   if (!gemm_tcgen05_supported(p.M, p.N, p.K)) return cudaErrorInvalidValue;
-  const size_t smem = 2 * STAGES * TILE_BYTES + 1024;
-  cudaError_t e = cudaFuncSetAttribute(gemm_f16_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
-  gemm_f16_tcgen05_kernel<<<dim3((p.N + BN - 1) / BN, (p.M + BM - 1) / BM), 128, smem, s>>>(p);
-  return cudaGetLastError();
+  if ((reinterpret_cast<uintptr_t>(p.a) | reinterpret_cast<uintptr_t>(p.w)) & 15) return cudaErrorMisalignedAddress;
+  // 128 x 256 tiles halve the shared-memory reads per flop; use them once they still fill the GPU
+  const size_t tiles256 = (size_t)((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
+  if (tiles256 >= 148) return launch_bn<256>(p, s);
+  return launch_bn<128>(p, s);
 }
 
 cudaError_t launch_swiglu_f32(const float *gate, const float *up, __half *out, size_t n, cudaStream_t s) {
