@@ -10,11 +10,13 @@
 //     (cp.async.bulk + mbarrier) into a shared-memory ring. Weights never depend
 //     on activations, so the producer runs ahead across op boundaries and HBM
 //     stays busy while the consumers sit in a grid barrier, a norm or attention;
-//   * eight consumer warps take ring stages (8 groups of 4 Q8_0 blocks x 16 rows),
-//     convert codes to fp16 exactly, multiply on the tensor cores (m16n8k16, fp32
-//     accumulate), apply block scales in fp32, reduce across warps in fixed order
-//     and run the fused epilogue (RMSNorm prologue, residual add, SwiGLU, fp32
-//     logits, running arg-max);
+//   * fifteen consumer warps take one group (4 Q8_0 blocks x 16 rows) of every ring
+//     stage each, convert codes to fp16 exactly, multiply on the tensor cores
+//     (m16n8k16, fp32 accumulate), apply block scales in fp32, reduce across warps
+//     in fixed order and run the fused epilogue (RMSNorm prologue, residual add,
+//     SwiGLU, fp32 logits, running arg-max). An int8 tensor-core variant (m16n8k32
+//     on three exact byte slices of the input) was measured 30 % slower: the legacy
+//     int8 mma.sync path is slow on this GPU;
 //   * ops are separated by a grid barrier (one atomic counter, bounded spin).
 //
 // Tiles of op i go to CTA (tile + rot_i) mod grid; rot_i advances by the op's
@@ -32,12 +34,11 @@ namespace {
 constexpr int NCW = 15;                // consumer warps (+1 producer warp = 512 threads, 128 registers each)
 constexpr int CT = NCW * 32;           // consumer threads
 constexpr int THREADS = CT + 32;       // + producer warp
-constexpr int SG = 16;                 // 4-block groups per ring stage; owners rotate over the warps
+constexpr int SG = (int)MEGA_SG;       // 4-block groups per ring stage: one per consumer warp
 constexpr uint32_t STAGE_CODES = SG * 2048, STAGE_SCALES = SG * 128;
-constexpr uint32_t STAGE_BYTES = STAGE_CODES + STAGE_SCALES;  // 17408
-constexpr int NST = 5;                 // ring stages (170 KB)
+constexpr uint32_t STAGE_BYTES = STAGE_CODES + STAGE_SCALES;  // 32640
+constexpr int MAX_NST = 6;             // ring stages are a launch parameter (whatever fits), at most this many
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
-constexpr int RED_SLOTS = 20;          // (tiles of one CTA) x (matrices) an op may have
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t a, uint32_t n) {
@@ -79,12 +80,6 @@ __device__ __forceinline__ uint64_t ld_acq_u64(const unsigned long long *p) {
   return v;
 }
 
-// Default: codes are converted to signed fp16 exactly (one subtract per pair). The
-// optional "bias trick" multiplies the raw pairs (1024+u) and removes the bias afterwards
-// with the per-block sum of the input, sum_k (1152 + q_k) x_k = sum_k q_k x_k + 1152 *
-// sum_k x_k: 8 fewer instructions per block, but the large common term costs accumulator
-// precision (about 1e-5 relative per block) and the extra fp16 rounding flips were enough
-// to break greedy-id parity on the 7B model, so it is off unless asked for.
 __device__ __forceinline__ bool getenv_prologue(const MegaParams &p) { return (p.timing_mode & 1u) != 0; }
 
 struct Ctx {
@@ -96,10 +91,11 @@ struct Ctx {
     atomicCAS(p.error, 0u, code);
   }
   // Bounded mbarrier wait; false (and the abort flag set) on time-out.
-  __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, uint32_t code) const {
+  __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, uint32_t code, uint32_t sleep_ns = 0) const {
     if (mbar_try(bar, parity)) return !aborted();  // fast path: the phase is already complete
     if (aborted()) return false;
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+      if (sleep_ns) __nanosleep(sleep_ns);  // keep a waiting warp off the shared-memory pipe the working warps need
       if (mbar_try(bar, parity)) return true;
       if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || aborted())) {
         *abort_s = 1;
@@ -111,28 +107,20 @@ struct Ctx {
   }
 };
 
-// First tile of this CTA for an op and the walk over (tile, matrix, stage).
-__device__ __forceinline__ uint32_t first_tile(const MegaOp &op, uint32_t cta, uint32_t G) {
-  return (cta + G - (op.rot % G)) % G;
-}
-
 // ------------------------------------------------------------------ producer
 // The producer warp walks this CTA's precomputed stage table (one entry per ring
 // stage of the whole token, in consumer order). Lane 0 keeps the shared-memory ring
-// full with bulk copies and, `l2_lookahead` stages further on, asks L2 for the codes
-// of later stages (cp.async.bulk.prefetch.L2): while the ring is full because the
-// consumers sit in a barrier, a norm or attention, HBM keeps streaming into L2 and the
-// ring is refilled from there afterwards. The other lanes only fetch table chunks.
+// full with bulk copies; the other lanes only fetch table chunks.
 __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint64_t *full, uint64_t *empty,
                                          MegaStage *tabs /* [64] in shared memory */) {
   const MegaParams &p = c.p;
   const uint32_t lane = threadIdx.x & 31;
   const MegaStage *table = p.stages + (size_t)blockIdx.x * p.stage_stride;
   const uint32_t n = p.stage_count[blockIdx.x];
-  const uint32_t LA = min(p.l2_lookahead, 32u);
+  const uint32_t NST = p.nst;
   if (lane < min(n, 32u)) tabs[lane] = table[lane];
   __syncwarp();
-  uint32_t it = 0;
+  uint32_t it = 0, slot = 0, ph = 0;
   bool stop = false;
   for (uint32_t base = 0; base < n && !stop; base += 32) {
     // chunk base/32 is in tabs[(base/32 % 2)*32 ..]; fetch the next one beside it
@@ -141,13 +129,7 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
     if (lane == 0) {
       const uint32_t end = min(base + 32, n);
       for (; it < end; ++it) {
-        if (LA && it + LA < n) {
-          const MegaStage &f = tabs[(it + LA) & 63];
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(f.codes)), "r"(f.ng * 2048u)
-                       : "memory");
-        }
-        const uint32_t slot = it % NST, ph = (it / NST) & 1u;
-        if (it >= NST && !c.wait(s32(&empty[slot]), ph ^ 1u, 2)) {
+        if (it >= NST && !c.wait(s32(&empty[slot]), ph ^ 1u, 2, p.producer_sleep_ns)) {
           stop = true;
           break;
         }
@@ -155,11 +137,21 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
         const uint32_t fb = s32(&full[slot]);
         if (p.timing_mode & 2u) {  // diagnostic: consumer speed without the weight stream
           mbar_arrive(fb);
-          continue;
+        } else {
+          const uint32_t n0 = e.n0, n1 = e.n1;
+          const uint32_t dst = s32(ring + (size_t)slot * STAGE_BYTES);
+          mbar_expect(fb, (n0 + n1) * (2048u + 128u));
+          bulk_g2s(dst, e.codes0, n0 * 2048u, fb);
+          bulk_g2s(dst + STAGE_CODES, e.scales0, n0 * 128u, fb);
+          if (n1) {
+            bulk_g2s(dst + n0 * 2048u, e.codes1, n1 * 2048u, fb);
+            bulk_g2s(dst + STAGE_CODES + n0 * 128u, e.scales1, n1 * 128u, fb);
+          }
         }
-        mbar_expect(fb, e.ng * (2048u + 128u));
-        bulk_g2s(s32(ring + (size_t)slot * STAGE_BYTES), e.codes, e.ng * 2048u, fb);
-        bulk_g2s(s32(ring + (size_t)slot * STAGE_BYTES + STAGE_CODES), e.scales, e.ng * 128u, fb);
+        if (++slot == NST) {
+          slot = 0;
+          ph ^= 1u;
+        }
       }
     }
     stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
@@ -167,10 +159,10 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
   it = __shfl_sync(0xffffffffu, it, 0);
   // Nothing may still be landing in this CTA's shared memory when it exits.
   if (lane == 0) {
-    const uint32_t lo = it > (uint32_t)NST ? it - NST : 0;
+    const uint32_t lo = it > NST ? it - NST : 0;
     for (uint32_t j = lo; j < it; ++j) {
-      const uint32_t fb = s32(&full[j % NST]), ph = (j / NST) & 1u;
-      for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(fb, ph); ++i) {
+      const uint32_t fb = s32(&full[j % NST]), ph2 = (j / NST) & 1u;
+      for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(fb, ph2); ++i) {
       }
     }
   }
@@ -212,10 +204,14 @@ __device__ __forceinline__ bool better(float v, uint32_t i, const Best &b) {
   return b.i == 0xffffffffu || v > b.v || (v == b.v && i < b.i);
 }
 
-template <bool EXACT>
-__device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global, uint32_t &it, unsigned char *ring, uint64_t *full,
-                          uint64_t *empty, __half *xs, float *red, float *ssum, float *xsum, const __half *zero16, Best &best,
-                          unsigned long long *tw, uint32_t ar_parity) {
+// Two stored codes (bytes 0 and 2, or 1 and 3, of a plane word) as a pair of fp16 subnormals u * 2^-24.
+__device__ __forceinline__ uint32_t codes_sub_h2(uint32_t w, bool hi) { return __byte_perm(w, 0u, hi ? 0x4341u : 0x4240u); }
+
+// One mat-vec op of the token: y[N] = W[N,K] . x[K] for up to three matrices that share x.
+template <bool TIMED>
+__device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global, uint32_t &it, uint32_t &slot, uint32_t &ph,
+                                          unsigned char *ring, uint64_t *full, uint64_t *empty, __half *xs, float *xbias, const __half *zero16,
+                                          float *red, float *ssum, Best &best, unsigned long long *tw, uint32_t ar_parity) {
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t G = gridDim.x, cta = blockIdx.x;
   // Scalars in registers: the barriers' memory clobbers would otherwise make every use
@@ -233,15 +229,17 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   op.norm_w = op_global.norm_w; op.eps = op_global.eps; op.in = op_global.in;
   op.out[0] = op_global.out[0]; op.out[1] = op_global.out[1]; op.out[2] = op_global.out[2];
   op.out_f32 = op_global.out_f32;
-  const uint32_t K = op.K, kpad = op.groups * 128;
+  const uint32_t K = op.K, groups = op.groups, nmat = op.nmat, tiles = op.tiles, NST = c.p.nst;
+  const uint32_t tile0 = (cta + G - (op.rot % G)) % G;
+  const uint32_t tl = tile0 < tiles ? (tiles - tile0 + G - 1) / G : 0u;  // this CTA's tiles
+  const uint32_t ntm = tl * nmat;                                        // (tile, matrix) row blocks of this CTA
   // ---- input vector -> shared memory (RMSNorm fused, rounded to fp16 where the
-  // reference's RMSNorm op rounds: rms_norm_fp16.comp:70-77), plus 1152 * (sum of
-  // the 32 inputs of every block) for the bias removal. Norm weights and input are
+  // reference's RMSNorm op rounds: rms_norm_fp16.comp:70-77). Norm weights and input are
   // requested together: one memory round trip.
   {
     constexpr int MAXV = (2048 + CT - 1) / CT;  // 8-half vectors per thread: K <= 16384
     uint4 v[MAXV];
-    const uint32_t nv = K / 8;
+    const uint32_t nv = K / 8, kpad = groups * 128;
     const bool norm = op.norm_w != nullptr;
 #pragma unroll
     for (int j = 0; j < MAXV; ++j) {
@@ -249,14 +247,9 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
       v[j] = make_uint4(0, 0, 0, 0);
       if (i < nv) v[j] = __ldcg(reinterpret_cast<const uint4 *>(op.in) + i);
     }
+    for (uint32_t i = tid; i < ntm * NCW * 16; i += CT) red[i] = 0.f;  // warps that get no group of a row block leave zeros
     float alpha = 1.f;
     if (norm) {
-      // the norm weights are not needed before alpha: start them towards L2/L1 now
-#pragma unroll
-      for (int j = 0; j < MAXV; ++j) {
-        const uint32_t i = tid + j * CT;
-        if (i < nv) asm volatile("prefetch.global.L2 [%0];" ::"l"(op.norm_w + 8 * i));
-      }
       float s = 0.f;
 #pragma unroll
       for (int j = 0; j < MAXV; ++j) {
@@ -304,105 +297,96 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
       // a block of 32 inputs = 4 consecutive vectors = 4 consecutive lanes
       bs += __shfl_xor_sync(0xffffffffu, bs, 1);
       bs += __shfl_xor_sync(0xffffffffu, bs, 2);
-      if ((lane & 3) == 0 && i < nv) xsum[i >> 2] = 1152.0f * bs;
+      if ((lane & 3) == 0 && i < nv) xbias[i >> 2] = 128.0f * bs;
     }
     for (uint32_t i = K + tid; i < kpad; i += CT) xs[i] = __ushort_as_half(0);
-    for (uint32_t b = K / 32 + tid; b < kpad / 32; b += CT) xsum[b] = 0.f;
+    for (uint32_t b = K / 32 + tid; b < kpad / 32; b += CT) xbias[b] = 0.f;
     cons_sync();
   }
-  if (tw) tw[1] = clock64();
+  if (TIMED && tw) tw[1] = clock64();
 
-  // ---- stream this CTA's tiles. A warp owns one group (4 blocks x 16 rows) of every
-  // stage; its partial sums of a (tile, matrix) go to the warp's own slot in shared
-  // memory, so nothing synchronises until the op's single reduction at the end.
-  const uint32_t nstg = (op.groups + SG - 1) / SG;
-  const uint32_t groups = op.groups, nmat = op.nmat, tiles = op.tiles;
-  const uint32_t tile0 = (cta + G - (op.rot % G)) % G;
-  const uint32_t xstep = g == 0 ? 32u : 0u;  // token 0 is column 0 of B: other columns read zeros
-  uint32_t tl = 0;                           // local tile counter
-  uint32_t slot = it % NST, ph = (it / NST) & 1u, rotc = it % NCW;  // kept incrementally
-  for (uint32_t tile = tile0; tile < tiles; tile += G, ++tl) {
-    for (uint32_t m = 0; m < nmat; ++m) {
-      float a0 = 0.f, a1 = 0.f;
-      for (uint32_t s = 0; s < nstg; ++s, ++it) {
-        unsigned long long w0 = 0, w1 = 0;
-        if (tw) w0 = clock64();
-        const bool ok = c.wait(s32(&full[slot]), ph, 1);
-        if (tw) {
-          w1 = clock64();
-          tw[0] += (w1 - w0) * 1000ull / 1965ull;  // SM cycles -> ns at the 1965 MHz boost clock
-        }
-        const uint32_t ng = min((uint32_t)SG, groups - s * SG);
-        const unsigned char *st = ring + (size_t)slot * STAGE_BYTES;
-        // Groups of a stage go to warps round-robin, starting one warp later every stage,
-        // so the warp that takes two of the 16 groups rotates.
-        uint32_t gi = warp >= rotc ? warp - rotc : warp + NCW - rotc;
-        for (;;) {
-          const bool have = ok && gi < ng;
-          const bool last = !(ok && gi + NCW < ng);
-          uint4 cw[4], sv;
-          if (have) {
+  // ---- stream this CTA's row blocks. Every stage holds one group (4 blocks x 16 rows) per
+  // consumer warp; stages run on across (tile, matrix) boundaries, so a warp's partial sums
+  // of a row block go to the warp's own slot in shared memory when its groups move on to the
+  // next row block, and nothing synchronises until the op's single reduction at the end.
+  {
+    uint32_t tm = 0, kg = 0, cur = 0xffffffffu;
+    float a0 = 0.f, a1 = 0.f;
+    while (tm < ntm) {
+      const MegaCut cut = mega_stage_cut(kg, groups, tm + 1 < ntm);
+      unsigned long long w0 = 0;
+      if (TIMED && tw) w0 = clock64();
+      const bool ok = c.wait(s32(&full[slot]), ph, 1, c.p.consumer_sleep_ns);
+      if (TIMED && tw) tw[0] += (clock64() - w0) * 1000ull / 1965ull;  // SM cycles -> ns at the 1965 MHz boost clock
+      const bool have = ok && warp < cut.n0 + cut.n1;
+      const uint32_t mt = warp < cut.n0 ? tm : tm + 1, mk = warp < cut.n0 ? kg + warp : warp - cut.n0;
+      const unsigned char *st = ring + (size_t)slot * STAGE_BYTES;
+      uint4 cw[4], sv;
+      if (have) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) cw[j] = *reinterpret_cast<const uint4 *>(st + (gi * 4 + j) * 512 + lane * 16);
-            sv = *reinterpret_cast<const uint4 *>(st + STAGE_CODES + gi * 128 + g * 16);
+        for (int j = 0; j < 4; ++j) cw[j] = *reinterpret_cast<const uint4 *>(st + (warp * 4 + j) * 512 + lane * 16);
+        sv = *reinterpret_cast<const uint4 *>(st + STAGE_CODES + warp * 128 + g * 16);
+      }
+      __syncwarp();
+      if (lane == 0 && ok) mbar_arrive(s32(&empty[slot]));  // this warp has read all it needs from the stage
+      if (have) {
+        if (mt != cur) {
+          if (cur != 0xffffffffu && t == 0) {  // lanes t == 0 hold column 0 = token 0: rows g and g+8
+            float *slotp = red + ((size_t)cur * NCW + warp) * 16;
+            slotp[g] = a0;
+            slotp[g + 8] = a1;
           }
-          if (last) {  // this warp has read all it needs from the stage: release it
-            __syncwarp();
-            if (lane == 0 && ok) mbar_arrive(s32(&empty[slot]));
-          }
-          if (have && (c.p.timing_mode & 4u)) {  // diagnostic: ring traffic without arithmetic
-            a0 += __uint_as_float(cw[0].x ^ cw[1].y ^ cw[2].z ^ cw[3].w ^ sv.x);
-          } else if (have) {
-            const uint32_t blk0 = (s * SG + gi) * 4;
-            const __half *xp = g == 0 ? xs + blk0 * 32 + t * 8 : zero16;
-            const float2 da = __half22float2(*reinterpret_cast<const __half2 *>(&sv.x));
-            const float2 db = __half22float2(*reinterpret_cast<const __half2 *>(&sv.y));
-            const float2 ea = __half22float2(*reinterpret_cast<const __half2 *>(&sv.z));
-            const float2 eb = __half22float2(*reinterpret_cast<const __half2 *>(&sv.w));
-            const float dgs[4] = {da.x, da.y, db.x, db.y}, dg8s[4] = {ea.x, ea.y, eb.x, eb.y};
-            const float4 bias4 = *reinterpret_cast<const float4 *>(xsum + blk0);
-            const float biases[4] = {bias4.x, bias4.y, bias4.z, bias4.w};
+          cur = mt;
+          a0 = a1 = 0.f;
+        }
+        if (TIMED && (c.p.timing_mode & 4u)) {  // diagnostic: ring traffic without arithmetic
+          a0 += __uint_as_float(cw[0].x ^ cw[1].y ^ cw[2].z ^ cw[3].w ^ sv.x);
+        } else {
+          // The stored codes u = q + 128 go into the MMA as fp16 subnormals u * 2^-24 (one byte
+          // permute per pair, no arithmetic): products and their fp32 sums are exact up to the
+          // accumulator's rounding, and sum_k u_k x_k = sum_k q_k x_k + 128 * sum_k x_k, so the
+          // block result is 2^24 * acc - 128 * sum(x of the block). Token 0 is column 0 of B,
+          // the other columns read zeros.
+          const __half *xp = g == 0 ? xs + mk * 128 + t * 8 : zero16;
+          const uint32_t xstep = g == 0 ? 32u : 0u;
+          const float4 xb4 = *reinterpret_cast<const float4 *>(xbias + mk * 4);
+          const float xb[4] = {xb4.x, xb4.y, xb4.z, xb4.w};
+          const float2 da = __half22float2(*reinterpret_cast<const __half2 *>(&sv.x));
+          const float2 db = __half22float2(*reinterpret_cast<const __half2 *>(&sv.y));
+          const float2 ea = __half22float2(*reinterpret_cast<const __half2 *>(&sv.z));
+          const float2 eb = __half22float2(*reinterpret_cast<const __half2 *>(&sv.w));
+          const float dgs[4] = {da.x, da.y, db.x, db.y}, dg8s[4] = {ea.x, ea.y, eb.x, eb.y};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 X = *reinterpret_cast<const uint4 *>(xp + j * xstep);
-              float cacc[4] = {0.f, 0.f, 0.f, 0.f};
-              if (EXACT) {  // signed codes as fp16, exact products, fp32 accumulation
-                mma16816(cacc, codes_to_h2(cw[j].x, false), codes_to_h2(cw[j].z, false), codes_to_h2(cw[j].x, true),
-                         codes_to_h2(cw[j].z, true), X.x, X.y);
-                mma16816(cacc, codes_to_h2(cw[j].y, false), codes_to_h2(cw[j].w, false), codes_to_h2(cw[j].y, true),
-                         codes_to_h2(cw[j].w, true), X.z, X.w);
-              } else {
-                mma16816(cacc, codes_raw_h2(cw[j].x, false), codes_raw_h2(cw[j].z, false), codes_raw_h2(cw[j].x, true),
-                         codes_raw_h2(cw[j].z, true), X.x, X.y);
-                mma16816(cacc, codes_raw_h2(cw[j].y, false), codes_raw_h2(cw[j].w, false), codes_raw_h2(cw[j].y, true),
-                         codes_raw_h2(cw[j].w, true), X.z, X.w);
-              }
-              a0 = fmaf(cacc[0], dgs[j], a0);
-              a1 = fmaf(cacc[2], dg8s[j], a1);
-            }
-            if (!EXACT) {  // remove the +128 code bias of the four blocks: sum_j d_j * 1152 * sum(x_j)
-              a0 -= biases[0] * dgs[0] + biases[1] * dgs[1] + biases[2] * dgs[2] + biases[3] * dgs[3];
-              a1 -= biases[0] * dg8s[0] + biases[1] * dg8s[1] + biases[2] * dg8s[2] + biases[3] * dg8s[3];
-            }
+          for (int j = 0; j < 4; ++j) {
+            const uint4 X = *reinterpret_cast<const uint4 *>(xp + j * xstep);
+            float cacc[4] = {0.f, 0.f, 0.f, 0.f};
+            mma16816(cacc, codes_sub_h2(cw[j].x, false), codes_sub_h2(cw[j].z, false), codes_sub_h2(cw[j].x, true), codes_sub_h2(cw[j].z, true),
+                     X.x, X.y);
+            mma16816(cacc, codes_sub_h2(cw[j].y, false), codes_sub_h2(cw[j].w, false), codes_sub_h2(cw[j].y, true), codes_sub_h2(cw[j].w, true),
+                     X.z, X.w);
+            a0 = fmaf(fmaf(cacc[0], 16777216.f, -xb[j]), dgs[j], a0);
+            a1 = fmaf(fmaf(cacc[2], 16777216.f, -xb[j]), dg8s[j], a1);
           }
-          if (last) break;
-          gi += NCW;
         }
-        if (++slot == NST) {
-          slot = 0;
-          ph ^= 1u;
-        }
-        if (++rotc == NCW) rotc = 0;
       }
-      if (t == 0) {  // lanes t == 0 hold column 0 = token 0: rows g and g+8
-        float *slotp = red + ((size_t)(tl * nmat + m) * NCW + warp) * 16;
-        slotp[g] = a0;
-        slotp[g + 8] = a1;
+      mega_stage_advance(cut, groups, tm, kg);
+      ++it;
+      if (++slot == NST) {
+        slot = 0;
+        ph ^= 1u;
       }
+    }
+    if (cur != 0xffffffffu && t == 0) {
+      float *slotp = red + ((size_t)cur * NCW + warp) * 16;
+      slotp[g] = a0;
+      slotp[g + 8] = a1;
     }
   }
   // ---- one fixed-order reduction over the warps and the epilogue for all tiles
-  if (tw) tw[2] = clock64();
+  if (TIMED && tw) {
+    tw[2] = clock64();
+    if (c.p.timing_mode & 32u) tw[0] = (((tw[2] - tw[1]) * 1000ull / 1965ull) << 16) | (uint64_t)min(ntm * ((groups + SG - 1) / SG), 65535u);
+  }
   cons_sync();
   for (uint32_t idx = tid; idx < tl * 16; idx += CT) {
     const uint32_t lt = idx >> 4, r = idx & 15;
@@ -743,27 +727,27 @@ __device__ __forceinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uin
   }
 }
 
-template <bool TIMED, bool EXACT>
+template <bool TIMED>
 __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t NST = p.nst;
   unsigned char *ring = smem;
-  __half *xs = reinterpret_cast<__half *>(smem + (size_t)NST * STAGE_BYTES);
-  float *red = reinterpret_cast<float *>(smem + (size_t)NST * STAGE_BYTES + p.xs_bytes);
-  float *ssum = red + RED_SLOTS * NCW * 16;
-  float *xsum = ssum + 32;  // [512]
-  __half *zero16 = reinterpret_cast<__half *>(xsum + 512);  // 16 zero bytes
-  MegaStage *tabs = reinterpret_cast<MegaStage *>(xsum + 512 + 4);  // [64], 16-byte aligned
+  unsigned char *xq = smem + (size_t)NST * STAGE_BYTES;  // quantised input vector; attention scratch
+  float *red = reinterpret_cast<float *>(xq + p.xs_bytes);
+  float *ssum = red + (size_t)p.red_slots * NCW * 16;  // [32]
+  const __half *zero16 = reinterpret_cast<const __half *>(ssum + 32);  // 16 zero bytes
+  MegaStage *tabs = reinterpret_cast<MegaStage *>(ssum + 36);  // [64], 16-byte aligned
   uint64_t *full = reinterpret_cast<uint64_t *>(tabs + 64);
-  uint64_t *empty = full + NST;
-  volatile uint32_t *abort_s = reinterpret_cast<volatile uint32_t *>(empty + NST);
+  uint64_t *empty = full + MAX_NST;
+  volatile uint32_t *abort_s = reinterpret_cast<volatile uint32_t *>(empty + MAX_NST);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NST; ++i) {
+    for (uint32_t i = 0; i < NST; ++i) {
       mbar_init(s32(&full[i]), 1);
       mbar_init(s32(&empty[i]), NCW);
     }
     *abort_s = 0;
-    *reinterpret_cast<uint4 *>(zero16) = make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4 *>(ssum + 32) = make_uint4(0, 0, 0, 0);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -783,7 +767,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
   uint32_t ar_i = 0;
   const uint32_t Lnow = min(pos0 + 1, p.maxlen);
   const uint32_t S_eff = Lnow <= p.single_split_len ? 1u : p.splits;
-  uint32_t it = 0;
+  uint32_t it = 0, slot = 0, ph = 0;  // ring position, carried across the ops of the token
   Best best = {0.f, 0xffffffffu};
   const bool timed = TIMED && p.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
   unsigned long long t0 = 0, twait[3] = {0, 0, 0}, c0 = 0;
@@ -794,15 +778,15 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
     if (timed) c0 = clock64();
     switch (op.kind) {
       case MK_EMBED: embed_op(c, tok); break;
-      case MK_MATVEC: matvec_op<EXACT>(c, op, it, ring, full, empty, xs, red, ssum, xsum, zero16, best, (TIMED && timed) ? twait : nullptr, (seq0 + ar_i + 1) & 1u); break;
-      case MK_ATTN_PART: attn_part_op(c, op, reinterpret_cast<float *>(xs), pos0, S_eff); break;
+      case MK_MATVEC: matvec_op<TIMED>(c, op, it, slot, ph, ring, full, empty, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_groups * 256), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, (seq0 + ar_i + 1) & 1u); break;
+      case MK_ATTN_PART: attn_part_op(c, op, reinterpret_cast<float *>(xq), pos0, S_eff); break;
       case MK_ATTN_COMBINE: attn_combine_op(c, pos0); break;
       case MK_ALLREDUCE:
         ++ar_i;
         allreduce_op(c, op, seq0 + ar_i);
         break;
       case MK_ARGMAX:
-        argmax_final_op(c, reinterpret_cast<float *>(xs), pos0, base_rounds + rounds, seq0 + ar_i);
+        argmax_final_op(c, reinterpret_cast<float *>(xq), pos0, base_rounds + rounds, seq0 + ar_i);
         break;
     }
     if (op.kind == MK_MATVEC && op.track_argmax) {
@@ -880,34 +864,32 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
 }  // namespace
 
 size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits) {
-  size_t x = (size_t)max_groups * 128 * 2;
+  size_t x = (size_t)max_groups * (128 * 2 + 4 * 4);  // fp16 input + one fp32 bias term per block
   uint32_t chunk = ((maxlen + splits - 1) / splits + 31) & ~31u;
   size_t a = (size_t)((2 + NCW / 2) * head_dim + 2 * NCW + 32 + chunk + 32) * 4;
   size_t b = x > a ? x : a;
   return (b + 127) / 128 * 128;
 }
-size_t decode_mega_smem(size_t xs_bytes) {
-  return (size_t)NST * STAGE_BYTES + xs_bytes + (RED_SLOTS * NCW * 16 + 32 + 512 + 4) * 4 + 64 * sizeof(MegaStage) + 2 * NST * 8 + 64;
+size_t decode_mega_smem(size_t xs_bytes, uint32_t nst, uint32_t red_slots) {
+  return (size_t)nst * STAGE_BYTES + xs_bytes + ((size_t)red_slots * NCW * 16 + 36) * 4 + 64 * sizeof(MegaStage) + 2 * MAX_NST * 8 + 64;
 }
 int decode_mega_max_k() { return 16384; }
-int decode_mega_red_slots() { return RED_SLOTS; }
-int decode_mega_stage_groups() { return SG; }
+int decode_mega_max_stages() { return MAX_NST; }
 
 cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s) {
-  const size_t smem = decode_mega_smem(p.xs_bytes);
-  auto kern = p.timing ? (p.bias_trick ? decode_mega_kernel<true, false> : decode_mega_kernel<true, true>)
-                       : (p.bias_trick ? decode_mega_kernel<false, false> : decode_mega_kernel<false, true>);
+  if (p.nst < 2 || p.nst > (uint32_t)MAX_NST) return cudaErrorInvalidValue;
+  const size_t smem = decode_mega_smem(p.xs_bytes, p.nst, p.red_slots);
+  auto kern = p.timing ? decode_mega_kernel<true> : decode_mega_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   void *args[] = {(void *)&p};
   return cudaLaunchCooperativeKernel((void *)kern, dim3(grid), dim3(THREADS), args, smem, s);
 }
 
-cudaError_t decode_mega_occupancy(size_t xs_bytes, int *blocks_per_sm) {
-  const size_t smem = decode_mega_smem(xs_bytes);
-  cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+cudaError_t decode_mega_occupancy(size_t smem, int *blocks_per_sm) {
+  cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, decode_mega_kernel<false, true>, THREADS, smem);
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, decode_mega_kernel<false>, THREADS, smem);
 }
 
 }  // namespace vkl

@@ -122,12 +122,40 @@ struct MegaOp {
   float *out_f32;
   __half *kcache, *vcache;  // MK_ATTN_PART
 };
-// One ring stage of the persistent kernel: up to 16 groups of one (tile, matrix).
+// One ring stage of the persistent kernel: up to MEGA_SG consecutive groups (4 Q8_0 blocks x
+// 16 rows each) of a CTA's weight stream, as at most two contiguous runs: the tail of one
+// (tile, matrix) and the head of the next.
 struct MegaStage {
-  const uint8_t *codes;
-  const uint8_t *scales;
-  uint32_t ng, pad[3];
+  const uint8_t *codes0, *scales0;
+  const uint8_t *codes1, *scales1;
+  uint32_t n0, n1, pad[2];
 };
+constexpr uint32_t MEGA_SG = 15;  // groups per stage = consumer warps: one group per warp per stage
+// How a stage that starts at group `kg` of a (tile, matrix) of `groups` groups is cut: n0 groups
+// of this (tile, matrix), then n1 of the next one (if the op has one for this CTA). Host and
+// device walk the stream with the same rule.
+struct MegaCut {
+  uint32_t n0, n1;
+};
+__host__ __device__ inline MegaCut mega_stage_cut(uint32_t kg, uint32_t groups, bool has_next) {
+  MegaCut c;
+  c.n0 = groups - kg < MEGA_SG ? groups - kg : MEGA_SG;
+  const uint32_t rem = MEGA_SG - c.n0;
+  c.n1 = has_next ? (rem < groups ? rem : groups) : 0u;
+  return c;
+}
+__host__ __device__ inline void mega_stage_advance(const MegaCut &c, uint32_t groups, uint32_t &tm, uint32_t &kg) {
+  if (c.n1) {
+    tm += 1;
+    kg = c.n1;
+  } else {
+    kg += c.n0;
+  }
+  if (kg >= groups) {
+    kg = 0;
+    tm += 1;
+  }
+}
 struct MegaParams {
   const MegaOp *ops;
   const MegaStage *stages;       // [grid][stage_stride]: every CTA's stages in consumer order
@@ -150,25 +178,26 @@ struct MegaParams {
   uint32_t *error;          // 0, or the code of the wait that timed out
   uint32_t dim, heads, head_dim, maxlen, splits, vocab;
   uint32_t xs_bytes;
+  uint32_t xmax_groups;  // largest K of any op, in groups of 128 inputs: the input area holds that many fp16 values
   // Tensor parallelism: every rank's exchange buffer (peer pointers, own included).
   // Layout of one buffer, in 4-byte words: partial sums [2 parities][tp][dim] fp32, then
   // at word tp_flag_off: flags[16] (all-reduce sequence per source rank), arg flags[16],
   // arg candidates [16][2].
   uint32_t tp_rank, tp_size, tp_flag_off;
   void *tp_peer[8];
-  uint32_t l2_lookahead;      // weight stages kept in flight towards L2 ahead of the ring
+  uint32_t nst;               // ring stages (as many as fit beside the input and reduction areas)
+  uint32_t red_slots;         // reduction slots: the largest (tiles of one CTA) x (matrices) of any op
   uint32_t single_split_len;  // KV lengths up to this use one CTA per head (no combine phase)
+  uint32_t producer_sleep_ns, consumer_sleep_ns;  // back-off between polls of a ring barrier that is not ready
   // Optional timeline of CTA 0: per op, nanoseconds of work and of barrier wait.
   unsigned long long *timing;
-  uint32_t bias_trick;   // 1: raw code pairs + bias removal (faster, less exact); 0: exact codes
   uint32_t timing_mode;  // third column of the timeline: 0 = ring wait, 1 = op prologue
 };
 size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits);
-size_t decode_mega_smem(size_t xs_bytes);
+size_t decode_mega_smem(size_t xs_bytes, uint32_t nst, uint32_t red_slots);
 int decode_mega_max_k();
-int decode_mega_red_slots();
-int decode_mega_stage_groups();
-cudaError_t decode_mega_occupancy(size_t xs_bytes, int *blocks_per_sm);
+int decode_mega_max_stages();
+cudaError_t decode_mega_occupancy(size_t smem_bytes, int *blocks_per_sm);
 cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s);
 
 // ---- dense FP16 GEMM on tcgen05 tensor cores: C[M,N] = A[M,K] . W[N,K]^T (gemm_tcgen05.cu) ----

@@ -335,15 +335,15 @@ int build_mega(vkl_model *m) {
   if (splits > 8) splits = 8;
   const uint32_t max_groups = (std::max(c.dim, m->ffn_l) / 32 + 3) / 4;
   const size_t xs_bytes = decode_mega_xs_bytes(max_groups, m->head_dim, c.maxlen, splits);
-  if (decode_mega_smem(xs_bytes) > (size_t)m->dev->prop.sharedMemPerBlockOptin) return VKL_OK;
+  // every op's (tiles per CTA) x (matrices) needs a reduction slot
+  auto slots = [&](uint32_t rows, uint32_t nmat) { return (((rows + 15) / 16 + G - 1) / G) * nmat; };
+  const uint32_t red_slots = std::max({slots(m->dim_l, 3), slots(c.dim, 1), slots(m->ffn_l, 2), slots(m->vocab_l, 1)});
+  uint32_t nst = (uint32_t)decode_mega_max_stages();  // as many ring stages as fit
+  while (nst >= 2 && decode_mega_smem(xs_bytes, nst, red_slots) > (size_t)m->dev->prop.sharedMemPerBlockOptin) --nst;
+  if (nst < 2) return VKL_OK;
   int occ = 0;
-  VKL_CUDA(decode_mega_occupancy(xs_bytes, &occ));
+  VKL_CUDA(decode_mega_occupancy(decode_mega_smem(xs_bytes, nst, red_slots), &occ));
   if (occ < 1) return VKL_OK;
-  {  // every op's (tiles per CTA) x (matrices) must fit the kernel's reduction slots
-    auto slots = [&](uint32_t rows, uint32_t nmat) { return (((rows + 15) / 16 + G - 1) / G) * nmat; };
-    const uint32_t need = std::max({slots(m->dim_l, 3), slots(c.dim, 1), slots(m->ffn_l, 2), slots(m->vocab_l, 1)});
-    if ((int)need > decode_mega_red_slots()) return VKL_OK;
-  }
   VKL_OKAY(ensure_rows(m, 1));
 
   std::vector<MegaOp> ops;
@@ -409,23 +409,32 @@ int build_mega(vkl_model *m) {
   am.kind = MK_ARGMAX;
   ops.push_back(am);
 
-  // Stage tables: every CTA's ring stages for one token, in the order its consumers walk them.
-  const uint32_t SGR = (uint32_t)decode_mega_stage_groups();
+  // Stage tables: every CTA's ring stages for one token, in the order its consumers walk them
+  // (the same cutting rule as the kernel: mega_stage_cut / mega_stage_advance).
   std::vector<std::vector<MegaStage>> per_cta(G);
   for (const MegaOp &o : ops) {
     if (o.kind != MK_MATVEC) continue;
-    const uint32_t nstg = (o.groups + SGR - 1) / SGR;
-    for (int cta = 0; cta < G; ++cta)
-      for (uint32_t tile = ((uint32_t)cta + G - (o.rot % G)) % G; tile < o.tiles; tile += G)
-        for (uint32_t mt = 0; mt < o.nmat; ++mt)
-          for (uint32_t st = 0; st < nstg; ++st) {
-            MegaStage e = {};
-            const size_t g0 = (size_t)tile * o.groups + (size_t)st * SGR;
-            e.codes = o.codes[mt] + g0 * 2048;
-            e.scales = o.scales[mt] + g0 * 128;
-            e.ng = std::min(SGR, o.groups - st * SGR);
-            per_cta[cta].push_back(e);
-          }
+    for (int cta = 0; cta < G; ++cta) {
+      const uint32_t tile0 = ((uint32_t)cta + G - (o.rot % G)) % G;
+      const uint32_t tl = tile0 < o.tiles ? (o.tiles - tile0 + G - 1) / G : 0u;
+      const uint32_t ntm = tl * o.nmat;
+      auto run = [&](uint32_t tm, uint32_t kg, const uint8_t *&codes, const uint8_t *&scales) {
+        const size_t g0 = (size_t)(tile0 + (tm / o.nmat) * G) * o.groups + kg;
+        codes = o.codes[tm % o.nmat] + g0 * 2048;
+        scales = o.scales[tm % o.nmat] + g0 * 128;
+      };
+      uint32_t tm = 0, kg = 0;
+      while (tm < ntm) {
+        const MegaCut cut = mega_stage_cut(kg, o.groups, tm + 1 < ntm);
+        MegaStage e = {};
+        e.n0 = cut.n0;
+        e.n1 = cut.n1;
+        run(tm, kg, e.codes0, e.scales0);
+        if (cut.n1) run(tm + 1, 0, e.codes1, e.scales1);
+        per_cta[cta].push_back(e);
+        mega_stage_advance(cut, o.groups, tm, kg);
+      }
+    }
   }
   size_t stride = 0;
   for (auto &v : per_cta) stride = std::max(stride, v.size());
@@ -477,10 +486,13 @@ int build_mega(vkl_model *m) {
   p.error = (uint32_t *)m->mega_sync->data() + 4;
   p.dim = c.dim; p.heads = m->heads_l; p.head_dim = m->head_dim; p.maxlen = c.maxlen; p.splits = splits; p.vocab = m->vocab_l;
   p.xs_bytes = (uint32_t)xs_bytes;
+  p.xmax_groups = max_groups;
   {
-    p.bias_trick = getenv("VKLLAMA_DECODE_BIAS_TRICK") ? 1u : 0u;
-    const char *la = getenv("VKLLAMA_L2_LOOKAHEAD");
-    p.l2_lookahead = la ? (uint32_t)atoi(la) : 0u;
+    p.nst = nst;
+    p.red_slots = red_slots;
+    const char *ps = getenv("VKLLAMA_PRODUCER_SLEEP"), *cs = getenv("VKLLAMA_CONSUMER_SLEEP");
+    p.producer_sleep_ns = ps ? (uint32_t)atoi(ps) : 0u;
+    p.consumer_sleep_ns = cs ? (uint32_t)atoi(cs) : 0u;
     const uint32_t chunk_cap = ((c.maxlen + splits - 1) / splits + 31) & ~31u;
     const char *ss = getenv("VKLLAMA_SINGLE_SPLIT_LEN");
     p.single_split_len = std::min(ss ? (uint32_t)atoi(ss) : 0u, chunk_cap);
@@ -956,7 +968,8 @@ int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float 
     VKL_OKAY(m->dev->alloc(n * 24, &buf));
     MegaParams p = m->mp;
     p.timing = (unsigned long long *)buf;
-    p.timing_mode = (getenv("VKLLAMA_DEBUG_PROLOGUE") ? 1 : 0) | (getenv("VKLLAMA_DEBUG_NOCOPY") ? 2 : 0) | (getenv("VKLLAMA_DEBUG_NOMATH") ? 4 : 0) | (getenv("VKLLAMA_DEBUG_EPILOGUE") ? 8 : 0);
+    p.timing_mode = (getenv("VKLLAMA_DEBUG_PROLOGUE") ? 1 : 0) | (getenv("VKLLAMA_DEBUG_NOCOPY") ? 2 : 0) | (getenv("VKLLAMA_DEBUG_NOMATH") ? 4 : 0) | (getenv("VKLLAMA_DEBUG_EPILOGUE") ? 8 : 0) |
+                    (getenv("VKLLAMA_DEBUG_LOOP") ? 32 : 0);
     std::vector<unsigned long long> tl(3 * n);
     std::vector<MegaOp> ops(n);
     cudaError_t e = cudaMemsetAsync(buf, 0, n * 24, m->stream);
@@ -983,6 +996,10 @@ int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float 
       }
       out_us[cls] += (float)(tl[2 * i] + tl[2 * i + 1]) * 1e-3f;
       out_us[8 + cls] += (float)tl[2 * i + 1] * 1e-3f;
+      if (getenv("VKLLAMA_DEBUG_LOOP")) {  // diagnostic: [cls] = loop time, [8+cls] = stages of CTA 0
+        out_us[cls] += (float)(tl[2 * n + i] >> 16) * 1e-3f - (float)(tl[2 * i] + tl[2 * i + 1]) * 1e-3f;
+        out_us[8 + cls] += (float)(tl[2 * n + i] & 0xffff) - (float)tl[2 * i + 1] * 1e-3f;
+      }
       if (getenv("VKLLAMA_DEBUG_RING")) out_us[8 + cls] = out_us[8 + cls] - (float)tl[2 * i + 1] * 1e-3f + (float)tl[2 * n + i] * 1e-3f;
     }
     return check_mega(m);
