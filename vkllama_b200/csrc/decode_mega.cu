@@ -92,7 +92,7 @@ struct Ctx {
   }
   // Bounded mbarrier wait; false (and the abort flag set) on time-out.
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, uint32_t code, uint32_t sleep_ns = 0) const {
-    if (mbar_try(bar, parity)) return !aborted();  // fast path: the phase is already complete
+    if (mbar_try(bar, parity)) return true;  // fast path: the phase is already complete
     if (aborted()) return false;
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
       if (sleep_ns) __nanosleep(sleep_ns);  // keep a waiting warp off the shared-memory pipe the working warps need
@@ -112,7 +112,7 @@ struct Ctx {
 // stage of the whole token, in consumer order). Lane 0 keeps the shared-memory ring
 // full with bulk copies; the other lanes only fetch table chunks.
 __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint64_t *full, uint64_t *empty,
-                                         MegaStage *tabs /* [64] in shared memory */) {
+                                         MegaStage *tabs /* [128] in shared memory */) {
   const MegaParams &p = c.p;
   const uint32_t lane = threadIdx.x & 31;
   const MegaStage *table = p.stages + (size_t)blockIdx.x * p.stage_stride;
@@ -123,17 +123,19 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
   uint32_t it = 0, slot = 0, ph = 0;
   bool stop = false;
   for (uint32_t base = 0; base < n && !stop; base += 32) {
-    // chunk base/32 is in tabs[(base/32 % 2)*32 ..]; fetch the next one beside it
-    if (base + 32 + lane < n) tabs[((base / 32 + 1) & 1) * 32 + lane] = table[base + 32 + lane];
+    // chunk base/32 is in tabs[(base/32 % 4)*32 ..]; fetch the next one behind it. The table is a
+    // ring of four chunks because the consumers, up to a ring depth of stages behind, still read
+    // their stages' entries.
+    if (base + 32 + lane < n) tabs[((base / 32 + 1) & 3) * 32 + lane] = table[base + 32 + lane];
     __syncwarp();
     if (lane == 0) {
       const uint32_t end = min(base + 32, n);
       for (; it < end; ++it) {
-        if (it >= NST && !c.wait(s32(&empty[slot]), ph ^ 1u, 2, p.producer_sleep_ns)) {
+        if (it >= NST && !c.wait(s32(&empty[slot]), ph ^ 1u, 2, 0)) {
           stop = true;
           break;
         }
-        const MegaStage &e = tabs[it & 63];
+        const MegaStage &e = tabs[it & 127];
         const uint32_t fb = s32(&full[slot]);
         if (p.timing_mode & 2u) {  // diagnostic: consumer speed without the weight stream
           mbar_arrive(fb);
@@ -169,22 +171,36 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
 }
 
 // ------------------------------------------------------------ grid barrier
-__device__ __forceinline__ bool grid_barrier(const Ctx &c, uint64_t target) {
+__device__ __forceinline__ bool grid_barrier(const Ctx &c, uint64_t target, uint32_t round, volatile uint32_t *seen_s) {
   cons_sync();  // every consumer store of this op is issued
-  if (threadIdx.x == 0 && !c.aborted()) {
-    // release-add without a return value: orders this CTA's stores (made visible to
-    // thread 0 by the bar.sync above) before the arrival, one L2 trip instead of two
-    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(c.p.bar), "l"(1ull) : "memory");
+  // Lane 0 of the first POLLERS warps poll the counter, each a fraction of a memory round trip
+  // after the previous one, so that the last arrival is seen a fraction of a round trip after it
+  // lands instead of half a round trip on average. `seen_s` holds the last round (1, 2, ... within
+  // this launch) that one of them has seen complete.
+  const uint32_t POLLERS = c.p.barrier_pollers;
+  const uint32_t w = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0 && w < POLLERS && !c.aborted()) {
+    if (w == 0) {
+      // release-add without a return value: orders this CTA's stores (made visible to
+      // thread 0 by the bar.sync above) before the arrival, one L2 trip instead of two
+      asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(c.p.bar), "l"(1ull) : "memory");
+    } else {
+      __nanosleep(160 * w);
+    }
+    const uint32_t tgt = round;
     bool ok = false;
     for (uint32_t i = 0; i < WAIT_LIMIT * 8u; ++i) {
-      if (ld_acq_u64(c.p.bar) >= target) {
+      if (*seen_s == tgt || ld_acq_u64(c.p.bar) >= target) {
         ok = true;
         break;
       }
       if (i > 100000u) __nanosleep(64);
       if ((i & 1023u) == 1023u && *(volatile uint32_t *)c.p.error != 0u) break;
     }
-    if (!ok) c.raise(3);
+    if (ok)
+      *seen_s = tgt;
+    else
+      c.raise(3);
     __threadfence();
   }
   cons_sync();
@@ -208,10 +224,12 @@ __device__ __forceinline__ bool better(float v, uint32_t i, const Best &b) {
 __device__ __forceinline__ uint32_t codes_sub_h2(uint32_t w, bool hi) { return __byte_perm(w, 0u, hi ? 0x4341u : 0x4240u); }
 
 // One mat-vec op of the token: y[N] = W[N,K] . x[K] for up to three matrices that share x.
-template <bool TIMED>
+template <bool TIMED, bool DBG>
 __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global, uint32_t &it, uint32_t &slot, uint32_t &ph,
-                                          unsigned char *ring, uint64_t *full, uint64_t *empty, __half *xs, float *xbias, const __half *zero16,
-                                          float *red, float *ssum, Best &best, unsigned long long *tw, uint32_t ar_parity) {
+                                          unsigned char *ring, uint64_t *full, uint64_t *empty, const MegaStage *tabs, __half *xs, float *xbias,
+                                          const __half *zero16,
+                                          float *red, float *ssum, Best &best, unsigned long long *tw, uint32_t ar_parity,
+                                          uint32_t combine_splits) {
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t G = gridDim.x, cta = blockIdx.x;
   // Scalars in registers: the barriers' memory clobbers would otherwise make every use
@@ -233,6 +251,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   const uint32_t tile0 = (cta + G - (op.rot % G)) % G;
   const uint32_t tl = tile0 < tiles ? (tiles - tile0 + G - 1) / G : 0u;  // this CTA's tiles
   const uint32_t ntm = tl * nmat;                                        // (tile, matrix) row blocks of this CTA
+  const uint32_t nstages_dbg = op_global.stages_per_cta[cta];
   // ---- input vector -> shared memory (RMSNorm fused, rounded to fp16 where the
   // reference's RMSNorm op rounds: rms_norm_fp16.comp:70-77). Norm weights and input are
   // requested together: one memory round trip.
@@ -241,11 +260,58 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     uint4 v[MAXV];
     const uint32_t nv = K / 8, kpad = groups * 128;
     const bool norm = op.norm_w != nullptr;
+    constexpr int NWV = 2;  // vectors per thread whose norm weights are requested early (K <= 7680: every norm op of the model shapes)
+    float4 nw[NWV][2];
+    if (combine_splits) {
+      // The input is the attention output: merge the split partials of every head here (in
+      // split order, as the separate combine op does) instead of spending an op and a grid
+      // barrier on it. Vector i = 8 consecutive dims of head 8i / head_dim.
+      const MegaParams &pp = c.p;
+      const uint32_t D = pp.head_dim, ST = D + 4;
 #pragma unroll
-    for (int j = 0; j < MAXV; ++j) {
-      const uint32_t i = tid + j * CT;
-      v[j] = make_uint4(0, 0, 0, 0);
-      if (i < nv) v[j] = __ldcg(reinterpret_cast<const uint4 *>(op.in) + i);
+      for (int j = 0; j < MAXV; ++j) {
+        const uint32_t i = tid + j * CT;
+        v[j] = make_uint4(0, 0, 0, 0);
+        if (i < nv) {
+          const uint32_t h = (8 * i) / D, d0 = (8 * i) % D;
+          const float *base = pp.attn_scratch + (size_t)h * pp.splits * ST;
+          float M = -INFINITY;
+          for (uint32_t sp = 0; sp < combine_splits; ++sp) M = fmaxf(M, __ldcg(base + sp * ST + D));
+          float den = 0.f, num[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (uint32_t sp = 0; sp < combine_splits; ++sp) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(base + sp * ST + D));
+            if (ml.y > 0.f) {
+              const float w = expf(ml.x - M);
+              den += ml.y * w;
+              const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(base + sp * ST + d0));
+              const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(base + sp * ST + d0 + 4));
+              num[0] += p0.x * w; num[1] += p0.y * w; num[2] += p0.z * w; num[3] += p0.w * w;
+              num[4] += p1.x * w; num[5] += p1.y * w; num[6] += p1.z * w; num[7] += p1.w * w;
+            }
+          }
+          __half2 o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = __halves2half2(__float2half_rn(num[2 * e] / den), __float2half_rn(num[2 * e + 1] / den));
+          v[j] = *reinterpret_cast<uint4 *>(o);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j) {
+        const uint32_t i = tid + j * CT;
+        v[j] = make_uint4(0, 0, 0, 0);
+        if (i < nv) v[j] = __ldcg(reinterpret_cast<const uint4 *>(op.in) + i);
+      }
+    }
+    if (norm) {  // the norm weights do not depend on the reduction below: request them in the same round trip
+#pragma unroll
+      for (int j = 0; j < NWV; ++j) {
+        const uint32_t i = tid + j * CT;
+        if (i < nv) {
+          nw[j][0] = __ldg(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i);
+          nw[j][1] = __ldg(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i + 1);
+        }
+      }
     }
     for (uint32_t i = tid; i < ntm * NCW * 16; i += CT) red[i] = 0.f;  // warps that get no group of a row block leave zeros
     float alpha = 1.f;
@@ -275,8 +341,8 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
       if (i < nv) {
         uint4 ov = v[j];
         if (norm) {
-          const float4 w0 = __ldg(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i);
-          const float4 w1 = __ldg(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i + 1);
+          const float4 w0 = j < NWV ? nw[j][0] : __ldg(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i);
+          const float4 w1 = j < NWV ? nw[j][1] : __ldg(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i + 1);
           const __half2 *h = reinterpret_cast<const __half2 *>(&v[j]);
           const float2 a = __half22float2(h[0]), b = __half22float2(h[1]), cc = __half22float2(h[2]), d = __half22float2(h[3]);
           __half2 o[4];
@@ -310,16 +376,20 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   // of a row block go to the warp's own slot in shared memory when its groups move on to the
   // next row block, and nothing synchronises until the op's single reduction at the end.
   {
-    uint32_t tm = 0, kg = 0, cur = 0xffffffffu;
+    uint32_t cur = 0xffffffffu;
     float a0 = 0.f, a1 = 0.f;
-    while (tm < ntm) {
-      const MegaCut cut = mega_stage_cut(kg, groups, tm + 1 < ntm);
+    const uint32_t nstages = op_global.stages_per_cta[cta];
+    for (uint32_t sidx = 0; sidx < nstages; ++sidx) {
       unsigned long long w0 = 0;
       if (TIMED && tw) w0 = clock64();
-      const bool ok = c.wait(s32(&full[slot]), ph, 1, c.p.consumer_sleep_ns);
+      const bool ok = c.wait(s32(&full[slot]), ph, 1);
       if (TIMED && tw) tw[0] += (clock64() - w0) * 1000ull / 1965ull;  // SM cycles -> ns at the 1965 MHz boost clock
-      const bool have = ok && warp < cut.n0 + cut.n1;
-      const uint32_t mt = warp < cut.n0 ? tm : tm + 1, mk = warp < cut.n0 ? kg + warp : warp - cut.n0;
+      // the stage's place in the op (row block, first group, run lengths) is in the producer's
+      // table entry, which the producer wrote before it armed the stage's barrier
+      const uint4 meta = *reinterpret_cast<const uint4 *>(&tabs[it & 127].n0);
+      const uint32_t n0 = meta.x, n1 = meta.y, tm = meta.z, kg = meta.w;
+      const bool have = ok && warp < n0 + n1;
+      const uint32_t mt = warp < n0 ? tm : tm + 1, mk = warp < n0 ? kg + warp : warp - n0;
       const unsigned char *st = ring + (size_t)slot * STAGE_BYTES;
       uint4 cw[4], sv;
       if (have) {
@@ -339,7 +409,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
           cur = mt;
           a0 = a1 = 0.f;
         }
-        if (TIMED && (c.p.timing_mode & 4u)) {  // diagnostic: ring traffic without arithmetic
+        if (DBG && (c.p.timing_mode & 4u)) {  // diagnostic: ring traffic without arithmetic
           a0 += __uint_as_float(cw[0].x ^ cw[1].y ^ cw[2].z ^ cw[3].w ^ sv.x);
         } else {
           // The stored codes u = q + 128 go into the MMA as fp16 subnormals u * 2^-24 (one byte
@@ -369,7 +439,6 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
           }
         }
       }
-      mega_stage_advance(cut, groups, tm, kg);
       ++it;
       if (++slot == NST) {
         slot = 0;
@@ -385,7 +454,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   // ---- one fixed-order reduction over the warps and the epilogue for all tiles
   if (TIMED && tw) {
     tw[2] = clock64();
-    if (c.p.timing_mode & 32u) tw[0] = (((tw[2] - tw[1]) * 1000ull / 1965ull) << 16) | (uint64_t)min(ntm * ((groups + SG - 1) / SG), 65535u);
+    if (c.p.timing_mode & 32u) tw[0] = (((tw[2] - tw[1]) * 1000ull / 1965ull) << 16) | (uint64_t)min(nstages_dbg, 65535u);
   }
   cons_sync();
   for (uint32_t idx = tid; idx < tl * 16; idx += CT) {
@@ -548,7 +617,7 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
     pv[grp * D + 2 * dp + 1] = acc.y;
   }
   cons_sync();
-  float *part = p.attn_scratch + ((size_t)h * p.splits + split) * (D + 2);
+  float *part = p.attn_scratch + ((size_t)h * p.splits + split) * (D + 4);
   if (tid < D) {
     float s = 0.f;
 #pragma unroll
@@ -569,16 +638,16 @@ __device__ __forceinline__ void attn_combine_op(const Ctx &c, uint32_t) {
   const MegaParams &p = c.p;
   const uint32_t h = blockIdx.x, tid = threadIdx.x, D = p.head_dim;
   if (h >= p.heads || tid >= D) return;
-  const float *base = p.attn_scratch + (size_t)h * p.splits * (D + 2);
+  const float *base = p.attn_scratch + (size_t)h * p.splits * (D + 4);
   float M = -INFINITY;
-  for (uint32_t s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(base + s * (D + 2) + D));
+  for (uint32_t s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(base + s * (D + 4) + D));
   float den = 0.f, num = 0.f;
   for (uint32_t s = 0; s < p.splits; ++s) {
-    const float ms = __ldcg(base + s * (D + 2) + D), ls = __ldcg(base + s * (D + 2) + D + 1);
+    const float ms = __ldcg(base + s * (D + 4) + D), ls = __ldcg(base + s * (D + 4) + D + 1);
     if (ls > 0.f) {
       const float w = expf(ms - M);
       den += ls * w;
-      num += __ldcg(base + s * (D + 2) + tid) * w;
+      num += __ldcg(base + s * (D + 4) + tid) * w;
     }
   }
   p.ao[(size_t)h * D + tid] = __float2half_rn(num / den);
@@ -727,7 +796,7 @@ __device__ __forceinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uin
   }
 }
 
-template <bool TIMED>
+template <bool TIMED, bool DBG>
 __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t NST = p.nst;
@@ -736,8 +805,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
   float *red = reinterpret_cast<float *>(xq + p.xs_bytes);
   float *ssum = red + (size_t)p.red_slots * NCW * 16;  // [32]
   const __half *zero16 = reinterpret_cast<const __half *>(ssum + 32);  // 16 zero bytes
-  MegaStage *tabs = reinterpret_cast<MegaStage *>(ssum + 36);  // [64], 16-byte aligned
-  uint64_t *full = reinterpret_cast<uint64_t *>(tabs + 64);
+  MegaStage *tabs = reinterpret_cast<MegaStage *>(ssum + 36);  // [128], 16-byte aligned
+  uint64_t *full = reinterpret_cast<uint64_t *>(tabs + 128);
   uint64_t *empty = full + MAX_NST;
   volatile uint32_t *abort_s = reinterpret_cast<volatile uint32_t *>(empty + MAX_NST);
 
@@ -746,7 +815,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
       mbar_init(s32(&full[i]), 1);
       mbar_init(s32(&empty[i]), NCW);
     }
-    *abort_s = 0;
+    abort_s[0] = 0;
+    abort_s[1] = 0;
     *reinterpret_cast<uint4 *>(ssum + 32) = make_uint4(0, 0, 0, 0);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -778,7 +848,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
     if (timed) c0 = clock64();
     switch (op.kind) {
       case MK_EMBED: embed_op(c, tok); break;
-      case MK_MATVEC: matvec_op<TIMED>(c, op, it, slot, ph, ring, full, empty, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_groups * 256), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, (seq0 + ar_i + 1) & 1u); break;
+      case MK_MATVEC: matvec_op<TIMED, DBG>(c, op, it, slot, ph, ring, full, empty, tabs, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_groups * 256), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, (seq0 + ar_i + 1) & 1u,
+                         (op.combine_in && S_eff > 1) ? p.splits : 0u);
+        break;
       case MK_ATTN_PART: attn_part_op(c, op, reinterpret_cast<float *>(xq), pos0, S_eff); break;
       case MK_ATTN_COMBINE: attn_combine_op(c, pos0); break;
       case MK_ALLREDUCE:
@@ -843,7 +915,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
         }
       }
       ++rounds;
-      grid_barrier(c, (base_rounds + rounds) * G);
+      grid_barrier(c, (base_rounds + rounds) * G, (uint32_t)rounds, abort_s + 1);
     }
     if (timed) {
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t2));
@@ -871,7 +943,7 @@ size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t max
   return (b + 127) / 128 * 128;
 }
 size_t decode_mega_smem(size_t xs_bytes, uint32_t nst, uint32_t red_slots) {
-  return (size_t)nst * STAGE_BYTES + xs_bytes + ((size_t)red_slots * NCW * 16 + 36) * 4 + 64 * sizeof(MegaStage) + 2 * MAX_NST * 8 + 64;
+  return (size_t)nst * STAGE_BYTES + xs_bytes + ((size_t)red_slots * NCW * 16 + 36) * 4 + 128 * sizeof(MegaStage) + 2 * MAX_NST * 8 + 64;
 }
 int decode_mega_max_k() { return 16384; }
 int decode_mega_max_stages() { return MAX_NST; }
@@ -879,7 +951,9 @@ int decode_mega_max_stages() { return MAX_NST; }
 cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s) {
   if (p.nst < 2 || p.nst > (uint32_t)MAX_NST) return cudaErrorInvalidValue;
   const size_t smem = decode_mega_smem(p.xs_bytes, p.nst, p.red_slots);
-  auto kern = p.timing ? decode_mega_kernel<true> : decode_mega_kernel<false>;
+  // the diagnostic switches (no weight copies, no arithmetic) are compiled into separate instances
+  const bool dbg = (p.timing_mode & 6u) != 0;
+  auto kern = p.timing ? decode_mega_kernel<true, true> : dbg ? decode_mega_kernel<false, true> : decode_mega_kernel<false, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   void *args[] = {(void *)&p};
@@ -887,9 +961,9 @@ cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s) {
 }
 
 cudaError_t decode_mega_occupancy(size_t smem, int *blocks_per_sm) {
-  cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(decode_mega_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, decode_mega_kernel<false>, THREADS, smem);
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, decode_mega_kernel<false, false>, THREADS, smem);
 }
 
 }  // namespace vkl

@@ -117,6 +117,8 @@ struct MegaOp {
   const float *norm_w;  // fused RMSNorm of the input, or null
   float eps;
   uint32_t track_argmax;  // lm head: keep a per-CTA (max, index) candidate
+  uint32_t combine_in;    // the input is the attention output: merge the split partials in the prologue
+  const uint32_t *stages_per_cta;  // [grid]: ring stages of this op per CTA
   const __half *in;       // input vector [K]
   __half *out[3];         // EPI_ADD: out[0] is also the residual
   float *out_f32;
@@ -128,7 +130,8 @@ struct MegaOp {
 struct MegaStage {
   const uint8_t *codes0, *scales0;
   const uint8_t *codes1, *scales1;
-  uint32_t n0, n1, pad[2];
+  uint32_t n0, n1;  // groups of the first and of the second run
+  uint32_t tm, kg;  // consumers' view: row block (local tile x matrix) and first group of run 0; run 1 starts row block tm + 1
 };
 constexpr uint32_t MEGA_SG = 15;  // groups per stage = consumer warps: one group per warp per stage
 // How a stage that starts at group `kg` of a (tile, matrix) of `groups` groups is cut: n0 groups
@@ -188,7 +191,7 @@ struct MegaParams {
   uint32_t nst;               // ring stages (as many as fit beside the input and reduction areas)
   uint32_t red_slots;         // reduction slots: the largest (tiles of one CTA) x (matrices) of any op
   uint32_t single_split_len;  // KV lengths up to this use one CTA per head (no combine phase)
-  uint32_t producer_sleep_ns, consumer_sleep_ns;  // back-off between polls of a ring barrier that is not ready
+  uint32_t barrier_pollers;   // warps whose lane 0 polls the grid barrier counter, staggered in time
   // Optional timeline of CTA 0: per op, nanoseconds of work and of barrier wait.
   unsigned long long *timing;
   uint32_t timing_mode;  // third column of the timeline: 0 = ring wait, 1 = op prologue

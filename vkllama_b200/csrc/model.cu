@@ -386,9 +386,15 @@ int build_mega(vkl_model *m) {
     a.kcache = (__half *)y.kcache->data();
     a.vcache = (__half *)y.vcache->data();
     ops.push_back(a);
-    MegaOp cb = {};
-    cb.kind = MK_ATTN_COMBINE;
-    ops.push_back(cb);
+    // VKLLAMA_DECODE_COMBINE=fused merges the split partials in o_proj's prologue instead of a
+    // combine op and its grid barrier; measured slower (every CTA re-reads all heads' partials)
+    const char *cenv = getenv("VKLLAMA_DECODE_COMBINE");
+    const bool fuse_combine = (m->head_dim % 8 == 0) && cenv && !strcmp(cenv, "fused");
+    if (!fuse_combine) {
+      MegaOp cb = {};
+      cb.kind = MK_ATTN_COMBINE;
+      ops.push_back(cb);
+    }
     auto allreduce = [&]() {
       MegaOp r = {};
       r.kind = MK_ALLREDUCE;
@@ -397,6 +403,7 @@ int build_mega(vkl_model *m) {
       ops.push_back(r);
     };
     matvec({y.wo}, nullptr, 0.f, ao, {x}, tp > 1 ? EPI_PARTIAL : EPI_ADD);
+    ops.back().combine_in = fuse_combine ? 1u : 0u;
     if (tp > 1) allreduce();
     matvec({y.gate, y.up}, (const float *)y.ffn_norm->data(), c.eps, x, {tb}, EPI_SWIGLU);
     matvec({y.down}, nullptr, 0.f, tb, {x}, tp > 1 ? EPI_PARTIAL : EPI_ADD);
@@ -412,9 +419,14 @@ int build_mega(vkl_model *m) {
   // Stage tables: every CTA's ring stages for one token, in the order its consumers walk them
   // (the same cutting rule as the kernel: mega_stage_cut / mega_stage_advance).
   std::vector<std::vector<MegaStage>> per_cta(G);
-  for (const MegaOp &o : ops) {
+  std::vector<uint32_t> op_stages;  // [mat-vec op][cta]
+  std::vector<size_t> op_index;     // index into `ops` of every mat-vec op
+  for (size_t oi = 0; oi < ops.size(); ++oi) {
+    const MegaOp &o = ops[oi];
     if (o.kind != MK_MATVEC) continue;
+    op_index.push_back(oi);
     for (int cta = 0; cta < G; ++cta) {
+      const size_t before = per_cta[cta].size();
       const uint32_t tile0 = ((uint32_t)cta + G - (o.rot % G)) % G;
       const uint32_t tl = tile0 < o.tiles ? (o.tiles - tile0 + G - 1) / G : 0u;
       const uint32_t ntm = tl * o.nmat;
@@ -429,11 +441,14 @@ int build_mega(vkl_model *m) {
         MegaStage e = {};
         e.n0 = cut.n0;
         e.n1 = cut.n1;
+        e.tm = tm;
+        e.kg = kg;
         run(tm, kg, e.codes0, e.scales0);
         if (cut.n1) run(tm + 1, 0, e.codes1, e.scales1);
         per_cta[cta].push_back(e);
         mega_stage_advance(cut, o.groups, tm, kg);
       }
+      op_stages.push_back((uint32_t)(per_cta[cta].size() - before));
     }
   }
   size_t stride = 0;
@@ -445,16 +460,18 @@ int build_mega(vkl_model *m) {
     std::copy(per_cta[cta].begin(), per_cta[cta].end(), flat.begin() + (size_t)cta * stride);
   }
   VKL_OKAY(tensor_new(m->dev, 1, 1, flat.size() * sizeof(MegaStage) / 4, VKL_UINT32, &m->mega_stages));
-  VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)G, VKL_UINT32, &m->mega_counts));
+  VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)G + op_stages.size(), VKL_UINT32, &m->mega_counts));  // totals, then per op
   VKL_CUDA(cudaMemcpyAsync(m->mega_stages->data(), flat.data(), flat.size() * sizeof(MegaStage), cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaMemcpyAsync(m->mega_counts->data(), counts.data(), (size_t)G * 4, cudaMemcpyHostToDevice, m->stream));
+  VKL_CUDA(cudaMemcpyAsync((uint32_t *)m->mega_counts->data() + G, op_stages.data(), op_stages.size() * 4, cudaMemcpyHostToDevice, m->stream));
+  for (size_t k = 0; k < op_index.size(); ++k) ops[op_index[k]].stages_per_cta = (const uint32_t *)m->mega_counts->data() + G + k * (size_t)G;
   VKL_CUDA(cudaStreamSynchronize(m->stream));
 
   const size_t ob = ops.size() * sizeof(MegaOp);
   VKL_OKAY(tensor_new(m->dev, 1, 1, (ob + 3) / 4, VKL_UINT32, &m->mega_ops));
   VKL_OKAY(tensor_new(m->dev, 1, 1, 16, VKL_UINT32, &m->mega_sync));  // [0..3] barrier words, [4] error
   VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)G * 2, VKL_FP32, &m->mega_arg));
-  VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)m->heads_l * splits * (m->head_dim + 2), VKL_FP32, &m->mega_attn));
+  VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)m->heads_l * splits * (m->head_dim + 4), VKL_FP32, &m->mega_attn));
   VKL_CUDA(cudaMemcpyAsync(m->mega_ops->data(), ops.data(), ob, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaMemsetAsync(m->mega_sync->data(), 0, 64, m->stream));
   VKL_CUDA(cudaStreamSynchronize(m->stream));
@@ -490,9 +507,9 @@ int build_mega(vkl_model *m) {
   {
     p.nst = nst;
     p.red_slots = red_slots;
-    const char *ps = getenv("VKLLAMA_PRODUCER_SLEEP"), *cs = getenv("VKLLAMA_CONSUMER_SLEEP");
-    p.producer_sleep_ns = ps ? (uint32_t)atoi(ps) : 0u;
-    p.consumer_sleep_ns = cs ? (uint32_t)atoi(cs) : 0u;
+    p.timing_mode = (getenv("VKLLAMA_DEBUG_NOCOPY") ? 2 : 0) | (getenv("VKLLAMA_DEBUG_NOMATH") ? 4 : 0);  // diagnostics
+    const char *bp = getenv("VKLLAMA_BARRIER_POLLERS");
+    p.barrier_pollers = bp ? std::min(std::max((uint32_t)atoi(bp), 1u), 8u) : 1u;
     const uint32_t chunk_cap = ((c.maxlen + splits - 1) / splits + 31) & ~31u;
     const char *ss = getenv("VKLLAMA_SINGLE_SPLIT_LEN");
     p.single_split_len = std::min(ss ? (uint32_t)atoi(ss) : 0u, chunk_cap);
