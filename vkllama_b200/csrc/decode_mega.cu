@@ -375,31 +375,60 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   // consumer warp; stages run on across (tile, matrix) boundaries, so a warp's partial sums
   // of a row block go to the warp's own slot in shared memory when its groups move on to the
   // next row block, and nothing synchronises until the op's single reduction at the end.
+  // A loop iteration takes two stages: the waits, table reads, loads and slot releases of both
+  // are issued back to back (their latencies overlap) before the arithmetic of either, because a
+  // single warp runs its per-stage chain of dependent barrier and shared-memory operations at a
+  // fraction of the issue rate.
   {
     uint32_t cur = 0xffffffffu;
     float a0 = 0.f, a1 = 0.f;
     const uint32_t nstages = op_global.stages_per_cta[cta];
-    for (uint32_t sidx = 0; sidx < nstages; ++sidx) {
+    for (uint32_t sidx = 0; sidx < nstages; sidx += 2) {
+      const bool two = sidx + 1 < nstages;
+      const uint32_t slotA = slot, phA = ph;
+      if (++slot == NST) {
+        slot = 0;
+        ph ^= 1u;
+      }
+      const uint32_t slotB = slot, phB = ph;
+      if (two && ++slot == NST) {
+        slot = 0;
+        ph ^= 1u;
+      }
       unsigned long long w0 = 0;
       if (TIMED && tw) w0 = clock64();
-      const bool ok = c.wait(s32(&full[slot]), ph, 1);
+      bool ok[2];
+      ok[0] = c.wait(s32(&full[slotA]), phA, 1);
+      ok[1] = two && c.wait(s32(&full[slotB]), phB, 1);
       if (TIMED && tw) tw[0] += (clock64() - w0) * 1000ull / 1965ull;  // SM cycles -> ns at the 1965 MHz boost clock
-      // the stage's place in the op (row block, first group, run lengths) is in the producer's
+      // a stage's place in the op (row block, first group, run lengths) is in the producer's
       // table entry, which the producer wrote before it armed the stage's barrier
-      const uint4 meta = *reinterpret_cast<const uint4 *>(&tabs[it & 127].n0);
-      const uint32_t n0 = meta.x, n1 = meta.y, tm = meta.z, kg = meta.w;
-      const bool have = ok && warp < n0 + n1;
-      const uint32_t mt = warp < n0 ? tm : tm + 1, mk = warp < n0 ? kg + warp : warp - n0;
-      const unsigned char *st = ring + (size_t)slot * STAGE_BYTES;
-      uint4 cw[4], sv;
-      if (have) {
+      uint4 meta[2], cw[2][4], sv[2];
+      meta[0] = *reinterpret_cast<const uint4 *>(&tabs[it & 127].n0);
+      meta[1] = *reinterpret_cast<const uint4 *>(&tabs[(it + 1) & 127].n0);
+      const unsigned char *stA = ring + (size_t)slotA * STAGE_BYTES, *stB = ring + (size_t)slotB * STAGE_BYTES;
+      // every warp reads "its" group of the stage whether or not the stage has one for it
+      // (a short last stage): such bytes are never used
 #pragma unroll
-        for (int j = 0; j < 4; ++j) cw[j] = *reinterpret_cast<const uint4 *>(st + (warp * 4 + j) * 512 + lane * 16);
-        sv = *reinterpret_cast<const uint4 *>(st + STAGE_CODES + warp * 128 + g * 16);
+      for (int j = 0; j < 4; ++j) cw[0][j] = *reinterpret_cast<const uint4 *>(stA + (warp * 4 + j) * 512 + lane * 16);
+      sv[0] = *reinterpret_cast<const uint4 *>(stA + STAGE_CODES + warp * 128 + g * 16);
+      if (two) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cw[1][j] = *reinterpret_cast<const uint4 *>(stB + (warp * 4 + j) * 512 + lane * 16);
+        sv[1] = *reinterpret_cast<const uint4 *>(stB + STAGE_CODES + warp * 128 + g * 16);
       }
       __syncwarp();
-      if (lane == 0 && ok) mbar_arrive(s32(&empty[slot]));  // this warp has read all it needs from the stage
-      if (have) {
+      if (lane == 0) {  // ordered after this warp's reads of the stages
+        if (ok[0]) mbar_arrive(s32(&empty[slotA]));
+        if (ok[1]) mbar_arrive(s32(&empty[slotB]));
+      }
+      it += two ? 2u : 1u;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t n0 = meta[h].x, n1 = meta[h].y, tm = meta[h].z, kg = meta[h].w;
+        const bool have = ok[h] && warp < n0 + n1;
+        const uint32_t mt = warp < n0 ? tm : tm + 1, mk = warp < n0 ? kg + warp : warp - n0;
+        if (!have) continue;
         if (mt != cur) {
           if (cur != 0xffffffffu && t == 0) {  // lanes t == 0 hold column 0 = token 0: rows g and g+8
             float *slotp = red + ((size_t)cur * NCW + warp) * 16;
@@ -410,7 +439,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
           a0 = a1 = 0.f;
         }
         if (DBG && (c.p.timing_mode & 4u)) {  // diagnostic: ring traffic without arithmetic
-          a0 += __uint_as_float(cw[0].x ^ cw[1].y ^ cw[2].z ^ cw[3].w ^ sv.x);
+          a0 += __uint_as_float(cw[h][0].x ^ cw[h][1].y ^ cw[h][2].z ^ cw[h][3].w ^ sv[h].x);
         } else {
           // The stored codes u = q + 128 go into the MMA as fp16 subnormals u * 2^-24 (one byte
           // permute per pair, no arithmetic): products and their fp32 sums are exact up to the
@@ -421,28 +450,22 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
           const uint32_t xstep = g == 0 ? 32u : 0u;
           const float4 xb4 = *reinterpret_cast<const float4 *>(xbias + mk * 4);
           const float xb[4] = {xb4.x, xb4.y, xb4.z, xb4.w};
-          const float2 da = __half22float2(*reinterpret_cast<const __half2 *>(&sv.x));
-          const float2 db = __half22float2(*reinterpret_cast<const __half2 *>(&sv.y));
-          const float2 ea = __half22float2(*reinterpret_cast<const __half2 *>(&sv.z));
-          const float2 eb = __half22float2(*reinterpret_cast<const __half2 *>(&sv.w));
+          const float2 da = __half22float2(*reinterpret_cast<const __half2 *>(&sv[h].x));
+          const float2 db = __half22float2(*reinterpret_cast<const __half2 *>(&sv[h].y));
+          const float2 ea = __half22float2(*reinterpret_cast<const __half2 *>(&sv[h].z));
+          const float2 eb = __half22float2(*reinterpret_cast<const __half2 *>(&sv[h].w));
           const float dgs[4] = {da.x, da.y, db.x, db.y}, dg8s[4] = {ea.x, ea.y, eb.x, eb.y};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const uint4 X = *reinterpret_cast<const uint4 *>(xp + j * xstep);
+            const uint4 w = cw[h][j];
             float cacc[4] = {0.f, 0.f, 0.f, 0.f};
-            mma16816(cacc, codes_sub_h2(cw[j].x, false), codes_sub_h2(cw[j].z, false), codes_sub_h2(cw[j].x, true), codes_sub_h2(cw[j].z, true),
-                     X.x, X.y);
-            mma16816(cacc, codes_sub_h2(cw[j].y, false), codes_sub_h2(cw[j].w, false), codes_sub_h2(cw[j].y, true), codes_sub_h2(cw[j].w, true),
-                     X.z, X.w);
+            mma16816(cacc, codes_sub_h2(w.x, false), codes_sub_h2(w.z, false), codes_sub_h2(w.x, true), codes_sub_h2(w.z, true), X.x, X.y);
+            mma16816(cacc, codes_sub_h2(w.y, false), codes_sub_h2(w.w, false), codes_sub_h2(w.y, true), codes_sub_h2(w.w, true), X.z, X.w);
             a0 = fmaf(fmaf(cacc[0], 16777216.f, -xb[j]), dgs[j], a0);
             a1 = fmaf(fmaf(cacc[2], 16777216.f, -xb[j]), dg8s[j], a1);
           }
         }
-      }
-      ++it;
-      if (++slot == NST) {
-        slot = 0;
-        ph ^= 1u;
       }
     }
     if (cur != 0xffffffffu && t == 0) {
