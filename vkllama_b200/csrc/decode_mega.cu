@@ -31,7 +31,8 @@
 namespace vkl {
 namespace {
 
-constexpr int NCW = 15;                // consumer warps (+1 producer warp = 512 threads, 128 registers each)
+constexpr int WPG = 1;                 // consumer warps per group of a stage: each takes 4 / WPG of the group's blocks
+constexpr int NCW = 15 * WPG;          // consumer warps (+1 producer warp = 512 threads of 128 registers; two warps per group at 64 registers spill and run 1.6x slower)
 constexpr int CT = NCW * 32;           // consumer threads
 constexpr int THREADS = CT + 32;       // + producer warp
 constexpr int SG = (int)MEGA_SG;       // 4-block groups per ring stage: one per consumer warp
@@ -369,66 +370,47 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     for (uint32_t b = K / 32 + tid; b < kpad / 32; b += CT) xbias[b] = 0.f;
     cons_sync();
   }
+  // EPI_ADD: this thread's residual value, requested now so that its memory round trip is not
+  // on the path between the end of the stream and the grid barrier
+  float resid = 0.f;
+  if (op.epi == EPI_ADD && tid < tl * 16) {
+    const uint32_t n = (tile0 + (tid >> 4) * G) * 16 + (tid & 15);
+    if (n < op.N) resid = ldcg_h(op.out[0] + n);
+  }
   if (TIMED && tw) tw[1] = clock64();
 
   // ---- stream this CTA's row blocks. Every stage holds one group (4 blocks x 16 rows) per
   // consumer warp; stages run on across (tile, matrix) boundaries, so a warp's partial sums
   // of a row block go to the warp's own slot in shared memory when its groups move on to the
   // next row block, and nothing synchronises until the op's single reduction at the end.
-  // A loop iteration takes two stages: the waits, table reads, loads and slot releases of both
-  // are issued back to back (their latencies overlap) before the arithmetic of either, because a
-  // single warp runs its per-stage chain of dependent barrier and shared-memory operations at a
-  // fraction of the issue rate.
+  // WPG warps share a group: warp w takes blocks (w % WPG) * BPW .. of group w / WPG.
   {
+    constexpr int BPW = 4 / WPG;  // blocks per warp per stage
+    const uint32_t gi = warp / WPG, hb = (warp % WPG) * BPW;
     uint32_t cur = 0xffffffffu;
     float a0 = 0.f, a1 = 0.f;
     const uint32_t nstages = op_global.stages_per_cta[cta];
-    for (uint32_t sidx = 0; sidx < nstages; sidx += 2) {
-      const bool two = sidx + 1 < nstages;
-      const uint32_t slotA = slot, phA = ph;
-      if (++slot == NST) {
-        slot = 0;
-        ph ^= 1u;
-      }
-      const uint32_t slotB = slot, phB = ph;
-      if (two && ++slot == NST) {
-        slot = 0;
-        ph ^= 1u;
-      }
+    for (uint32_t sidx = 0; sidx < nstages; ++sidx) {
       unsigned long long w0 = 0;
       if (TIMED && tw) w0 = clock64();
-      bool ok[2];
-      ok[0] = c.wait(s32(&full[slotA]), phA, 1);
-      ok[1] = two && c.wait(s32(&full[slotB]), phB, 1);
+      const bool ok = c.wait(s32(&full[slot]), ph, 1);
       if (TIMED && tw) tw[0] += (clock64() - w0) * 1000ull / 1965ull;  // SM cycles -> ns at the 1965 MHz boost clock
-      // a stage's place in the op (row block, first group, run lengths) is in the producer's
+      // the stage's place in the op (row block, first group, run lengths) is in the producer's
       // table entry, which the producer wrote before it armed the stage's barrier
-      uint4 meta[2], cw[2][4], sv[2];
-      meta[0] = *reinterpret_cast<const uint4 *>(&tabs[it & 127].n0);
-      meta[1] = *reinterpret_cast<const uint4 *>(&tabs[(it + 1) & 127].n0);
-      const unsigned char *stA = ring + (size_t)slotA * STAGE_BYTES, *stB = ring + (size_t)slotB * STAGE_BYTES;
-      // every warp reads "its" group of the stage whether or not the stage has one for it
-      // (a short last stage): such bytes are never used
+      const uint4 meta = *reinterpret_cast<const uint4 *>(&tabs[it & 127].n0);
+      const uint32_t n0 = meta.x, n1 = meta.y, tm = meta.z, kg = meta.w;
+      const bool have = ok && gi < n0 + n1;
+      const uint32_t mt = gi < n0 ? tm : tm + 1, mk = gi < n0 ? kg + gi : gi - n0;
+      const unsigned char *st = ring + (size_t)slot * STAGE_BYTES;
+      uint4 cw[BPW], sv;
+      if (have) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) cw[0][j] = *reinterpret_cast<const uint4 *>(stA + (warp * 4 + j) * 512 + lane * 16);
-      sv[0] = *reinterpret_cast<const uint4 *>(stA + STAGE_CODES + warp * 128 + g * 16);
-      if (two) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) cw[1][j] = *reinterpret_cast<const uint4 *>(stB + (warp * 4 + j) * 512 + lane * 16);
-        sv[1] = *reinterpret_cast<const uint4 *>(stB + STAGE_CODES + warp * 128 + g * 16);
+        for (int j = 0; j < BPW; ++j) cw[j] = *reinterpret_cast<const uint4 *>(st + (gi * 4 + hb + j) * 512 + lane * 16);
+        sv = *reinterpret_cast<const uint4 *>(st + STAGE_CODES + gi * 128 + g * 16);
       }
       __syncwarp();
-      if (lane == 0) {  // ordered after this warp's reads of the stages
-        if (ok[0]) mbar_arrive(s32(&empty[slotA]));
-        if (ok[1]) mbar_arrive(s32(&empty[slotB]));
-      }
-      it += two ? 2u : 1u;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t n0 = meta[h].x, n1 = meta[h].y, tm = meta[h].z, kg = meta[h].w;
-        const bool have = ok[h] && warp < n0 + n1;
-        const uint32_t mt = warp < n0 ? tm : tm + 1, mk = warp < n0 ? kg + warp : warp - n0;
-        if (!have) continue;
+      if (lane == 0 && ok) mbar_arrive(s32(&empty[slot]));  // this warp has read all it needs from the stage
+      if (have) {
         if (mt != cur) {
           if (cur != 0xffffffffu && t == 0) {  // lanes t == 0 hold column 0 = token 0: rows g and g+8
             float *slotp = red + ((size_t)cur * NCW + warp) * 16;
@@ -439,33 +421,38 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
           a0 = a1 = 0.f;
         }
         if (DBG && (c.p.timing_mode & 4u)) {  // diagnostic: ring traffic without arithmetic
-          a0 += __uint_as_float(cw[h][0].x ^ cw[h][1].y ^ cw[h][2].z ^ cw[h][3].w ^ sv[h].x);
+          a0 += __uint_as_float(cw[0].x ^ cw[BPW - 1].y ^ sv.x);
         } else {
           // The stored codes u = q + 128 go into the MMA as fp16 subnormals u * 2^-24 (one byte
           // permute per pair, no arithmetic): products and their fp32 sums are exact up to the
           // accumulator's rounding, and sum_k u_k x_k = sum_k q_k x_k + 128 * sum_k x_k, so the
           // block result is 2^24 * acc - 128 * sum(x of the block). Token 0 is column 0 of B,
           // the other columns read zeros.
-          const __half *xp = g == 0 ? xs + mk * 128 + t * 8 : zero16;
+          const __half *xp = g == 0 ? xs + mk * 128 + hb * 32 + t * 8 : zero16;
           const uint32_t xstep = g == 0 ? 32u : 0u;
-          const float4 xb4 = *reinterpret_cast<const float4 *>(xbias + mk * 4);
-          const float xb[4] = {xb4.x, xb4.y, xb4.z, xb4.w};
-          const float2 da = __half22float2(*reinterpret_cast<const __half2 *>(&sv[h].x));
-          const float2 db = __half22float2(*reinterpret_cast<const __half2 *>(&sv[h].y));
-          const float2 ea = __half22float2(*reinterpret_cast<const __half2 *>(&sv[h].z));
-          const float2 eb = __half22float2(*reinterpret_cast<const __half2 *>(&sv[h].w));
-          const float dgs[4] = {da.x, da.y, db.x, db.y}, dg8s[4] = {ea.x, ea.y, eb.x, eb.y};
+          // block scales of the group: halves 0..3 = rows g, blocks 0..3; halves 4..7 = rows g+8
+          const uint32_t dg_lo = hb < 2 ? sv.x : sv.y, dg_hi = hb < 2 ? sv.z : sv.w;
+          const uint32_t dg_lo2 = sv.y, dg_hi2 = sv.w;  // blocks 2, 3 (used when a warp takes all four)
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < BPW; ++j) {
             const uint4 X = *reinterpret_cast<const uint4 *>(xp + j * xstep);
-            const uint4 w = cw[h][j];
+            const float xb = xbias[mk * 4 + hb + j];
+            const uint4 w = cw[j];
             float cacc[4] = {0.f, 0.f, 0.f, 0.f};
             mma16816(cacc, codes_sub_h2(w.x, false), codes_sub_h2(w.z, false), codes_sub_h2(w.x, true), codes_sub_h2(w.z, true), X.x, X.y);
             mma16816(cacc, codes_sub_h2(w.y, false), codes_sub_h2(w.w, false), codes_sub_h2(w.y, true), codes_sub_h2(w.w, true), X.z, X.w);
-            a0 = fmaf(fmaf(cacc[0], 16777216.f, -xb[j]), dgs[j], a0);
-            a1 = fmaf(fmaf(cacc[2], 16777216.f, -xb[j]), dg8s[j], a1);
+            const uint32_t lo = j < 2 ? dg_lo : dg_lo2, hi = j < 2 ? dg_hi : dg_hi2;
+            const float2 dl = __half22float2(*reinterpret_cast<const __half2 *>(&lo));
+            const float2 dh = __half22float2(*reinterpret_cast<const __half2 *>(&hi));
+            a0 = fmaf(fmaf(cacc[0], 16777216.f, -xb), (j & 1) ? dl.y : dl.x, a0);
+            a1 = fmaf(fmaf(cacc[2], 16777216.f, -xb), (j & 1) ? dh.y : dh.x, a1);
           }
         }
+      }
+      ++it;
+      if (++slot == NST) {
+        slot = 0;
+        ph ^= 1u;
       }
     }
     if (cur != 0xffffffffu && t == 0) {
@@ -496,7 +483,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
         const float gate = v[0], up = v[1];
         op.out[0][n] = __float2half_rn(gate / (1.0f + expf(-gate)) * up);
       } else if (op.epi == EPI_ADD) {
-        op.out[0][n] = __float2half_rn(round_h(v[0]) + ldcg_h(op.out[0] + n));
+        op.out[0][n] = __float2half_rn(round_h(v[0]) + (idx == tid ? resid : ldcg_h(op.out[0] + n)));
       } else if (op.epi == EPI_PARTIAL) {
         // this rank's share of a row-split projection: the raw fp32 sum goes into slot
         // [parity][my rank] of every rank's exchange buffer (plain peer stores over NVLink)
@@ -826,9 +813,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
   unsigned char *ring = smem;
   unsigned char *xq = smem + (size_t)NST * STAGE_BYTES;  // quantised input vector; attention scratch
   float *red = reinterpret_cast<float *>(xq + p.xs_bytes);
-  float *ssum = red + (size_t)p.red_slots * NCW * 16;  // [32]
-  const __half *zero16 = reinterpret_cast<const __half *>(ssum + 32);  // 16 zero bytes
-  MegaStage *tabs = reinterpret_cast<MegaStage *>(ssum + 36);  // [128], 16-byte aligned
+  float *ssum = red + (size_t)p.red_slots * NCW * 16;  // [64]
+  const __half *zero16 = reinterpret_cast<const __half *>(ssum + 64);  // 16 zero bytes
+  MegaStage *tabs = reinterpret_cast<MegaStage *>(ssum + 68);  // [128], 16-byte aligned
   uint64_t *full = reinterpret_cast<uint64_t *>(tabs + 128);
   uint64_t *empty = full + MAX_NST;
   volatile uint32_t *abort_s = reinterpret_cast<volatile uint32_t *>(empty + MAX_NST);
@@ -840,7 +827,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
     }
     abort_s[0] = 0;
     abort_s[1] = 0;
-    *reinterpret_cast<uint4 *>(ssum + 32) = make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4 *>(ssum + 64) = make_uint4(0, 0, 0, 0);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -966,7 +953,7 @@ size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t max
   return (b + 127) / 128 * 128;
 }
 size_t decode_mega_smem(size_t xs_bytes, uint32_t nst, uint32_t red_slots) {
-  return (size_t)nst * STAGE_BYTES + xs_bytes + ((size_t)red_slots * NCW * 16 + 36) * 4 + 128 * sizeof(MegaStage) + 2 * MAX_NST * 8 + 64;
+  return (size_t)nst * STAGE_BYTES + xs_bytes + ((size_t)red_slots * NCW * 16 + 68) * 4 + 128 * sizeof(MegaStage) + 2 * MAX_NST * 8 + 64;
 }
 int decode_mega_max_k() { return 16384; }
 int decode_mega_max_stages() { return MAX_NST; }
