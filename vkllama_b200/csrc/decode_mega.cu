@@ -132,7 +132,7 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
     if (lane == 0) {
       const uint32_t end = min(base + 32, n);
       for (; it < end; ++it) {
-        if (it >= NST && !c.wait(s32(&empty[slot]), ph ^ 1u, 2, 0)) {
+        if (it >= NST && !(p.timing_mode & 128u) && !c.wait(s32(&empty[slot]), ph ^ 1u, 2, 0)) {
           stop = true;
           break;
         }
@@ -393,8 +393,18 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     for (uint32_t sidx = 0; sidx < nstages; ++sidx) {
       unsigned long long w0 = 0;
       if (TIMED && tw) w0 = clock64();
-      const bool ok = c.wait(s32(&full[slot]), ph, 1);
+      const bool ok = (DBG && (c.p.timing_mode & 128u)) ? true : c.wait(s32(&full[slot]), ph, 1);
       if (TIMED && tw) tw[0] += (clock64() - w0) * 1000ull / 1965ull;  // SM cycles -> ns at the 1965 MHz boost clock
+      if (DBG && (c.p.timing_mode & 64u)) {  // diagnostic: handshake only
+        __syncwarp();
+        if (lane == 0 && !(c.p.timing_mode & 128u)) mbar_arrive(s32(&empty[slot]));
+        ++it;
+        if (++slot == NST) {
+          slot = 0;
+          ph ^= 1u;
+        }
+        continue;
+      }
       // the stage's place in the op (row block, first group, run lengths) is in the producer's
       // table entry, which the producer wrote before it armed the stage's barrier
       const uint4 meta = *reinterpret_cast<const uint4 *>(&tabs[it & 127].n0);
@@ -640,6 +650,36 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
   if (tid == 0) {
     part[D] = mloc;
     part[D + 1] = lloc;
+  }
+  if (S > 1 && p.attn_counters) {
+    // The split that finishes last merges the head's partials (in split order, so the result
+    // does not depend on who is last): no separate combine op and no grid barrier before it.
+    __threadfence();  // this thread's partial results before the CTA's arrival below
+    cons_sync();
+    volatile uint32_t *last_s = reinterpret_cast<volatile uint32_t *>(red_s);
+    if (tid == 0) {
+      uint32_t old;
+      asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.attn_counters + h) : "memory");
+      const bool last = old == S - 1;
+      if (last) p.attn_counters[h] = 0;  // all splits of the head have arrived; its next use is a grid barrier away
+      *last_s = last ? 1u : 0u;
+    }
+    cons_sync();
+    if (*last_s && tid < D) {
+      const float *base = p.attn_scratch + (size_t)h * p.splits * (D + 4);
+      float M = -INFINITY;
+      for (uint32_t sp = 0; sp < S; ++sp) M = fmaxf(M, __ldcg(base + sp * (D + 4) + D));
+      float den = 0.f, num = 0.f;
+      for (uint32_t sp = 0; sp < S; ++sp) {
+        const float ms = __ldcg(base + sp * (D + 4) + D), ls = __ldcg(base + sp * (D + 4) + D + 1);
+        if (ls > 0.f) {
+          const float w = expf(ms - M);
+          den += ls * w;
+          num += __ldcg(base + sp * (D + 4) + tid) * w;
+        }
+      }
+      p.ao[row + tid] = __float2half_rn(num / den);
+    }
   }
 }
 
@@ -962,7 +1002,7 @@ cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s) {
   if (p.nst < 2 || p.nst > (uint32_t)MAX_NST) return cudaErrorInvalidValue;
   const size_t smem = decode_mega_smem(p.xs_bytes, p.nst, p.red_slots);
   // the diagnostic switches (no weight copies, no arithmetic) are compiled into separate instances
-  const bool dbg = (p.timing_mode & 6u) != 0;
+  const bool dbg = (p.timing_mode & (2u | 4u | 64u | 128u)) != 0;
   auto kern = p.timing ? decode_mega_kernel<true, true> : dbg ? decode_mega_kernel<false, true> : decode_mega_kernel<false, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;

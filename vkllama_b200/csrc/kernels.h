@@ -175,7 +175,8 @@ struct MegaParams {
   uint32_t embd_rows;
   __half *x, *q, *k, *v, *ao;
   const float *freqc, *freqs;
-  float *attn_scratch;      // heads*splits*(head_dim+2)
+  float *attn_scratch;      // heads*splits*(head_dim+4): per (head, split) the un-normalised P.V row, its max and its sum
+  uint32_t *attn_counters;  // [heads] arrivals of a head's splits (the last one merges them), or null: separate combine op
   float *arg_scratch;       // grid*2
   unsigned long long *bar;  // [0] arrivals, [1] completed launches
   uint32_t *error;          // 0, or the code of the wait that timed out

@@ -386,11 +386,13 @@ int build_mega(vkl_model *m) {
     a.kcache = (__half *)y.kcache->data();
     a.vcache = (__half *)y.vcache->data();
     ops.push_back(a);
-    // VKLLAMA_DECODE_COMBINE=fused merges the split partials in o_proj's prologue instead of a
-    // combine op and its grid barrier; measured slower (every CTA re-reads all heads' partials)
+    // How the split partials of a head are merged (VKLLAMA_DECODE_COMBINE): "last" (default) = by
+    // the split CTA that finishes last, inside the attention op; "separate" = a combine op after a
+    // grid barrier; "fused" = in o_proj's prologue (measured slower: every CTA re-reads all partials).
     const char *cenv = getenv("VKLLAMA_DECODE_COMBINE");
     const bool fuse_combine = (m->head_dim % 8 == 0) && cenv && !strcmp(cenv, "fused");
-    if (!fuse_combine) {
+    const bool last_combine = !fuse_combine && !(cenv && !strcmp(cenv, "separate"));
+    if (!fuse_combine && !last_combine) {
       MegaOp cb = {};
       cb.kind = MK_ATTN_COMBINE;
       ops.push_back(cb);
@@ -471,7 +473,7 @@ int build_mega(vkl_model *m) {
   VKL_OKAY(tensor_new(m->dev, 1, 1, (ob + 3) / 4, VKL_UINT32, &m->mega_ops));
   VKL_OKAY(tensor_new(m->dev, 1, 1, 16, VKL_UINT32, &m->mega_sync));  // [0..3] barrier words, [4] error
   VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)G * 2, VKL_FP32, &m->mega_arg));
-  VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)m->heads_l * splits * (m->head_dim + 4), VKL_FP32, &m->mega_attn));
+  VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)m->heads_l * splits * (m->head_dim + 4) + m->heads_l, VKL_FP32, &m->mega_attn));
   VKL_CUDA(cudaMemcpyAsync(m->mega_ops->data(), ops.data(), ob, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaMemsetAsync(m->mega_sync->data(), 0, 64, m->stream));
   VKL_CUDA(cudaStreamSynchronize(m->stream));
@@ -498,6 +500,12 @@ int build_mega(vkl_model *m) {
   p.freqc = (const float *)m->fc->data();
   p.freqs = (const float *)m->fs->data();
   p.attn_scratch = (float *)m->mega_attn->data();
+  {
+    const char *cenv = getenv("VKLLAMA_DECODE_COMBINE");
+    const bool last_combine = !(cenv && (!strcmp(cenv, "separate") || (!strcmp(cenv, "fused") && m->head_dim % 8 == 0)));
+    p.attn_counters = last_combine ? (uint32_t *)(p.attn_scratch + (size_t)m->heads_l * splits * (m->head_dim + 4)) : nullptr;
+    VKL_CUDA(cudaMemsetAsync(p.attn_scratch + (size_t)m->heads_l * splits * (m->head_dim + 4), 0, (size_t)m->heads_l * 4, m->stream));
+  }
   p.arg_scratch = (float *)m->mega_arg->data();
   p.bar = (unsigned long long *)m->mega_sync->data();
   p.error = (uint32_t *)m->mega_sync->data() + 4;
@@ -507,7 +515,8 @@ int build_mega(vkl_model *m) {
   {
     p.nst = nst;
     p.red_slots = red_slots;
-    p.timing_mode = (getenv("VKLLAMA_DEBUG_NOCOPY") ? 2 : 0) | (getenv("VKLLAMA_DEBUG_NOMATH") ? 4 : 0);  // diagnostics
+    p.timing_mode = (getenv("VKLLAMA_DEBUG_NOCOPY") ? 2 : 0) | (getenv("VKLLAMA_DEBUG_NOMATH") ? 4 : 0) |
+                    (getenv("VKLLAMA_DEBUG_NOBODY") ? 64 : 0) | (getenv("VKLLAMA_DEBUG_NOHANDSHAKE") ? 128 : 0);  // diagnostics
     const char *bp = getenv("VKLLAMA_BARRIER_POLLERS");
     p.barrier_pollers = bp ? std::min(std::max((uint32_t)atoi(bp), 1u), 8u) : 1u;
     const uint32_t chunk_cap = ((c.maxlen + splits - 1) / splits + 31) & ~31u;
@@ -528,6 +537,7 @@ int check_mega(vkl_model *m) {
   VKL_CUDA(cudaStreamSynchronize(m->stream));
   if (err) {
     cudaMemsetAsync(m->mega_sync->data(), 0, 64, m->stream);
+    if (m->mp.attn_counters) cudaMemsetAsync(m->mp.attn_counters, 0, (size_t)m->heads_l * 4, m->stream);
     cudaStreamSynchronize(m->stream);
     return fail(VKL_INTERNAL, "decode kernel: a bounded wait ran out (code %u: 1 weight stage, 2 ring slot, 3 grid barrier)", err);
   }
@@ -986,7 +996,8 @@ int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float 
     MegaParams p = m->mp;
     p.timing = (unsigned long long *)buf;
     p.timing_mode = (getenv("VKLLAMA_DEBUG_PROLOGUE") ? 1 : 0) | (getenv("VKLLAMA_DEBUG_NOCOPY") ? 2 : 0) | (getenv("VKLLAMA_DEBUG_NOMATH") ? 4 : 0) | (getenv("VKLLAMA_DEBUG_EPILOGUE") ? 8 : 0) |
-                    (getenv("VKLLAMA_DEBUG_LOOP") ? 32 : 0);
+                    (getenv("VKLLAMA_DEBUG_LOOP") ? 32 : 0) | (getenv("VKLLAMA_DEBUG_NOBODY") ? 64 : 0) |
+                    (getenv("VKLLAMA_DEBUG_NOHANDSHAKE") ? 128 : 0);
     std::vector<unsigned long long> tl(3 * n);
     std::vector<MegaOp> ops(n);
     cudaError_t e = cudaMemsetAsync(buf, 0, n * 24, m->stream);
