@@ -75,6 +75,20 @@ __device__ __forceinline__ void st_rel_sys_u32(uint32_t *p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// ---- tagged activation words: fp16 value | (low 16 bits of the producing op's sequence number) << 16
+__device__ __forceinline__ uint32_t ll_pack(__half v, uint32_t tag) { return (uint32_t)__half_as_ushort(v) | (tag << 16); }
+__device__ __forceinline__ __half ll_half(uint32_t w) { return __ushort_as_half((unsigned short)(w & 0xffffu)); }
+__device__ __forceinline__ uint32_t ld_vol_u32(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_vol_v4(const uint32_t *p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ uint64_t ld_acq_u64(const unsigned long long *p) {
   uint64_t v;
   asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -105,6 +119,47 @@ struct Ctx {
     }
     raise(code);
     return false;
+  }
+  // One tagged word, polled (bounded) until its tag is `tag`. Returns the word; on a time-out
+  // or an abort returns what it last read (the caller's results are discarded on abort).
+  __device__ __forceinline__ uint32_t ll_wait1(const uint32_t *src, uint32_t tag) const {
+    uint32_t w = ld_vol_u32(src);
+    if ((w >> 16) == tag) return w;
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+      w = ld_vol_u32(src);
+      if ((w >> 16) == tag) return w;
+      if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || aborted())) {
+        *abort_s = 1;
+        return w;
+      }
+    }
+    raise(6);
+    return w;
+  }
+  // Eight consecutive tagged words (32-byte aligned) -> eight packed halves, polled the same way.
+  __device__ __forceinline__ bool ll_ready8(const uint4 &a, const uint4 &b, uint32_t tag) const {
+    return ((a.x >> 16) == tag) & ((a.y >> 16) == tag) & ((a.z >> 16) == tag) & ((a.w >> 16) == tag) & ((b.x >> 16) == tag) &
+           ((b.y >> 16) == tag) & ((b.z >> 16) == tag) & ((b.w >> 16) == tag);
+  }
+  __device__ __forceinline__ uint4 ll_wait8(const uint32_t *src, uint4 a, uint4 b, uint32_t tag) const {
+    if (!ll_ready8(a, b, tag)) {
+      bool ok = false;
+      for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        a = ld_vol_v4(src);
+        b = ld_vol_v4(src + 4);
+        if (ll_ready8(a, b, tag)) {
+          ok = true;
+          break;
+        }
+        if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || aborted())) {
+          *abort_s = 1;
+          ok = true;  // give up quietly: another wait has already raised the error
+          break;
+        }
+      }
+      if (!ok) raise(6);
+    }
+    return make_uint4((a.x & 0xffffu) | (a.y << 16), (a.z & 0xffffu) | (a.w << 16), (b.x & 0xffffu) | (b.y << 16), (b.z & 0xffffu) | (b.w << 16));
   }
 };
 
@@ -230,7 +285,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
                                           unsigned char *ring, uint64_t *full, uint64_t *empty, const MegaStage *tabs, __half *xs, float *xbias,
                                           const __half *zero16,
                                           float *red, float *ssum, Best &best, unsigned long long *tw, uint32_t ar_parity,
-                                          uint32_t combine_splits) {
+                                          uint32_t tag_in, uint32_t tag_out) {
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t G = gridDim.x, cta = blockIdx.x;
   // Scalars in registers: the barriers' memory clobbers would otherwise make every use
@@ -239,7 +294,8 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     uint32_t N, K, groups, nmat, tiles, epi, rot, track_argmax;
     const float *norm_w;
     float eps;
-    const __half *in;
+    const uint32_t *in;
+    uint32_t *out_ll[3];
     __half *out[3];
     float *out_f32;
   } op;
@@ -247,10 +303,14 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   op.tiles = op_global.tiles; op.epi = op_global.epi; op.rot = op_global.rot; op.track_argmax = op_global.track_argmax;
   op.norm_w = op_global.norm_w; op.eps = op_global.eps; op.in = op_global.in;
   op.out[0] = op_global.out[0]; op.out[1] = op_global.out[1]; op.out[2] = op_global.out[2];
+  op.out_ll[0] = op_global.out_ll[0]; op.out_ll[1] = op_global.out_ll[1]; op.out_ll[2] = op_global.out_ll[2];
   op.out_f32 = op_global.out_f32;
   const uint32_t K = op.K, groups = op.groups, nmat = op.nmat, tiles = op.tiles, NST = c.p.nst;
   const uint32_t tile0 = (cta + G - (op.rot % G)) % G;
   const uint32_t tl = tile0 < tiles ? (tiles - tile0 + G - 1) / G : 0u;  // this CTA's tiles
+  // No tile here: nothing to read either. (It must not wait for the input: nobody waits for this
+  // CTA's results, so by the time it looked the producers of a later op may have re-tagged the words.)
+  if (tl == 0) return;
   const uint32_t ntm = tl * nmat;                                        // (tile, matrix) row blocks of this CTA
   const uint32_t nstages_dbg = op_global.stages_per_cta[cta];
   // ---- input vector -> shared memory (RMSNorm fused, rounded to fp16 where the
@@ -263,45 +323,28 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     const bool norm = op.norm_w != nullptr;
     constexpr int NWV = 2;  // vectors per thread whose norm weights are requested early (K <= 7680: every norm op of the model shapes)
     float4 nw[NWV][2];
-    if (combine_splits) {
-      // The input is the attention output: merge the split partials of every head here (in
-      // split order, as the separate combine op does) instead of spending an op and a grid
-      // barrier on it. Vector i = 8 consecutive dims of head 8i / head_dim.
-      const MegaParams &pp = c.p;
-      const uint32_t D = pp.head_dim, ST = D + 4;
+    {
+      // the first loads together (one memory round trip when the producers are done), then the tag checks
+      constexpr int LFIRST = 3;  // K <= 11520 in one round trip
+      uint4 la[LFIRST], lb[LFIRST];
+#pragma unroll
+      for (int j = 0; j < LFIRST; ++j) {
+        const uint32_t i = tid + j * CT;
+        if (i < nv) {
+          la[j] = ld_vol_v4(op.in + 8 * i);
+          lb[j] = ld_vol_v4(op.in + 8 * i + 4);
+        }
+      }
 #pragma unroll
       for (int j = 0; j < MAXV; ++j) {
         const uint32_t i = tid + j * CT;
         v[j] = make_uint4(0, 0, 0, 0);
         if (i < nv) {
-          const uint32_t h = (8 * i) / D, d0 = (8 * i) % D;
-          const float *base = pp.attn_scratch + (size_t)h * pp.splits * ST;
-          float M = -INFINITY;
-          for (uint32_t sp = 0; sp < combine_splits; ++sp) M = fmaxf(M, __ldcg(base + sp * ST + D));
-          float den = 0.f, num[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (uint32_t sp = 0; sp < combine_splits; ++sp) {
-            const float2 ml = __ldcg(reinterpret_cast<const float2 *>(base + sp * ST + D));
-            if (ml.y > 0.f) {
-              const float w = expf(ml.x - M);
-              den += ml.y * w;
-              const float4 p0 = __ldcg(reinterpret_cast<const float4 *>(base + sp * ST + d0));
-              const float4 p1 = __ldcg(reinterpret_cast<const float4 *>(base + sp * ST + d0 + 4));
-              num[0] += p0.x * w; num[1] += p0.y * w; num[2] += p0.z * w; num[3] += p0.w * w;
-              num[4] += p1.x * w; num[5] += p1.y * w; num[6] += p1.z * w; num[7] += p1.w * w;
-            }
-          }
-          __half2 o[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) o[e] = __halves2half2(__float2half_rn(num[2 * e] / den), __float2half_rn(num[2 * e + 1] / den));
-          v[j] = *reinterpret_cast<uint4 *>(o);
+          if (j < LFIRST)
+            v[j] = c.ll_wait8(op.in + 8 * i, la[j], lb[j], tag_in);
+          else
+            v[j] = c.ll_wait8(op.in + 8 * i, ld_vol_v4(op.in + 8 * i), ld_vol_v4(op.in + 8 * i + 4), tag_in);
         }
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < MAXV; ++j) {
-        const uint32_t i = tid + j * CT;
-        v[j] = make_uint4(0, 0, 0, 0);
-        if (i < nv) v[j] = __ldcg(reinterpret_cast<const uint4 *>(op.in) + i);
       }
     }
     if (norm) {  // the norm weights do not depend on the reduction below: request them in the same round trip
@@ -375,7 +418,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   float resid = 0.f;
   if (op.epi == EPI_ADD && tid < tl * 16) {
     const uint32_t n = (tile0 + (tid >> 4) * G) * 16 + (tid & 15);
-    if (n < op.N) resid = ldcg_h(op.out[0] + n);
+    if (n < op.N) resid = __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
   }
   if (TIMED && tw) tw[1] = clock64();
 
@@ -491,9 +534,10 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     if (n < op.N && !c.aborted()) {
       if (op.epi == EPI_SWIGLU) {
         const float gate = v[0], up = v[1];
-        op.out[0][n] = __float2half_rn(gate / (1.0f + expf(-gate)) * up);
+        op.out_ll[0][n] = ll_pack(__float2half_rn(gate / (1.0f + expf(-gate)) * up), tag_out);
       } else if (op.epi == EPI_ADD) {
-        op.out[0][n] = __float2half_rn(round_h(v[0]) + (idx == tid ? resid : ldcg_h(op.out[0] + n)));
+        const float res = idx == tid ? resid : __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
+        op.out_ll[0][n] = ll_pack(__float2half_rn(round_h(v[0]) + res), tag_out);
       } else if (op.epi == EPI_PARTIAL) {
         // this rank's share of a row-split projection: the raw fp32 sum goes into slot
         // [parity][my rank] of every rank's exchange buffer (plain peer stores over NVLink)
@@ -503,9 +547,13 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
         __threadfence_system();
       } else {
         const __half h0 = __float2half_rn(v[0]);
-        op.out[0][n] = h0;
-        if (nmat > 1) op.out[1][n] = __float2half_rn(v[1]);
-        if (nmat > 2) op.out[2][n] = __float2half_rn(v[2]);
+        if (op.out_ll[0]) {
+          op.out_ll[0][n] = ll_pack(h0, tag_out);
+          if (nmat > 1) op.out_ll[1][n] = ll_pack(__float2half_rn(v[1]), tag_out);
+          if (nmat > 2) op.out_ll[2][n] = ll_pack(__float2half_rn(v[2]), tag_out);
+        } else {
+          op.out[0][n] = h0;
+        }
         if (op.out_f32) op.out_f32[n] = __half2float(h0);
         if (op.track_argmax && better(__half2float(h0), n, best)) {
           best.v = __half2float(h0);
@@ -525,12 +573,14 @@ __device__ __forceinline__ void rope_pair(float x0, float x1, float cs, float sn
 // One (head, split) per CTA: RoPE(q), RoPE(k) + cache append by the split that
 // owns the new column, scores over its column range, partial softmax and P.V.
 // Same arithmetic as attention_kernel<true> (attention.cu).
-__device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, float *sm, uint32_t pos0, uint32_t S) {
+__device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, float *sm, uint32_t pos0, uint32_t S, uint32_t tag_in,
+                                             uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t cta = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (cta >= p.heads * S) return;
   const uint32_t h = cta / S, split = cta % S, D = p.head_dim;
-  float *q_s = sm, *kn_s = sm + D, *red_s = sm + 2 * D, *s_s = sm + (2 + NCW / 2) * D + 2 * NCW + 32;
+  float *q_s = sm, *kn_s = sm + D, *red_s = sm + 3 * D, *s_s = sm + (3 + NCW / 2) * D + 2 * NCW + 32;
+  uint32_t *vn_s = reinterpret_cast<uint32_t *>(sm + 2 * D);  // the new V row as packed half pairs
   const uint32_t L = min(pos0 + 1, p.maxlen);
   uint32_t chunk = (L + S - 1) / S;
   chunk = (chunk + 31) & ~31u;
@@ -542,18 +592,23 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
     const size_t fi = (size_t)pos0 * (D / 2) + tid;
     const float cs = p.freqc[fi], sn = p.freqs[fi];
     __half r0, r1;
-    rope_pair(ldcg_h(p.q + row + 2 * tid), ldcg_h(p.q + row + 2 * tid + 1), cs, sn, r0, r1);
+    // q, k, v of this head come from the projection op before: wait for its tagged words
+    rope_pair(__half2float(ll_half(c.ll_wait1(p.q + row + 2 * tid, tag_in))), __half2float(ll_half(c.ll_wait1(p.q + row + 2 * tid + 1, tag_in))), cs,
+              sn, r0, r1);
     q_s[2 * tid] = __half2float(r0);
     q_s[2 * tid + 1] = __half2float(r1);
     if (owns) {
-      rope_pair(ldcg_h(p.k + row + 2 * tid), ldcg_h(p.k + row + 2 * tid + 1), cs, sn, r0, r1);
+      rope_pair(__half2float(ll_half(c.ll_wait1(p.k + row + 2 * tid, tag_in))), __half2float(ll_half(c.ll_wait1(p.k + row + 2 * tid + 1, tag_in))),
+                cs, sn, r0, r1);
       kn_s[2 * tid] = __half2float(r0);
       kn_s[2 * tid + 1] = __half2float(r1);
       const size_t dst = ((size_t)h * p.maxlen + jn) * D + 2 * tid;
       op.kcache[dst] = r0;
       op.kcache[dst + 1] = r1;
-      op.vcache[dst] = __ushort_as_half(__ldcg(reinterpret_cast<const unsigned short *>(p.v + row + 2 * tid)));
-      op.vcache[dst + 1] = __ushort_as_half(__ldcg(reinterpret_cast<const unsigned short *>(p.v + row + 2 * tid + 1)));
+      const __half v0 = ll_half(c.ll_wait1(p.v + row + 2 * tid, tag_in)), v1 = ll_half(c.ll_wait1(p.v + row + 2 * tid + 1, tag_in));
+      op.vcache[dst] = v0;
+      op.vcache[dst + 1] = v1;
+      vn_s[tid] = (uint32_t)__half_as_ushort(v0) | ((uint32_t)__half_as_ushort(v1) << 16);  // the new row, for this CTA's P.V
     }
   }
   cons_sync();
@@ -615,7 +670,7 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
         const uint32_t j = jb + u * NG;
         raw[u] = 0;
         if (j < c1)
-          raw[u] = (owns && j == jn) ? __ldcg(reinterpret_cast<const unsigned int *>(p.v + row + 2 * dp))
+          raw[u] = (owns && j == jn) ? vn_s[dp]
                                      : __ldg(reinterpret_cast<const unsigned int *>(vc + (size_t)j * D));
       }
 #pragma unroll
@@ -643,7 +698,7 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
 #pragma unroll
     for (int gq = 0; gq < CT / 64; ++gq) s += pv[gq * D + tid];
     if (S == 1)
-      p.ao[row + tid] = __float2half_rn(s / lloc);  // whole row in this CTA: no combine phase
+      p.ao[row + tid] = ll_pack(__float2half_rn(s / lloc), tag_out);  // whole row in this CTA: no combine phase
     else
       part[tid] = s;
   }
@@ -678,13 +733,13 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
           num += __ldcg(base + sp * (D + 4) + tid) * w;
         }
       }
-      p.ao[row + tid] = __float2half_rn(num / den);
+      p.ao[row + tid] = ll_pack(__float2half_rn(num / den), tag_out);
     }
   }
 }
 
 // One head per CTA: merge the split partials in split order.
-__device__ __forceinline__ void attn_combine_op(const Ctx &c, uint32_t) {
+__device__ __forceinline__ void attn_combine_op(const Ctx &c, uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t h = blockIdx.x, tid = threadIdx.x, D = p.head_dim;
   if (h >= p.heads || tid >= D) return;
@@ -700,11 +755,11 @@ __device__ __forceinline__ void attn_combine_op(const Ctx &c, uint32_t) {
       num += __ldcg(base + s * (D + 4) + tid) * w;
     }
   }
-  p.ao[(size_t)h * D + tid] = __float2half_rn(num / den);
+  p.ao[(size_t)h * D + tid] = ll_pack(__float2half_rn(num / den), tag_out);
 }
 
 // Embedding gather + dequantisation of the current token (embedding_q8_0.comp:39-85).
-__device__ __forceinline__ void embed_op(const Ctx &c, uint32_t tok) {
+__device__ __forceinline__ void embed_op(const Ctx &c, uint32_t tok, uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t per = (p.dim + gridDim.x - 1) / gridDim.x;
   const uint32_t k = blockIdx.x * per + threadIdx.x;
@@ -716,12 +771,13 @@ __device__ __forceinline__ void embed_op(const Ctx &c, uint32_t tok) {
   const uint8_t cb = p.embd[(((size_t)tile * L.groups * 4 + b) * 32 + g * 4 + t) * 16 + half * 8 + q8_byte_pos(i)];
   const uint16_t *sc = reinterpret_cast<const uint16_t *>(p.embd + L.codes_bytes());
   const uint16_t d = sc[(((size_t)tile * L.groups + (b >> 2)) * 8 + g) * 8 + half * 4 + (b & 3)];
-  p.x[k] = __float2half_rn((float)((int)cb - 128) * __half2float(__ushort_as_half(d)));
+  p.x[k] = ll_pack(__float2half_rn((float)((int)cb - 128) * __half2float(__ushort_as_half(d))), tag_out);
 }
 
 // CTA 0: best of the per-CTA candidates (lowest index on ties), then publish the id,
 // feed it back and advance position, step and launch epoch.
-__device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_t pos0, uint64_t rounds_done, uint32_t ar_done) {
+__device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_t pos0, uint64_t rounds_done, uint32_t ar_done,
+                                                uint32_t next_ebase) {
   const MegaParams &p = c.p;
   if (blockIdx.x != 0) return;
   const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -803,6 +859,7 @@ __device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_
       }
       p.state[0] = pos0 + 1;
       p.state[3] = ar_done;
+      p.state[7] = next_ebase;
       p.bar[1] = rounds_done;
     }
   }
@@ -813,7 +870,7 @@ __device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_
 // CTA 0 tells every rank "my partials for sequence `seq` are out"; every CTA waits
 // (bounded) until all ranks have said so, then reduces its slice of rows in rank order:
 // x <- fp16( fp16(sum_r partial_r) + x ), the same rounding as o_proj/down + residual add.
-__device__ __forceinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t seq) {
+__device__ __forceinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t seq, uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t tid = threadIdx.x, tp = p.tp_size;
   uint32_t *my_flags = static_cast<uint32_t *>(p.tp_peer[p.tp_rank]) + p.tp_flag_off;
@@ -842,7 +899,8 @@ __device__ __forceinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uin
     const float *part = static_cast<const float *>(p.tp_peer[p.tp_rank]) + (size_t)(seq & 1u) * tp * p.dim;
     float s = 0.f;
     for (uint32_t r = 0; r < tp; ++r) s += __ldcg(part + (size_t)r * p.dim + i);
-    op.out[0][i] = __float2half_rn(round_h(s) + ldcg_h(op.out[0] + i));
+    const float res = __half2float(ll_half(ld_vol_u32(op.out_ll[0] + i)));  // the residual, whatever op tagged it
+    op.out_ll[0][i] = ll_pack(__float2half_rn(round_h(s) + res), tag_out);
   }
 }
 
@@ -888,6 +946,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
   const uint32_t Lnow = min(pos0 + 1, p.maxlen);
   const uint32_t S_eff = Lnow <= p.single_split_len ? 1u : p.splits;
   uint32_t it = 0, slot = 0, ph = 0;  // ring position, carried across the ops of the token
+  const uint32_t ebase = p.state[7];  // sequence number of this launch's first op; op oi tags its results with ebase + oi
+  auto tag = [&](uint32_t op_index) { return (ebase + op_index) & 0xffffu; };
   Best best = {0.f, 0xffffffffu};
   const bool timed = TIMED && p.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
   unsigned long long t0 = 0, twait[3] = {0, 0, 0}, c0 = 0;
@@ -897,18 +957,18 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
     if (op.kind == MK_ATTN_COMBINE && S_eff == 1) continue;  // nothing to merge, no barrier either
     if (timed) c0 = clock64();
     switch (op.kind) {
-      case MK_EMBED: embed_op(c, tok); break;
+      case MK_EMBED: embed_op(c, tok, tag(oi)); break;
       case MK_MATVEC: matvec_op<TIMED, DBG>(c, op, it, slot, ph, ring, full, empty, tabs, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_groups * 256), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, (seq0 + ar_i + 1) & 1u,
-                         (op.combine_in && S_eff > 1) ? p.splits : 0u);
+                         tag(op.src_op), tag(oi));
         break;
-      case MK_ATTN_PART: attn_part_op(c, op, reinterpret_cast<float *>(xq), pos0, S_eff); break;
-      case MK_ATTN_COMBINE: attn_combine_op(c, pos0); break;
+      case MK_ATTN_PART: attn_part_op(c, op, reinterpret_cast<float *>(xq), pos0, S_eff, tag(op.src_op), tag(op.tag_op)); break;
+      case MK_ATTN_COMBINE: attn_combine_op(c, tag(oi)); break;
       case MK_ALLREDUCE:
         ++ar_i;
-        allreduce_op(c, op, seq0 + ar_i);
+        allreduce_op(c, op, seq0 + ar_i, tag(oi));
         break;
       case MK_ARGMAX:
-        argmax_final_op(c, reinterpret_cast<float *>(xq), pos0, base_rounds + rounds, seq0 + ar_i);
+        argmax_final_op(c, reinterpret_cast<float *>(xq), pos0, base_rounds + rounds, seq0 + ar_i, ebase + p.nops);
         break;
     }
     if (op.kind == MK_MATVEC && op.track_argmax) {
@@ -964,8 +1024,12 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
           asm volatile("prefetch.global.L2 [%0];" ::"l"(vb + o));
         }
       }
-      ++rounds;
-      grid_barrier(c, (base_rounds + rounds) * G, (uint32_t)rounds, abort_s + 1);
+      if (op.barrier_after) {
+        ++rounds;
+        grid_barrier(c, (base_rounds + rounds) * G, (uint32_t)rounds, abort_s + 1);
+      } else {
+        cons_sync();  // the next op reuses this one's shared memory; its input words carry their own arrival tags
+      }
     }
     if (timed) {
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t2));
@@ -988,7 +1052,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
 size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits) {
   size_t x = (size_t)max_groups * (128 * 2 + 4 * 4);  // fp16 input + one fp32 bias term per block
   uint32_t chunk = ((maxlen + splits - 1) / splits + 31) & ~31u;
-  size_t a = (size_t)((2 + NCW / 2) * head_dim + 2 * NCW + 32 + chunk + 32) * 4;
+  size_t a = (size_t)((3 + NCW / 2) * head_dim + 2 * NCW + 32 + chunk + 32) * 4;
   size_t b = x > a ? x : a;
   return (b + 127) / 128 * 128;
 }

@@ -117,10 +117,17 @@ struct MegaOp {
   const float *norm_w;  // fused RMSNorm of the input, or null
   float eps;
   uint32_t track_argmax;  // lm head: keep a per-CTA (max, index) candidate
-  uint32_t combine_in;    // the input is the attention output: merge the split partials in the prologue
   const uint32_t *stages_per_cta;  // [grid]: ring stages of this op per CTA
-  const __half *in;       // input vector [K]
-  __half *out[3];         // EPI_ADD: out[0] is also the residual
+  // Activations that cross CTAs inside a token live in "tagged" buffers: one 32-bit word per
+  // element, fp16 value in the low half and the low 16 bits of the producing op's sequence
+  // number in the high half. A reader that knows which op produced its input polls the words
+  // until every tag matches: the data is its own arrival flag, so most ops need no grid barrier.
+  const uint32_t *in;     // input vector [K], tagged words
+  uint32_t src_op;        // index of the op that produced `in` (MK_ATTN_PART: of the op that produced q, k, v)
+  uint32_t tag_op;        // index of the op whose tag this op's tagged results carry (its own, unless a skipped op is expected)
+  uint32_t barrier_after; // a grid barrier follows this op (its results are not tagged, or the next op needs one)
+  uint32_t *out_ll[3];    // tagged outputs; EPI_ADD: out_ll[0] is also the residual
+  __half *out[3];         // plain fp16 outputs (lm head)
   float *out_f32;
   __half *kcache, *vcache;  // MK_ATTN_PART
 };
@@ -166,14 +173,14 @@ struct MegaParams {
   uint32_t stage_stride;
   uint32_t nops, nbarriers;
   uint32_t *state;    // [0] position, [1] step, [2] picked id, [3] all-reduces done, [4] arg-max exchanges done,
-                      // [5] number of forced (prompt) tokens
+                      // [5] number of forced (prompt) tokens, [6] prefill GEMM error, [7] sequence number of the next launch's first op
   const uint32_t *forced;  // prompt ids: while position+1 < state[5] the next input is forced[position+1]
   uint32_t *tok;      // current token id
   uint32_t *out_ids;
   uint32_t out_cap;
   const uint8_t *embd;  // token embedding, Q8_0 tiled planes
   uint32_t embd_rows;
-  __half *x, *q, *k, *v, *ao;
+  uint32_t *x, *q, *k, *v, *ao;  // tagged words (see MegaOp)
   const float *freqc, *freqs;
   float *attn_scratch;      // heads*splits*(head_dim+4): per (head, split) the un-normalised P.V row, its max and its sum
   uint32_t *attn_counters;  // [heads] arrivals of a head's splits (the last one merges them), or null: separate combine op

@@ -78,7 +78,7 @@ struct vkl_model {
   // persistent single-kernel decode step (decode_mega.cu)
   bool mega_ready = false, mega_tried = false;
   int mega_grid = 0;
-  vkl_tensor *mega_ops = nullptr, *mega_sync = nullptr, *mega_arg = nullptr, *mega_attn = nullptr, *mega_stages = nullptr, *mega_counts = nullptr;
+  vkl_tensor *mega_ops = nullptr, *mega_sync = nullptr, *mega_arg = nullptr, *mega_attn = nullptr, *mega_stages = nullptr, *mega_counts = nullptr, *mega_ll = nullptr;
   MegaParams mp;
   uint32_t mega_launches_per_token = 1;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
@@ -90,7 +90,7 @@ struct vkl_model {
     if (tp_buf) cudaFree(tp_buf);
     for (auto &l : L)
       for (vkl_tensor *p : {l.attn_norm, l.ffn_norm, l.wq, l.wk, l.wv, l.wo, l.gate, l.up, l.down, l.kcache, l.vcache}) vkl_tensor_release(p);
-    for (vkl_tensor *p : {tok_embd, output_norm, output, fc, fs, x, xn, q, k, v, ao, t, gu32, logits16, logits32, toks, state, out_ids, forced, argpart, attn_scratch, attn_counters, mega_ops, mega_sync, mega_arg, mega_attn, mega_stages, mega_counts})
+    for (vkl_tensor *p : {tok_embd, output_norm, output, fc, fs, x, xn, q, k, v, ao, t, gu32, logits16, logits32, toks, state, out_ids, forced, argpart, attn_scratch, attn_counters, mega_ops, mega_sync, mega_arg, mega_attn, mega_stages, mega_counts, mega_ll})
       vkl_tensor_release(p);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
@@ -111,7 +111,7 @@ int ensure_rows(vkl_model *m, uint32_t T) {
   }
   VKL_CUDA(cudaStreamSynchronize(m->stream));
   if (m->mega_tried) {  // the op table of the persistent kernel holds the old buffers too
-    for (vkl_tensor **t : {&m->mega_ops, &m->mega_sync, &m->mega_arg, &m->mega_attn, &m->mega_stages, &m->mega_counts}) {
+    for (vkl_tensor **t : {&m->mega_ops, &m->mega_sync, &m->mega_arg, &m->mega_attn, &m->mega_stages, &m->mega_counts, &m->mega_ll}) {
       vkl_tensor_release(*t);
       *t = nullptr;
     }
@@ -348,7 +348,19 @@ int build_mega(vkl_model *m) {
 
   std::vector<MegaOp> ops;
   uint32_t rot = 0;
-  auto matvec = [&](std::initializer_list<const vkl_tensor *> ws, const float *norm, float eps, const __half *in, std::initializer_list<__half *> outs, int epi) {
+  // Tagged activation buffers of the kernel (one 32-bit word per element): x [dim], k, q, v and the
+  // attention output [dim_l each], the SwiGLU output [ffn_l].
+  const size_t ll_words = (size_t)c.dim + 4 * (size_t)m->dim_l + m->ffn_l;
+  VKL_OKAY(tensor_new(m->dev, 1, 1, ll_words, VKL_UINT32, &m->mega_ll));
+  VKL_CUDA(cudaMemsetAsync(m->mega_ll->data(), 0, ll_words * 4, m->stream));
+  {  // no op of the first launches may expect tag 0, the tag of the zeroed words
+    const uint32_t one = 1;
+    VKL_CUDA(cudaMemcpyAsync((uint32_t *)m->state->data() + 7, &one, 4, cudaMemcpyHostToDevice, m->stream));
+  }
+  uint32_t *x = (uint32_t *)m->mega_ll->data(), *kb = x + c.dim, *qb = kb + m->dim_l, *vb = qb + m->dim_l, *ao = vb + m->dim_l, *tb = ao + m->dim_l;
+  uint32_t x_writer = 0;  // index of the op that last wrote the residual stream x
+  auto matvec = [&](std::initializer_list<const vkl_tensor *> ws, const float *norm, float eps, const uint32_t *in, uint32_t src_op,
+                    std::initializer_list<uint32_t *> outs, int epi) {
     MegaOp o = {};
     o.kind = MK_MATVEC;
     o.epi = epi;
@@ -365,55 +377,65 @@ int build_mega(vkl_model *m) {
       ++i;
     }
     i = 0;
-    for (__half *p : outs) o.out[i++] = p;
+    for (uint32_t *p : outs) o.out_ll[i++] = p;
     o.norm_w = norm;
     o.eps = eps;
     o.in = in;
+    o.src_op = src_op;
+    o.tag_op = (uint32_t)ops.size();
+    o.barrier_after = epi == EPI_PARTIAL ? 1u : 0u;  // raw fp32 partials for the all-reduce are not tagged
     o.rot = rot;
     rot = (rot + o.tiles) % (uint32_t)G;
     ops.push_back(o);
+    return (uint32_t)ops.size() - 1;
   };
-  __half *x = (__half *)m->x->data(), *qb = (__half *)m->q->data(), *kb = (__half *)m->k->data(), *vb = (__half *)m->v->data();
-  __half *ao = (__half *)m->ao->data(), *tb = (__half *)m->t->data();
+  // How the split partials of a head are merged (VKLLAMA_DECODE_COMBINE): "last" (default) = by the
+  // split CTA that finishes last, inside the attention op; "separate" = a combine op after a grid barrier.
+  const char *cenv = getenv("VKLLAMA_DECODE_COMBINE");
+  const bool last_combine = !(cenv && !strcmp(cenv, "separate"));
   MegaOp e = {};
   e.kind = MK_EMBED;
-  ops.push_back(e);
+  ops.push_back(e);  // op 0 writes x
   for (uint32_t l = 0; l < c.layers; ++l) {
     Layer &y = m->L[l];
-    matvec({y.wk, y.wq, y.wv}, (const float *)y.attn_norm->data(), c.eps, x, {kb, qb, vb}, EPI_PLAIN);
+    const uint32_t qkv = matvec({y.wk, y.wq, y.wv}, (const float *)y.attn_norm->data(), c.eps, x, x_writer, {kb, qb, vb}, EPI_PLAIN);
     MegaOp a = {};
     a.kind = MK_ATTN_PART;
     a.kcache = (__half *)y.kcache->data();
     a.vcache = (__half *)y.vcache->data();
+    a.src_op = qkv;
+    // with one split per head the attention op writes the output itself, under the tag the reader expects
+    a.tag_op = (uint32_t)ops.size() + (last_combine ? 0u : 1u);
+    a.barrier_after = last_combine ? 0u : 1u;
     ops.push_back(a);
-    // How the split partials of a head are merged (VKLLAMA_DECODE_COMBINE): "last" (default) = by
-    // the split CTA that finishes last, inside the attention op; "separate" = a combine op after a
-    // grid barrier; "fused" = in o_proj's prologue (measured slower: every CTA re-reads all partials).
-    const char *cenv = getenv("VKLLAMA_DECODE_COMBINE");
-    const bool fuse_combine = (m->head_dim % 8 == 0) && cenv && !strcmp(cenv, "fused");
-    const bool last_combine = !fuse_combine && !(cenv && !strcmp(cenv, "separate"));
-    if (!fuse_combine && !last_combine) {
+    uint32_t ao_writer = (uint32_t)ops.size() - 1;
+    if (!last_combine) {
       MegaOp cb = {};
       cb.kind = MK_ATTN_COMBINE;
+      cb.tag_op = (uint32_t)ops.size();
       ops.push_back(cb);
+      ao_writer = (uint32_t)ops.size() - 1;
     }
     auto allreduce = [&]() {
       MegaOp r = {};
       r.kind = MK_ALLREDUCE;
       r.N = c.dim;
-      r.out[0] = x;
+      r.out_ll[0] = x;
+      r.tag_op = (uint32_t)ops.size();
       ops.push_back(r);
+      return (uint32_t)ops.size() - 1;
     };
-    matvec({y.wo}, nullptr, 0.f, ao, {x}, tp > 1 ? EPI_PARTIAL : EPI_ADD);
-    ops.back().combine_in = fuse_combine ? 1u : 0u;
-    if (tp > 1) allreduce();
-    matvec({y.gate, y.up}, (const float *)y.ffn_norm->data(), c.eps, x, {tb}, EPI_SWIGLU);
-    matvec({y.down}, nullptr, 0.f, tb, {x}, tp > 1 ? EPI_PARTIAL : EPI_ADD);
-    if (tp > 1) allreduce();
+    x_writer = matvec({y.wo}, nullptr, 0.f, ao, ao_writer, {x}, tp > 1 ? EPI_PARTIAL : EPI_ADD);
+    if (tp > 1) x_writer = allreduce();
+    const uint32_t gu = matvec({y.gate, y.up}, (const float *)y.ffn_norm->data(), c.eps, x, x_writer, {tb}, EPI_SWIGLU);
+    x_writer = matvec({y.down}, nullptr, 0.f, tb, gu, {x}, tp > 1 ? EPI_PARTIAL : EPI_ADD);
+    if (tp > 1) x_writer = allreduce();
   }
-  matvec({m->output}, (const float *)m->output_norm->data(), c.final_eps, x, {(__half *)m->logits16->data()}, EPI_PLAIN);
+  matvec({m->output}, (const float *)m->output_norm->data(), c.final_eps, x, x_writer, {}, EPI_PLAIN);
+  ops.back().out[0] = (__half *)m->logits16->data();  // plain fp16 + fp32 logits and arg-max candidates: a grid barrier follows
   ops.back().out_f32 = (float *)m->logits32->data();
   ops.back().track_argmax = 1;
+  ops.back().barrier_after = 1;
   MegaOp am = {};
   am.kind = MK_ARGMAX;
   ops.push_back(am);
@@ -496,13 +518,13 @@ int build_mega(vkl_model *m) {
   p.out_cap = m->out_cap;
   p.embd = m->tok_embd->data();
   p.embd_rows = (uint32_t)m->tok_embd->h;
-  p.x = x; p.q = qb; p.k = kb; p.v = vb; p.ao = ao;
+  p.x = x; p.q = qb; p.k = kb; p.v = vb; p.ao = ao;  // tagged words
   p.freqc = (const float *)m->fc->data();
   p.freqs = (const float *)m->fs->data();
   p.attn_scratch = (float *)m->mega_attn->data();
   {
     const char *cenv = getenv("VKLLAMA_DECODE_COMBINE");
-    const bool last_combine = !(cenv && (!strcmp(cenv, "separate") || (!strcmp(cenv, "fused") && m->head_dim % 8 == 0)));
+    const bool last_combine = !(cenv && !strcmp(cenv, "separate"));
     p.attn_counters = last_combine ? (uint32_t *)(p.attn_scratch + (size_t)m->heads_l * splits * (m->head_dim + 4)) : nullptr;
     VKL_CUDA(cudaMemsetAsync(p.attn_scratch + (size_t)m->heads_l * splits * (m->head_dim + 4), 0, (size_t)m->heads_l * 4, m->stream));
   }
@@ -528,6 +550,8 @@ int build_mega(vkl_model *m) {
   return VKL_OK;
 }
 
+__global__ void bump_sequence_kernel(uint32_t *seq, uint32_t by) { *seq += by; }
+
 // After a batch of decode launches: a wait that timed out inside the kernel is
 // reported as an error and the barrier words are reset.
 int check_mega(vkl_model *m) {
@@ -538,8 +562,10 @@ int check_mega(vkl_model *m) {
   if (err) {
     cudaMemsetAsync(m->mega_sync->data(), 0, 64, m->stream);
     if (m->mp.attn_counters) cudaMemsetAsync(m->mp.attn_counters, 0, (size_t)m->heads_l * 4, m->stream);
+    // the aborted launch did not advance the ops' sequence base: words it tagged must not look current
+    bump_sequence_kernel<<<1, 1, 0, m->stream>>>((uint32_t *)m->state->data() + 7, m->mp.nops);
     cudaStreamSynchronize(m->stream);
-    return fail(VKL_INTERNAL, "decode kernel: a bounded wait ran out (code %u: 1 weight stage, 2 ring slot, 3 grid barrier)", err);
+    return fail(VKL_INTERNAL, "decode kernel: a bounded wait ran out (code %u: 1 weight stage, 2 ring slot, 3 grid barrier, 4 all-reduce, 5 arg-max exchange, 6 tagged input)", err);
   }
   return VKL_OK;
 }
