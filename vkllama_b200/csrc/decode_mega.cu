@@ -83,6 +83,11 @@ __device__ __forceinline__ uint32_t ld_vol_u32(const uint32_t *p) {
   asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint2 ld_vol_v2(const uint32_t *p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ uint4 ld_vol_v4(const uint32_t *p) {
   uint4 v;
   asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
@@ -128,6 +133,20 @@ struct Ctx {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
       w = ld_vol_u32(src);
       if ((w >> 16) == tag) return w;
+      if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || aborted())) {
+        *abort_s = 1;
+        return w;
+      }
+    }
+    raise(6);
+    return w;
+  }
+  // Two consecutive tagged words (8-byte aligned), already requested once.
+  __device__ __forceinline__ uint2 ll_wait2(const uint32_t *src, uint2 w, uint32_t tag) const {
+    if (((w.x >> 16) == tag) & ((w.y >> 16) == tag)) return w;
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+      w = ld_vol_v2(src);
+      if (((w.x >> 16) == tag) & ((w.y >> 16) == tag)) return w;
       if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || aborted())) {
         *abort_s = 1;
         return w;
@@ -592,23 +611,30 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
     const size_t fi = (size_t)pos0 * (D / 2) + tid;
     const float cs = p.freqc[fi], sn = p.freqs[fi];
     __half r0, r1;
-    // q, k, v of this head come from the projection op before: wait for its tagged words
-    rope_pair(__half2float(ll_half(c.ll_wait1(p.q + row + 2 * tid, tag_in))), __half2float(ll_half(c.ll_wait1(p.q + row + 2 * tid + 1, tag_in))), cs,
-              sn, r0, r1);
+    // q, k, v of this head come from the projection op before: request this thread's pairs of
+    // tagged words together (one memory round trip when they are there), then poll what is missing
+    const uint32_t *qp = p.q + row + 2 * tid, *kp = p.k + row + 2 * tid, *vp = p.v + row + 2 * tid;
+    uint2 qw = ld_vol_v2(qp), kw = make_uint2(0, 0), vw = make_uint2(0, 0);
+    if (owns) {
+      kw = ld_vol_v2(kp);
+      vw = ld_vol_v2(vp);
+    }
+    qw = c.ll_wait2(qp, qw, tag_in);
+    rope_pair(__half2float(ll_half(qw.x)), __half2float(ll_half(qw.y)), cs, sn, r0, r1);
     q_s[2 * tid] = __half2float(r0);
     q_s[2 * tid + 1] = __half2float(r1);
     if (owns) {
-      rope_pair(__half2float(ll_half(c.ll_wait1(p.k + row + 2 * tid, tag_in))), __half2float(ll_half(c.ll_wait1(p.k + row + 2 * tid + 1, tag_in))),
-                cs, sn, r0, r1);
+      kw = c.ll_wait2(kp, kw, tag_in);
+      vw = c.ll_wait2(vp, vw, tag_in);
+      rope_pair(__half2float(ll_half(kw.x)), __half2float(ll_half(kw.y)), cs, sn, r0, r1);
       kn_s[2 * tid] = __half2float(r0);
       kn_s[2 * tid + 1] = __half2float(r1);
       const size_t dst = ((size_t)h * p.maxlen + jn) * D + 2 * tid;
       op.kcache[dst] = r0;
       op.kcache[dst + 1] = r1;
-      const __half v0 = ll_half(c.ll_wait1(p.v + row + 2 * tid, tag_in)), v1 = ll_half(c.ll_wait1(p.v + row + 2 * tid + 1, tag_in));
-      op.vcache[dst] = v0;
-      op.vcache[dst + 1] = v1;
-      vn_s[tid] = (uint32_t)__half_as_ushort(v0) | ((uint32_t)__half_as_ushort(v1) << 16);  // the new row, for this CTA's P.V
+      op.vcache[dst] = ll_half(vw.x);
+      op.vcache[dst + 1] = ll_half(vw.y);
+      vn_s[tid] = (vw.x & 0xffffu) | (vw.y << 16);  // the new row, for this CTA's P.V
     }
   }
   cons_sync();
