@@ -303,7 +303,7 @@ template <bool TIMED, bool DBG>
 __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global, uint32_t &it, uint32_t &slot, uint32_t &ph,
                                           unsigned char *ring, uint64_t *full, uint64_t *empty, const MegaStage *tabs, __half *xs, float *xbias,
                                           const __half *zero16,
-                                          float *red, float *ssum, Best &best, unsigned long long *tw, uint32_t ar_parity,
+                                          float *red, float *ssum, Best &best, unsigned long long *tw, uint32_t ar_seq,
                                           uint32_t tag_in, uint32_t tag_out) {
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t G = gridDim.x, cta = blockIdx.x;
@@ -558,12 +558,14 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
         const float res = idx == tid ? resid : __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
         op.out_ll[0][n] = ll_pack(__float2half_rn(round_h(v[0]) + res), tag_out);
       } else if (op.epi == EPI_PARTIAL) {
-        // this rank's share of a row-split projection: the raw fp32 sum goes into slot
-        // [parity][my rank] of every rank's exchange buffer (plain peer stores over NVLink)
+        // this rank's share of a row-split projection: the raw fp32 sum and the all-reduce's
+        // sequence number go, as one 8-byte word, into slot [parity][my rank] of every rank's
+        // exchange buffer (plain peer stores over NVLink; the word is its own arrival flag)
         const MegaParams &pp = c.p;
-        for (uint32_t r = 0; r < pp.tp_size; ++r)
-          static_cast<float *>(pp.tp_peer[r])[((size_t)ar_parity * pp.tp_size + pp.tp_rank) * pp.dim + n] = v[0];
-        __threadfence_system();
+        for (uint32_t r = 0; r < pp.tp_size; ++r) {
+          uint32_t *dst = static_cast<uint32_t *>(pp.tp_peer[r]) + 2 * (((size_t)(ar_seq & 1u) * pp.tp_size + pp.tp_rank) * pp.dim + n);
+          asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v[0])), "r"(ar_seq) : "memory");
+        }
       } else {
         const __half h0 = __float2half_rn(v[0]);
         if (op.out_ll[0]) {
@@ -891,40 +893,44 @@ __device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_
   }
 }
 
-// Tensor-parallel all-reduce, second half. The partial sums were pushed to every rank
-// by the preceding row-split projection and made visible by the grid barrier after it.
-// CTA 0 tells every rank "my partials for sequence `seq` are out"; every CTA waits
-// (bounded) until all ranks have said so, then reduces its slice of rows in rank order:
-// x <- fp16( fp16(sum_r partial_r) + x ), the same rounding as o_proj/down + residual add.
+// Tensor-parallel all-reduce, second half. The partial sums were pushed to every rank by the
+// preceding row-split projection as 8-byte words {fp32 sum, all-reduce sequence number}.
+// Every CTA reduces its slice of rows in rank order as soon as the words of all ranks carry
+// this all-reduce's number: x <- fp16( fp16(sum_r partial_r) + x ), the same rounding as
+// o_proj/down + residual add. No grid barrier and no separate flags: two parities of slots
+// keep a fast rank's next push from overwriting what a slow rank still reads.
 __device__ __forceinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t seq, uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t tid = threadIdx.x, tp = p.tp_size;
-  uint32_t *my_flags = static_cast<uint32_t *>(p.tp_peer[p.tp_rank]) + p.tp_flag_off;
-  if (tid == 0 && !c.aborted()) {
-    if (blockIdx.x == 0)
-      for (uint32_t r = 0; r < tp; ++r) st_rel_sys_u32(static_cast<uint32_t *>(p.tp_peer[r]) + p.tp_flag_off + p.tp_rank, seq);
-    for (uint32_t r = 0; r < tp && !c.aborted(); ++r) {
-      bool ok = false;
-      for (uint32_t i = 0; i < WAIT_LIMIT * 8u; ++i) {
-        if ((int32_t)(ld_acq_sys_u32(my_flags + r) - seq) >= 0) {
-          ok = true;
-          break;
-        }
-        if (i > 100000u) __nanosleep(64);
-        if ((i & 1023u) == 1023u && *(volatile uint32_t *)p.error != 0u) break;
-      }
-      if (!ok) c.raise(4);
-    }
-    __threadfence_system();
-  }
-  cons_sync();
   if (c.aborted()) return;
   const uint32_t per = (p.dim + gridDim.x - 1) / gridDim.x;
   const uint32_t i = blockIdx.x * per + tid;
   if (tid < per && i < p.dim) {
-    const float *part = static_cast<const float *>(p.tp_peer[p.tp_rank]) + (size_t)(seq & 1u) * tp * p.dim;
+    // every rank pushed {partial sum, sequence number} words into this rank's buffer: poll this
+    // row's word of every rank (bounded), add in rank order
+    const uint32_t *part = static_cast<const uint32_t *>(p.tp_peer[p.tp_rank]) + 2 * ((size_t)(seq & 1u) * tp * p.dim);
     float s = 0.f;
-    for (uint32_t r = 0; r < tp; ++r) s += __ldcg(part + (size_t)r * p.dim + i);
+    for (uint32_t r = 0; r < tp; ++r) {
+      const uint32_t *src = part + 2 * ((size_t)r * p.dim + i);
+      uint2 w = ld_vol_v2(src);
+      if (w.y != seq) {
+        bool ok = false;
+        for (uint32_t it = 0; it < WAIT_LIMIT * 8u; ++it) {
+          w = ld_vol_v2(src);
+          if (w.y == seq) {
+            ok = true;
+            break;
+          }
+          if (it > 100000u) __nanosleep(64);
+          if ((it & 1023u) == 1023u && (*(volatile uint32_t *)p.error != 0u || c.aborted())) break;
+        }
+        if (!ok) {
+          c.raise(4);
+          return;
+        }
+      }
+      s += __uint_as_float(w.x);
+    }
     const float res = __half2float(ll_half(ld_vol_u32(op.out_ll[0] + i)));  // the residual, whatever op tagged it
     op.out_ll[0][i] = ll_pack(__float2half_rn(round_h(s) + res), tag_out);
   }
@@ -984,7 +990,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
     if (timed) c0 = clock64();
     switch (op.kind) {
       case MK_EMBED: embed_op(c, tok, tag(oi)); break;
-      case MK_MATVEC: matvec_op<TIMED, DBG>(c, op, it, slot, ph, ring, full, empty, tabs, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_groups * 256), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, (seq0 + ar_i + 1) & 1u,
+      case MK_MATVEC: matvec_op<TIMED, DBG>(c, op, it, slot, ph, ring, full, empty, tabs, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_groups * 256), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, seq0 + ar_i + 1,
                          tag(op.src_op), tag(oi));
         break;
       case MK_ATTN_PART: attn_part_op(c, op, reinterpret_cast<float *>(xq), pos0, S_eff, tag(op.src_op), tag(op.tag_op)); break;

@@ -191,7 +191,7 @@ struct MegaParams {
   uint32_t xs_bytes;
   uint32_t xmax_groups;  // largest K of any op, in groups of 128 inputs: the input area holds that many fp16 values
   // Tensor parallelism: every rank's exchange buffer (peer pointers, own included).
-  // Layout of one buffer, in 4-byte words: partial sums [2 parities][tp][dim] fp32, then
+  // Layout of one buffer, in 4-byte words: partial sums [2 parities][tp][dim] x {fp32 sum, sequence number}, then
   // at word tp_flag_off: flags[16] (all-reduce sequence per source rank), arg flags[16],
   // arg candidates [16][2].
   uint32_t tp_rank, tp_size, tp_flag_off;

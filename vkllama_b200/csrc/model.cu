@@ -383,7 +383,7 @@ int build_mega(vkl_model *m) {
     o.in = in;
     o.src_op = src_op;
     o.tag_op = (uint32_t)ops.size();
-    o.barrier_after = epi == EPI_PARTIAL ? 1u : 0u;  // raw fp32 partials for the all-reduce are not tagged
+    o.barrier_after = 0;
     o.rot = rot;
     rot = (rot + o.tiles) % (uint32_t)G;
     ops.push_back(o);
@@ -733,7 +733,7 @@ int vkl_model_create(vkl_device *dev, const vkl_model_config *cfg, vkl_model **o
     return bail(st);
   cudaMemsetAsync(m->state->data(), 0, 32, m->stream);
   if (tp > 1) {
-    m->tp_flag_off = 2 * tp * c.dim;
+    m->tp_flag_off = 4 * tp * c.dim;  // partial sums: [2 parities][tp][dim] words of {fp32 sum, sequence number}
     m->tp_bytes = ((size_t)m->tp_flag_off + 64) * 4;
     if (cudaMalloc(&m->tp_buf, m->tp_bytes) != cudaSuccess) return bail(fail(VKL_RESOURCE_EXHAUSTED, "model_create: exchange buffer allocation failed"));
     cudaMemsetAsync(m->tp_buf, 0, m->tp_bytes, m->stream);
