@@ -170,7 +170,7 @@ def run_reference(args, w, name):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_mega_kernel launch from ncu (see profiles/), per workload
-TRAFFIC_NCU = {"llama2-7b-q8_0": 7.06e9}  # 1.008 x algorithmic, scaled from the 4-block capture (profiles/decode_mega_kernel_7b_shape_4blocks.md)
+TRAFFIC_NCU = {"llama2-7b-q8_0": 7.06e9}  # 1.005 x algorithmic, scaled from the 4-block capture (profiles/decode_mega_kernel_7b_shape_4blocks.md)
 
 MICRO_SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)]  # rows x K: qkvo, gate/up, down, lm head
 
