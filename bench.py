@@ -203,15 +203,11 @@ def run_micro(args):
             cmd.begin()
             x = vk.Tensor(1, M, K, dev, vk.FP16)
             cmd.fill_synthetic(x, 20240605, 100 + M, 0.0, 1.0)
-            for _ in range(max(args.warmup, 3)):
-                for op in ops:
-                    op(x)
+            vk.matmul_run_many(ops, x, max(args.warmup, 3) * len(ops))
             cmd.end()
             cmd.submit_and_wait()
             cmd.begin()
-            for _ in range(args.steps):
-                for op in ops:
-                    op(x)
+            vk.matmul_run_many(ops, x, args.steps * len(ops))  # recorded back to back from C: no Python between launches
             cmd.end()
             cmd.submit_and_wait()
             n = args.steps * len(ops)

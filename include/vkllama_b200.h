@@ -106,6 +106,10 @@ int vkl_matmul_create(vkl_device *dev, vkl_command *cmd, vkl_tensor *weight, flo
                       float bias, int act, int broadcast_type, int transpose_b, int a_dtype,
                       int b_dtype, vkl_op **out);
 int vkl_matmul_run(vkl_op *op, vkl_tensor *a, vkl_tensor *b, vkl_tensor **out);
+/* Benchmark helper (no counterpart in the reference, whose tests time one op call at a time):
+ * records `reps` weight-form MatMul calls on `a`, rotating over `n_ops` ops (copies of one
+ * weight matrix larger than L2 in total), without a round trip to the caller in between. */
+int vkl_matmul_run_many(vkl_op *const *ops, size_t n_ops, vkl_tensor *a, size_t reps);
 
 /* FeedForward, src/ops/feed_forward.h:17-22 (w1 = gate, w2 = down, w3 = up). */
 int vkl_feed_forward_create(vkl_device *dev, vkl_command *cmd, vkl_tensor *w1, vkl_tensor *w2,

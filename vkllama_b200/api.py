@@ -61,6 +61,7 @@ def load_library():
         "vkl_op_init": [vp], "vkl_op_time": [vp, C.POINTER(u64)], "vkl_op_destroy": [vp],
         "vkl_matmul_create": [vp, vp, vp, f32, f32, i32, i32, i32, i32, i32, pvp],
         "vkl_matmul_run": [vp, vp, vp, pvp],
+        "vkl_matmul_run_many": [C.POINTER(vp), sz, vp, sz],
         "vkl_feed_forward_create": [vp, vp, vp, vp, vp, i32, i32, pvp], "vkl_feed_forward_run": [vp, vp, pvp],
         "vkl_mha_create": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, pvp],
         "vkl_mha_run": [vp, vp, sz, pvp], "vkl_mha_caches": [vp, pvp, pvp],
@@ -363,6 +364,12 @@ class MatMul(Op):
         out = vp()
         _ck(self.L.vkl_matmul_run(self.h, a.h, _h(b), C.byref(out)))
         return self._out(out)
+
+
+def matmul_run_many(ops, a, reps):
+    """Benchmark helper: `reps` weight-form MatMul calls on `a`, rotating over `ops`."""
+    arr = (vp * len(ops))(*[o.h for o in ops])
+    _ck(load_library().vkl_matmul_run_many(arr, len(ops), a.h, reps))
 
 
 class FeedForward(Op):

@@ -649,7 +649,7 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
       for (uint32_t d = 0; d < D; ++d) a = fmaf(q_s[d], kn_s[d], a);
     } else {
       const uint4 *kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * D);
-#pragma unroll 8
+#pragma unroll 16  // a whole 128-wide row in flight: one memory round trip per column
       for (uint32_t d8 = 0; d8 < D / 8; ++d8) {
         const uint4 kv = __ldg(kr + d8);
         const float4 qa = *reinterpret_cast<const float4 *>(q_s + d8 * 8);
@@ -690,7 +690,7 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
   float2 acc = make_float2(0.f, 0.f);
   if (dp < npair && grp < CT / 64) {
     const __half *vc = op.vcache + (size_t)h * p.maxlen * D + 2 * dp;
-    constexpr uint32_t NG = CT / 64, UN = 4;  // threads beyond NG*64 sit this part out
+    constexpr uint32_t NG = CT / 64, UN = 16;  // threads beyond NG*64 sit this part out; UN loads in flight per thread
     for (uint32_t jb = c0 + grp; jb < c1; jb += NG * UN) {
       uint32_t raw[UN];
 #pragma unroll
@@ -720,6 +720,55 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
     pv[grp * D + 2 * dp + 1] = acc.y;
   }
   cons_sync();
+  if (S > 1 && p.attn_merge == 2) {
+    // Every split publishes its partial row as 8-byte words {value, this op's sequence number}
+    // and then merges its own share of the head's dims from all splits' words (polling until
+    // they carry the number): no fence, no counter, no combine op. Merged in split order.
+    uint32_t *part2 = reinterpret_cast<uint32_t *>(p.attn_scratch) + 2 * ((size_t)h * p.splits + split) * (D + 4);
+    if (tid < D) {
+      float s = 0.f;
+#pragma unroll
+      for (int gq = 0; gq < CT / 64; ++gq) s += pv[gq * D + tid];
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(part2 + 2 * tid), "r"(__float_as_uint(s)), "r"(tag_out) : "memory");
+    }
+    if (tid == 0) {
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(part2 + 2 * D), "r"(__float_as_uint(mloc)), "r"(tag_out) : "memory");
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(part2 + 2 * (D + 1)), "r"(__float_as_uint(lloc)), "r"(tag_out) : "memory");
+    }
+    const uint32_t per = (D + S - 1) / S, d = split * per + tid;
+    if (tid < per && d < D) {
+      const uint32_t *base = reinterpret_cast<const uint32_t *>(p.attn_scratch) + 2 * ((size_t)h * p.splits) * (D + 4);
+      float ms[8], ls[8], as[8];
+      for (uint32_t sp = 0; sp < S; ++sp) {
+        const uint32_t *b = base + 2 * (size_t)sp * (D + 4);
+        uint2 wm = ld_vol_v2(b + 2 * D), wl = ld_vol_v2(b + 2 * (D + 1)), wa = ld_vol_v2(b + 2 * d);
+        for (uint32_t i = 0; (wm.y != tag_out || wl.y != tag_out || wa.y != tag_out) && i < WAIT_LIMIT; ++i) {
+          wm = ld_vol_v2(b + 2 * D);
+          wl = ld_vol_v2(b + 2 * (D + 1));
+          wa = ld_vol_v2(b + 2 * d);
+          if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || c.aborted())) break;
+        }
+        if (wm.y != tag_out || wl.y != tag_out || wa.y != tag_out) {
+          c.raise(6);
+          return;
+        }
+        ms[sp] = __uint_as_float(wm.x);
+        ls[sp] = __uint_as_float(wl.x);
+        as[sp] = __uint_as_float(wa.x);
+      }
+      float M = -INFINITY;
+      for (uint32_t sp = 0; sp < S; ++sp) M = fmaxf(M, ms[sp]);
+      float den = 0.f, num = 0.f;
+      for (uint32_t sp = 0; sp < S; ++sp)
+        if (ls[sp] > 0.f) {
+          const float w = expf(ms[sp] - M);
+          den += ls[sp] * w;
+          num += as[sp] * w;
+        }
+      p.ao[row + d] = ll_pack(__float2half_rn(num / den), tag_out);
+    }
+    return;
+  }
   float *part = p.attn_scratch + ((size_t)h * p.splits + split) * (D + 4);
   if (tid < D) {
     float s = 0.f;

@@ -183,6 +183,7 @@ struct MegaParams {
   uint32_t *x, *q, *k, *v, *ao;  // tagged words (see MegaOp)
   const float *freqc, *freqs;
   float *attn_scratch;      // heads*splits*(head_dim+4): per (head, split) the un-normalised P.V row, its max and its sum
+  uint32_t attn_merge;      // how a head's split partials are merged: 0 combine op, 1 last-arriving split, 2 tagged words, every split merges its share
   uint32_t *attn_counters;  // [heads] arrivals of a head's splits (the last one merges them), or null: separate combine op
   float *arg_scratch;       // grid*2
   unsigned long long *bar;  // [0] arrivals, [1] completed launches

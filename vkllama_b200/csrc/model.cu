@@ -495,7 +495,7 @@ int build_mega(vkl_model *m) {
   VKL_OKAY(tensor_new(m->dev, 1, 1, (ob + 3) / 4, VKL_UINT32, &m->mega_ops));
   VKL_OKAY(tensor_new(m->dev, 1, 1, 16, VKL_UINT32, &m->mega_sync));  // [0..3] barrier words, [4] error
   VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)G * 2, VKL_FP32, &m->mega_arg));
-  VKL_OKAY(tensor_new(m->dev, 1, 1, (size_t)m->heads_l * splits * (m->head_dim + 4) + m->heads_l, VKL_FP32, &m->mega_attn));
+  VKL_OKAY(tensor_new(m->dev, 1, 1, 2 * (size_t)m->heads_l * splits * (m->head_dim + 4) + m->heads_l, VKL_FP32, &m->mega_attn));
   VKL_CUDA(cudaMemcpyAsync(m->mega_ops->data(), ops.data(), ob, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaMemsetAsync(m->mega_sync->data(), 0, 64, m->stream));
   VKL_CUDA(cudaStreamSynchronize(m->stream));
@@ -524,9 +524,11 @@ int build_mega(vkl_model *m) {
   p.attn_scratch = (float *)m->mega_attn->data();
   {
     const char *cenv = getenv("VKLLAMA_DECODE_COMBINE");
-    const bool last_combine = !(cenv && !strcmp(cenv, "separate"));
-    p.attn_counters = last_combine ? (uint32_t *)(p.attn_scratch + (size_t)m->heads_l * splits * (m->head_dim + 4)) : nullptr;
-    VKL_CUDA(cudaMemsetAsync(p.attn_scratch + (size_t)m->heads_l * splits * (m->head_dim + 4), 0, (size_t)m->heads_l * 4, m->stream));
+    p.attn_merge = cenv && !strcmp(cenv, "separate") ? 0u : cenv && !strcmp(cenv, "last") ? 1u : 2u;
+    if (splits > 8) p.attn_merge = 1u;
+    uint32_t *counters = (uint32_t *)(p.attn_scratch + 2 * (size_t)m->heads_l * splits * (m->head_dim + 4));
+    p.attn_counters = p.attn_merge == 1 ? counters : nullptr;
+    VKL_CUDA(cudaMemsetAsync(m->mega_attn->data(), 0, (2 * (size_t)m->heads_l * splits * (m->head_dim + 4) + m->heads_l) * 4, m->stream));
   }
   p.arg_scratch = (float *)m->mega_arg->data();
   p.bar = (unsigned long long *)m->mega_sync->data();

@@ -675,6 +675,16 @@ int vkl_matmul_run(vkl_op *op, vkl_tensor *a, vkl_tensor *b, vkl_tensor **out) {
   if (!out) return fail(VKL_INVALID_ARGUMENT, "matmul_run: null output");
   return b ? m->run_pair(a, b, out) : m->run_weight(a, out);
 }
+int vkl_matmul_run_many(vkl_op *const *ops, size_t n_ops, vkl_tensor *a, size_t reps) {
+  if (!ops || !n_ops || !a) return fail(VKL_INVALID_ARGUMENT, "matmul_run_many: null argument");
+  for (size_t i = 0; i < reps; ++i) {
+    MatMulOp *m;
+    VKL_OKAY(as(ops[i % n_ops], &m, "matmul_run_many"));
+    vkl_tensor *out = nullptr;
+    VKL_OKAY(m->run_weight(a, &out));
+  }
+  return VKL_OK;
+}
 int vkl_feed_forward_create(vkl_device *dev, vkl_command *cmd, vkl_tensor *w1, vkl_tensor *w2, vkl_tensor *w3, int transposed_weight,
                             int dtype, vkl_op **out) {
   if (!w1 || !w2 || !w3) return fail(VKL_INVALID_ARGUMENT, "feed_forward_create: null weight");
