@@ -649,7 +649,7 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
       for (uint32_t d = 0; d < D; ++d) a = fmaf(q_s[d], kn_s[d], a);
     } else {
       const uint4 *kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * D);
-#pragma unroll 16  // a whole 128-wide row in flight: one memory round trip per column
+#pragma unroll 8
       for (uint32_t d8 = 0; d8 < D / 8; ++d8) {
         const uint4 kv = __ldg(kr + d8);
         const float4 qa = *reinterpret_cast<const float4 *>(q_s + d8 * 8);
@@ -690,7 +690,7 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
   float2 acc = make_float2(0.f, 0.f);
   if (dp < npair && grp < CT / 64) {
     const __half *vc = op.vcache + (size_t)h * p.maxlen * D + 2 * dp;
-    constexpr uint32_t NG = CT / 64, UN = 16;  // threads beyond NG*64 sit this part out; UN loads in flight per thread
+    constexpr uint32_t NG = CT / 64, UN = 4;  // threads beyond NG*64 sit this part out (16 loads in flight per thread measured slower)
     for (uint32_t jb = c0 + grp; jb < c1; jb += NG * UN) {
       uint32_t raw[UN];
 #pragma unroll

@@ -524,7 +524,7 @@ int build_mega(vkl_model *m) {
   p.attn_scratch = (float *)m->mega_attn->data();
   {
     const char *cenv = getenv("VKLLAMA_DECODE_COMBINE");
-    p.attn_merge = cenv && !strcmp(cenv, "separate") ? 0u : cenv && !strcmp(cenv, "last") ? 1u : 2u;
+    p.attn_merge = cenv && !strcmp(cenv, "separate") ? 0u : cenv && !strcmp(cenv, "tagged") ? 2u : 1u;  // "tagged" measured equal to "last"
     if (splits > 8) p.attn_merge = 1u;
     uint32_t *counters = (uint32_t *)(p.attn_scratch + 2 * (size_t)m->heads_l * splits * (m->head_dim + 4));
     p.attn_counters = p.attn_merge == 1 ? counters : nullptr;
