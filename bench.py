@@ -207,18 +207,17 @@ def run_micro(args):
             cmd.end()
             cmd.submit_and_wait()
             cmd.begin()
-            vk.matmul_run_many(ops, x, args.steps * len(ops))  # recorded back to back from C: no Python between launches
+            n = args.steps * len(ops)
+            us = vk.matmul_run_many(ops, x, n, timed=True)  # one CUDA graph of n launches: device time, no host gaps
             cmd.end()
             cmd.submit_and_wait()
-            n = args.steps * len(ops)
-            us = cmd.elapsed_us() / n
             algo = wbytes + M * K * 2 + M * N * 2
             gbs = algo / (us * 1e-6) / 1e9
             rows.append({"rows": N, "K": K, "tokens": M, "us_per_launch": us, "bytes_per_launch": algo, "GBps": gbs,
                          "frac_of_peak": gbs / peak, "tflops": 2.0 * M * N * K / (us * 1e-6) / 1e12})
         del ops, ws
     print(json.dumps({"metric": "q8_0_matvec_GBps", "unit": "GB/s", "peak": peak, "peak_kind": peak_kind, "steps": args.steps,
-                      "timing": "CUDA events on the launching stream around back-to-back launches over rotated weight copies",
+                      "timing": "CUDA events around one CUDA graph of steps x copies MatMul op calls (each call = event, kernel, event; no host work between them) over rotated weight copies larger than L2",
                       "gpu_launches": int(vk.kernel_launches() - launches0), "results": rows}))
 
 

@@ -108,8 +108,11 @@ int vkl_matmul_create(vkl_device *dev, vkl_command *cmd, vkl_tensor *weight, flo
 int vkl_matmul_run(vkl_op *op, vkl_tensor *a, vkl_tensor *b, vkl_tensor **out);
 /* Benchmark helper (no counterpart in the reference, whose tests time one op call at a time):
  * records `reps` weight-form MatMul calls on `a`, rotating over `n_ops` ops (copies of one
- * weight matrix larger than L2 in total), without a round trip to the caller in between. */
-int vkl_matmul_run_many(vkl_op *const *ops, size_t n_ops, vkl_tensor *a, size_t reps);
+ * weight matrix larger than L2 in total). With `us_per_launch` non-null the calls are captured
+ * into a CUDA graph, run once to warm up and once between two events, and the mean device time
+ * of one call is returned (the command must be recording and the ops must have run once before,
+ * so that nothing is allocated during the capture). */
+int vkl_matmul_run_many(vkl_op *const *ops, size_t n_ops, vkl_tensor *a, size_t reps, float *us_per_launch);
 
 /* FeedForward, src/ops/feed_forward.h:17-22 (w1 = gate, w2 = down, w3 = up). */
 int vkl_feed_forward_create(vkl_device *dev, vkl_command *cmd, vkl_tensor *w1, vkl_tensor *w2,

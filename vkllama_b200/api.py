@@ -61,7 +61,7 @@ def load_library():
         "vkl_op_init": [vp], "vkl_op_time": [vp, C.POINTER(u64)], "vkl_op_destroy": [vp],
         "vkl_matmul_create": [vp, vp, vp, f32, f32, i32, i32, i32, i32, i32, pvp],
         "vkl_matmul_run": [vp, vp, vp, pvp],
-        "vkl_matmul_run_many": [C.POINTER(vp), sz, vp, sz],
+        "vkl_matmul_run_many": [C.POINTER(vp), sz, vp, sz, C.POINTER(f32)],
         "vkl_feed_forward_create": [vp, vp, vp, vp, vp, i32, i32, pvp], "vkl_feed_forward_run": [vp, vp, pvp],
         "vkl_mha_create": [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, pvp],
         "vkl_mha_run": [vp, vp, sz, pvp], "vkl_mha_caches": [vp, pvp, pvp],
@@ -366,10 +366,13 @@ class MatMul(Op):
         return self._out(out)
 
 
-def matmul_run_many(ops, a, reps):
-    """Benchmark helper: `reps` weight-form MatMul calls on `a`, rotating over `ops`."""
+def matmul_run_many(ops, a, reps, timed=False):
+    """Benchmark helper: `reps` weight-form MatMul calls on `a`, rotating over `ops`. With
+    `timed` the calls run as one CUDA graph and the mean device time per call (us) is returned."""
     arr = (vp * len(ops))(*[o.h for o in ops])
-    _ck(load_library().vkl_matmul_run_many(arr, len(ops), a.h, reps))
+    us = f32(0.0)
+    _ck(load_library().vkl_matmul_run_many(arr, len(ops), a.h, reps, C.byref(us) if timed else None))
+    return us.value if timed else None
 
 
 class FeedForward(Op):

@@ -675,13 +675,53 @@ int vkl_matmul_run(vkl_op *op, vkl_tensor *a, vkl_tensor *b, vkl_tensor **out) {
   if (!out) return fail(VKL_INVALID_ARGUMENT, "matmul_run: null output");
   return b ? m->run_pair(a, b, out) : m->run_weight(a, out);
 }
-int vkl_matmul_run_many(vkl_op *const *ops, size_t n_ops, vkl_tensor *a, size_t reps) {
-  if (!ops || !n_ops || !a) return fail(VKL_INVALID_ARGUMENT, "matmul_run_many: null argument");
-  for (size_t i = 0; i < reps; ++i) {
-    MatMulOp *m;
-    VKL_OKAY(as(ops[i % n_ops], &m, "matmul_run_many"));
-    vkl_tensor *out = nullptr;
-    VKL_OKAY(m->run_weight(a, &out));
+int vkl_matmul_run_many(vkl_op *const *ops, size_t n_ops, vkl_tensor *a, size_t reps, float *us_per_launch) {
+  if (!ops || !n_ops || !a || !reps) return fail(VKL_INVALID_ARGUMENT, "matmul_run_many: null argument");
+  MatMulOp *first;
+  VKL_OKAY(as(ops[0], &first, "matmul_run_many"));
+  cudaStream_t st = first->cmd->stream;
+  auto record_all = [&]() -> int {
+    for (size_t i = 0; i < reps; ++i) {
+      MatMulOp *m;
+      VKL_OKAY(as(ops[i % n_ops], &m, "matmul_run_many"));
+      vkl_tensor *out = nullptr;
+      VKL_OKAY(m->run_weight(a, &out));
+    }
+    return VKL_OK;
+  };
+  if (!us_per_launch) return record_all();
+  // Timed form: the launches are captured into a CUDA graph (outputs were allocated by an earlier
+  // untimed call), so the device runs them back to back with no host work in between.
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  VKL_CUDA(cudaEventCreate(&e0));
+  VKL_CUDA(cudaEventCreate(&e1));
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  int status = VKL_OK;
+  cudaError_t e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+  if (e == cudaSuccess) {
+    status = record_all();
+    e = cudaStreamEndCapture(st, &graph);
+  }
+  if (status == VKL_OK && e == cudaSuccess && graph) e = cudaGraphInstantiate(&exec, graph, 0);
+  if (status == VKL_OK && e == cudaSuccess && exec) {
+    cudaGraphLaunch(exec, st);  // warm
+    cudaEventRecord(e0, st);
+    cudaGraphLaunch(exec, st);
+    cudaEventRecord(e1, st);
+    e = cudaStreamSynchronize(st);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+    *us_per_launch = ms * 1000.f / (float)reps;
+  }
+  if (exec) cudaGraphExecDestroy(exec);
+  if (graph) cudaGraphDestroy(graph);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (status != VKL_OK) return status;
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(VKL_INTERNAL, "matmul_run_many: %s", cudaGetErrorString(e));
   }
   return VKL_OK;
 }
