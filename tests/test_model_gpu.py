@@ -218,3 +218,25 @@ def test_llama2_7b_q8_0_teacher_forced_steps(model7b):
     decided = gap >= UNDECIDED_GAP
     assert np.array_equal(picks[decided], ids[decided])
     assert decided.sum() >= 50 and (picks == ids).mean() >= 0.9
+
+
+@pytest.mark.parametrize("switch", [("VKLLAMA_DECODE", "graph"), ("VKLLAMA_DECODE_COMBINE", "separate"),
+                                    ("VKLLAMA_DECODE_COMBINE", "tagged"), ("VKLLAMA_PREFILL", "sequential")])
+def test_decode_plan_switches_keep_parity(dev, monkeypatch, switch):
+    """The alternative decode plans (multi-kernel CUDA graph, combine op after a grid barrier,
+    tagged-word merge of the attention partials, token-by-token prefill through the decode
+    kernel) give the same logits and greedy ids as the default plan, against the oracle."""
+    monkeypatch.setenv(*switch)
+    om, dm, cfg = small_pair(dev, seed=13)
+    prompt = O.synth_tokens(13, 1000, 9, cfg["vocab"])
+    want, gap = om.generate(prompt, 24)
+    got = dm.generate(prompt, 24)[0]
+    bad = [i for i in range(24) if got[i] != want[i]]
+    assert not bad or gap[bad[0]] < UNDECIDED_GAP, (switch, bad, gap)
+    om2, dm2, _ = small_pair(dev, seed=13)
+    tok = np.array([int(prompt[0])], np.uint32)
+    for i in range(4):  # one-token calls: the decode plan under test
+        w = om2.forward(tok, i)
+        g = dm2(tok, i)
+        assert np.abs(g - w).max() <= LOGITS_MAX_ABS, (switch, i)
+        tok = np.array([int(np.argmax(w))], np.uint32)

@@ -485,3 +485,22 @@ def test_op_errors(dev):
     with pytest.raises(vk.VklError) as e:  # ops record only between begin() and end()
         op(vk.Tensor(1, 2, 64, dev, vk.FP16))
     assert e.value.code == 9
+
+
+def test_matmul_run_many_matches_single_calls_and_times_them(dev):
+    """The benchmark helper records the same MatMul calls as one-by-one use of the op."""
+    M, N, K = 2, 64, 256
+    x = O.synth_f16(61, 1, M * K).reshape(M, K)
+    ws = [O.synth_q8_0(61, 10 + i, N, K) for i in range(3)]
+    want = O.matmul_q8_0(x, ws[2], M, N, K)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tx = up(cmd, dev, x, vk.FP16, 1, M, K)
+    ops = [vk.MatMul(dev, cmd, up(cmd, dev, w, vk.Q8_0, 1, N, K), 1.0, 0.0, 0, 0, True, vk.FP16, vk.Q8_0).init() for w in ws]
+    vk.matmul_run_many(ops, tx, 6)                  # allocates the outputs
+    us = vk.matmul_run_many(ops, tx, 6, timed=True)  # the same calls as one CUDA graph
+    got = cmd.download(ops[2](tx))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert us > 0.0
+    assert_close(got, want, what="matmul after run_many")

@@ -10,6 +10,9 @@
 // Rounding points kept: roped q and k are fp16, the scaled score is rounded to
 // fp16 before the softmax, the head output is fp16. The probabilities are kept
 // in fp32 here (the reference stores them as fp16 between two dispatches).
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -213,6 +216,155 @@ size_t attn_smem(const AttnParams &p) {
   return (size_t)(4 * p.dim + 8 + chunk) * sizeof(float);
 }
 
+
+// ---- multi-token calls with many rows: 64 query rows of one head per CTA ----------------------
+// The per-row kernel above re-reads the head's K and V rows for every query row. This one stages
+// a 64-position K/V tile in shared memory once for 64 query rows and runs both products on the
+// tensor cores (mma.sync m16n8k16, fp32 accumulate): S = Q.K^T per warp of 16 rows, the scaled
+// score rounded to fp16 as the reference's softmax input is, a running (max, sum) per row, the
+// probabilities as fp16 MMA operands (the reference stores them as fp16 between two dispatches),
+// O += P.V with V fragments transposed by ldmatrix. Columns are physical cache rows 0..L-1 with
+// the reference's mask col <= row + (L - T) (softmax_fp16.comp:52-60), so a wrapped ring behaves
+// as in the per-row kernel.
+__device__ __forceinline__ void mma16816_h(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  const __half2 v = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
+  return *reinterpret_cast<const uint32_t *>(&v);
+}
+
+template <int D>
+__global__ void __launch_bounds__(128) attention_tile_kernel(const AttnParams p) {
+  constexpr int QT = 64, KT = 64, LD = D + 8;  // padded rows: conflict-free fragment loads
+  extern __shared__ __align__(16) __half smh[];
+  __half *q_s = smh;             // [QT][LD] roped queries
+  __half *k_s = q_s + QT * LD;   // [KT][LD]
+  __half *v_s = k_s + KT * LD;   // [KT][LD]
+  const uint32_t h = blockIdx.x, m0 = blockIdx.y * QT, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t = lane & 3;
+  const uint32_t T = p.T, pos0 = *p.pos_dev;
+  const uint32_t L = min(pos0 + T, p.maxlen), shift = L - T;
+  for (uint32_t i = tid; i < QT * (D / 2); i += 128) {  // rotate the query tile at positions pos0 + row
+    const uint32_t r = i / (D / 2), pr = i % (D / 2), m = m0 + r;
+    __half r0 = __float2half_rn(0.f), r1 = r0;
+    if (m < T) {
+      const size_t fi = (size_t)(pos0 + m) * (D / 2) + pr, src = (size_t)m * p.heads * D + (size_t)h * D + 2 * pr;
+      rope_pair(__half2float(p.q[src]), __half2float(p.q[src + 1]), p.freqc[fi], p.freqs[fi], r0, r1);
+    }
+    q_s[r * LD + 2 * pr] = r0;
+    q_s[r * LD + 2 * pr + 1] = r1;
+  }
+  const uint32_t r_lo = m0 + warp * 16 + g, r_hi = r_lo + 8;
+  const uint32_t vis_lo = r_lo < T ? min(L, r_lo + shift + 1) : 0u, vis_hi = r_hi < T ? min(L, r_hi + shift + 1) : 0u;
+  const uint32_t jmax = min(L, min(m0 + QT, T) + shift);  // columns any row of this tile can see
+  const float scale = 1.0f / sqrtf((float)D);
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  const __half *kc = p.kcache + (size_t)h * p.maxlen * D, *vc = p.vcache + (size_t)h * p.maxlen * D;
+  const __half *qw = q_s + (warp * 16 + g) * LD + 2 * t;
+  for (uint32_t j0 = 0; j0 < jmax; j0 += KT) {
+    __syncthreads();  // the previous tile is consumed (and, first time, the query tile is written)
+    for (uint32_t i = tid; i < KT * (D / 8); i += 128) {
+      const uint32_t r = i / (D / 8), c8 = i % (D / 8), j = j0 + r;
+      uint4 kv = make_uint4(0, 0, 0, 0), vv = kv;
+      if (j < L) {
+        kv = __ldg(reinterpret_cast<const uint4 *>(kc + (size_t)j * D) + c8);
+        vv = __ldg(reinterpret_cast<const uint4 *>(vc + (size_t)j * D) + c8);
+      }
+      *reinterpret_cast<uint4 *>(k_s + r * LD + c8 * 8) = kv;
+      *reinterpret_cast<uint4 *>(v_s + r * LD + c8 * 8) = vv;
+    }
+    __syncthreads();
+    // ---- S = Q.K^T: 16 rows x 64 columns per warp
+    float sc[KT / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < KT / 8; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint32_t a0 = *reinterpret_cast<const uint32_t *>(qw + kk * 16), a1 = *reinterpret_cast<const uint32_t *>(qw + 8 * LD + kk * 16);
+      const uint32_t a2 = *reinterpret_cast<const uint32_t *>(qw + kk * 16 + 8), a3 = *reinterpret_cast<const uint32_t *>(qw + 8 * LD + kk * 16 + 8);
+#pragma unroll
+      for (int nt = 0; nt < KT / 8; ++nt) {
+        const __half *kr = k_s + (nt * 8 + g) * LD + kk * 16 + 2 * t;
+        mma16816_h(sc[nt], a0, a1, a2, a3, *reinterpret_cast<const uint32_t *>(kr), *reinterpret_cast<const uint32_t *>(kr + 8));
+      }
+    }
+    // ---- scaled fp16 scores, mask, running max and sum
+    float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < KT / 8; ++nt) {
+      const uint32_t c = j0 + nt * 8 + 2 * t;
+      sc[nt][0] = c < vis_lo ? round_h(sc[nt][0] * scale) : -INFINITY;
+      sc[nt][1] = c + 1 < vis_lo ? round_h(sc[nt][1] * scale) : -INFINITY;
+      sc[nt][2] = c < vis_hi ? round_h(sc[nt][2] * scale) : -INFINITY;
+      sc[nt][3] = c + 1 < vis_hi ? round_h(sc[nt][3] * scale) : -INFINITY;
+      tmax_lo = fmaxf(tmax_lo, fmaxf(sc[nt][0], sc[nt][1]));
+      tmax_hi = fmaxf(tmax_hi, fmaxf(sc[nt][2], sc[nt][3]));
+    }
+    tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 1));
+    tmax_lo = fmaxf(tmax_lo, __shfl_xor_sync(0xffffffffu, tmax_lo, 2));
+    tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 1));
+    tmax_hi = fmaxf(tmax_hi, __shfl_xor_sync(0xffffffffu, tmax_hi, 2));
+    const float mn_lo = fmaxf(m_lo, tmax_lo), mn_hi = fmaxf(m_hi, tmax_hi);
+    const float corr_lo = m_lo == -INFINITY ? 0.f : expf(m_lo - mn_lo), corr_hi = m_hi == -INFINITY ? 0.f : expf(m_hi - mn_hi);
+    float rs_lo = 0.f, rs_hi = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < KT / 8; ++nt) {
+      sc[nt][0] = sc[nt][0] == -INFINITY ? 0.f : expf(sc[nt][0] - mn_lo);
+      sc[nt][1] = sc[nt][1] == -INFINITY ? 0.f : expf(sc[nt][1] - mn_lo);
+      sc[nt][2] = sc[nt][2] == -INFINITY ? 0.f : expf(sc[nt][2] - mn_hi);
+      sc[nt][3] = sc[nt][3] == -INFINITY ? 0.f : expf(sc[nt][3] - mn_hi);
+      rs_lo += sc[nt][0] + sc[nt][1];
+      rs_hi += sc[nt][2] + sc[nt][3];
+    }
+    rs_lo += __shfl_xor_sync(0xffffffffu, rs_lo, 1);
+    rs_lo += __shfl_xor_sync(0xffffffffu, rs_lo, 2);
+    rs_hi += __shfl_xor_sync(0xffffffffu, rs_hi, 1);
+    rs_hi += __shfl_xor_sync(0xffffffffu, rs_hi, 2);
+    l_lo = l_lo * corr_lo + rs_lo;
+    l_hi = l_hi * corr_hi + rs_hi;
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= corr_lo;
+      o[i][1] *= corr_lo;
+      o[i][2] *= corr_hi;
+      o[i][3] *= corr_hi;
+    }
+    // ---- O += P.V: 16 cache rows per step, V fragments transposed by ldmatrix
+#pragma unroll
+    for (int j16 = 0; j16 < KT / 16; ++j16) {
+      const uint32_t a0 = pack_h2(sc[2 * j16][0], sc[2 * j16][1]), a1 = pack_h2(sc[2 * j16][2], sc[2 * j16][3]);
+      const uint32_t a2 = pack_h2(sc[2 * j16 + 1][0], sc[2 * j16 + 1][1]), a3 = pack_h2(sc[2 * j16 + 1][2], sc[2 * j16 + 1][3]);
+      // lane l gives the address of row l % 8 of matrix l / 8: matrices (rows +0, cols +0), (rows +8, cols +0), (rows +0, cols +8), (rows +8, cols +8)
+      const __half *vrow = v_s + (j16 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + ((lane >> 4) & 1) * 8;
+#pragma unroll
+      for (int dt = 0; dt < D / 16; ++dt) {
+        uint32_t b0, b1, b2, b3;
+        const uint32_t addr = (uint32_t)__cvta_generic_to_shared(vrow + dt * 16);
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+        mma16816_h(o[2 * dt], a0, a1, a2, a3, b0, b1);
+        mma16816_h(o[2 * dt + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+  }
+  // ---- out[m, h*D + d] = fp16(O / sum)
+  const float inv_lo = l_lo > 0.f ? 1.0f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.0f / l_hi : 0.f;
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) {
+    const uint32_t d = nt * 8 + 2 * t;
+    if (r_lo < T) *reinterpret_cast<uint32_t *>(p.out + (size_t)r_lo * p.heads * D + (size_t)h * D + d) = pack_h2(o[nt][0] * inv_lo, o[nt][1] * inv_lo);
+    if (r_hi < T) *reinterpret_cast<uint32_t *>(p.out + (size_t)r_hi * p.heads * D + (size_t)h * D + d) = pack_h2(o[nt][2] * inv_hi, o[nt][3] * inv_hi);
+  }
+}
+
+constexpr uint32_t kTileMinRows = 32;  // below this the per-row kernel is used
+
 }  // namespace
 
 size_t attention_scratch_bytes(uint32_t T, uint32_t heads, uint32_t dim, uint32_t splits) {
@@ -225,6 +377,15 @@ cudaError_t launch_attention(const AttnParams &p, cudaStream_t s) {
     rope_append_kernel<<<dim3(p.heads, p.T), 64, 0, s>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
+  }
+  static const bool tile_off = [] { const char *e = getenv("VKLLAMA_PREFILL_ATTENTION"); return e && !strcmp(e, "rows"); }();
+  if (!tile_off && p.T >= kTileMinRows && !p.clip && (p.dim == 64 || p.dim == 128)) {
+    const size_t tsmem = (size_t)3 * 64 * (p.dim + 8) * sizeof(__half);
+    auto tk = p.dim == 128 ? attention_tile_kernel<128> : attention_tile_kernel<64>;
+    cudaError_t e = cudaFuncSetAttribute(tk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem);
+    if (e != cudaSuccess) return e;
+    tk<<<dim3(p.heads, (p.T + 63) / 64), 128, tsmem, s>>>(p);
+    return cudaGetLastError();
   }
   const size_t smem = attn_smem(p);
   auto kern = p.T == 1 ? attention_kernel<true> : attention_kernel<false>;
