@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
       for (uint32_t d = 0; d < D; ++d) acc = fmaf(q_s[d], kn_s[d], acc);
     } else {
       const uint4 *kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * D);
-#pragma unroll 4
+#pragma unroll 16  // the whole row in flight: one memory round trip per column
       for (uint32_t d8 = 0; d8 < D / 8; ++d8) {
         const uint4 kv = __ldg(kr + d8);
         const float4 qa = *reinterpret_cast<const float4 *>(q_s + d8 * 8);
@@ -142,15 +142,27 @@ __global__ void __launch_bounds__(kAttnThreads) attention_kernel(const AttnParam
   float2 acc = make_float2(0.f, 0.f);
   if (dp < npair) {
     const __half *vc = p.vcache + (size_t)h * p.maxlen * D + 2 * dp;
-    for (uint32_t j = c0 + grp; j < c1; j += 2) {
-      float2 vv;
-      if (owns_new && j == jn)
-        vv = __half22float2(*reinterpret_cast<const __half2 *>(p.v + row_in + 2 * dp));
-      else
-        vv = __half22float2(*reinterpret_cast<const __half2 *>(vc + (size_t)j * D));
-      const float pj = s_s[j - c0];
-      acc.x = fmaf(pj, vv.x, acc.x);
-      acc.y = fmaf(pj, vv.y, acc.y);
+    constexpr uint32_t UN = 8;  // cache rows in flight per thread
+    for (uint32_t jb = c0 + grp; jb < c1; jb += 2 * UN) {
+      uint32_t raw[UN];
+#pragma unroll
+      for (uint32_t u = 0; u < UN; ++u) {
+        const uint32_t j = jb + 2 * u;
+        raw[u] = 0;
+        if (j < c1)
+          raw[u] = (owns_new && j == jn) ? *reinterpret_cast<const uint32_t *>(p.v + row_in + 2 * dp)
+                                         : __ldg(reinterpret_cast<const uint32_t *>(vc + (size_t)j * D));
+      }
+#pragma unroll
+      for (uint32_t u = 0; u < UN; ++u) {
+        const uint32_t j = jb + 2 * u;
+        if (j < c1) {
+          const float2 vv = __half22float2(*reinterpret_cast<const __half2 *>(&raw[u]));
+          const float pj = s_s[j - c0];
+          acc.x = fmaf(pj, vv.x, acc.x);
+          acc.y = fmaf(pj, vv.y, acc.y);
+        }
+      }
     }
   }
   __syncthreads();
