@@ -1,5 +1,5 @@
 """Host logic of the tensor-parallel path on CPU: shard geometry, slicing of 34-byte
-block matrices, and the handle exchange over a world_size-2 gloo group. The exchange step
+block matrices, and the handle exchange over world_size-2 and -4 gloo groups. The exchange step
 itself (peer stores inside the decode kernel) needs GPUs: tests/test_tp_gpu.py."""
 import os
 import subprocess
@@ -56,11 +56,15 @@ def test_shard_geometry():
     assert np.array_equal(vk.q8_0_dequantize(s, 4, 64), full[2:6, 32:96])
 
 
-def test_two_rank_gloo_exchange_and_sharded_matvec(tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gloo_exchange_and_sharded_matvec(tmp_path, world):
     script = tmp_path / "w.py"
     script.write_text(WORKER)
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", "29613", str(script), ROOT]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % world, "--master-addr", "127.0.0.1",
+           "--master-port", str(29613 + world), str(script), ROOT]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
-    assert r.stdout.count("ok") == 2
+    assert r.stdout.count("ok") == world
