@@ -76,9 +76,12 @@ __global__ void __launch_bounds__(kThreads) mv_kernel(const MvParams p) {
     }
   };
 
-  Stage<Q8, NW> st[kDepth];
+  // FP16 weights: 16-byte fragments, twice the registers per stage; one stage in flight per warp
+  // and more resident CTAs measured faster than two stages (7B FP16 decode 240 -> 277 tok/s)
+  constexpr int KD = !Q8 ? 1 : kDepth;
+  Stage<Q8, NW> st[KD];
 #pragma unroll
-  for (int d = 0; d < kDepth; ++d)
+  for (int d = 0; d < KD; ++d)
     if (g0 + d < g1) load(st[d], g0 + d);
 
   // ---- input rows -------------------------------------------------------
@@ -192,13 +195,13 @@ __global__ void __launch_bounds__(kThreads) mv_kernel(const MvParams p) {
     }
   };
 
-  for (uint32_t base = g0; base < g1; base += kDepth) {
+  for (uint32_t base = g0; base < g1; base += KD) {
 #pragma unroll
-    for (int d = 0; d < kDepth; ++d) {
+    for (int d = 0; d < KD; ++d) {
       const uint32_t grp = base + d;
       if (grp < g1) {
         process(st[d], grp);
-        if (grp + kDepth < g1) load(st[d], grp + kDepth);
+        if (grp + KD < g1) load(st[d], grp + KD);
       }
     }
   }
