@@ -504,3 +504,30 @@ def test_matmul_run_many_matches_single_calls_and_times_them(dev):
     cmd.submit_and_wait()
     assert us > 0.0
     assert_close(got, want, what="matmul after run_many")
+
+
+# 32 rows and more go through the tensor-core tile kernel (64 query rows per CTA): from an
+# empty cache, on top of history (chunked prefill) and across the end of the ring.
+@pytest.mark.parametrize("T,offset,maxlen", [(100, 0, 256), (70, 90, 256), (64, 100, 128), (33, 0, 64)])
+def test_multiheadattention_many_rows(dev, T, offset, maxlen):
+    heads, dim = 4, 64
+    Wd = heads * dim
+    ws = [O.synth_q8_0(161, i, Wd, Wd, 0.0, 0.05) for i in range(4)]  # wk, wq, wv, wo
+    att = O.lib().orc_attn_create(heads, dim, maxlen)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tw = [up(cmd, dev, w, vk.Q8_0, 1, Wd, Wd) for w in ws]
+    op = vk.MultiHeadAttentionV2(dev, cmd, tw[0], tw[1], tw[2], tw[3], maxlen, dim, True, vk.FP16, True, False).init()
+    cmd.end()
+    cmd.submit_and_wait()
+    steps = ([(offset, 0)] if offset else []) + [(T, offset)]
+    for (t, off) in steps:
+        x = O.synth_f16(161, 10 + off, t * Wd).reshape(t, Wd)
+        want = np.empty(t * Wd, np.uint16)
+        O.lib().orc_attn_forward_q8_0(att, x, ws[0], ws[1], ws[2], ws[3], t, off, 0, want)
+        cmd.begin()
+        tx = up(cmd, dev, x, vk.FP16, 1, t, Wd)
+        got = cmd.download(op(tx, off))
+        cmd.end()
+        cmd.submit_and_wait()
+    assert_close(got, want, what="mha T=%d offset=%d maxlen=%d" % (T, offset, maxlen))
