@@ -7,13 +7,19 @@ the weight-plus-KV stream beside it and the CPU port timed on the host cores.
     python bench.py --impl reference --steps K --warmup W    # CPU port of the reference's op math
 
 One step = one whole job of the workload: prefill of the seeded prompt, then
-the greedy decode tokens, each decode token one replay of the captured CUDA
-graph. `value` is decoded tokens per second over the decode phases (the
+the greedy decode tokens, each decode token one launch of the persistent decode
+kernel. `value` is decoded tokens per second over the decode phases (the
 reference's "eval speed", app/llama2_infer.cpp:212-218), timed with CUDA events
-on the stream the graph is launched on. Weights are synthetic (seeded N(0,0.02),
+on the stream the kernel is launched on. Weights are synthetic (seeded N(0,0.02),
 Q8_0-quantised on the device): no checkpoint is read.
+
+Every line carries `parity`: a hash of the first greedy ids of the timed job, whether all
+ranks produced the same ids, and (13B) how far the ids follow the single-GPU model's, which
+rank 0 runs beside the sharded one. The 1-GPU line also carries `tp_anchor`: the 13B model on
+one GPU, the base of the 2/4/8-GPU curve.
 """
 import argparse
+import hashlib
 import json
 import os
 import subprocess
@@ -26,12 +32,20 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# Tensor ids of the seeded prompts. They were picked by tests/golden/screen_prompts_gpu.py so that the
+# first PARITY_IDS greedy steps are each decided by several fp16 ulps: implementations that differ
+# only in fp32 summation order (decode plans, tensor-parallel degrees) then produce the same ids,
+# and `parity.ids_sha` can be compared across lines.
+PROMPT_ID_7B = 1000
+PROMPT_ID_13B = 1000
+PARITY_IDS = 32
+
 WORKLOADS = {
     # name: dims, prompt, decode tokens
     "llama2-7b-q8_0": dict(dim=4096, heads=32, ffn=11008, vocab=32000, layers=32, maxlen=4096,
-                           prompt=32, decode=256, seed=20240602),
+                           prompt=32, decode=256, seed=20240602, prompt_id=PROMPT_ID_7B),
     "llama2-13b-q8_0": dict(dim=5120, heads=40, ffn=13824, vocab=32000, layers=40, maxlen=4096,
-                            prompt=128, decode=512, seed=20240604),
+                            prompt=128, decode=512, seed=20240604, prompt_id=PROMPT_ID_13B),
     # FP16 weights, 512-token prompt: the prefill runs on the tcgen05 tensor-core GEMMs (a parity/profiling case, not the headline)
     "llama2-7b-f16": dict(dim=4096, heads=32, ffn=11008, vocab=32000, layers=32, maxlen=4096,
                           prompt=512, decode=256, seed=20240603, weights="f16"),
@@ -52,8 +66,23 @@ def bytes_per_token(w, L, tp=1):
     mats = nl * (4 * wb(d, d) + 3 * wb(f, d)) + wb(v, d)
     norms = (2 * nl + 1) * d * 4
     emb = wb(1, d)
-    kv = 2 * d * 2  # K and V, fp16, all heads, per cached position
+    kv = 2 * d * 2 * nl  # K and V, fp16, all heads, all layers, per cached position
     return mats / tp + norms + emb + kv * (L + 1) / tp
+
+
+def config_of(name, w, world):
+    """The `config` object of a line: the same for both arms, so the lines can be compared."""
+    Ls = np.arange(w["prompt"] + 1, w["prompt"] + w["decode"] + 1)
+    bytes_tok = float(np.mean([bytes_per_token(w, L, world) for L in Ls]))
+    return {"workload": name, "batch": 1, "prompt_tokens": w["prompt"], "decode_tokens": w["decode"],
+            "kv_len": "%d..%d" % (w["prompt"] + 1, w["prompt"] + w["decode"]),
+            "parallelism": "tp%d" % world, "l2": "inputs (%.1f GB of weights per token) larger than L2" % (bytes_tok / 1e9),
+            "step": "one job = prefill + %d decode tokens; value counts decode tokens over decode time" % w["decode"]}
+
+
+def ids_sha(ids):
+    """Short sha256 over the first PARITY_IDS greedy ids (uint32, little endian)."""
+    return hashlib.sha256(np.asarray(ids[:PARITY_IDS], "<u4").tobytes()).hexdigest()[:16]
 
 
 def peak_hbm():
@@ -119,53 +148,71 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_port_tokens_per_s(w, budget_s=20.0, layers_sample=2):
-    """The CPU port (oracle) on a bounded sample: `layers_sample` decoder blocks of the
-    workload's shape plus the output layer, decode steps at mid-range KV length; the
-    per-token time of the full model is layers/layers_sample * block time + head time."""
+def cpu_port_sample(w, layers_sample=2, steps=16):
+    """One bounded sample of the CPU port (oracle): `steps` decode steps through `layers_sample`
+    decoder blocks of the workload's shape at mid-range KV length, plus the output layer. Returns
+    a closure that runs the sample once and gives (seconds for the sample, seconds per token
+    EXTRAPOLATED to the full model: layers / layers_sample x block time + output-layer time)."""
     from oracle import oracle as O
-    cores = os.cpu_count() or 1
+    O.set_threads(os.cpu_count() or 1)  # a launcher may have pinned OMP_NUM_THREADS to 1
     om = O.Model(dim=w["dim"], heads=w["heads"], ffn=w["ffn"], vocab=w["vocab"], layers=layers_sample,
                  maxlen=512, seed=w["seed"])
     L0 = w["prompt"] + w["decode"] // 2
     x = O.synth_f16(w["seed"], 999, w["dim"]).reshape(1, w["dim"])
-    # warm + fill the caches so the attention reads a realistic history length
+    # fill the caches so the attention reads a realistic history length
     for l in range(layers_sample):
         om.kcache(l)[:, :L0] = O.synth_f16(w["seed"], 900 + l, w["heads"] * L0 * (w["dim"] // w["heads"])).reshape(w["heads"], L0, -1)
         om.vcache(l)[:, :L0] = om.kcache(l)[:, :L0]
-    om.block(0, x, 1, L0)
-    t0, n = time.time(), 0
-    t_block = 0.0
-    while time.time() - t0 < budget_s * 0.6 and n < 64:
-        a = time.time()
-        for l in range(layers_sample):
-            om.block(l, x, 1, L0 + 1 + (n % 8))
-        t_block += time.time() - a
-        n += 1
-    t_block /= n * layers_sample
     tok = np.array([1], np.uint32)
-    # output layer: time a zero-layer-equivalent forward by differencing
-    t1, k = time.time(), 0
-    while time.time() - t1 < budget_s * 0.3 and k < 16:
-        om.forward(tok, L0 + 10 + k)
-        k += 1
-    t_fwd = (time.time() - t1) / k
-    t_head = max(t_fwd - layers_sample * t_block, 0.0)
-    per_token = w["layers"] * t_block + t_head
-    return 1.0 / per_token, cores, ("%d of %d decoder blocks + output layer, %d decode steps at KV length ~%d, scaled to %d blocks"
-                                    % (layers_sample, w["layers"], n, L0, w["layers"]))
+
+    def run():
+        a = time.time()
+        for n in range(steps):
+            for l in range(layers_sample):
+                om.block(l, x, 1, L0 + 1 + (n % 8))
+        t_block = (time.time() - a) / (steps * layers_sample)
+        b = time.time()
+        k = max(2, steps // 4)
+        for i in range(k):  # whole small model = layers_sample blocks + output layer; the head is the difference
+            om.forward(tok, L0 + 10 + i)
+        t_fwd = (time.time() - b) / k
+        t_head = max(t_fwd - layers_sample * t_block, 0.0)
+        return time.time() - a, w["layers"] * t_block + t_head
+
+    what = ("EXTRAPOLATED from a sample: %d of %d decoder blocks + output layer, %d decode steps at KV length ~%d per step, "
+            "block time scaled to %d blocks" % (layers_sample, w["layers"], steps, L0, w["layers"]))
+    return run, O.threads(), what
+
+
+def cpu_port_tokens_per_s(w, reps=2):
+    run, threads, what = cpu_port_sample(w)
+    run()
+    per_tok = min(run()[1] for _ in range(reps))
+    return 1.0 / per_tok, threads, what
 
 
 def run_reference(args, w, name):
-    v, cores, sample = cpu_port_tokens_per_s(w, budget_s=max(10.0, 6.0 * (args.steps + args.warmup)))
+    """The reference arm: the CPU port of the reference's op math on all host threads. One step is
+    one bounded sample (see cpu_port_sample); `value` is tokens/s extrapolated to the full model,
+    `ms_per_step` the measured duration of a sample step."""
+    run, threads, what = cpu_port_sample(w)
+    for _ in range(max(args.warmup, 1)):
+        run()
+    t_steps, per_tok = [], []
+    for _ in range(max(args.steps, 1)):
+        t, pt = run()
+        t_steps.append(t)
+        per_tok.append(pt)
+    v = 1.0 / float(np.mean(per_tok))
     line = {"impl": "reference", "metric": "decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * w["decode"] / v, "higher_is_better": True,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * float(np.mean(t_steps)), "higher_is_better": True,
             "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "q8_0 weights, fp16 activations, fp32 accumulate",
-            "data": "synthetic", "config": {"workload": name, "batch": 1, "prompt_tokens": w["prompt"], "decode_tokens": w["decode"]},
-            "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "data": "synthetic", "config": config_of(name, w, args.gpus),
+            "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": what},
             "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "the reference runs only through Vulkan (unavailable on this box) and ships no CPU implementation of its ops; "
-                    "this arm times the CPU restatement of its shader math (oracle/) on the host cores"}
+                    "this arm times the CPU restatement of its shader math (oracle/) on the host cores; value is extrapolated "
+                    "from the sample, ms_per_step is the measured time of one sample step"}
     print(json.dumps(line))
 
 
@@ -265,6 +312,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=[None] + list(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-anchor", action="store_true", help="skip the single-GPU 13B model run beside the timed workload")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -286,7 +334,7 @@ def main():
         return 0
 
     import vkllama_b200 as vk
-    from oracle import oracle as O  # seeded prompt generator and cpu_baseline leg only
+    from vkllama_b200.synth import synth_tokens
 
     tp = world
     dist = None
@@ -303,7 +351,7 @@ def main():
     if tp > 1:
         from vkllama_b200 import tp as vtp
         vtp.connect(model, dist, rank, world)
-    prompt = O.synth_tokens(w["seed"], 1000, w["prompt"], w["vocab"])
+    prompt = synth_tokens(w["seed"], w.get("prompt_id", 1000), w["prompt"], w["vocab"])
     n_gen = w["decode"] + 1  # the prefill yields the first id, then `decode` one-token steps
 
     def barrier():
@@ -321,6 +369,7 @@ def main():
     launches0 = vk.kernel_launches()
     dec_ms, pre_ms = [], []
     t0 = time.time()
+    ids = None
     for _ in range(args.steps):
         ids, p_ms, d_ms = model.generate(prompt, n_gen)  # synchronises its stream before returning
         dec_ms.append(d_ms)
@@ -331,11 +380,17 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     dec_total = float(sum(dec_ms))
     job_ms = float(sum(dec_ms) + sum(pre_ms)) / args.steps
+    parity = {"n_ids": PARITY_IDS, "ids_sha": ids_sha(ids), "ranks_agree": True,
+              "what": "sha256 over the first %d greedy ids of the last timed job" % PARITY_IDS}
     if dist is not None:
         import torch
         t = torch.tensor([dec_total, job_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dec_total, job_ms = float(t[0]), float(t[1])
+        mine = torch.tensor(np.asarray(ids, np.int64), device="cuda")
+        every = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        parity["ranks_agree"] = bool(all(torch.equal(e, mine) for e in every))  # over all generated ids
     tok_s = args.steps * w["decode"] / (dec_total / 1000.0)
     ms_tok = dec_total / (args.steps * w["decode"])
 
@@ -357,11 +412,34 @@ def main():
         barrier()
         e2e_t += time.time() - a
     e2e = e2e_jobs * w["decode"] / e2e_t
-    prof = np.zeros(16)
+    prof = np.zeros(20)
     reps = 16
     for i in range(reps):  # collective under tensor parallelism: every rank runs it
         prof += np.array(model.decode_profile(int(prompt[i % len(prompt)]), w["prompt"] + 100 + i))
     prof /= reps
+    barrier()
+
+    # ---- the single-GPU 13B model beside the sharded one (rank 0): the parity oracle of tensor
+    # parallelism (the reference is single-device) and, on the 1-GPU line, the base of the curve
+    anchor = None
+    want_anchor = (not args.no_anchor) and rank == 0 and (tp > 1 or name == "llama2-7b-q8_0")
+    if want_anchor:
+        model.close() if tp == 1 else None
+        aw = WORKLOADS["llama2-13b-q8_0"]
+        one = vk.Model(dev, aw["dim"], aw["heads"], aw["ffn"], aw["vocab"], aw["layers"], aw["maxlen"])
+        one.synth_weights(aw["seed"])
+        ap = synth_tokens(aw["seed"], aw["prompt_id"], aw["prompt"], aw["vocab"])
+        one.generate(ap, aw["decode"] + 1)
+        a_ids, a_pre, a_dec = one.generate(ap, aw["decode"] + 1)
+        one.close()
+        anchor = {"workload": "llama2-13b-q8_0", "tp": 1, "value": aw["decode"] / (a_dec / 1000.0), "unit": "tokens/s",
+                  "ms_per_token": a_dec / aw["decode"], "prefill_ms": a_pre, "ids_sha": ids_sha(a_ids), "n_ids": PARITY_IDS}
+        if tp > 1:
+            same = np.asarray(a_ids) == np.asarray(ids)
+            parity["tp1"] = {"ids_sha": anchor["ids_sha"], "matches_tp1": anchor["ids_sha"] == parity["ids_sha"],
+                             "ids_equal_until": int(np.argmin(same)) if not same.all() else int(same.size),
+                             "of": int(same.size)}
+    barrier()
 
     if rank != 0:
         if dist is not None:
@@ -373,7 +451,7 @@ def main():
     Ls = np.arange(w["prompt"] + 1, w["prompt"] + w["decode"] + 1)
     bytes_tok = float(np.mean([bytes_per_token(w, L, tp) for L in Ls]))
     step_gbs = bytes_tok / (ms_tok * 1e-3) / 1e9
-    persistent = os.environ.get("VKLLAMA_DECODE", "") != "graph" and prof[8:].sum() > 0
+    persistent = os.environ.get("VKLLAMA_DECODE", "") != "graph" and prof[10:].sum() > 0
     if persistent:
         # one kernel launch per token: the dominant kernel is the whole decode step
         kname = "decode_mega_kernel (persistent decode step: TMA weight ring + mma.sync consumers, all ops of a token)"
@@ -383,15 +461,13 @@ def main():
         k_bytes = 2 * (w["ffn"] // tp * w["dim"] * 2 if f16w else q8_bytes(w["ffn"] // tp, w["dim"])) + w["dim"] * 2 + w["dim"] * 4 + (w["ffn"] // tp) * 2
         k_us = prof[4] / w["layers"]
     k_gbs = k_bytes / (k_us * 1e-6) / 1e9
+    classes = ["embedding", "norm_qkv", "attention", "o_proj_add", "norm_gateup_swiglu", "down_add", "norm_lm_head", "argmax", "allreduce"]
     line = {
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": job_ms, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
         "dtype": "%s weights, fp16 activations, fp32 accumulate" % ("fp16" if f16w else "q8_0"), "data": "synthetic",
-        "config": {"workload": name, "batch": 1, "prompt_tokens": w["prompt"], "decode_tokens": w["decode"],
-                   "kv_len": "%d..%d" % (w["prompt"] + 1, w["prompt"] + w["decode"]),
-                   "parallelism": "tp%d" % world, "l2": "inputs (%.1f GB of weights per token) larger than L2" % (bytes_tok / 1e9),
-                   "step": "one job = prefill + %d decode tokens; value counts decode tokens over decode time" % w["decode"]},
+        "config": config_of(name, w, world),
         "ms_per_token": ms_tok, "prefill_ms": float(np.mean(pre_ms)),
         "roofline": {"bound": "hbm", "kernel": kname, "achieved": k_gbs,
                      "peak": peak, "unit": "GB/s", "frac": k_gbs / peak, "traffic": TRAFFIC_NCU.get(name) if persistent else None,
@@ -399,16 +475,17 @@ def main():
         "roofline_step": {"bound": "hbm", "what": "whole decode token: weights + norm weights + embedding row + KV", "achieved": step_gbs,
                           "peak": peak, "unit": "GB/s", "frac": step_gbs / peak, "frac_of_8TBs_nominal": step_gbs / 8000.0,
                           "bytes_per_token": bytes_tok, "peak_kind": peak_kind},
-        "op_us_per_token": dict(zip(["embedding", "norm_qkv", "attention", "o_proj_add", "norm_gateup_swiglu", "down_add",
-                                     "norm_lm_head", "argmax"], [float(x) for x in prof[:8]])),
-        "op_barrier_wait_us_per_token": dict(zip(["embedding", "norm_qkv", "attention", "o_proj_add", "norm_gateup_swiglu", "down_add",
-                                                  "norm_lm_head", "argmax"], [float(x) for x in prof[8:]])),
+        "op_us_per_token": dict(zip(classes, [float(x) for x in prof[:9]])),
+        "op_wait_us_per_token": dict(zip(classes, [float(x) for x in prof[10:19]])),
         "decode_path": "persistent kernel" if persistent else "cuda graph of 5 kernels per layer",
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 4 * (w["prompt"] + w["decode"]),
                 "d2h_bytes_per_step": 4 * (w["vocab"] // tp) * (w["decode"] + 1),
                 "what": "vkl_model_forward per token: host id in, fp32 logits out, host arg-max"},
+        "parity": parity,
         "gpu_launches": int(launches), "clocks": clocks, "wall_s": wall,
     }
+    if anchor is not None and tp == 1:
+        line["tp_anchor"] = anchor
     if f16w:
         # dense prefill on the tensor cores: 2 flops per weight per prompt token (attention and the 1-row lm head left out)
         d, f, nl = w["dim"], w["ffn"], w["layers"]

@@ -27,6 +27,8 @@ typedef struct vkl_tensor vkl_tensor;
 typedef struct vkl_command vkl_command;
 typedef struct vkl_op vkl_op;
 typedef struct vkl_model vkl_model;
+typedef struct vkl_gguf vkl_gguf;
+typedef struct vkl_sampler vkl_sampler;
 
 /* src/core/common.h:15-22 (enum DType), same numeric values. */
 enum vkl_dtype { VKL_FP32 = 0, VKL_FP16 = 1, VKL_UINT32 = 2, VKL_INT8 = 3, VKL_Q8_0 = 4 };
@@ -35,6 +37,7 @@ enum vkl_dtype { VKL_FP32 = 0, VKL_FP16 = 1, VKL_UINT32 = 2, VKL_INT8 = 3, VKL_Q
 enum vkl_status {
   VKL_OK = 0,
   VKL_INVALID_ARGUMENT = 3,
+  VKL_NOT_FOUND = 5,
   VKL_RESOURCE_EXHAUSTED = 8,
   VKL_FAILED_PRECONDITION = 9,
   VKL_OUT_OF_RANGE = 11,
@@ -51,6 +54,11 @@ int vkl_device_create(int ordinal, vkl_device **out);
 int vkl_device_destroy(vkl_device *dev);
 /* name: at least 256 bytes. */
 int vkl_device_info(vkl_device *dev, char *name, int *sm_count, size_t *total_mem);
+/* Bytes of released device memory the device keeps for reuse (the counterpart of VMA's
+ * block pool behind src/core/tensor.cpp:112-156). A released block is handed out again
+ * only after the work that was queued on the device's streams at release time has
+ * finished; the pool holds at most an eighth of the device memory. */
+int vkl_device_pool_bytes(vkl_device *dev, size_t *bytes);
 
 /* ---- tensor: Tensor, src/core/tensor.h:16-90 ------------------------------
  * Shape [c,h,w], row-major, strides in bytes (tensor.cpp:248-258). A handle is
@@ -181,8 +189,11 @@ int vkl_cast_run(vkl_op *op, vkl_tensor *in, vkl_tensor **out);
  * uint32; lowest index wins ties, as ArgMax. The scratch of the two-stage reduction
  * is a fixed 64 KiB array inside the library, resident on every GPU that loads it:
  * rows * ceil(width/1024) may not exceed 8192, larger inputs are refused with
- * VKL_OUT_OF_RANGE. The first call on a device looks the array's device address up
- * (with that device current); make that first call before any stream capture.
+ * VKL_OUT_OF_RANGE. The first call on a device looks the array's device address up;
+ * make that first call before any stream capture. The device that owns x_fp16, out_idx
+ * and the stream must be the current device on EVERY call (the address is looked up
+ * for the current device); pointers of another device, or host pointers, are refused
+ * with VKL_INVALID_ARGUMENT before anything is launched.
  * All calls share the array: calls that overlap on the GPU race and must be
  * serialised by the caller. Enqueues on cuda_stream (cudaStream_t, may be NULL) and
  * does not synchronise. */
@@ -231,15 +242,22 @@ int vkl_model_synth_weights(vkl_model *m, uint64_t seed, float wstd, float nstd)
 int vkl_model_forward(vkl_model *m, const uint32_t *toks, size_t n, size_t offset,
                       float *logits_out);
 /* llama2_infer's loop (app/llama2_infer.cpp:141-210) with the greedy pick kept
- * on the device: prefill `prompt`, then n_gen - 1 one-token steps, each step one
- * replay of a captured CUDA graph. out_ids receives n_gen ids. If
- * device_ms is not NULL it receives the device time of the decode steps only. */
+ * on the device: prefill `prompt`, then n_gen - 1 one-token steps. With Q8_0 weights a
+ * step is one launch of the persistent decode kernel (all ops of the token in one
+ * cooperative launch); with FP16 weights, or under VKLLAMA_DECODE=graph, it is one replay
+ * of a captured CUDA graph of five kernels per layer. out_ids receives n_gen ids.
+ * prefill_ms / decode_ms, when not NULL, receive the device time of the two phases. */
 int vkl_model_generate(vkl_model *m, const uint32_t *prompt, size_t n_prompt, size_t n_gen,
                        uint32_t *out_ids, float *prefill_ms, float *decode_ms);
 /* The id the device picked after the last forward/generate step (greedy arg-max over the
  * whole vocabulary, also when the output layer is split over tensor-parallel ranks); the
  * device-side counterpart of TopkSampler(1)::sample (models/samplers.cpp:37-64). */
 int vkl_model_last_token(vkl_model *m, uint32_t *id);
+/* The k largest logits of the last forward / generate step and their token ids, sorted
+ * descending (equal values: lowest id first), selected on the device so that a top-k
+ * sampler needs k pairs instead of the 128 KB of logits that the reference downloads
+ * per token (models/llama2.h:283-298, 835-842). 1 <= k <= 64. Single-GPU models. */
+int vkl_model_topk(vkl_model *m, uint32_t k, float *values, uint32_t *ids);
 /* Copy one layer's caches [heads_local, maxlen, head_dim] fp16 to / from the host. */
 int vkl_model_read_kv(vkl_model *m, uint32_t layer, void *kcache, void *vcache);
 int vkl_model_write_kv(vkl_model *m, uint32_t layer, const void *kcache, const void *vcache);
@@ -248,13 +266,23 @@ int vkl_model_write_kv(vkl_model *m, uint32_t layer, const void *kcache, const v
 int vkl_model_block_forward(vkl_model *m, uint32_t layer, const void *x_fp16, size_t T,
                             size_t offset, void *out_fp16);
 /* Op::time() for the model path (models/llama2.h:816-841 prints per-op costs): one
- * decode step with a time stamp after each op. out_us[0..7]: device microseconds
+ * decode step with a time stamp after each op. out_us[0..8]: device microseconds
  * summed over layers of 0 embedding, 1 RMSNorm+QKV, 2 RoPE+append+attention,
  * 3 o_proj+residual, 4 RMSNorm+gate/up+SwiGLU, 5 down+residual, 6 RMSNorm+lm head,
- * 7 arg-max; out_us[8..15]: the part of each spent waiting at the grid barrier (the
- * persistent kernel, timeline of its first CTA; 0 on the multi-kernel path, which is
- * timed with an event after every launch). Appends to the KV cache at `offset`. */
-int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[16]);
+ * 7 arg-max, 8 tensor-parallel all-reduce (9 unused); out_us[10..19]: the part of each
+ * spent waiting for the other CTAs after the op (the persistent kernel, timeline of its
+ * first CTA; 0 on the multi-kernel path, which is timed with an event after every launch).
+ * Appends to the KV cache at `offset`. */
+int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[20]);
+/* The same step with a global-timer stamp (ns) by every CTA of the persistent kernel at six
+ * points of every op: out[(op * grid + cta) * 8 + k], k = 0 op entered, 1 input vector
+ * complete, 2 the CTA's first warp finished its weight stream, 3 all its warps did,
+ * 4 results stored, 5 end-of-op synchronisation passed (unset stamps are 0). With out == NULL
+ * only *nops and *grid are returned (out needs nops * grid * 8 words). kinds[nops], when
+ * not NULL, receives per op: kind | matrices << 8 | epilogue << 16. A profiling aid with no
+ * counterpart in the reference beyond Op::time(). */
+int vkl_model_decode_trace(vkl_model *m, uint32_t token, size_t offset, unsigned long long *out, size_t cap,
+                           uint32_t *nops, uint32_t *grid, uint32_t *kinds);
 /* Tensor-parallel set-up (no counterpart in the reference, which is single-device:
  * gpu_device.cpp:14-21). One process per GPU creates its shard (tp_rank of tp_size);
  * each exports its exchange buffer over CUDA IPC, the processes swap the 64-byte handles
@@ -268,6 +296,41 @@ int vkl_model_tp_buffer(vkl_model *m, void **local_ptr, size_t *bytes);
 int vkl_model_tp_connect(vkl_model *m, void *const *peer_ptrs, int n);
 int vkl_ipc_export(void *device_ptr, unsigned char handle[64]);
 int vkl_ipc_open(vkl_device *dev, const unsigned char handle[64], void **device_ptr);
+
+
+/* ---- checkpoint container: gguflib as used by app/llama2_infer.cpp:46-73 ---------------
+ * Read-only view of a GGUF file (versions 2 and 3), memory mapped. Keys are the metadata
+ * the reference reads (models/llama2.h:367-370: llama.attention.head_count,
+ * llama.block_count, llama.attention.layer_norm_rms_epsilon, llama.context_length);
+ * tensors are looked up by index (name == NULL) or by name and handed out as pointers
+ * into the mapping, valid until vkl_gguf_close. dims[0] is the row length, as in GGUF;
+ * ggml_type 0/1/8 = F32/F16/Q8_0 (llama2.h:382-397); bytes is 0 for other types. */
+int vkl_gguf_open(const char *path, vkl_gguf **out);
+int vkl_gguf_close(vkl_gguf *g);
+int vkl_gguf_counts(const vkl_gguf *g, uint32_t *version, size_t *n_keys, size_t *n_tensors);
+int vkl_gguf_get_u32(const vkl_gguf *g, const char *key, uint32_t *out);
+int vkl_gguf_get_f32(const vkl_gguf *g, const char *key, float *out);
+int vkl_gguf_get_string(const vkl_gguf *g, const char *key, char *buf, size_t cap);
+int vkl_gguf_tensor(const vkl_gguf *g, size_t index, const char *name, char *name_out, size_t name_cap,
+                    uint32_t *ndim, uint64_t dims[4], uint32_t *ggml_type, const void **data, size_t *bytes);
+/* Model::init (models/llama2.h:348-681) from an open file: configuration from the llama.*
+ * keys and the tensor shapes, every tensor uploaded (and sharded when tp_size > 1).
+ * maxlen 0 keeps llama.context_length, otherwise the smaller of the two is used. */
+int vkl_model_load_gguf(vkl_device *dev, const vkl_gguf *g, uint32_t maxlen, int tp_rank, int tp_size,
+                        vkl_model **out);
+
+/* ---- samplers: models/samplers.h, samplers.cpp:37-101 -----------------------------------
+ * kind 0 = TopkSampler(topk): softmax over the k largest logits, one draw.
+ * kind 1 = TopPSampler(topp): the shortest descending prefix whose softmax mass reaches p,
+ * renormalised, one draw. seed 0 seeds the generator from std::random_device as the
+ * reference does; any other seed makes the draws reproducible. Equal logits are ordered by
+ * token id (the reference's std::sort leaves ties unspecified).
+ * vkl_sampler_sample_candidates draws from a descending candidate list such as
+ * vkl_model_topk returns (top-k samplers only). */
+int vkl_sampler_create(int kind, size_t topk, float topp, uint64_t seed, vkl_sampler **out);
+int vkl_sampler_destroy(vkl_sampler *s);
+int vkl_sampler_sample(vkl_sampler *s, const float *logits, size_t n, int *id);
+int vkl_sampler_sample_candidates(vkl_sampler *s, const float *values, const uint32_t *ids, size_t k, int *id);
 
 #ifdef __cplusplus
 }

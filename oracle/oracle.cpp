@@ -43,6 +43,13 @@ static inline uint16_t f2h(float f) {
   return u;
 }
 
+// Host threads of the OpenMP loops below (a launcher may have pinned OMP_NUM_THREADS to 1).
+#include <omp.h>
+ORC_API int orc_threads(void) { return omp_get_max_threads(); }
+ORC_API void orc_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+}
+
 // ---------------------------------------------------------------------------
 // Seeded synthetic data (stands in for real checkpoints). Integer-only up to
 // one fp32 fma, so a device implementation reproduces it bit for bit.

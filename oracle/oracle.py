@@ -21,13 +21,25 @@ f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
 u32, u64, f32, i32, vp = C.c_uint32, C.c_uint64, C.c_float, C.c_int, C.c_void_p
 
 
+def reference_tree():
+    """Path of a vkllama source tree to build the reference's own quantizer from: the
+    VKLLAMA_REFERENCE environment variable, else a `reference` folder beside this repository's
+    parent; None when neither holds src/core/quants.h."""
+    cands = [os.environ.get("VKLLAMA_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "src", "core", "quants.h")):
+            return c
+    return None
+
+
 def build(force=False):
     """Compile liboracle.so (and oracle/_ref when the reference tree is here)."""
     src = os.path.join(_HERE, "oracle.cpp")
     if force or not os.path.exists(_LIB) or os.path.getmtime(_LIB) < os.path.getmtime(src):
         subprocess.check_call(["make", "-C", _HERE, "liboracle.so"], stdout=subprocess.DEVNULL)
-    if os.path.exists("/root/reference/src/core/quants.h") and (force or not os.path.exists(_REF)):
-        subprocess.check_call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
+    ref = reference_tree()
+    if ref and (force or not os.path.exists(_REF)):
+        subprocess.check_call(["make", "-C", _HERE, "ref", "REF=" + ref], stdout=subprocess.DEVNULL)
 
 
 _lib = None
@@ -45,6 +57,8 @@ def lib():
         f.restype = res
         f.argtypes = list(args)
 
+    sig("orc_threads", i32)
+    sig("orc_set_threads", None, i32)
     sig("orc_synth_normal_f32", None, u64, u64, u64, u64, f32, f32, f32p)
     sig("orc_synth_normal_f16", None, u64, u64, u64, u64, f32, f32, u16p)
     sig("orc_synth_tokens", None, u64, u64, u64, u32, u32p)
@@ -139,6 +153,15 @@ def synth_f16(seed, tensor, n, mean=0.0, std=1.0, first=0):
     out = np.empty(n, np.uint16)
     lib().orc_synth_normal_f16(seed, tensor, first, n, mean, std, out)
     return out
+
+
+def threads():
+    """OpenMP threads the oracle's loops run on."""
+    return int(lib().orc_threads())
+
+
+def set_threads(n):
+    lib().orc_set_threads(int(n))
 
 
 def synth_tokens(seed, tensor, n, vocab):

@@ -1,6 +1,6 @@
 """Generates tests/golden/llama2_7b_q8_0_greedy.npz with the CPU oracle.
 
-    python tests/golden/make_golden_7b.py [n_gen]
+    python tests/golden/make_golden_7b.py [n_gen] [--sel-id TENSOR_ID]
 
 Full Llama-2-7B shape (32 layers, dim 4096, 32 heads, FFN 11008, vocab 32000),
 synthetic N(0,0.02) weights quantised to Q8_0 (seed 20240602), a 32-token
@@ -12,11 +12,17 @@ Two records are stored:
           are decided by a gap of 0 or 1 fp16 ulp (1/128 at |logit| in [4,8)),
           which no implementation with another summation order can be expected
           to reproduce; the GPU test walks this record teacher-forced and
-          checks every step whose gap is above 2 ulps.
-  sel_*   the first prompt id 1001, 1002, ... for which the oracle's gap stays
-          >= 2 ulps (0.015625) over all n_gen steps; the GPU test requires the
-          free-running greedy ids to match on this one exactly.
-Takes several minutes per candidate prompt and about 8 GB of host memory.
+          checks every step whose gap is at least 4 ulps.
+  sel_*   a prompt whose every step the oracle decides by at least 4 ulps
+          (MIN_GAP): the GPU test requires the free-running greedy ids of both
+          decode plans to equal the oracle's on all n_gen steps. Such prompts are
+          about one in a hundred; --sel-id names a candidate that
+          tests/golden/screen_prompts_gpu.py found on the device (a minute of GPU time
+          instead of hours of oracle time). The candidate is only a hint: everything
+          stored here is computed by the oracle, and a candidate whose oracle gap
+          falls below MIN_GAP is rejected. Without --sel-id the ids 1001, 1002, ...
+          are tried in turn.
+About a minute per candidate prompt on 8 cores and 8 GB of host memory.
 """
 import os
 import sys
@@ -29,7 +35,7 @@ sys.path.insert(0, ROOT)
 from oracle import oracle as O  # noqa: E402
 
 SEED = 20240602  # base 20240601 + config index 1 (full 7B decode)
-MIN_GAP = 2.0 / 128.0
+MIN_GAP = 4.0 / 128.0  # 4 fp16 ulps at |logit| in [4, 8)
 
 
 def greedy(m, prompt, n_gen, min_gap=None):
@@ -51,21 +57,29 @@ def greedy(m, prompt, n_gen, min_gap=None):
 
 
 def main():
-    n_gen = int(sys.argv[1]) if len(sys.argv) > 1 else 64
+    args = [a for a in sys.argv[1:]]
+    sel_id = None
+    if "--sel-id" in args:
+        i = args.index("--sel-id")
+        sel_id = int(args[i + 1])
+        del args[i:i + 2]
+    n_gen = int(args[0]) if args else 64
     t0 = time.time()
     m = O.Model(dim=4096, heads=32, ffn=11008, vocab=32000, layers=32, maxlen=4096, seed=SEED)
     print("weights: %.1f s" % (time.time() - t0), flush=True)
     base_prompt = O.synth_tokens(SEED, 1000, 32, 32000)
     b_ids, b_gap, b_logits = greedy(m, base_prompt, n_gen)
     print("base prompt done: min gap %.4f (%.1f s)" % (b_gap.min(), time.time() - t0), flush=True)
-    pid = 1000
+    pid = (sel_id - 1) if sel_id is not None else 1000
     while True:
         pid += 1
         prompt = O.synth_tokens(SEED, pid, 32, 32000)
         ids, gap, logits = greedy(m, prompt, n_gen, MIN_GAP)
-        print("prompt id %d: %s (%.1f s)" % (pid, "ok" if ids is not None else "gap below 2 ulps", time.time() - t0), flush=True)
+        print("prompt id %d: %s (%.1f s)" % (pid, "ok" if ids is not None else "gap below 4 ulps", time.time() - t0), flush=True)
         if ids is not None:
             break
+        if sel_id is not None:
+            sys.exit("candidate %d does not hold up under the oracle" % sel_id)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "llama2_7b_q8_0_greedy.npz")
     np.savez_compressed(path, seed=np.int64(SEED), base_prompt=base_prompt, base_ids=b_ids, base_gap=b_gap,
                         base_prefill_logits=b_logits, sel_prompt_id=np.int64(pid), sel_prompt=prompt, sel_ids=ids,

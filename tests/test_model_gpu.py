@@ -240,3 +240,84 @@ def test_decode_plan_switches_keep_parity(dev, monkeypatch, switch):
         g = dm2(tok, i)
         assert np.abs(g - w).max() <= LOGITS_MAX_ABS, (switch, i)
         tok = np.array([int(np.argmax(w))], np.uint32)
+
+
+# ---- callers either side of the token loop: checkpoint loading, samplers, chat-style sessions ----
+@pytest.mark.parametrize("f16", [False, True])
+def test_model_from_gguf_equals_model_from_set_weight(dev, tmp_path, f16):
+    """Model::init from a GGUF file (models/llama2.h:348-681): the same logits, bit for bit, as
+    the model whose tensors were handed over one by one."""
+    from test_gguf_samplers_cpu import write_gguf
+    cfg = dict(dim=256, heads=4, ffn=512, vocab=1000, layers=2, maxlen=128)
+    om = O.Model(seed=31, fp16=f16, **cfg)
+    path = str(tmp_path / "m.gguf")
+    write_gguf(path, om, cfg, f16=f16)
+    g = vk.Gguf(path)
+    dm = vk.Model.from_gguf(dev, g)
+    g.close()  # the weights are on the device: the mapping may go
+    ref = vk.Model(dev, cfg["dim"], cfg["heads"], cfg["ffn"], cfg["vocab"], cfg["layers"], cfg["maxlen"], weight_dtype=vk.FP16 if f16 else vk.Q8_0)
+    load_from_oracle(ref, om)
+    prompt = O.synth_tokens(31, 1000, 11, cfg["vocab"])
+    a, b = dm(prompt, 0), ref(prompt, 0)
+    assert np.array_equal(a, b)
+    assert np.abs(a - om.forward(prompt, 0)).max() <= LOGITS_MAX_ABS
+    assert dm.generate(prompt, 12)[0].tolist() == ref.generate(prompt, 12)[0].tolist()
+    # a shorter context than the file's llama.context_length
+    g = vk.Gguf(path)
+    short = vk.Model.from_gguf(dev, g, maxlen=32)
+    assert short.cfg.maxlen == 32 and np.array_equal(short(prompt, 0), b)
+
+
+def test_device_topk_and_topk_sampler(dev):
+    om, dm, cfg = small_pair(dev, seed=14)
+    prompt = O.synth_tokens(14, 1000, 9, cfg["vocab"])
+    logits = dm(prompt, 0)
+    for k in (1, 5, 40, 64):
+        vals, ids = dm.topk(k)
+        order = np.lexsort((np.arange(logits.size), -logits))[:k]
+        assert ids.tolist() == order.tolist() and np.array_equal(vals, logits[order])
+    assert dm.topk(1)[1][0] == dm.last_token()
+    s = vk.TopkSampler(1, seed=3)
+    assert s.sample_candidates(*dm.topk(8)) == int(np.argmax(logits))
+    with pytest.raises(vk.VklError) as e:
+        dm.topk(65)
+    assert e.value.code == 3
+
+
+def test_chat_session_multi_token_turns_on_top_of_history(dev):
+    """app/chat.cpp:286-304 calls model(tokens, offset) with several new tokens on top of the cached
+    history, then samples token by token, turn after turn: multi-token calls at offset > 0 and
+    one-token calls must interleave on one cache."""
+    om, dm, cfg = small_pair(dev, seed=15)
+    pos = 0
+    for turn, T in enumerate((7, 40, 3, 33)):  # short turns take the mat-vec path, long ones the 64-row passes
+        toks = O.synth_tokens(15, 1100 + turn, T, cfg["vocab"])
+        want, got = om.forward(toks, pos), dm(toks, pos)
+        assert np.abs(got - want).max() <= LOGITS_MAX_ABS, "turn %d" % turn
+        pos += T
+        tok = np.array([int(np.argmax(want))], np.uint32)
+        for i in range(3):
+            want, got = om.forward(tok, pos), dm(tok, pos)
+            assert np.abs(got - want).max() <= LOGITS_MAX_ABS, "turn %d step %d" % (turn, i)
+            pos += 1
+            tok = np.array([int(np.argmax(want))], np.uint32)
+    for l in range(cfg["layers"]):
+        gk, gv = dm.read_kv(l)
+        assert_close(gk[:, :pos], om.kcache(l)[:, :pos], tol=5e-3, what="kcache layer %d" % l)
+        assert_close(gv[:, :pos], om.vcache(l)[:, :pos], tol=5e-3, what="vcache layer %d" % l)
+
+
+def test_multi_token_call_wraps_the_ring_cache(dev):
+    """Positions beyond maxlen overwrite the oldest cache rows ((offset+row) % maxlen,
+    update_kvcache_fp16.comp:35), also inside a multi-token call."""
+    om, dm, cfg = small_pair(dev, seed=16, maxlen=32)
+    a = O.synth_tokens(16, 1000, 28, cfg["vocab"])
+    b = O.synth_tokens(16, 1001, 9, cfg["vocab"])
+    om.forward(a, 0)
+    dm(a, 0)
+    want, got = om.forward(b, 28), dm(b, 28)  # rows 28..36: wraps at 32
+    assert np.abs(got - want).max() <= LOGITS_MAX_ABS
+    for l in range(cfg["layers"]):
+        gk, gv = dm.read_kv(l)
+        assert_close(gk, om.kcache(l), tol=5e-3, what="kcache layer %d" % l)
+        assert_close(gv, om.vcache(l), tol=5e-3, what="vcache layer %d" % l)

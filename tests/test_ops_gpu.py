@@ -531,3 +531,50 @@ def test_multiheadattention_many_rows(dev, T, offset, maxlen):
         cmd.end()
         cmd.submit_and_wait()
     assert_close(got, want, what="mha T=%d offset=%d maxlen=%d" % (T, offset, maxlen))
+
+
+# ---- device memory pool -----------------------------------------------------------------------
+def test_released_block_is_not_reused_while_queued_work_still_writes_it(dev):
+    """Ops return without synchronising and every command has its own stream. A tensor released on
+    command A while A's kernels are still queued must not be handed to command B before they have
+    run: B's data would be overwritten by A's late writes."""
+    n = 64 * 1024 * 1024  # 128 MB of fp16: the fill kernels below run for a while
+    a, b = vk.Command(dev), vk.Command(dev)
+    for rep in range(3):
+        a.begin()
+        ta = vk.Tensor(1, 1, n, dev, vk.FP16)
+        for k in range(6):
+            a.fill_synthetic(ta, 7, 100 + k, 0.0, 1.0)  # queued on A's stream
+        a.end()
+        a.submit()
+        del ta  # released while A is still running
+        b.begin()
+        tb = vk.Tensor(1, 1, n, dev, vk.FP16)  # same size class: the pooled block, if it were free
+        b.fill_synthetic(tb, 9, 1, 0.0, 1.0)
+        got = b.download(tb)
+        b.end()
+        b.submit_and_wait()
+        a.wait()
+        assert np.array_equal(got.ravel()[:4096], O.synth_f16(9, 1, 4096)), "rep %d" % rep
+        assert np.array_equal(got.ravel()[-4096:], O.synth_f16(9, 1, 4096, first=n - 4096)), "rep %d" % rep
+        del tb
+
+
+def test_pool_is_bounded_under_varying_sizes(dev):
+    """Calls with many different row counts land in a bounded set of size classes, and what the
+    pool keeps never exceeds its cap (an eighth of the device memory)."""
+    cmd = vk.Command(dev)
+    cap = dev.info()[2] // 8
+    before = dev.pool_bytes()  # other tests' blocks
+    cmd.begin()
+    for rep in range(3):
+        for T in range(1, 200, 3):
+            t = vk.Tensor(1, T, 4096, dev, vk.FP16)
+            del t
+    cmd.end()
+    cmd.submit_and_wait()
+    kept = dev.pool_bytes()
+    assert kept <= cap
+    # 67 different sizes between 8 KB and 1.6 MB, three times over: at most one block per size class
+    # (a class is at most 25 % over the request) unless a block was still fenced when its size came up again
+    assert kept - before <= 2 * 67 * 1.25 * 200 * 4096 * 2

@@ -47,4 +47,7 @@ def test_argmax_noalloc_matches_argmax_op_on_two_calls_in_a_row():
     st = L.vkl_argmax_noalloc(tx.device_ptr(), 9000, 1024, out.device_ptr(), stream)
     assert st == 11 and b"8192" in L.vkl_last_error()
     assert L.vkl_argmax_noalloc(None, 1, 8, out.device_ptr(), stream) == 3
+    # a pointer that is not memory of the current device is refused on the host, before any launch
+    host = np.zeros(64, np.uint16)
+    assert L.vkl_argmax_noalloc(host.ctypes.data_as(C.c_void_p), 1, 64, out.device_ptr(), stream) == 3
     dev.close()

@@ -13,4 +13,5 @@ from .api import (  # noqa: F401
     ArgOp, ArgMax, ArgMin, Embedding, ElementWise, Transpose, Slice, Cast,
     Model, ModelConfig, q8_0_quantize, q8_0_quantize36, q8_0_dequantize, blocks36_to_34,
     kernel_launches, library_path, load_library, matmul_run_many,
+    Gguf, Sampler, TopkSampler, TopPSampler,
 )

@@ -48,6 +48,7 @@ def load_library():
     sigs = {
         "vkl_device_create": [i32, pvp], "vkl_device_destroy": [vp],
         "vkl_device_info": [vp, C.c_char_p, C.POINTER(i32), C.POINTER(sz)],
+        "vkl_device_pool_bytes": [vp, C.POINTER(sz)],
         "vkl_tensor_create": [vp, i32, i32, i32, i32, pvp], "vkl_tensor_retain": [vp],
         "vkl_tensor_release": [vp], "vkl_tensor_view": [vp, sz, sz, sz, pvp],
         "vkl_tensor_reshape": [vp, sz, sz, sz], "vkl_tensor_shape": [vp, C.POINTER(u32)],
@@ -88,8 +89,19 @@ def load_library():
         "vkl_model_last_token": [vp, C.POINTER(u32)], "vkl_model_read_kv": [vp, u32, vp, vp], "vkl_model_write_kv": [vp, u32, vp, vp],
         "vkl_model_block_forward": [vp, u32, vp, sz, sz, vp],
         "vkl_model_decode_profile": [vp, u32, sz, C.POINTER(f32)],
+        "vkl_model_decode_trace": [vp, u32, sz, vp, sz, C.POINTER(u32), C.POINTER(u32), vp],
         "vkl_model_tp_buffer": [vp, pvp, C.POINTER(sz)], "vkl_model_tp_connect": [vp, pvp, i32],
         "vkl_ipc_export": [vp, C.c_char_p], "vkl_ipc_open": [vp, C.c_char_p, pvp],
+        "vkl_model_topk": [vp, u32, vp, vp],
+        "vkl_gguf_open": [C.c_char_p, pvp], "vkl_gguf_close": [vp],
+        "vkl_gguf_counts": [vp, C.POINTER(u32), C.POINTER(sz), C.POINTER(sz)],
+        "vkl_gguf_get_u32": [vp, C.c_char_p, C.POINTER(u32)], "vkl_gguf_get_f32": [vp, C.c_char_p, C.POINTER(f32)],
+        "vkl_gguf_get_string": [vp, C.c_char_p, C.c_char_p, sz],
+        "vkl_gguf_tensor": [vp, sz, C.c_char_p, C.c_char_p, sz, C.POINTER(u32), C.POINTER(u64), C.POINTER(u32), pvp, C.POINTER(sz)],
+        "vkl_model_load_gguf": [vp, vp, u32, i32, i32, pvp],
+        "vkl_sampler_create": [i32, sz, f32, u64, pvp], "vkl_sampler_destroy": [vp],
+        "vkl_sampler_sample": [vp, vp, sz, C.POINTER(i32)],
+        "vkl_sampler_sample_candidates": [vp, vp, vp, sz, C.POINTER(i32)],
     }
     for name, args in sigs.items():
         f = getattr(L, name)
@@ -158,6 +170,12 @@ class Device:
         sms, mem = i32(), sz()
         _ck(self.L.vkl_device_info(self.h, name, C.byref(sms), C.byref(mem)))
         return name.value.decode(), sms.value, mem.value
+
+    def pool_bytes(self):
+        """Released device memory currently kept for reuse."""
+        n = sz()
+        _ck(self.L.vkl_device_pool_bytes(self.h, C.byref(n)))
+        return n.value
 
     def close(self):
         if self.h:
@@ -544,6 +562,28 @@ class Model:
         self.h = vp()
         _ck(self.L.vkl_model_create(dev.h, C.byref(self.cfg), C.byref(self.h)))
 
+    @classmethod
+    def from_gguf(cls, dev, gguf, maxlen=0, tp_rank=0, tp_size=1):
+        """Model::init from an open GGUF file (models/llama2.h:348-681)."""
+        self = cls.__new__(cls)
+        self.L = load_library()
+        self.dev = dev
+        self.h = vp()
+        _ck(self.L.vkl_model_load_gguf(dev.h, gguf.h, maxlen, tp_rank, tp_size, C.byref(self.h)))
+        heads, layers, eps, ctx = gguf.u32("llama.attention.head_count"), gguf.u32("llama.block_count"), \
+            gguf.f32("llama.attention.layer_norm_rms_epsilon"), gguf.u32("llama.context_length")
+        emb, outw = gguf.tensor("token_embd.weight"), gguf.tensor("output.weight")
+        ffn = gguf.tensor("blk.0.ffn_gate.weight")["dims"][1] if layers else emb["dims"][0]
+        self.cfg = ModelConfig(emb["dims"][0], heads, ffn, emb["dims"][1], layers, min(maxlen, ctx) if maxlen else ctx, eps, 1e-6,
+                               {0: FP32, 1: FP16, 8: Q8_0}[outw["type"]], tp_rank, max(1, tp_size))
+        return self
+
+    def topk(self, k):
+        """The k largest logits of the last step and their ids, selected on the device."""
+        vals, ids = np.empty(k, np.float32), np.empty(k, np.uint32)
+        _ck(self.L.vkl_model_topk(self.h, k, _ptr(vals), _ptr(ids)))
+        return vals, ids
+
     def set_weight(self, name, dtype, data):
         a = np.ascontiguousarray(data)
         _ck(self.L.vkl_model_set_weight(self.h, name.encode(), dtype, _ptr(a), a.nbytes))
@@ -596,9 +636,18 @@ class Model:
 
     def decode_profile(self, token, offset):
         """Per-kernel-class device microseconds of one decode step (see the header)."""
-        out = (f32 * 16)()
+        out = (f32 * 20)()
         _ck(self.L.vkl_model_decode_profile(self.h, token, offset, out))
         return list(out)
+
+    def decode_trace(self, token, offset):
+        """(stamps [nops, grid, 8] in ns, kinds [nops]) of one traced decode step (see the header)."""
+        nops, grid = u32(), u32()
+        _ck(self.L.vkl_model_decode_trace(self.h, token, offset, None, 0, C.byref(nops), C.byref(grid), None))
+        out = np.zeros((nops.value, grid.value, 8), np.uint64)
+        kinds = np.zeros(nops.value, np.uint32)
+        _ck(self.L.vkl_model_decode_trace(self.h, token, offset, _ptr(out), out.size, C.byref(nops), C.byref(grid), _ptr(kinds)))
+        return out, kinds
 
     def tp_export(self):
         """CUDA IPC handle (64 bytes) of this rank's exchange buffer."""
@@ -629,3 +678,98 @@ class Model:
             self.close()
         except Exception:
             pass
+
+
+# ---- checkpoint container and samplers ---------------------------------------------------
+class Gguf:
+    """Read-only GGUF file as the reference's app opens it (app/llama2_infer.cpp:46-73)."""
+
+    def __init__(self, path):
+        self.L = load_library()
+        self.h = vp()
+        _ck(self.L.vkl_gguf_open(os.fsencode(path), C.byref(self.h)))
+
+    def counts(self):
+        v, nk, nt = u32(), sz(), sz()
+        _ck(self.L.vkl_gguf_counts(self.h, C.byref(v), C.byref(nk), C.byref(nt)))
+        return v.value, nk.value, nt.value
+
+    def u32(self, key):
+        v = u32()
+        _ck(self.L.vkl_gguf_get_u32(self.h, key.encode(), C.byref(v)))
+        return v.value
+
+    def f32(self, key):
+        v = f32()
+        _ck(self.L.vkl_gguf_get_f32(self.h, key.encode(), C.byref(v)))
+        return v.value
+
+    def string(self, key, cap=4096):
+        b = C.create_string_buffer(cap)
+        _ck(self.L.vkl_gguf_get_string(self.h, key.encode(), b, cap))
+        return b.value.decode("utf-8", "replace")
+
+    def tensor(self, name_or_index):
+        """dict(name, dims (row length first, as in GGUF), type (GGML id), data (uint8 view of the mapping))."""
+        nm = C.create_string_buffer(512)
+        nd, dims, ty, data, nb = u32(), (u64 * 4)(), u32(), vp(), sz()
+        byname = isinstance(name_or_index, str)
+        _ck(self.L.vkl_gguf_tensor(self.h, 0 if byname else name_or_index, name_or_index.encode() if byname else None, nm, 512,
+                                   C.byref(nd), dims, C.byref(ty), C.byref(data), C.byref(nb)))
+        arr = np.ctypeslib.as_array(C.cast(data, C.POINTER(C.c_uint8)), shape=(nb.value,)) if nb.value else np.empty(0, np.uint8)
+        return {"name": nm.value.decode(), "dims": [int(dims[i]) for i in range(nd.value)], "type": ty.value, "data": arr}
+
+    def close(self):
+        if self.h:
+            self.L.vkl_gguf_close(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Sampler:
+    def __init__(self, kind, topk, topp, seed):
+        self.L = load_library()
+        self.h = vp()
+        _ck(self.L.vkl_sampler_create(kind, topk, topp, seed, C.byref(self.h)))
+
+    def sample(self, logits):
+        a = np.ascontiguousarray(logits, np.float32)
+        out = i32()
+        _ck(self.L.vkl_sampler_sample(self.h, _ptr(a), a.size, C.byref(out)))
+        return out.value
+
+    def sample_candidates(self, values, ids):
+        v, i = np.ascontiguousarray(values, np.float32), np.ascontiguousarray(ids, np.uint32)
+        out = i32()
+        _ck(self.L.vkl_sampler_sample_candidates(self.h, _ptr(v), _ptr(i), v.size, C.byref(out)))
+        return out.value
+
+    def close(self):
+        if self.h:
+            self.L.vkl_sampler_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class TopkSampler(Sampler):
+    """TopkSampler(topk = 40) (models/samplers.h:27-35)."""
+
+    def __init__(self, topk=40, seed=0):
+        super().__init__(0, topk, 1.0, seed)
+
+
+class TopPSampler(Sampler):
+    """TopPSampler(p) (models/samplers.h:37-45)."""
+
+    def __init__(self, p, seed=0):
+        super().__init__(1, 0, p, seed)

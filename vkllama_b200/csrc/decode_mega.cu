@@ -38,6 +38,7 @@ constexpr int THREADS = CT + 32;       // + producer warp
 constexpr int SG = (int)MEGA_SG;       // 4-block groups per ring stage: one per consumer warp
 constexpr uint32_t STAGE_CODES = SG * 2048, STAGE_SCALES = SG * 128;
 constexpr uint32_t STAGE_BYTES = STAGE_CODES + STAGE_SCALES;  // 32640
+static_assert(STAGE_BYTES == MEGA_STAGE_BYTES, "host and device agree on the stage size");
 constexpr int MAX_NST = 6;             // ring stages are a launch parameter (whatever fits), at most this many
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
@@ -101,6 +102,19 @@ __device__ __forceinline__ uint64_t ld_acq_u64(const unsigned long long *p) {
 }
 
 __device__ __forceinline__ bool getenv_prologue(const MegaParams &p) { return (p.timing_mode & 1u) != 0; }
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Trace mode (timing_mode bit 256, TIMED instances): thread 0 of EVERY CTA stamps the global
+// timer at fixed points of every op: [0] op entered, [1] input vector complete (after the
+// norm), [2] this warp's stream done, [3] all warps' streams done, [4] results stored,
+// [5] end-of-op synchronisation passed. Layout: trace[(op * grid + cta) * 8 + k].
+#define VKL_TRACE(k)                                                   \
+  do {                                                                 \
+    if (TIMED && trace) trace[k] = gtime();                            \
+  } while (0)
 
 struct Ctx {
   const MegaParams &p;
@@ -196,7 +210,15 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
   if (lane < min(n, 32u)) tabs[lane] = table[lane];
   __syncwarp();
   uint32_t it = 0, slot = 0, ph = 0;
+  uint32_t issued = 0;  // ring stages issued so far (table entries and stages differ: a KV entry is 0..n stages)
   bool stop = false;
+  // this CTA's (head, split) and row range of the attention ops: the same for every layer of the token
+  const uint32_t pos0 = p.state[0];
+  const uint32_t Lnow = min(pos0 + 1, p.maxlen);
+  const uint32_t S_eff = Lnow <= p.single_split_len ? 1u : p.splits;
+  uint32_t kv_c0 = 0, kv_c1 = 0;
+  if (blockIdx.x < p.heads * S_eff) mega_kv_range(Lnow, S_eff, blockIdx.x % S_eff, kv_c0, kv_c1);
+  const uint32_t kv_head = blockIdx.x / S_eff, kv_rps = mega_kv_rows_per_stage(p.head_dim);
   for (uint32_t base = 0; base < n && !stop; base += 32) {
     // chunk base/32 is in tabs[(base/32 % 4)*32 ..]; fetch the next one behind it. The table is a
     // ring of four chunks because the consumers, up to a ring depth of stages behind, still read
@@ -206,12 +228,41 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
     if (lane == 0) {
       const uint32_t end = min(base + 32, n);
       for (; it < end; ++it) {
-        if (it >= NST && !(p.timing_mode & 128u) && !c.wait(s32(&empty[slot]), ph ^ 1u, 2, 0)) {
+        const MegaStage &e = tabs[it & 127];
+        if (e.n0 == MEGA_KV_MARK) {
+          // K rows, then V rows, of this CTA's split of an attention op: whole cache rows,
+          // contiguous in [heads, maxlen, head_dim], up to kv_rps rows per stage
+          const uint32_t rowb = p.head_dim * 2u;
+          for (uint32_t kv = 0; kv < 2 && !stop; ++kv) {
+            const uint8_t *src = (kv ? e.scales0 : e.codes0) + ((size_t)kv_head * p.maxlen + kv_c0) * rowb;
+            for (uint32_t r0 = kv_c0; r0 < kv_c1; r0 += kv_rps) {
+              if (issued >= NST && !(p.timing_mode & 128u) && !c.wait(s32(&empty[slot]), ph ^ 1u, 2, 0)) {
+                stop = true;
+                break;
+              }
+              const uint32_t fb = s32(&full[slot]), bytes = min(kv_rps, kv_c1 - r0) * rowb;
+              if (p.timing_mode & 2u) {
+                mbar_arrive(fb);
+              } else {
+                mbar_expect(fb, bytes);
+                bulk_g2s(s32(ring + (size_t)slot * STAGE_BYTES), src + (size_t)(r0 - kv_c0) * rowb, bytes, fb);
+              }
+              ++issued;
+              if (++slot == NST) {
+                slot = 0;
+                ph ^= 1u;
+              }
+            }
+          }
+          if (stop) break;
+          continue;
+        }
+        if (issued >= NST && !(p.timing_mode & 128u) && !c.wait(s32(&empty[slot]), ph ^ 1u, 2, 0)) {
           stop = true;
           break;
         }
-        const MegaStage &e = tabs[it & 127];
         const uint32_t fb = s32(&full[slot]);
+        ++issued;
         if (p.timing_mode & 2u) {  // diagnostic: consumer speed without the weight stream
           mbar_arrive(fb);
         } else {
@@ -233,11 +284,10 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
     }
     stop = __shfl_sync(0xffffffffu, stop ? 1 : 0, 0) != 0;
   }
-  it = __shfl_sync(0xffffffffu, it, 0);
   // Nothing may still be landing in this CTA's shared memory when it exits.
   if (lane == 0) {
-    const uint32_t lo = it > NST ? it - NST : 0;
-    for (uint32_t j = lo; j < it; ++j) {
+    const uint32_t lo = issued > NST ? issued - NST : 0;
+    for (uint32_t j = lo; j < issued; ++j) {
       const uint32_t fb = s32(&full[j % NST]), ph2 = (j / NST) & 1u;
       for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(fb, ph2); ++i) {
       }
@@ -304,7 +354,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
                                           unsigned char *ring, uint64_t *full, uint64_t *empty, const MegaStage *tabs, __half *xs, float *xbias,
                                           const __half *zero16,
                                           float *red, float *ssum, Best &best, unsigned long long *tw, uint32_t ar_seq,
-                                          uint32_t tag_in, uint32_t tag_out) {
+                                          uint32_t tag_in, uint32_t tag_out, unsigned long long *trace) {
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t G = gridDim.x, cta = blockIdx.x;
   // Scalars in registers: the barriers' memory clobbers would otherwise make every use
@@ -331,7 +381,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   // CTA's results, so by the time it looked the producers of a later op may have re-tagged the words.)
   if (tl == 0) return;
   const uint32_t ntm = tl * nmat;                                        // (tile, matrix) row blocks of this CTA
-  const uint32_t nstages_dbg = op_global.stages_per_cta[cta];
+  const uint32_t nstages = op_global.stages_per_cta[cta];  // requested here, together with the input: needed when the stream starts
   // ---- input vector -> shared memory (RMSNorm fused, rounded to fp16 where the
   // reference's RMSNorm op rounds: rms_norm_fp16.comp:70-77). Norm weights and input are
   // requested together: one memory round trip.
@@ -440,6 +490,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     if (n < op.N) resid = __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
   }
   if (TIMED && tw) tw[1] = clock64();
+  VKL_TRACE(1);
 
   // ---- stream this CTA's row blocks. Every stage holds one group (4 blocks x 16 rows) per
   // consumer warp; stages run on across (tile, matrix) boundaries, so a warp's partial sums
@@ -451,12 +502,11 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     const uint32_t gi = warp / WPG, hb = (warp % WPG) * BPW;
     uint32_t cur = 0xffffffffu;
     float a0 = 0.f, a1 = 0.f;
-    const uint32_t nstages = op_global.stages_per_cta[cta];
     for (uint32_t sidx = 0; sidx < nstages; ++sidx) {
       unsigned long long w0 = 0;
       if (TIMED && tw) w0 = clock64();
       const bool ok = (DBG && (c.p.timing_mode & 128u)) ? true : c.wait(s32(&full[slot]), ph, 1);
-      if (TIMED && tw) tw[0] += (clock64() - w0) * 1000ull / 1965ull;  // SM cycles -> ns at the 1965 MHz boost clock
+      if (TIMED && tw) tw[0] += (clock64() - w0) * 1000ull / c.p.sm_mhz;  // SM cycles -> ns at the SM clock the host measured
       if (DBG && (c.p.timing_mode & 64u)) {  // diagnostic: handshake only
         __syncwarp();
         if (lane == 0 && !(c.p.timing_mode & 128u)) mbar_arrive(s32(&empty[slot]));
@@ -534,11 +584,13 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     }
   }
   // ---- one fixed-order reduction over the warps and the epilogue for all tiles
+  VKL_TRACE(2);
   if (TIMED && tw) {
     tw[2] = clock64();
-    if (c.p.timing_mode & 32u) tw[0] = (((tw[2] - tw[1]) * 1000ull / 1965ull) << 16) | (uint64_t)min(nstages_dbg, 65535u);
+    if (c.p.timing_mode & 32u) tw[0] = (((tw[2] - tw[1]) * 1000ull / c.p.sm_mhz) << 16) | (uint64_t)min(nstages, 65535u);
   }
   cons_sync();
+  VKL_TRACE(3);
   for (uint32_t idx = tid; idx < tl * 16; idx += CT) {
     const uint32_t lt = idx >> 4, r = idx & 15;
     const uint32_t n = (tile0 + lt * G) * 16 + r;
@@ -593,22 +645,26 @@ __device__ __forceinline__ void rope_pair(float x0, float x1, float cs, float sn
 
 // One (head, split) per CTA: RoPE(q), RoPE(k) + cache append by the split that
 // owns the new column, scores over its column range, partial softmax and P.V.
-// Same arithmetic as attention_kernel<true> (attention.cu).
+// Same arithmetic as attention_kernel<true> (attention.cu). The cached K and V rows of the
+// split come through the weight ring: they do not depend on this token (only the row of the
+// new position does, and that one is taken from the fresh projections), so the producer warp
+// has copied them into shared memory before q, k and v arrive.
 __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, float *sm, uint32_t pos0, uint32_t S, uint32_t tag_in,
-                                             uint32_t tag_out) {
+                                             uint32_t tag_out, uint32_t &slot, uint32_t &ph, const unsigned char *ring, uint64_t *full,
+                                             uint64_t *empty) {
   const MegaParams &p = c.p;
   const uint32_t cta = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (cta >= p.heads * S) return;
-  const uint32_t h = cta / S, split = cta % S, D = p.head_dim;
+  const uint32_t h = cta / S, split = cta % S, D = p.head_dim, NST = p.nst;
   float *q_s = sm, *kn_s = sm + D, *red_s = sm + 3 * D, *s_s = sm + (3 + NCW / 2) * D + 2 * NCW + 32;
   uint32_t *vn_s = reinterpret_cast<uint32_t *>(sm + 2 * D);  // the new V row as packed half pairs
   const uint32_t L = min(pos0 + 1, p.maxlen);
-  uint32_t chunk = (L + S - 1) / S;
-  chunk = (chunk + 31) & ~31u;
-  const uint32_t c0 = min(split * chunk, L), c1 = min(c0 + chunk, L);
+  uint32_t c0, c1;
+  mega_kv_range(L, S, split, c0, c1);
   const uint32_t jn = pos0 % p.maxlen;
   const bool owns = jn >= c0 && jn < c1;
   const size_t row = (size_t)h * D;
+  __half *kcache = op.kcache, *vcache = op.vcache;
   if (2 * tid < D) {
     const size_t fi = (size_t)pos0 * (D / 2) + tid;
     const float cs = p.freqc[fi], sn = p.freqs[fi];
@@ -632,51 +688,71 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
       kn_s[2 * tid] = __half2float(r0);
       kn_s[2 * tid + 1] = __half2float(r1);
       const size_t dst = ((size_t)h * p.maxlen + jn) * D + 2 * tid;
-      op.kcache[dst] = r0;
-      op.kcache[dst + 1] = r1;
-      op.vcache[dst] = ll_half(vw.x);
-      op.vcache[dst + 1] = ll_half(vw.y);
+      kcache[dst] = r0;
+      kcache[dst + 1] = r1;
+      vcache[dst] = ll_half(vw.x);
+      vcache[dst + 1] = ll_half(vw.y);
       vn_s[tid] = (vw.x & 0xffffu) | (vw.y << 16);  // the new row, for this CTA's P.V
     }
   }
   cons_sync();
   const float scale = 1.0f / sqrtf((float)D);
-  const __half *kc = op.kcache + (size_t)h * p.maxlen * D;
-  float lmax = -INFINITY;
-  for (uint32_t j = c0 + tid; j < c1; j += CT) {
-    float a = 0.f;
-    if (owns && j == jn) {
-      for (uint32_t d = 0; d < D; ++d) a = fmaf(q_s[d], kn_s[d], a);
-    } else {
-      const uint4 *kr = reinterpret_cast<const uint4 *>(kc + (size_t)j * D);
-#pragma unroll 8
-      for (uint32_t d8 = 0; d8 < D / 8; ++d8) {
-        const uint4 kv = __ldg(kr + d8);
-        const float4 qa = *reinterpret_cast<const float4 *>(q_s + d8 * 8);
-        const float4 qb = *reinterpret_cast<const float4 *>(q_s + d8 * 8 + 4);
-        const float2 k0 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.x));
-        const float2 k1 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.y));
-        const float2 k2 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.z));
-        const float2 k3 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.w));
-        a = fmaf(qa.x, k0.x, a); a = fmaf(qa.y, k0.y, a); a = fmaf(qa.z, k1.x, a); a = fmaf(qa.w, k1.y, a);
-        a = fmaf(qb.x, k2.x, a); a = fmaf(qb.y, k2.y, a); a = fmaf(qb.z, k3.x, a); a = fmaf(qb.w, k3.y, a);
+  const uint32_t rps = mega_kv_rows_per_stage(D), rows = c1 - c0;
+  // ---- scores: 16 lanes per cached row (8 dims each), two rows per warp and step
+  {
+    const uint32_t sub = lane & 15, hi = lane >> 4;
+    const bool act = sub * 8 < D;
+    float qv[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qv[e] = act ? q_s[sub * 8 + e] : 0.f;
+    for (uint32_t r0 = 0; r0 < rows; r0 += rps) {
+      const bool ok = (p.timing_mode & 128u) ? true : c.wait(s32(&full[slot]), ph, 1);
+      const uint32_t nr = min(rps, rows - r0);
+      const unsigned char *ks = ring + (size_t)slot * STAGE_BYTES;
+      for (uint32_t rb = warp * 2; rb < nr; rb += NCW * 2) {
+        const uint32_t r = rb + hi, j = c0 + r0 + r;
+        float a = 0.f;
+        if (ok && act && r < nr) {
+          if (owns && j == jn) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a = fmaf(qv[e], kn_s[sub * 8 + e], a);
+          } else {
+            const uint4 kv = *reinterpret_cast<const uint4 *>(ks + ((size_t)r * D + sub * 8) * 2);
+            const float2 k0 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.x));
+            const float2 k1 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.y));
+            const float2 k2 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.z));
+            const float2 k3 = __half22float2(*reinterpret_cast<const __half2 *>(&kv.w));
+            a = fmaf(qv[0], k0.x, a); a = fmaf(qv[1], k0.y, a); a = fmaf(qv[2], k1.x, a); a = fmaf(qv[3], k1.y, a);
+            a = fmaf(qv[4], k2.x, a); a = fmaf(qv[5], k2.y, a); a = fmaf(qv[6], k3.x, a); a = fmaf(qv[7], k3.y, a);
+          }
+        }
+        a += __shfl_xor_sync(0xffffffffu, a, 8);
+        a += __shfl_xor_sync(0xffffffffu, a, 4);
+        a += __shfl_xor_sync(0xffffffffu, a, 2);
+        a += __shfl_xor_sync(0xffffffffu, a, 1);
+        if (sub == 0 && r < nr) s_s[r0 + r] = round_h(a * scale);
+      }
+      __syncwarp();
+      if (lane == 0 && ok && !(p.timing_mode & 128u)) mbar_arrive(s32(&empty[slot]));
+      if (++slot == NST) {
+        slot = 0;
+        ph ^= 1u;
       }
     }
-    const float sc = round_h(a * scale);
-    s_s[j - c0] = sc;
-    lmax = fmaxf(lmax, sc);
   }
+  cons_sync();
+  float lmax = -INFINITY;
+  for (uint32_t i = tid; i < rows; i += CT) lmax = fmaxf(lmax, s_s[i]);
   lmax = warp_max(lmax);
   if (lane == 0) red_s[warp] = lmax;
   cons_sync();
   float mloc = red_s[0];
 #pragma unroll
   for (int w = 1; w < NCW; ++w) mloc = fmaxf(mloc, red_s[w]);
-  cons_sync();
   float lsum = 0.f;
-  for (uint32_t j = c0 + tid; j < c1; j += CT) {
-    const float pj = expf(s_s[j - c0] - mloc);
-    s_s[j - c0] = pj;
+  for (uint32_t i = tid; i < rows; i += CT) {
+    const float pj = expf(s_s[i] - mloc);
+    s_s[i] = pj;
     lsum += pj;
   }
   lsum = warp_sum(lsum);
@@ -685,31 +761,32 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
   float lloc = 0.f;
 #pragma unroll
   for (int w = 0; w < NCW; ++w) lloc += red_s[NCW + w];
-  // P.V: CT/64 column groups x up to 64 dim pairs
+  // P.V: CT/64 row groups x up to 64 dim pairs, rows of a group in ascending order
   const uint32_t npair = D / 2, grp = tid / 64, dp = tid % 64;
+  constexpr uint32_t NG = CT / 64;  // threads beyond NG*64 sit this part out
   float2 acc = make_float2(0.f, 0.f);
-  if (dp < npair && grp < CT / 64) {
-    const __half *vc = op.vcache + (size_t)h * p.maxlen * D + 2 * dp;
-    constexpr uint32_t NG = CT / 64, UN = 4;  // threads beyond NG*64 sit this part out (16 loads in flight per thread measured slower)
-    for (uint32_t jb = c0 + grp; jb < c1; jb += NG * UN) {
-      uint32_t raw[UN];
-#pragma unroll
-      for (uint32_t u = 0; u < UN; ++u) {  // all loads of the batch in flight together
-        const uint32_t j = jb + u * NG;
-        raw[u] = 0;
-        if (j < c1)
-          raw[u] = (owns && j == jn) ? vn_s[dp]
-                                     : __ldg(reinterpret_cast<const unsigned int *>(vc + (size_t)j * D));
-      }
-#pragma unroll
-      for (uint32_t u = 0; u < UN; ++u) {
-        const uint32_t j = jb + u * NG;
-        if (j < c1) {
-          const float2 vv = __half22float2(*reinterpret_cast<const __half2 *>(&raw[u]));
-          const float pj = s_s[j - c0];
+  {
+    const bool act = dp < npair && grp < NG;
+    uint32_t rnext = grp;  // this thread's next row of the split (rows grp, grp + NG, ...)
+    for (uint32_t r0 = 0; r0 < rows; r0 += rps) {
+      const bool ok = (p.timing_mode & 128u) ? true : c.wait(s32(&full[slot]), ph, 1);
+      const uint32_t nr = min(rps, rows - r0);
+      const unsigned char *vs = ring + (size_t)slot * STAGE_BYTES;
+      if (ok && act) {
+        for (; rnext < r0 + nr; rnext += NG) {
+          const uint32_t j = c0 + rnext;
+          const uint32_t raw = (owns && j == jn) ? vn_s[dp] : *reinterpret_cast<const uint32_t *>(vs + ((size_t)(rnext - r0) * D + 2 * dp) * 2);
+          const float2 vv = __half22float2(*reinterpret_cast<const __half2 *>(&raw));
+          const float pj = s_s[rnext];
           acc.x = fmaf(pj, vv.x, acc.x);
           acc.y = fmaf(pj, vv.y, acc.y);
         }
+      }
+      __syncwarp();
+      if (lane == 0 && ok) mbar_arrive(s32(&empty[slot]));
+      if (++slot == NST) {
+        slot = 0;
+        ph ^= 1u;
       }
     }
   }
@@ -998,6 +1075,15 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
   uint64_t *full = reinterpret_cast<uint64_t *>(tabs + 128);
   uint64_t *empty = full + MAX_NST;
   volatile uint32_t *abort_s = reinterpret_cast<volatile uint32_t *>(empty + MAX_NST);
+  // The op table lives in global memory; reading an entry there costs a chain of L2 round trips
+  // (kind, then the fields, then what they point to) at the start of every op. Three entries are
+  // kept in shared memory instead: the running op, the next one (looked at when this one ends)
+  // and the one after, which is copied in asynchronously while this op runs.
+  MegaOp *opbuf = reinterpret_cast<MegaOp *>(reinterpret_cast<unsigned char *>(empty + MAX_NST) + 16);
+  constexpr uint32_t OPV = sizeof(MegaOp) / 16;
+  static_assert(sizeof(MegaOp) % 16 == 0, "MegaOp is copied in 16-byte pieces");
+  if (threadIdx.x < 2 * OPV && threadIdx.x / OPV < p.nops)
+    reinterpret_cast<uint4 *>(opbuf)[threadIdx.x] = reinterpret_cast<const uint4 *>(p.ops)[threadIdx.x];
 
   if (threadIdx.x == 0) {
     for (uint32_t i = 0; i < NST; ++i) {
@@ -1030,19 +1116,33 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
   const uint32_t ebase = p.state[7];  // sequence number of this launch's first op; op oi tags its results with ebase + oi
   auto tag = [&](uint32_t op_index) { return (ebase + op_index) & 0xffffu; };
   Best best = {0.f, 0xffffffffu};
-  const bool timed = TIMED && p.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+  const bool tracing = TIMED && p.timing != nullptr && (p.timing_mode & 256u) != 0;
+  const bool timed = TIMED && p.timing != nullptr && !tracing && blockIdx.x == 0 && threadIdx.x == 0;
   unsigned long long t0 = 0, twait[3] = {0, 0, 0}, c0 = 0;
   if (timed) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   for (uint32_t oi = 0; oi < p.nops; ++oi) {
-    const MegaOp &op = p.ops[oi];
-    if (op.kind == MK_ATTN_COMBINE && S_eff == 1) continue;  // nothing to merge, no barrier either
+    const MegaOp &op = opbuf[oi % 3];
+    if (oi + 2 < p.nops && threadIdx.x < OPV) {  // entry oi + 2 replaces entry oi - 1, which every thread has left
+      const uint32_t dst = s32(reinterpret_cast<uint4 *>(opbuf + (oi + 2) % 3) + threadIdx.x);
+      const uint4 *src = reinterpret_cast<const uint4 *>(p.ops + oi + 2) + threadIdx.x;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(__cvta_generic_to_global(src)) : "memory");
+    }
+    if (op.kind == MK_ATTN_COMBINE && S_eff == 1) {  // nothing to merge, no grid barrier either
+      cons_sync();  // every thread has read this entry before the next op's copy may replace it
+      continue;
+    }
     if (timed) c0 = clock64();
+    unsigned long long *trace = (tracing && threadIdx.x == 0) ? p.timing + ((size_t)oi * gridDim.x + blockIdx.x) * 8 : nullptr;
+    VKL_TRACE(0);
     switch (op.kind) {
       case MK_EMBED: embed_op(c, tok, tag(oi)); break;
       case MK_MATVEC: matvec_op<TIMED, DBG>(c, op, it, slot, ph, ring, full, empty, tabs, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_groups * 256), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, seq0 + ar_i + 1,
-                         tag(op.src_op), tag(oi));
+                         tag(op.src_op), tag(oi), trace);
         break;
-      case MK_ATTN_PART: attn_part_op(c, op, reinterpret_cast<float *>(xq), pos0, S_eff, tag(op.src_op), tag(op.tag_op)); break;
+      case MK_ATTN_PART:
+        attn_part_op(c, op, reinterpret_cast<float *>(xq), pos0, S_eff, tag(op.src_op), tag(op.tag_op), slot, ph, ring, full, empty);
+        if (blockIdx.x < p.heads * p.splits) ++it;  // this CTA's KV entry of the stage table
+        break;
       case MK_ATTN_COMBINE: attn_combine_op(c, tag(oi)); break;
       case MK_ALLREDUCE:
         ++ar_i;
@@ -1084,27 +1184,16 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
       }
     }
     unsigned long long t1 = 0, t2 = 0;
+    VKL_TRACE(4);
     if (timed) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
     if (oi + 1 < p.nops) {
       // While waiting for the other CTAs: start what the next op will need from DRAM and
-      // does not depend on this op's results (norm weights, this CTA's rows of the KV cache).
-      const MegaOp &nx = p.ops[oi + 1];
+      // does not depend on this op's results (its norm weights).
+      const MegaOp &nx = opbuf[(oi + 1) % 3];
       if (nx.kind == MK_MATVEC && nx.norm_w) {
         for (uint32_t i = threadIdx.x * 32; i < nx.K; i += CT * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(nx.norm_w + i));
-      } else if (nx.kind == MK_ATTN_PART && blockIdx.x < p.heads * S_eff) {
-        const uint32_t h = blockIdx.x / S_eff, sp = blockIdx.x % S_eff;
-        uint32_t chunk = (Lnow + S_eff - 1) / S_eff;
-        chunk = (chunk + 31) & ~31u;
-        const uint32_t a0 = min(sp * chunk, Lnow), a1 = min(a0 + chunk, Lnow);
-        const size_t rowb = (size_t)p.head_dim * 2;
-        const char *kb = reinterpret_cast<const char *>(nx.kcache) + ((size_t)h * p.maxlen + a0) * rowb;
-        const char *vb = reinterpret_cast<const char *>(nx.vcache) + ((size_t)h * p.maxlen + a0) * rowb;
-        const size_t bytes = (size_t)(a1 - a0) * rowb;
-        for (size_t o = (size_t)threadIdx.x * 128; o < bytes; o += (size_t)CT * 128) {
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(kb + o));
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(vb + o));
-        }
       }
+      asm volatile("cp.async.wait_all;" ::: "memory");  // entry oi + 2 has landed; the barrier below publishes it
       if (op.barrier_after) {
         ++rounds;
         grid_barrier(c, (base_rounds + rounds) * G, (uint32_t)rounds, abort_s + 1);
@@ -1112,13 +1201,14 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
         cons_sync();  // the next op reuses this one's shared memory; its input words carry their own arrival tags
       }
     }
+    VKL_TRACE(5);
     if (timed) {
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t2));
       p.timing[2 * oi] = t1 - t0;
       p.timing[2 * oi + 1] = t2 - t1;
       const unsigned long long cend = clock64();
-      p.timing[2 * p.nops + oi] = (p.timing_mode & 8u) ? (twait[2] ? (cend - twait[2]) * 1000ull / 1965ull - (t2 - t1) : 0ull)
-                                  : getenv_prologue(p) ? (twait[1] > c0 ? (twait[1] - c0) * 1000ull / 1965ull : 0ull)
+      p.timing[2 * p.nops + oi] = (p.timing_mode & 8u) ? (twait[2] ? (cend - twait[2]) * 1000ull / p.sm_mhz - (t2 - t1) : 0ull)
+                                  : getenv_prologue(p) ? (twait[1] > c0 ? (twait[1] - c0) * 1000ull / p.sm_mhz : 0ull)
                                                         : twait[0];
       twait[2] = 0;
       twait[0] = 0;
@@ -1138,7 +1228,7 @@ size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t max
   return (b + 127) / 128 * 128;
 }
 size_t decode_mega_smem(size_t xs_bytes, uint32_t nst, uint32_t red_slots) {
-  return (size_t)nst * STAGE_BYTES + xs_bytes + ((size_t)red_slots * NCW * 16 + 68) * 4 + 128 * sizeof(MegaStage) + 2 * MAX_NST * 8 + 64;
+  return (size_t)nst * STAGE_BYTES + xs_bytes + ((size_t)red_slots * NCW * 16 + 68) * 4 + 128 * sizeof(MegaStage) + 2 * MAX_NST * 8 + 16 + 3 * sizeof(MegaOp) + 64;
 }
 int decode_mega_max_k() { return 16384; }
 int decode_mega_max_stages() { return MAX_NST; }

@@ -558,6 +558,19 @@ extern "C" int vkl_argmax_noalloc(const void *x_fp16, uint32_t rows, uint32_t wi
   int dev = 0;
   VKL_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(VKL_UNIMPLEMENTED, "argmax_noalloc: device ordinal %d is beyond the 64 this entry point tracks", dev);
+  // The scratch address is looked up for the CURRENT device: input and output must live there
+  // too, or the kernels would be handed another GPU's address. (A host-side query, no allocation.)
+  for (const void *ptr : {x_fp16, (const void *)out_idx}) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(VKL_INVALID_ARGUMENT, "argmax_noalloc: %p is not a CUDA pointer", ptr);
+    }
+    if (at.type != cudaMemoryTypeDevice && at.type != cudaMemoryTypeManaged)
+      return fail(VKL_INVALID_ARGUMENT, "argmax_noalloc: %p is not device memory", ptr);
+    if (at.type == cudaMemoryTypeDevice && at.device != dev)
+      return fail(VKL_INVALID_ARGUMENT, "argmax_noalloc: %p lives on device %d but device %d is current; make the buffers' device current on every call", ptr, at.device, dev);
+  }
   void *scratch = nullptr;
   {
     // Set-up, once per device, with that device current: the array's name is only a
@@ -575,3 +588,80 @@ extern "C" int vkl_argmax_noalloc(const void *x_fp16, uint32_t rows, uint32_t wi
   return VKL_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// Device top-k over one row of fp32 logits, for the top-k sampler (models/samplers.cpp:37-64
+// sorts all pairs on the host after a 128 KB download). One CTA; pick i is the largest
+// (value, then lowest index) element that comes strictly after pick i-1 in that order, so
+// nothing has to be marked as taken: k passes over the row, which stays in L2.
+// ---------------------------------------------------------------------------------------
+namespace vkl {
+namespace {
+__device__ __forceinline__ bool topk_before(float v, uint32_t i, float w, uint32_t j) {  // (v,i) sorts before (w,j)
+  return v > w || (v == w && i < j);
+}
+__global__ void __launch_bounds__(1024) topk_f32_kernel(const float *__restrict__ x, uint32_t n, uint32_t k, float *vals, uint32_t *ids) {
+  __shared__ float sv[32];
+  __shared__ uint32_t si[32];
+  __shared__ float pv;
+  __shared__ uint32_t pi;
+  const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float prev_v = INFINITY;
+  uint32_t prev_i = 0;
+  bool first = true;
+  for (uint32_t pick = 0; pick < k; ++pick) {
+    float bv = -INFINITY;
+    uint32_t bi = 0xffffffffu;
+    for (uint32_t i = tid; i < n; i += 1024) {
+      const float v = x[i];
+      const bool after = first || topk_before(prev_v, prev_i, v, i);
+      if (after && (bi == 0xffffffffu || topk_before(v, i, bv, bi))) {
+        bv = v;
+        bi = i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (oi != 0xffffffffu && (bi == 0xffffffffu || topk_before(ov, oi, bv, bi))) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      sv[warp] = bv;
+      si[warp] = bi;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      bv = sv[lane];
+      bi = si[lane];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0xffffffffu && (bi == 0xffffffffu || topk_before(ov, oi, bv, bi))) {
+          bv = ov;
+          bi = oi;
+        }
+      }
+      if (lane == 0) {
+        pv = bv;
+        pi = bi;
+        vals[pick] = bv;
+        ids[pick] = bi;  // 0xffffffff when the row has fewer than k comparable values
+      }
+    }
+    __syncthreads();
+    prev_v = pv;
+    prev_i = pi;
+    first = false;
+    if (prev_i == 0xffffffffu) break;
+  }
+}
+}  // namespace
+cudaError_t launch_topk_f32(const float *x, uint32_t n, uint32_t k, float *vals, uint32_t *ids, cudaStream_t s) {
+  topk_f32_kernel<<<1, 1024, 0, s>>>(x, n, k, vals, ids);
+  return cudaGetLastError();
+}
+}  // namespace vkl

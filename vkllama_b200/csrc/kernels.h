@@ -63,6 +63,8 @@ cudaError_t launch_embedding(const uint8_t *vocab, int vocab_is_q8, const uint32
 cudaError_t launch_argop(const __half *x, uint32_t *out, void *partials, uint32_t rows,
                          uint32_t W, int op_type, cudaStream_t s);
 size_t argop_partials_bytes(uint32_t rows, uint32_t W);
+// The k largest of n fp32 values and their indices, descending (equal values: lowest index first).
+cudaError_t launch_topk_f32(const float *x, uint32_t n, uint32_t k, float *vals, uint32_t *ids, cudaStream_t s);
 cudaError_t launch_softmax(const __half *in, __half *out, uint32_t C, uint32_t H, uint32_t W,
                            int seq_mask, uint32_t offset, cudaStream_t s);
 cudaError_t launch_rope(__half *x, uint32_t C, uint32_t H, uint32_t W, uint64_t cs, uint64_t hs,
@@ -109,7 +111,10 @@ size_t attention_scratch_bytes(uint32_t T, uint32_t heads, uint32_t dim, uint32_
 
 // ---- persistent decode step (decode_mega.cu) --------------------------------
 enum MegaKind { MK_EMBED = 0, MK_MATVEC = 1, MK_ATTN_PART = 2, MK_ATTN_COMBINE = 3, MK_ARGMAX = 4, MK_ALLREDUCE = 5 };
-struct MegaOp {
+// One entry of the token's op table. The kernel keeps the current and the next entry in shared
+// memory (copied there with 16-byte asynchronous copies while the op before runs), so the size
+// is a multiple of 16 bytes.
+struct alignas(16) MegaOp {
   uint32_t kind, epi, nmat, rot;
   uint32_t N, K, tiles, groups;
   const uint8_t *codes[3];
@@ -134,13 +139,29 @@ struct MegaOp {
 // One ring stage of the persistent kernel: up to MEGA_SG consecutive groups (4 Q8_0 blocks x
 // 16 rows each) of a CTA's weight stream, as at most two contiguous runs: the tail of one
 // (tile, matrix) and the head of the next.
+//
+// An entry with n0 == MEGA_KV_MARK stands for the K and V rows of an attention op instead:
+// codes0 / scales0 are the layer's K / V cache. How many ring stages it becomes depends on the
+// token's KV length: producer and consumers both derive this CTA's (head, split) row range from
+// the position and cut it into stages of mega_kv_rows_per_stage() rows, all K stages first.
 struct MegaStage {
   const uint8_t *codes0, *scales0;
   const uint8_t *codes1, *scales1;
   uint32_t n0, n1;  // groups of the first and of the second run
   uint32_t tm, kg;  // consumers' view: row block (local tile x matrix) and first group of run 0; run 1 starts row block tm + 1
 };
+constexpr uint32_t MEGA_KV_MARK = 0xffffffffu;
 constexpr uint32_t MEGA_SG = 15;  // groups per stage = consumer warps: one group per warp per stage
+constexpr uint32_t MEGA_STAGE_BYTES = MEGA_SG * (2048 + 128);
+// Cache rows (head_dim fp16 values each) of one KV ring stage: whole rows, a multiple of 8.
+__host__ __device__ inline uint32_t mega_kv_rows_per_stage(uint32_t head_dim) { return (MEGA_STAGE_BYTES / (head_dim * 2u)) & ~7u; }
+// The cached rows [c0, c1) that split `split` of `S` reads at KV length L.
+__host__ __device__ inline void mega_kv_range(uint32_t L, uint32_t S, uint32_t split, uint32_t &c0, uint32_t &c1) {
+  uint32_t chunk = (L + S - 1) / S;
+  chunk = (chunk + 31) & ~31u;
+  c0 = split * chunk < L ? split * chunk : L;
+  c1 = c0 + chunk < L ? c0 + chunk : L;
+}
 // How a stage that starts at group `kg` of a (tile, matrix) of `groups` groups is cut: n0 groups
 // of this (tile, matrix), then n1 of the next one (if the op has one for this CTA). Host and
 // device walk the stream with the same rule.
@@ -204,6 +225,7 @@ struct MegaParams {
   // Optional timeline of CTA 0: per op, nanoseconds of work and of barrier wait.
   unsigned long long *timing;
   uint32_t timing_mode;  // third column of the timeline: 0 = ring wait, 1 = op prologue
+  uint32_t sm_mhz;       // SM clock for the timeline's cycle counts (measured by the host before a profiled launch)
 };
 size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits);
 size_t decode_mega_smem(size_t xs_bytes, uint32_t nst, uint32_t red_slots);

@@ -81,6 +81,7 @@ struct vkl_model {
   vkl_tensor *mega_ops = nullptr, *mega_sync = nullptr, *mega_arg = nullptr, *mega_attn = nullptr, *mega_stages = nullptr, *mega_counts = nullptr, *mega_ll = nullptr;
   MegaParams mp;
   uint32_t mega_launches_per_token = 1;
+  uint32_t sm_mhz = 0;  // measured SM clock, for the profiled launches' cycle counts
   cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
   uint32_t *pos_dev() { return (uint32_t *)state->data(); }
   uint32_t *step_dev() { return (uint32_t *)state->data() + 1; }
@@ -95,7 +96,10 @@ struct vkl_model {
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
     if (ev2) cudaEventDestroy(ev2);
-    if (stream) cudaStreamDestroy(stream);
+    if (stream) {
+      dev->remove_stream(stream);
+      cudaStreamDestroy(stream);
+    }
   }
 };
 
@@ -332,7 +336,14 @@ int build_mega(vkl_model *m) {
   const int G = m->dev->prop.multiProcessorCount;
   uint32_t splits = (uint32_t)G / m->heads_l;
   if (splits < 1) return VKL_OK;  // more heads than SMs: keep the graph path
-  if (splits > 8) splits = 8;
+  // One GPU: at most 8 splits per head. Tensor-parallel ranks have few heads each: there the
+  // splits spread a head's cache rows over (nearly) all SMs, the attention op's time would not
+  // shrink with the rank count otherwise.
+  {
+    const char *se = getenv("VKLLAMA_ATTN_SPLITS");
+    const uint32_t cap = se ? std::max(1u, (uint32_t)atoi(se)) : (tp > 1 ? 32u : 8u);
+    if (splits > cap) splits = cap;
+  }
   const uint32_t max_groups = (std::max(c.dim, m->ffn_l) / 32 + 3) / 4;
   const size_t xs_bytes = decode_mega_xs_bytes(max_groups, m->head_dim, c.maxlen, splits);
   // every op's (tiles per CTA) x (matrices) needs a reduction slot
@@ -447,6 +458,18 @@ int build_mega(vkl_model *m) {
   std::vector<size_t> op_index;     // index into `ops` of every mat-vec op
   for (size_t oi = 0; oi < ops.size(); ++oi) {
     const MegaOp &o = ops[oi];
+    if (o.kind == MK_ATTN_PART) {
+      // the cached K and V rows of every (head, split) CTA go through the ring too: one marker
+      // entry, which the kernel turns into as many stages as the token's KV length needs
+      for (uint32_t cta = 0; cta < m->heads_l * splits; ++cta) {
+        MegaStage e = {};
+        e.n0 = MEGA_KV_MARK;
+        e.codes0 = (const uint8_t *)o.kcache;
+        e.scales0 = (const uint8_t *)o.vcache;
+        per_cta[cta].push_back(e);
+      }
+      continue;
+    }
     if (o.kind != MK_MATVEC) continue;
     op_index.push_back(oi);
     for (int cta = 0; cta < G; ++cta) {
@@ -553,6 +576,18 @@ int build_mega(vkl_model *m) {
 }
 
 __global__ void bump_sequence_kernel(uint32_t *seq, uint32_t by) { *seq += by; }
+
+// SM cycles and nanoseconds of one thread spinning for about 50 us: the SM clock a profiled
+// launch converts its cycle counts with.
+__global__ void clock_probe_kernel(unsigned long long *out) {
+  unsigned long long t0, t1, c0 = clock64();
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  do {
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+  } while (t1 - t0 < 50000ull);
+  out[0] = clock64() - c0;
+  out[1] = t1 - t0;
+}
 
 // After a batch of decode launches: a wait that timed out inside the kernel is
 // reported as an error and the barrier words are reset.
@@ -714,6 +749,7 @@ int vkl_model_create(vkl_device *dev, const vkl_model_config *cfg, vkl_model **o
   };
   cudaError_t e = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking);
   if (e != cudaSuccess) return bail(fail(VKL_INTERNAL, "cudaStreamCreate: %s", cudaGetErrorString(e)));
+  dev->add_stream(m->stream);
   cudaEventCreate(&m->ev0);
   cudaEventCreate(&m->ev1);
   cudaEventCreate(&m->ev2);
@@ -926,6 +962,25 @@ int vkl_model_last_token(vkl_model *m, uint32_t *id) {
   return VKL_OK;
 }
 
+int vkl_model_topk(vkl_model *m, uint32_t k, float *values, uint32_t *ids) {
+  if (!m || !values || !ids) return fail(VKL_INVALID_ARGUMENT, "model_topk: null argument");
+  if (k < 1 || k > 64 || k > m->vocab_l) return fail(VKL_INVALID_ARGUMENT, "model_topk: k = %u (1..64, at most the vocabulary)", k);
+  if (m->cfg.tp_size > 1) return fail(VKL_UNIMPLEMENTED, "model_topk: the output layer of a tensor-parallel model is split over ranks");
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  void *buf = nullptr;
+  VKL_OKAY(m->dev->alloc(64 * 8, &buf));
+  float *dv = (float *)buf;
+  uint32_t *di = (uint32_t *)buf + 64;
+  cudaError_t e = launch_topk_f32((const float *)m->logits32->data(), m->vocab_l, k, dv, di, m->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(values, dv, k * 4, cudaMemcpyDeviceToHost, m->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(ids, di, k * 4, cudaMemcpyDeviceToHost, m->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+  m->dev->release(buf, 64 * 8);
+  count_launches(1);
+  if (e != cudaSuccess) return fail(VKL_INTERNAL, "model_topk: %s", cudaGetErrorString(e));
+  return VKL_OK;
+}
+
 int vkl_model_read_kv(vkl_model *m, uint32_t layer, void *kcache, void *vcache) {
   if (!m || layer >= m->cfg.layers) return fail(VKL_INVALID_ARGUMENT, "model_read_kv: bad model or layer");
   VKL_CUDA(cudaSetDevice(m->dev->ordinal));
@@ -1006,7 +1061,7 @@ int vkl_model_block_forward(vkl_model *m, uint32_t layer, const void *x_fp16, si
   return VKL_OK;
 }
 
-int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[16]) {
+int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float out_us[20]) {
   VKL_OKAY(check_ready(m));
   if (!out_us) return fail(VKL_INVALID_ARGUMENT, "model_decode_profile: null output");
   if (offset + 1 > (size_t)2 * m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_decode_profile: position out of range");
@@ -1015,14 +1070,28 @@ int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float 
   const uint32_t st[2] = {(uint32_t)offset, 0};
   VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaMemcpyAsync(m->toks->data(), &token, 4, cudaMemcpyHostToDevice, m->stream));
-  for (int i = 0; i < 16; ++i) out_us[i] = 0.f;
+  for (int i = 0; i < 20; ++i) out_us[i] = 0.f;
   if (m->mega_ready) {
+    if (!m->sm_mhz) {
+      void *cb = nullptr;
+      VKL_OKAY(m->dev->alloc(16, &cb));
+      unsigned long long r[2] = {0, 0};
+      clock_probe_kernel<<<1, 1, 0, m->stream>>>((unsigned long long *)cb);
+      cudaError_t ce = cudaMemcpyAsync(r, cb, 16, cudaMemcpyDeviceToHost, m->stream);
+      if (ce == cudaSuccess) ce = cudaStreamSynchronize(m->stream);
+      m->dev->release(cb, 16);
+      count_launches(1);
+      if (ce != cudaSuccess) return fail(VKL_INTERNAL, "model_decode_profile: %s", cudaGetErrorString(ce));
+      m->sm_mhz = r[1] ? (uint32_t)(r[0] * 1000ull / r[1]) : 0u;
+      if (m->sm_mhz < 100u) m->sm_mhz = (uint32_t)(m->dev->prop.clockRate / 1000);
+    }
     // Timeline of CTA 0 of the persistent kernel: per op, work and barrier wait.
     const size_t n = m->mp.nops;
     void *buf = nullptr;
     VKL_OKAY(m->dev->alloc(n * 24, &buf));
     MegaParams p = m->mp;
     p.timing = (unsigned long long *)buf;
+    p.sm_mhz = m->sm_mhz;
     p.timing_mode = (getenv("VKLLAMA_DEBUG_PROLOGUE") ? 1 : 0) | (getenv("VKLLAMA_DEBUG_NOCOPY") ? 2 : 0) | (getenv("VKLLAMA_DEBUG_NOMATH") ? 4 : 0) | (getenv("VKLLAMA_DEBUG_EPILOGUE") ? 8 : 0) |
                     (getenv("VKLLAMA_DEBUG_LOOP") ? 32 : 0) | (getenv("VKLLAMA_DEBUG_NOBODY") ? 64 : 0) |
                     (getenv("VKLLAMA_DEBUG_NOHANDSHAKE") ? 128 : 0);
@@ -1036,27 +1105,33 @@ int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float 
     m->dev->release(buf, n * 24);
     count_launches(1);
     if (e != cudaSuccess) return fail(VKL_INTERNAL, "model_decode_profile: %s", cudaGetErrorString(e));
-    int nmv = 0;
+    // Classes: 0 embedding, 1 norm+QKV, 2 attention, 3 o_proj, 4 gate/up, 5 down, 6 lm head,
+    // 7 arg-max, 8 tensor-parallel all-reduce. A mat-vec's class follows from what it is:
+    // three matrices = QKV, SwiGLU epilogue = gate/up, arg-max tracking = lm head, and of the
+    // two residual projections the one right after the attention op is o_proj.
+    bool after_attn = false;
     for (size_t i = 0; i < n; ++i) {
       int cls = 0;
       switch (ops[i].kind) {
         case MK_EMBED: cls = 0; break;
         case MK_ATTN_PART:
-        case MK_ATTN_COMBINE: cls = 2; break;
+        case MK_ATTN_COMBINE: cls = 2; after_attn = true; break;
         case MK_ARGMAX: cls = 7; break;
-        default: {
-          const int j = nmv++;
-          const int per = 4, layers = (int)m->cfg.layers;
-          cls = j >= per * layers ? 6 : (j % per == 0 ? 1 : j % per == 1 ? 3 : j % per == 2 ? 4 : 5);
-        }
+        case MK_ALLREDUCE: cls = 8; break;
+        default:
+          if (ops[i].track_argmax) cls = 6;
+          else if (ops[i].nmat == 3) cls = 1;
+          else if (ops[i].epi == EPI_SWIGLU) cls = 4;
+          else if (after_attn) { cls = 3; after_attn = false; }
+          else cls = 5;
       }
       out_us[cls] += (float)(tl[2 * i] + tl[2 * i + 1]) * 1e-3f;
-      out_us[8 + cls] += (float)tl[2 * i + 1] * 1e-3f;
-      if (getenv("VKLLAMA_DEBUG_LOOP")) {  // diagnostic: [cls] = loop time, [8+cls] = stages of CTA 0
+      out_us[10 + cls] += (float)tl[2 * i + 1] * 1e-3f;
+      if (getenv("VKLLAMA_DEBUG_LOOP")) {  // diagnostic: [cls] = loop time, [10+cls] = stages of CTA 0
         out_us[cls] += (float)(tl[2 * n + i] >> 16) * 1e-3f - (float)(tl[2 * i] + tl[2 * i + 1]) * 1e-3f;
-        out_us[8 + cls] += (float)(tl[2 * n + i] & 0xffff) - (float)tl[2 * i + 1] * 1e-3f;
+        out_us[10 + cls] += (float)(tl[2 * n + i] & 0xffff) - (float)tl[2 * i + 1] * 1e-3f;
       }
-      if (getenv("VKLLAMA_DEBUG_RING")) out_us[8 + cls] = out_us[8 + cls] - (float)tl[2 * i + 1] * 1e-3f + (float)tl[2 * n + i] * 1e-3f;
+      if (getenv("VKLLAMA_DEBUG_RING")) out_us[10 + cls] = out_us[10 + cls] - (float)tl[2 * i + 1] * 1e-3f + (float)tl[2 * n + i] * 1e-3f;
     }
     return check_mega(m);
   }
@@ -1073,6 +1148,43 @@ int vkl_model_decode_profile(vkl_model *m, uint32_t token, size_t offset, float 
   if (rc != VKL_OK) return rc;
   if (e != cudaSuccess) return fail(VKL_INTERNAL, "model_decode_profile: %s", cudaGetErrorString(e));
   return VKL_OK;
+}
+
+int vkl_model_decode_trace(vkl_model *m, uint32_t token, size_t offset, unsigned long long *out, size_t cap, uint32_t *nops, uint32_t *grid, uint32_t *kinds) {
+  VKL_OKAY(check_ready(m));
+  if (!nops || !grid) return fail(VKL_INVALID_ARGUMENT, "model_decode_trace: null argument");
+  if (offset + 1 > (size_t)2 * m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_decode_trace: position out of range");
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  VKL_OKAY(prepare_decode(m));
+  if (!m->mega_ready) return fail(VKL_FAILED_PRECONDITION, "model_decode_trace: the persistent decode kernel is not in use for this model");
+  const size_t n = m->mp.nops, G = (size_t)m->mega_grid, words = n * G * 8;
+  *nops = (uint32_t)n;
+  *grid = (uint32_t)G;
+  if (!out) return VKL_OK;  // size query
+  if (cap < words) return fail(VKL_INVALID_ARGUMENT, "model_decode_trace: %zu words needed, %zu given", words, cap);
+  const uint32_t st[2] = {(uint32_t)offset, 0};
+  VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
+  VKL_CUDA(cudaMemcpyAsync(m->toks->data(), &token, 4, cudaMemcpyHostToDevice, m->stream));
+  void *buf = nullptr;
+  VKL_OKAY(m->dev->alloc(words * 8, &buf));
+  MegaParams p = m->mp;
+  p.timing = (unsigned long long *)buf;
+  p.timing_mode = 256u;
+  p.sm_mhz = 1000;
+  cudaError_t e = cudaMemsetAsync(buf, 0, words * 8, m->stream);
+  if (e == cudaSuccess) e = launch_decode_mega(p, m->mega_grid, m->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(out, buf, words * 8, cudaMemcpyDeviceToHost, m->stream);
+  if (e == cudaSuccess && kinds) {
+    std::vector<MegaOp> ops(n);
+    e = cudaMemcpyAsync(ops.data(), m->mp.ops, n * sizeof(MegaOp), cudaMemcpyDeviceToHost, m->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    for (size_t i = 0; i < n; ++i) kinds[i] = ops[i].kind | (ops[i].nmat << 8) | (ops[i].epi << 16);
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+  m->dev->release(buf, words * 8);
+  count_launches(1);
+  if (e != cudaSuccess) return fail(VKL_INTERNAL, "model_decode_trace: %s", cudaGetErrorString(e));
+  return check_mega(m);
 }
 
 int vkl_model_tp_buffer(vkl_model *m, void **local_ptr, size_t *bytes) {

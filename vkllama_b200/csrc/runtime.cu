@@ -5,6 +5,8 @@
 
 #include <math.h>
 #include <stdio.h>
+
+#include <algorithm>
 #include <string.h>
 
 namespace vkl {
@@ -75,24 +77,49 @@ int ensure_tensor(vkl_device *dev, vkl_tensor **slot, size_t c, size_t h, size_t
 using namespace vkl;
 
 // ------------------------------------------------------------------ device
+// Size classes: multiples of 256 bytes up to 64 KiB, then four classes per power of two (at most
+// 25 % over the request), so that calls with varying row counts land in a bounded set of sizes.
+size_t vkl_device::size_class(size_t bytes) {
+  if (bytes <= 65536) return (bytes + 255) & ~(size_t)255;
+  size_t p2 = 65536;
+  while (p2 * 2 < bytes) p2 *= 2;  // p2 < bytes <= 2 * p2
+  const size_t step = p2 / 4;
+  return (bytes + step - 1) / step * step;
+}
+static bool fences_done(vkl_device::FreeBlock &b, std::vector<cudaEvent_t> &spare) {
+  while (!b.fences.empty()) {
+    const cudaError_t q = cudaEventQuery(b.fences.back());
+    if (q == cudaErrorNotReady) return false;
+    (void)cudaGetLastError();  // a failed query (sticky error elsewhere) is not this block's problem: treat as done
+    spare.push_back(b.fences.back());
+    b.fences.pop_back();
+  }
+  return true;
+}
 int vkl_device::alloc(size_t bytes, void **out) {
-  bytes = (bytes + 255) & ~(size_t)255;
+  bytes = size_class(bytes);
   {
     std::lock_guard<std::mutex> lk(mu);
-    auto it = pool.find(bytes);
-    if (it != pool.end()) {
-      *out = it->second;
+    auto range = pool.equal_range(bytes);
+    for (auto it = range.first; it != range.second; ++it) {
+      if (!fences_done(it->second, spare_events)) continue;  // queued work may still touch it
+      *out = it->second.ptr;
       pool.erase(it);
+      pooled_bytes -= bytes;
       return VKL_OK;
     }
   }
   cudaError_t e = cudaMalloc(out, bytes);
   if (e != cudaSuccess) {
-    // Give pooled blocks back to the driver once and retry.
+    // Give pooled blocks back to the driver once and retry (cudaFree waits for queued work).
     {
       std::lock_guard<std::mutex> lk(mu);
-      for (auto &kv : pool) cudaFree(kv.second);
+      for (auto &kv : pool) {
+        cudaFree(kv.second.ptr);
+        for (cudaEvent_t ev : kv.second.fences) spare_events.push_back(ev);
+      }
       pool.clear();
+      pooled_bytes = 0;
     }
     (void)cudaGetLastError();
     e = cudaMalloc(out, bytes);
@@ -104,12 +131,62 @@ int vkl_device::alloc(size_t bytes, void **out) {
   return VKL_OK;
 }
 void vkl_device::release(void *p, size_t bytes) {
-  bytes = (bytes + 255) & ~(size_t)255;
+  bytes = size_class(bytes);
   std::lock_guard<std::mutex> lk(mu);
-  pool.emplace(bytes, p);
+  if (pooled_bytes + bytes > pool_cap) {
+    cudaFree(p);  // synchronises with everything queued on the device
+    return;
+  }
+  FreeBlock b{p, {}};
+  int cur = -1;
+  cudaGetDevice(&cur);
+  if (cur != ordinal) cudaSetDevice(ordinal);
+  for (cudaStream_t s : streams) {
+    // a stream that is being captured runs nothing now (its work is being recorded into a graph):
+    // no fence, and no event record that would become a node of that graph
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cs) != cudaSuccess) (void)cudaGetLastError();
+    if (cs != cudaStreamCaptureStatusNone) continue;
+    cudaEvent_t ev = nullptr;
+    if (!spare_events.empty()) {
+      ev = spare_events.back();
+      spare_events.pop_back();
+    } else if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+      (void)cudaGetLastError();
+      ev = nullptr;
+    }
+    if (ev && cudaEventRecord(ev, s) == cudaSuccess) {
+      b.fences.push_back(ev);
+    } else {  // no fence could be set: wait for the stream instead
+      (void)cudaGetLastError();
+      if (ev) spare_events.push_back(ev);
+      cudaStreamSynchronize(s);
+      (void)cudaGetLastError();
+    }
+  }
+  if (cur != ordinal && cur >= 0) cudaSetDevice(cur);
+  pool.emplace(bytes, std::move(b));
+  pooled_bytes += bytes;
+}
+void vkl_device::add_stream(cudaStream_t s) {
+  std::lock_guard<std::mutex> lk(mu);
+  streams.push_back(s);
+}
+void vkl_device::remove_stream(cudaStream_t s) {
+  std::lock_guard<std::mutex> lk(mu);
+  // blocks fenced on this stream: the caller has synchronised it, the events are complete
+  streams.erase(std::remove(streams.begin(), streams.end(), s), streams.end());
+}
+size_t vkl_device::pool_bytes() {
+  std::lock_guard<std::mutex> lk(mu);
+  return pooled_bytes;
 }
 vkl_device::~vkl_device() {
-  for (auto &kv : pool) cudaFree(kv.second);
+  for (auto &kv : pool) {
+    cudaFree(kv.second.ptr);
+    for (cudaEvent_t ev : kv.second.fences) cudaEventDestroy(ev);
+  }
+  for (cudaEvent_t ev : spare_events) cudaEventDestroy(ev);
 }
 
 extern "C" {
@@ -140,7 +217,14 @@ int vkl_device_create(int ordinal, vkl_device **out) {
     delete d;
     return fail(VKL_FAILED_PRECONDITION, "device %d is sm_%d%d; this library is built for sm_100a only", ordinal, major, minor);
   }
+  // free blocks kept for reuse: at most an eighth of the device memory
+  d->pool_cap = d->prop.totalGlobalMem / 8;
   *out = d;
+  return VKL_OK;
+}
+int vkl_device_pool_bytes(vkl_device *dev, size_t *bytes) {
+  if (!dev || !bytes) return fail(VKL_INVALID_ARGUMENT, "device_pool_bytes: null argument");
+  *bytes = dev->pool_bytes();
   return VKL_OK;
 }
 int vkl_device_destroy(vkl_device *dev) {
@@ -282,6 +366,7 @@ int vkl_command_create(vkl_device *dev, vkl_command **out) {
   }
   cudaEventCreate(&c->ev0);
   cudaEventCreate(&c->ev1);
+  dev->add_stream(c->stream);
   *out = c;
   return VKL_OK;
 }
@@ -290,6 +375,7 @@ int vkl_command_destroy(vkl_command *cmd) {
   cudaStreamSynchronize(cmd->stream);
   for (auto &f : cmd->deferred) f();
   if (cmd->err_word) cmd->dev->release(cmd->err_word, 256);
+  cmd->dev->remove_stream(cmd->stream);
   cudaStreamDestroy(cmd->stream);
   if (cmd->ev0) cudaEventDestroy(cmd->ev0);
   if (cmd->ev1) cudaEventDestroy(cmd->ev1);

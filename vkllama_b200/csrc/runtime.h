@@ -42,15 +42,32 @@ void count_launches(uint64_t n);
 
 }  // namespace vkl
 
+// Device memory comes from a pool of free blocks in size classes. Ops enqueue work and return
+// without synchronising, and every command and model has its own non-blocking stream, so a block
+// that is released may still be in use by queued kernels. release() therefore records an event on
+// every stream of the device, and alloc() hands a pooled block out only when all of its events
+// have completed (otherwise it takes another block or allocates a new one). The pool is capped:
+// beyond `pool_cap` bytes a released block goes back to the driver (cudaFree synchronises).
 struct vkl_device {
+  struct FreeBlock {
+    void *ptr;
+    std::vector<cudaEvent_t> fences;  // work queued on the device's streams when the block was released
+  };
   int ordinal = 0;
   cudaDeviceProp prop;
   std::mutex mu;
-  std::multimap<size_t, void *> pool;  // free blocks by size
+  std::multimap<size_t, FreeBlock> pool;  // free blocks by size class
+  size_t pooled_bytes = 0, pool_cap = 0;
+  std::vector<cudaStream_t> streams;       // streams of the live commands and models
+  std::vector<cudaEvent_t> spare_events;
   std::atomic<int> live_buffers{0};    // tensors' buffers still referencing this device
   std::atomic<bool> closed{false};     // destroy was requested; the last buffer frees the device
+  static size_t size_class(size_t bytes);
   int alloc(size_t bytes, void **out);
   void release(void *p, size_t bytes);
+  void add_stream(cudaStream_t s);
+  void remove_stream(cudaStream_t s);
+  size_t pool_bytes();
   ~vkl_device();
 };
 
