@@ -25,6 +25,8 @@
 // copies, drains the copies in flight and leaves through the normal path.
 #include <cooperative_groups.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -95,6 +97,14 @@ __device__ __forceinline__ uint4 ld_vol_v4(const uint32_t *p) {
   return v;
 }
 
+// Read-only 128-bit load that keeps its place among the volatile polls around it (a plain
+// __ldg may be scheduled after them, behind a spin).
+__device__ __forceinline__ float4 ldg_f4_ordered(const float4 *p) {
+  float4 v;
+  asm volatile("ld.global.nc.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
 __device__ __forceinline__ uint64_t ld_acq_u64(const unsigned long long *p) {
   uint64_t v;
   asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -116,6 +126,74 @@ __device__ __forceinline__ unsigned long long gtime() {
     if (TIMED && trace) trace[k] = gtime();                            \
   } while (0)
 
+// The spin loops of the bounded waits are kept out of line: they are rarely entered (the
+// first try usually succeeds) and, inlined at every wait of every op, they made the kernel's
+// code larger than the instruction cache.
+struct Ctx;
+__device__ __noinline__ bool slow_mbar_wait(volatile uint32_t *abort_s, uint32_t *error, uint32_t bar, uint32_t parity, uint32_t code, uint32_t sleep_ns) {
+  #pragma unroll 1
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (sleep_ns) __nanosleep(sleep_ns);  // keep a waiting warp off the shared-memory pipe the working warps need
+    if (mbar_try(bar, parity)) return true;
+    if ((i & 255u) == 255u && (*(volatile uint32_t *)error != 0u || *abort_s != 0)) {
+      *abort_s = 1;
+      return false;
+    }
+  }
+  *abort_s = 1;
+  atomicCAS(error, 0u, code);
+  return false;
+}
+__device__ __noinline__ uint32_t slow_ll_wait1(volatile uint32_t *abort_s, uint32_t *error, const uint32_t *src, uint32_t tag) {
+  uint32_t w = 0;
+  #pragma unroll 1
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    w = ld_vol_u32(src);
+    if ((w >> 16) == tag) return w;
+    if ((i & 255u) == 255u && (*(volatile uint32_t *)error != 0u || *abort_s != 0)) {
+      *abort_s = 1;
+      return w;
+    }
+  }
+  *abort_s = 1;
+  atomicCAS(error, 0u, 6u);
+  return w;
+}
+__device__ __noinline__ uint2 slow_ll_wait2(volatile uint32_t *abort_s, uint32_t *error, const uint32_t *src, uint32_t tag) {
+  uint2 w = make_uint2(0, 0);
+  #pragma unroll 1
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    w = ld_vol_v2(src);
+    if (((w.x >> 16) == tag) & ((w.y >> 16) == tag)) return w;
+    if ((i & 255u) == 255u && (*(volatile uint32_t *)error != 0u || *abort_s != 0)) {
+      *abort_s = 1;
+      return w;
+    }
+  }
+  *abort_s = 1;
+  atomicCAS(error, 0u, 6u);
+  return w;
+}
+__device__ __forceinline__ bool ll_ready8(const uint4 &a, const uint4 &b, uint32_t tag) {
+  return ((a.x >> 16) == tag) & ((a.y >> 16) == tag) & ((a.z >> 16) == tag) & ((a.w >> 16) == tag) & ((b.x >> 16) == tag) &
+         ((b.y >> 16) == tag) & ((b.z >> 16) == tag) & ((b.w >> 16) == tag);
+}
+// polls eight consecutive tagged words until all carry `tag`; the words come back through a, b
+__device__ __noinline__ void slow_ll_wait8(volatile uint32_t *abort_s, uint32_t *error, const uint32_t *src, uint32_t tag, uint4 &a, uint4 &b) {
+  #pragma unroll 1
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    a = ld_vol_v4(src);
+    b = ld_vol_v4(src + 4);
+    if (ll_ready8(a, b, tag)) return;
+    if ((i & 255u) == 255u && (*(volatile uint32_t *)error != 0u || *abort_s != 0)) {
+      *abort_s = 1;  // give up quietly: another wait has already raised the error
+      return;
+    }
+  }
+  *abort_s = 1;
+  atomicCAS(error, 0u, 6u);
+}
+
 struct Ctx {
   const MegaParams &p;
   volatile uint32_t *abort_s;  // shared flag: some wait of this CTA timed out or *error was seen
@@ -128,70 +206,23 @@ struct Ctx {
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, uint32_t code, uint32_t sleep_ns = 0) const {
     if (mbar_try(bar, parity)) return true;  // fast path: the phase is already complete
     if (aborted()) return false;
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-      if (sleep_ns) __nanosleep(sleep_ns);  // keep a waiting warp off the shared-memory pipe the working warps need
-      if (mbar_try(bar, parity)) return true;
-      if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || aborted())) {
-        *abort_s = 1;
-        return false;
-      }
-    }
-    raise(code);
-    return false;
+    return slow_mbar_wait(abort_s, p.error, bar, parity, code, sleep_ns);
   }
   // One tagged word, polled (bounded) until its tag is `tag`. Returns the word; on a time-out
   // or an abort returns what it last read (the caller's results are discarded on abort).
   __device__ __forceinline__ uint32_t ll_wait1(const uint32_t *src, uint32_t tag) const {
-    uint32_t w = ld_vol_u32(src);
+    const uint32_t w = ld_vol_u32(src);
     if ((w >> 16) == tag) return w;
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-      w = ld_vol_u32(src);
-      if ((w >> 16) == tag) return w;
-      if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || aborted())) {
-        *abort_s = 1;
-        return w;
-      }
-    }
-    raise(6);
-    return w;
+    return slow_ll_wait1(abort_s, p.error, src, tag);
   }
   // Two consecutive tagged words (8-byte aligned), already requested once.
   __device__ __forceinline__ uint2 ll_wait2(const uint32_t *src, uint2 w, uint32_t tag) const {
     if (((w.x >> 16) == tag) & ((w.y >> 16) == tag)) return w;
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-      w = ld_vol_v2(src);
-      if (((w.x >> 16) == tag) & ((w.y >> 16) == tag)) return w;
-      if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || aborted())) {
-        *abort_s = 1;
-        return w;
-      }
-    }
-    raise(6);
-    return w;
+    return slow_ll_wait2(abort_s, p.error, src, tag);
   }
   // Eight consecutive tagged words (32-byte aligned) -> eight packed halves, polled the same way.
-  __device__ __forceinline__ bool ll_ready8(const uint4 &a, const uint4 &b, uint32_t tag) const {
-    return ((a.x >> 16) == tag) & ((a.y >> 16) == tag) & ((a.z >> 16) == tag) & ((a.w >> 16) == tag) & ((b.x >> 16) == tag) &
-           ((b.y >> 16) == tag) & ((b.z >> 16) == tag) & ((b.w >> 16) == tag);
-  }
   __device__ __forceinline__ uint4 ll_wait8(const uint32_t *src, uint4 a, uint4 b, uint32_t tag) const {
-    if (!ll_ready8(a, b, tag)) {
-      bool ok = false;
-      for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        a = ld_vol_v4(src);
-        b = ld_vol_v4(src + 4);
-        if (ll_ready8(a, b, tag)) {
-          ok = true;
-          break;
-        }
-        if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || aborted())) {
-          *abort_s = 1;
-          ok = true;  // give up quietly: another wait has already raised the error
-          break;
-        }
-      }
-      if (!ok) raise(6);
-    }
+    if (!ll_ready8(a, b, tag)) slow_ll_wait8(abort_s, p.error, src, tag, a, b);
     return make_uint4((a.x & 0xffffu) | (a.y << 16), (a.z & 0xffffu) | (a.w << 16), (b.x & 0xffffu) | (b.y << 16), (b.z & 0xffffu) | (b.w << 16));
   }
 };
@@ -215,7 +246,7 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
   // this CTA's (head, split) and row range of the attention ops: the same for every layer of the token
   const uint32_t pos0 = p.state[0];
   const uint32_t Lnow = min(pos0 + 1, p.maxlen);
-  const uint32_t S_eff = Lnow <= p.single_split_len ? 1u : p.splits;
+  const uint32_t S_eff = mega_splits(Lnow, p.splits, p.split_rows);
   uint32_t kv_c0 = 0, kv_c1 = 0;
   if (blockIdx.x < p.heads * S_eff) mega_kv_range(Lnow, S_eff, blockIdx.x % S_eff, kv_c0, kv_c1);
   const uint32_t kv_head = blockIdx.x / S_eff, kv_rps = mega_kv_rows_per_stage(p.head_dim);
@@ -289,6 +320,7 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
     const uint32_t lo = issued > NST ? issued - NST : 0;
     for (uint32_t j = lo; j < issued; ++j) {
       const uint32_t fb = s32(&full[j % NST]), ph2 = (j / NST) & 1u;
+      #pragma unroll 1
       for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(fb, ph2); ++i) {
       }
     }
@@ -296,7 +328,7 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
 }
 
 // ------------------------------------------------------------ grid barrier
-__device__ __forceinline__ bool grid_barrier(const Ctx &c, uint64_t target, uint32_t round, volatile uint32_t *seen_s) {
+__device__ __noinline__ bool grid_barrier(const Ctx &c, uint64_t target, uint32_t round, volatile uint32_t *seen_s) {
   cons_sync();  // every consumer store of this op is issued
   // Lane 0 of the first POLLERS warps poll the counter, each a fraction of a memory round trip
   // after the previous one, so that the last arrival is seen a fraction of a round trip after it
@@ -314,6 +346,7 @@ __device__ __forceinline__ bool grid_barrier(const Ctx &c, uint64_t target, uint
     }
     const uint32_t tgt = round;
     bool ok = false;
+    #pragma unroll 1
     for (uint32_t i = 0; i < WAIT_LIMIT * 8u; ++i) {
       if (*seen_s == tgt || ld_acq_u64(c.p.bar) >= target) {
         ok = true;
@@ -392,6 +425,16 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     const bool norm = op.norm_w != nullptr;
     constexpr int NWV = 2;  // vectors per thread whose norm weights are requested early (K <= 7680: every norm op of the model shapes)
     float4 nw[NWV][2];
+    if (norm) {  // the norm weights depend on nothing: request them before the polls, which can spin for a while
+#pragma unroll
+      for (int j = 0; j < NWV; ++j) {
+        const uint32_t i = tid + j * CT;
+        if (i < nv) {
+          nw[j][0] = ldg_f4_ordered(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i);
+          nw[j][1] = ldg_f4_ordered(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i + 1);
+        }
+      }
+    }
     {
       // the first loads together (one memory round trip when the producers are done), then the tag checks
       constexpr int LFIRST = 3;  // K <= 11520 in one round trip
@@ -413,16 +456,6 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
             v[j] = c.ll_wait8(op.in + 8 * i, la[j], lb[j], tag_in);
           else
             v[j] = c.ll_wait8(op.in + 8 * i, ld_vol_v4(op.in + 8 * i), ld_vol_v4(op.in + 8 * i + 4), tag_in);
-        }
-      }
-    }
-    if (norm) {  // the norm weights do not depend on the reduction below: request them in the same round trip
-#pragma unroll
-      for (int j = 0; j < NWV; ++j) {
-        const uint32_t i = tid + j * CT;
-        if (i < nv) {
-          nw[j][0] = __ldg(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i);
-          nw[j][1] = __ldg(reinterpret_cast<const float4 *>(op.norm_w) + 2 * i + 1);
         }
       }
     }
@@ -819,6 +852,7 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
       for (uint32_t sp = 0; sp < S; ++sp) {
         const uint32_t *b = base + 2 * (size_t)sp * (D + 4);
         uint2 wm = ld_vol_v2(b + 2 * D), wl = ld_vol_v2(b + 2 * (D + 1)), wa = ld_vol_v2(b + 2 * d);
+        #pragma unroll 1
         for (uint32_t i = 0; (wm.y != tag_out || wl.y != tag_out || wa.y != tag_out) && i < WAIT_LIMIT; ++i) {
           wm = ld_vol_v2(b + 2 * D);
           wl = ld_vol_v2(b + 2 * (D + 1));
@@ -893,7 +927,7 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
 }
 
 // One head per CTA: merge the split partials in split order.
-__device__ __forceinline__ void attn_combine_op(const Ctx &c, uint32_t tag_out) {
+__device__ __noinline__ void attn_combine_op(const Ctx &c, uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t h = blockIdx.x, tid = threadIdx.x, D = p.head_dim;
   if (h >= p.heads || tid >= D) return;
@@ -913,7 +947,7 @@ __device__ __forceinline__ void attn_combine_op(const Ctx &c, uint32_t tag_out) 
 }
 
 // Embedding gather + dequantisation of the current token (embedding_q8_0.comp:39-85).
-__device__ __forceinline__ void embed_op(const Ctx &c, uint32_t tok, uint32_t tag_out) {
+__device__ __noinline__ void embed_op(const Ctx &c, uint32_t tok, uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t per = (p.dim + gridDim.x - 1) / gridDim.x;
   const uint32_t k = blockIdx.x * per + threadIdx.x;
@@ -930,7 +964,7 @@ __device__ __forceinline__ void embed_op(const Ctx &c, uint32_t tok, uint32_t ta
 
 // CTA 0: best of the per-CTA candidates (lowest index on ties), then publish the id,
 // feed it back and advance position, step and launch epoch.
-__device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_t pos0, uint64_t rounds_done, uint32_t ar_done,
+__device__ __noinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_t pos0, uint64_t rounds_done, uint32_t ar_done,
                                                 uint32_t next_ebase) {
   const MegaParams &p = c.p;
   if (blockIdx.x != 0) return;
@@ -979,6 +1013,7 @@ __device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_
       const uint32_t *mine = static_cast<const uint32_t *>(p.tp_peer[p.tp_rank]) + p.tp_flag_off;
       for (uint32_t r = 0; r < tp && !c.aborted(); ++r) {
         bool ok = false;
+        #pragma unroll 1
         for (uint32_t i = 0; i < WAIT_LIMIT * 8u; ++i) {
           if ((int32_t)(ld_acq_sys_u32(mine + 16 + r) - aseq) >= 0) {
             ok = true;
@@ -1025,7 +1060,7 @@ __device__ __forceinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_
 // this all-reduce's number: x <- fp16( fp16(sum_r partial_r) + x ), the same rounding as
 // o_proj/down + residual add. No grid barrier and no separate flags: two parities of slots
 // keep a fast rank's next push from overwriting what a slow rank still reads.
-__device__ __forceinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t seq, uint32_t tag_out) {
+__device__ __noinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t seq, uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t tid = threadIdx.x, tp = p.tp_size;
   if (c.aborted()) return;
@@ -1041,6 +1076,7 @@ __device__ __forceinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uin
       uint2 w = ld_vol_v2(src);
       if (w.y != seq) {
         bool ok = false;
+        #pragma unroll 1
         for (uint32_t it = 0; it < WAIT_LIMIT * 8u; ++it) {
           w = ld_vol_v2(src);
           if (w.y == seq) {
@@ -1063,7 +1099,7 @@ __device__ __forceinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uin
 }
 
 template <bool TIMED, bool DBG>
-__global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParams p) {
+__global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_constant__ MegaParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const uint32_t NST = p.nst;
   unsigned char *ring = smem;
@@ -1111,7 +1147,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
   const uint32_t seq0 = p.state[3];  // all-reduces completed by earlier launches
   uint32_t ar_i = 0;
   const uint32_t Lnow = min(pos0 + 1, p.maxlen);
-  const uint32_t S_eff = Lnow <= p.single_split_len ? 1u : p.splits;
+  const uint32_t S_eff = mega_splits(Lnow, p.splits, p.split_rows);
   uint32_t it = 0, slot = 0, ph = 0;  // ring position, carried across the ops of the token
   const uint32_t ebase = p.state[7];  // sequence number of this launch's first op; op oi tags its results with ebase + oi
   auto tag = [&](uint32_t op_index) { return (ebase + op_index) & 0xffffu; };
@@ -1220,9 +1256,11 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const MegaParam
 
 }  // namespace
 
-size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits) {
+size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits, uint32_t split_rows) {
   size_t x = (size_t)max_groups * (128 * 2 + 4 * 4);  // fp16 input + one fp32 bias term per block
+  // most rows a split can get: all splits at the full context, or one of fewer splits of split_rows rows
   uint32_t chunk = ((maxlen + splits - 1) / splits + 31) & ~31u;
+  if (split_rows) chunk = std::max(chunk, (std::min(maxlen, split_rows) + 31) & ~31u);
   size_t a = (size_t)((3 + NCW / 2) * head_dim + 2 * NCW + 32 + chunk + 32) * 4;
   size_t b = x > a ? x : a;
   return (b + 127) / 128 * 128;

@@ -155,6 +155,14 @@ constexpr uint32_t MEGA_SG = 15;  // groups per stage = consumer warps: one grou
 constexpr uint32_t MEGA_STAGE_BYTES = MEGA_SG * (2048 + 128);
 // Cache rows (head_dim fp16 values each) of one KV ring stage: whole rows, a multiple of 8.
 __host__ __device__ inline uint32_t mega_kv_rows_per_stage(uint32_t head_dim) { return (MEGA_STAGE_BYTES / (head_dim * 2u)) & ~7u; }
+// Splits per head at KV length L: as few as keep a split within `split_rows` cache rows. With one
+// split a head needs no merge step between CTAs; more splits only pay when the rows of a head no
+// longer stream through one SM fast enough.
+__host__ __device__ inline uint32_t mega_splits(uint32_t L, uint32_t splits, uint32_t split_rows) {
+  if (!split_rows) return splits;
+  const uint32_t want = (L + split_rows - 1) / split_rows;
+  return want < 1 ? 1u : (want < splits ? want : splits);
+}
 // The cached rows [c0, c1) that split `split` of `S` reads at KV length L.
 __host__ __device__ inline void mega_kv_range(uint32_t L, uint32_t S, uint32_t split, uint32_t &c0, uint32_t &c1) {
   uint32_t chunk = (L + S - 1) / S;
@@ -220,14 +228,14 @@ struct MegaParams {
   void *tp_peer[8];
   uint32_t nst;               // ring stages (as many as fit beside the input and reduction areas)
   uint32_t red_slots;         // reduction slots: the largest (tiles of one CTA) x (matrices) of any op
-  uint32_t single_split_len;  // KV lengths up to this use one CTA per head (no combine phase)
+  uint32_t split_rows;        // cache rows one attention split should hold: a token at KV length L uses min(splits, ceil(L / split_rows)) splits per head (0: always `splits`)
   uint32_t barrier_pollers;   // warps whose lane 0 polls the grid barrier counter, staggered in time
   // Optional timeline of CTA 0: per op, nanoseconds of work and of barrier wait.
   unsigned long long *timing;
   uint32_t timing_mode;  // third column of the timeline: 0 = ring wait, 1 = op prologue
   uint32_t sm_mhz;       // SM clock for the timeline's cycle counts (measured by the host before a profiled launch)
 };
-size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits);
+size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits, uint32_t split_rows);
 size_t decode_mega_smem(size_t xs_bytes, uint32_t nst, uint32_t red_slots);
 int decode_mega_max_k();
 int decode_mega_max_stages();

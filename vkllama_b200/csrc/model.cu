@@ -345,7 +345,11 @@ int build_mega(vkl_model *m) {
     if (splits > cap) splits = cap;
   }
   const uint32_t max_groups = (std::max(c.dim, m->ffn_l) / 32 + 3) / 4;
-  const size_t xs_bytes = decode_mega_xs_bytes(max_groups, m->head_dim, c.maxlen, splits);
+  // Rows per attention split (VKLLAMA_SPLIT_ROWS; 0 = always all splits). Short contexts run one CTA
+  // per head and skip the merge between CTAs; the default keeps a split's K rows within three ring stages.
+  const char *sr_env = getenv("VKLLAMA_SPLIT_ROWS");
+  const uint32_t split_rows = sr_env ? (uint32_t)atoi(sr_env) : 384u;
+  const size_t xs_bytes = decode_mega_xs_bytes(max_groups, m->head_dim, c.maxlen, splits, split_rows);
   // every op's (tiles per CTA) x (matrices) needs a reduction slot
   auto slots = [&](uint32_t rows, uint32_t nmat) { return (((rows + 15) / 16 + G - 1) / G) * nmat; };
   const uint32_t red_slots = std::max({slots(m->dim_l, 3), slots(c.dim, 1), slots(m->ffn_l, 2), slots(m->vocab_l, 1)});
@@ -566,9 +570,7 @@ int build_mega(vkl_model *m) {
                     (getenv("VKLLAMA_DEBUG_NOBODY") ? 64 : 0) | (getenv("VKLLAMA_DEBUG_NOHANDSHAKE") ? 128 : 0);  // diagnostics
     const char *bp = getenv("VKLLAMA_BARRIER_POLLERS");
     p.barrier_pollers = bp ? std::min(std::max((uint32_t)atoi(bp), 1u), 8u) : 1u;
-    const uint32_t chunk_cap = ((c.maxlen + splits - 1) / splits + 31) & ~31u;
-    const char *ss = getenv("VKLLAMA_SINGLE_SPLIT_LEN");
-    p.single_split_len = std::min(ss ? (uint32_t)atoi(ss) : 0u, chunk_cap);
+    p.split_rows = split_rows;
   }
   m->mega_grid = G;
   m->mega_ready = true;
