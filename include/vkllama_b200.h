@@ -167,6 +167,24 @@ int vkl_embedding_run(vkl_op *op, vkl_tensor *indices, vkl_tensor **out);
  * 2 mul, 3 div; written into and returning the second operand. */
 int vkl_elementwise_create(vkl_device *dev, vkl_command *cmd, int type, int dtype, vkl_op **out);
 int vkl_elementwise_run(vkl_op *op, vkl_tensor *x, vkl_tensor *y, vkl_tensor **out);
+/* ElementWise::operator()(Tensor x, float y), src/ops/elementwise.cpp:104-133: x <- x (type) y
+ * in place (fp32 arithmetic, one rounding to fp16), returning x. */
+int vkl_elementwise_run_scalar(vkl_op *op, vkl_tensor *x, float y, vkl_tensor **out);
+
+/* Concat, src/ops/concat.h:10-17: `num` fp16 inputs joined along axis 0 (channels), 1 (rows)
+ * or 2 (columns); the other two extents must agree (concat.cpp:82-113). */
+int vkl_concat_create(vkl_device *dev, vkl_command *cmd, int num, int axis, int dtype, vkl_op **out);
+int vkl_concat_run(vkl_op *op, vkl_tensor *const *inputs, size_t n, vkl_tensor **out);
+
+/* Reduce, src/ops/reduce.h:18-67: over the rows of an fp16 [c,h,w] tensor -> [c,h,1];
+ * op_type 0 sum, 1 max, 2 min, 3 mean; fp32 accumulation, one rounding to fp16. */
+int vkl_reduce_create(vkl_device *dev, vkl_command *cmd, int op_type, int dtype, vkl_op **out);
+int vkl_reduce_run(vkl_op *op, vkl_tensor *a, vkl_tensor **out);
+
+/* ReadKVCache, src/ops/read_kvcache_op.h:10-16: the `len` rows of a ring cache
+ * [heads, maxlen, dim] starting at `offset` (row (offset + y) % maxlen) -> [heads, len, dim]. */
+int vkl_read_kvcache_create(vkl_device *dev, vkl_command *cmd, vkl_op **out);
+int vkl_read_kvcache_run(vkl_op *op, vkl_tensor *cache, uint32_t offset, uint32_t len, vkl_tensor **out);
 
 /* Transpose (type 0: [C,H,W] -> [H,C,W]), src/ops/transpose.h:14-19. */
 int vkl_transpose_create(vkl_device *dev, vkl_command *cmd, int type, int dtype, vkl_op **out);
@@ -293,6 +311,20 @@ int vkl_model_decode_trace(vkl_model *m, uint32_t token, size_t offset, unsigned
  * after down_proj per layer), and exchanges arg-max candidates of the vocabulary-split
  * output layer. vkl_model_forward returns this rank's slice of the logits. */
 int vkl_model_tp_buffer(vkl_model *m, void **local_ptr, size_t *bytes);
+/* Failure detection (the reference's counterpart is the 60 s fence time-out of
+ * src/core/command.h:389-395). Every wait inside the persistent decode kernel (weight
+ * stage, ring slot, tagged input, grid barrier, tensor-parallel all-reduce and arg-max
+ * exchange) gives up after `polls` polls of about half a microsecond each: the kernel
+ * then leaves through its normal path and the call returns VKL_INTERNAL naming the wait
+ * (code 1 weight stage, 2 ring slot, 3 grid barrier, 4 all-reduce, 5 arg-max exchange,
+ * 6 tagged input). The device context stays usable. Default (polls = 0): 2^21, and 2^24
+ * for tensor-parallel models, the same bound for every wait so that none gives up while
+ * another it depends on is still waiting; ranks may start a step up to that much apart.
+ * After such an error a tensor-parallel model refuses further steps
+ * (VKL_FAILED_PRECONDITION) until every rank has called vkl_model_tp_connect again
+ * between two host barriers, which clears the exchange buffers and restarts the
+ * sequence counters on all ranks together. */
+int vkl_model_set_wait_limit(vkl_model *m, uint32_t polls);
 int vkl_model_tp_connect(vkl_model *m, void *const *peer_ptrs, int n);
 int vkl_ipc_export(void *device_ptr, unsigned char handle[64]);
 int vkl_ipc_open(vkl_device *dev, const unsigned char handle[64], void **device_ptr);

@@ -256,3 +256,71 @@ class Model:
             self.close()
         except Exception:
             pass
+
+
+# ---- generic ops outside the token loop (numpy restatements of the shaders; fp16 bit patterns in and out) ----
+def elementwise(x_bits, y, op):
+    """src/shaders/element_wise_fp16.comp:19-48 (two tensors) and element_wise_constant_fp16.comp:19-44
+    (tensor and scalar): fp32 arithmetic, one rounding to fp16. op 0 add, 1 sub, 2 mul, 3 div."""
+    a = f16(x_bits)
+    b = f16(y) if isinstance(y, np.ndarray) else np.float32(y)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        r = [a + b, a - b, a * b, a / b][op]
+    return bits(r.astype(np.float32)).reshape(np.asarray(x_bits).shape)
+
+
+def concat(inputs, axis):
+    """src/ops/concat.cpp:115-170 + src/shaders/concat_fp16.comp:27-49: plain copies at growing offsets."""
+    return np.concatenate([np.asarray(t, np.uint16) for t in inputs], axis=axis)
+
+
+def reduce(x_bits, op):
+    """src/shaders/reduce_fp16.comp:24-76 with src/ops/reduce.h:96-99: per row, 32 lane-strided fp32 partial
+    results (max and min start from the row's first value), combined in lane order, times 1/W for the mean
+    (op 3), one rounding to fp16. [c,h,w] -> [c,h,1]."""
+    x = f16(x_bits)
+    C, H, W = x.shape
+    k = 0 if op == 3 else op
+    out = np.empty((C, H, 1), np.float32)
+    for c in range(C):
+        rows = x[c]
+        lanes = []
+        for l in range(32):
+            part = rows[:, l::32]
+            if k == 0:
+                acc = np.zeros(H, np.float32)
+                for j in range(part.shape[1]):
+                    acc = (acc + part[:, j]).astype(np.float32)
+            else:
+                acc = rows[:, 0].copy()
+                for j in range(part.shape[1]):
+                    acc = np.maximum(acc, part[:, j]) if k == 1 else np.minimum(acc, part[:, j])
+            lanes.append(acc)
+        tot = lanes[0]
+        for l in range(1, 32):
+            tot = (tot + lanes[l]).astype(np.float32) if k == 0 else (np.maximum(tot, lanes[l]) if k == 1 else np.minimum(tot, lanes[l]))
+        out[c, :, 0] = tot * (np.float32(1.0) / np.float32(W) if op == 3 else np.float32(1.0))
+    return bits(out)
+
+
+def read_kvcache(cache_bits, offset, length):
+    """src/shaders/read_kvcache_fp16.comp: out[c, y, :] = cache[c, (y + offset) % H, :]."""
+    c = np.asarray(cache_bits, np.uint16)
+    idx = (np.arange(length) + offset) % c.shape[1]
+    return np.ascontiguousarray(c[:, idx, :])
+
+
+def matmul_broadcast(a_bits, b_bits, broadcast_type, transpose_b, scale=1.0, bias=0.0, act=0):
+    """src/shaders/matmul_broadcast{0,1,2}_fp16_v2.comp: per channel C = act(A . B(^T) * scale + bias) with fp32
+    accumulation; type 1 shares one B among the channels of A, type 2 one A among the channels of B."""
+    a, b = f16(a_bits), f16(b_bits)
+    C = max(a.shape[0], b.shape[0])
+    outs = []
+    for c in range(C):
+        ac = a[0 if broadcast_type == 2 else c]
+        bc = b[0 if broadcast_type == 1 else c]
+        v = (ac.astype(np.float64) @ (bc.T if transpose_b else bc).astype(np.float64)).astype(np.float32) * np.float32(scale) + np.float32(bias)
+        if act == 1:
+            v = v / (1.0 + np.exp(-v))
+        outs.append(v)
+    return bits(np.stack(outs).astype(np.float32))

@@ -14,13 +14,13 @@ Two records are stored:
           to reproduce; the GPU test walks this record teacher-forced and
           checks every step whose gap is at least 4 ulps.
   sel_*   a prompt whose every step the oracle decides by at least 4 ulps
-          (MIN_GAP): the GPU test requires the free-running greedy ids of both
+          (MIN_ULPS): the GPU test requires the free-running greedy ids of both
           decode plans to equal the oracle's on all n_gen steps. Such prompts are
           about one in a hundred; --sel-id names a candidate that
           tests/golden/screen_prompts_gpu.py found on the device (a minute of GPU time
           instead of hours of oracle time). The candidate is only a hint: everything
           stored here is computed by the oracle, and a candidate whose oracle gap
-          falls below MIN_GAP is rejected. Without --sel-id the ids 1001, 1002, ...
+          falls below MIN_ULPS is rejected. Without --sel-id the ids 1001, 1002, ...
           are tried in turn.
 About a minute per candidate prompt on 8 cores and 8 GB of host memory.
 """
@@ -35,25 +35,32 @@ sys.path.insert(0, ROOT)
 from oracle import oracle as O  # noqa: E402
 
 SEED = 20240602  # base 20240601 + config index 1 (full 7B decode)
-MIN_GAP = 4.0 / 128.0  # 4 fp16 ulps at |logit| in [4, 8)
+MIN_ULPS = 4.0  # every step of the selected prompt is decided by at least this many fp16 ulps of its top logit
 
 
-def greedy(m, prompt, n_gen, min_gap=None):
-    """Greedy loop of app/llama2_infer.cpp:141-210; stops early below min_gap."""
-    ids, gaps = [], []
+def ulp_of(v):
+    """One fp16 ulp at |v| (the logits are fp16 values widened to fp32)."""
+    return 2.0 ** (np.floor(np.log2(max(abs(float(v)), 2.0 ** -14))) - 10)
+
+
+def greedy(m, prompt, n_gen, min_ulps=None):
+    """Greedy loop of app/llama2_infer.cpp:141-210; stops early when a step's top-2 gap is below
+    min_ulps fp16 ulps of the top logit. Returns ids, gaps (absolute), gaps in ulps, prefill logits."""
+    ids, gaps, ulps = [], [], []
     logits = m.forward(prompt, 0)
     first = logits.copy()
     for i in range(n_gen):
         if i:
             logits = m.forward(np.array([ids[-1]], np.uint32), len(prompt) + i - 1)
-        order = np.argsort(-logits, kind="stable")[:2]
-        top = int(np.flatnonzero(logits == logits[order[0]])[0])  # lowest index on ties
+        top = int(np.flatnonzero(logits == logits.max())[0])  # lowest index on ties
         second = np.max(np.delete(logits, top))
         ids.append(top)
         gaps.append(float(logits[top] - second))
-        if min_gap is not None and gaps[-1] < min_gap:
-            return None, None, None
-    return np.array(ids, np.uint32), np.array(gaps, np.float32), first
+        ulps.append(gaps[-1] / ulp_of(logits[top]))
+        if min_ulps is not None and ulps[-1] < min_ulps:
+            print("  step %d: gap %.4f = %.1f ulps at top logit %.3f" % (i, gaps[-1], ulps[-1], float(logits[top])), flush=True)
+            return None, None, None, None
+    return np.array(ids, np.uint32), np.array(gaps, np.float32), np.array(ulps, np.float32), first
 
 
 def main():
@@ -68,23 +75,23 @@ def main():
     m = O.Model(dim=4096, heads=32, ffn=11008, vocab=32000, layers=32, maxlen=4096, seed=SEED)
     print("weights: %.1f s" % (time.time() - t0), flush=True)
     base_prompt = O.synth_tokens(SEED, 1000, 32, 32000)
-    b_ids, b_gap, b_logits = greedy(m, base_prompt, n_gen)
+    b_ids, b_gap, b_ulps, b_logits = greedy(m, base_prompt, n_gen)
     print("base prompt done: min gap %.4f (%.1f s)" % (b_gap.min(), time.time() - t0), flush=True)
     pid = (sel_id - 1) if sel_id is not None else 1000
     while True:
         pid += 1
         prompt = O.synth_tokens(SEED, pid, 32, 32000)
-        ids, gap, logits = greedy(m, prompt, n_gen, MIN_GAP)
+        ids, gap, ulps, logits = greedy(m, prompt, n_gen, MIN_ULPS)
         print("prompt id %d: %s (%.1f s)" % (pid, "ok" if ids is not None else "gap below 4 ulps", time.time() - t0), flush=True)
         if ids is not None:
             break
         if sel_id is not None:
             sys.exit("candidate %d does not hold up under the oracle" % sel_id)
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "llama2_7b_q8_0_greedy.npz")
-    np.savez_compressed(path, seed=np.int64(SEED), base_prompt=base_prompt, base_ids=b_ids, base_gap=b_gap,
+    np.savez_compressed(path, seed=np.int64(SEED), base_prompt=base_prompt, base_ids=b_ids, base_gap=b_gap, base_gap_ulps=b_ulps,
                         base_prefill_logits=b_logits, sel_prompt_id=np.int64(pid), sel_prompt=prompt, sel_ids=ids,
-                        sel_gap=gap, sel_prefill_logits=logits)
-    print("wrote", path, "selected prompt id", pid, "min gap %.4f" % gap.min())
+                        sel_gap=gap, sel_gap_ulps=ulps, sel_prefill_logits=logits)
+    print("wrote", path, "selected prompt id", pid, "min gap %.4f = %.1f ulps" % (gap.min(), ulps.min()))
 
 
 if __name__ == "__main__":

@@ -578,3 +578,147 @@ def test_pool_is_bounded_under_varying_sizes(dev):
     # 67 different sizes between 8 KB and 1.6 MB, three times over: at most one block per size class
     # (a class is at most 25 % over the request) unless a block was still fenced when its size came up again
     assert kept - before <= 2 * 67 * 1.25 * 200 * 4096 * 2
+
+
+# ---- generic ops outside the token loop, at the reference's own test shapes ---------------------
+@pytest.mark.parametrize("op_type", [0, 1, 2, 3])
+@pytest.mark.parametrize("scalar", [False, True])
+def test_elementwise_all_types_tensor_and_scalar(dev, op_type, scalar):
+    """tests/test_elementwise.cpp:178-182: [3,1023,511], add / sub / mul / div, tensor and constant operand."""
+    C, H, W = 3, 1023, 511
+    x = O.synth_f16(122, 1, C * H * W).reshape(C, H, W)
+    y = O.synth_f16(122, 2, C * H * W, mean=2.0, std=0.25).reshape(C, H, W)  # away from zero: a divisor too
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tx, ty = up(cmd, dev, x, vk.FP16, C, H, W), up(cmd, dev, y, vk.FP16, C, H, W)
+    op = vk.ElementWise(dev, cmd, op_type, vk.FP16).init()
+    if scalar:
+        got = cmd.download(op(tx, 1.75))
+        same = cmd.download(tx)  # in place in x
+    else:
+        got = cmd.download(op(tx, ty))
+        same = cmd.download(ty)  # in place in the second operand
+    cmd.end()
+    cmd.submit_and_wait()
+    want = O.elementwise(x, 1.75 if scalar else y, op_type)
+    assert np.array_equal(got, want) and np.array_equal(same, want)
+
+
+@pytest.mark.parametrize("axis,shapes", [(0, [(1, 63, 31), (2, 63, 31), (5, 63, 31)]), (1, [(3, 63, 31), (3, 31, 31), (3, 22, 31)]),
+                                         (2, [(3, 63, 31), (3, 63, 63), (3, 63, 22)])])
+def test_concat(dev, axis, shapes):
+    """tests/test_concat.cpp:117-121."""
+    ins = [O.synth_f16(123, 10 + i, c * h * w).reshape(c, h, w) for i, (c, h, w) in enumerate(shapes)]
+    cmd = vk.Command(dev)
+    cmd.begin()
+    ts = [up(cmd, dev, a, vk.FP16, *a.shape) for a in ins]
+    op = vk.Concat(dev, cmd, len(ins), axis, vk.FP16).init()
+    got = cmd.download(op(ts))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert np.array_equal(got, O.concat(ins, axis))
+    cmd.begin()
+    with pytest.raises(vk.VklError) as e:  # wrong input count
+        op(ts[:2])
+    assert e.value.code == 3
+    bad = vk.Concat(dev, cmd, 2, (axis + 1) % 3, vk.FP16).init()
+    with pytest.raises(vk.VklError) as e:  # extents that agree along this test's axis only
+        bad([ts[1], ts[2]])
+    assert e.value.code == 3
+    cmd.end()
+    cmd.submit_and_wait()
+
+
+@pytest.mark.parametrize("op_type", [0, 1, 2, 3])
+def test_reduce(dev, op_type):
+    """tests/test_reduce.cpp:113-118: [1,1023,511], sum / max / min / mean."""
+    C, H, W = 1, 1023, 511
+    x = O.synth_f16(124, op_type, C * H * W).reshape(C, H, W)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    op = vk.Reduce(dev, cmd, op_type, vk.FP16).init()
+    got = cmd.download(op(up(cmd, dev, x, vk.FP16, C, H, W)))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert got.shape == (C, H, 1)
+    assert np.array_equal(got, O.reduce(x, op_type))
+
+
+@pytest.mark.parametrize("offset,length", [(0, 25), (1010, 25), (1022, 2), (5, 1024)])
+def test_read_kvcache_reads_back_what_update_wrote(dev, offset, length):
+    """tests/test_update_kv_cache.cpp:61-114: heads 32, maxlen 1024, dim 100; write at an offset (wrapping at the
+    end of the ring), read the same rows back."""
+    heads, maxlen, dim = 32, 1024, 100
+    base = O.synth_f16(125, 1, heads * maxlen * dim).reshape(heads, maxlen, dim)
+    kv = O.synth_f16(125, 2, heads * 25 * dim).reshape(heads, 25, dim)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    cache = up(cmd, dev, base, vk.FP16, heads, maxlen, dim)
+    vk.UpdateKVCache(dev, cmd, vk.FP16).init()(cache, up(cmd, dev, kv, vk.FP16, heads, 25, dim), 1010)
+    rd = vk.ReadKVCache(dev, cmd).init()
+    got = cmd.download(rd(cache, offset, length))
+    cmd.end()
+    cmd.submit_and_wait()
+    want_cache = base.copy()
+    want_cache[:, (np.arange(25) + 1010) % maxlen] = kv
+    assert np.array_equal(got, O.read_kvcache(want_cache, offset, length))
+    if (offset, length) == (1010, 25):
+        assert np.array_equal(got, kv)
+    cmd.begin()
+    with pytest.raises(vk.VklError) as e:
+        rd(cache, 0, maxlen + 1)
+    assert e.value.code == 11
+    cmd.end()
+    cmd.submit_and_wait()
+
+
+@pytest.mark.parametrize("C,M,N,K,bt,tb", [(5, 64, 48, 96, 1, True), (5, 64, 48, 96, 2, True), (4, 33, 50, 40, 1, False), (4, 33, 50, 40, 2, False),
+                                          (16, 31, 21, 129, 0, True)])
+def test_matmul_broadcast_types(dev, C, M, N, K, bt, tb):
+    """tests/test_matmul.cpp:121-174 (broadcast 0 / 1 / 2, with and without transposed B), scaled-down shapes."""
+    ca, cb = (1 if bt == 2 else C), (1 if bt == 1 else C)
+    a = O.synth_f16(126, 1, ca * M * K).reshape(ca, M, K)
+    bshape = (cb, N, K) if tb else (cb, K, N)
+    b = O.synth_f16(126, 2, cb * N * K, std=0.1).reshape(bshape)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    ta, tbn = up(cmd, dev, a, vk.FP16, *a.shape), up(cmd, dev, b, vk.FP16, *bshape)
+    pair = vk.MatMul(dev, cmd, None, 0.5, 0.25, 0, bt, tb, vk.FP16, vk.FP16).init()
+    got_pair = cmd.download(pair(ta, tbn))
+    wop = vk.MatMul(dev, cmd, tbn, 0.5, 0.25, 1, bt, tb, vk.FP16, vk.FP16).init()  # B as the op's weight, SiLU
+    got_w = cmd.download(wop(ta))
+    cmd.end()
+    cmd.submit_and_wait()
+    assert got_pair.shape == (C, M, N)
+    assert_close(got_pair, O.matmul_broadcast(a, b, bt, tb, 0.5, 0.25, 0), what="matmul broadcast %d" % bt)
+    assert_close(got_w, O.matmul_broadcast(a, b, bt, tb, 0.5, 0.25, 1), what="matmul broadcast %d weight form" % bt)
+    wrong = vk.MatMul(dev, cmd, None, 1.0, 0.0, 0, 1 if bt != 1 else 2, tb, vk.FP16, vk.FP16).init()
+    if C > 1 and bt != 0:
+        cmd.begin()
+        with pytest.raises(vk.VklError) as e:
+            wrong(ta, tbn)
+        assert e.value.code == 3
+        cmd.end()
+        cmd.submit_and_wait()
+
+
+def test_tensor_view_through_matmul_keeps_the_parent_strides(dev):
+    """src/core/tensor.cpp:294-302: a view narrows the extents and keeps the strides; the attention reads the first L
+    rows of every head of the [heads, maxlen, dim] cache through such a view (multiheadattention_v2.cpp:255-275)."""
+    heads, maxlen, dim, L, M = 6, 64, 32, 19, 3
+    cache = O.synth_f16(127, 1, heads * maxlen * dim).reshape(heads, maxlen, dim)
+    q = O.synth_f16(127, 2, heads * M * dim).reshape(heads, M, dim)
+    cmd = vk.Command(dev)
+    cmd.begin()
+    tc, tq = up(cmd, dev, cache, vk.FP16, heads, maxlen, dim), up(cmd, dev, q, vk.FP16, heads, M, dim)
+    view = tc.view(heads, L, dim)
+    assert view.shape() == (heads, L, dim) and view.shape_constant()[3:] == tc.shape_constant()[3:]  # extents narrowed, strides kept
+    scores = vk.MatMul(dev, cmd, None, 1.0 / np.sqrt(dim), 0.0, 0, 0, True, vk.FP16, vk.FP16).init()
+    got = cmd.download(scores(tq, view))  # q . K^T over the first L cached rows of every head
+    pv = vk.MatMul(dev, cmd, None, 1.0, 0.0, 0, 0, False, vk.FP16, vk.FP16).init()
+    p = O.synth_f16(127, 3, heads * M * L, std=0.2).reshape(heads, M, L)
+    got_pv = cmd.download(pv(up(cmd, dev, p, vk.FP16, heads, M, L), view))  # P . V with the same kind of view
+    cmd.end()
+    cmd.submit_and_wait()
+    assert_close(got, O.matmul_broadcast(q, cache[:, :L], 0, True, 1.0 / np.sqrt(dim)), what="q.K^T through a view")
+    assert_close(got_pv, O.matmul_broadcast(p, cache[:, :L], 0, False), what="P.V through a view")

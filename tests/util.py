@@ -54,3 +54,35 @@ def load_from_oracle(model, om):
             model.set_weight(name, vk.FP32, w.view(np.float32))
         else:
             model.set_weight(name, wdt, w)
+
+
+def fp16_ulp(v):
+    """One fp16 ulp at |v|."""
+    return 2.0 ** (np.floor(np.log2(max(abs(float(v)), 2.0 ** -14))) - 10)
+
+
+def oracle_walk(om, prompt, n_gen):
+    """Greedy ids of the oracle and, per step, its top-2 logit gap in fp16 ulps of the top logit."""
+    ids, ulps = [], []
+    logits = om.forward(np.ascontiguousarray(prompt, np.uint32), 0)
+    for i in range(n_gen):
+        if i:
+            logits = om.forward(np.array([ids[-1]], np.uint32), len(prompt) + i - 1)
+        top = int(np.flatnonzero(logits == logits.max())[0])
+        second = float(np.max(np.delete(logits, top)))
+        ids.append(top)
+        ulps.append((float(logits[top]) - second) / fp16_ulp(logits[top]))
+    return np.array(ids, np.uint32), np.array(ulps)
+
+
+def decided_prompt(make_oracle, seed, P, n_gen, vocab, min_ulps=4.0, tries=60):
+    """A seeded prompt whose every greedy step the oracle decides by at least `min_ulps` fp16 ulps, so
+    that a correct implementation with another fp32 summation order must produce the same ids.
+    make_oracle() returns a fresh oracle model (the walk fills its caches). Returns (prompt, ids)."""
+    for k in range(tries):
+        om = make_oracle()
+        prompt = O.synth_tokens(seed, 1000 + k, P, vocab)
+        ids, ulps = oracle_walk(om, prompt, n_gen)
+        if ulps.min() >= min_ulps:
+            return prompt, ids
+    raise AssertionError("no prompt with every step decided by %.1f ulps in %d tries" % (min_ulps, tries))

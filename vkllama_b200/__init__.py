@@ -10,7 +10,7 @@ from .api import (  # noqa: F401
     FP32, FP16, UINT32, INT8, Q8_0,
     VklError, Device, Tensor, Command,
     MatMul, FeedForward, MultiHeadAttentionV2, UpdateKVCache, RMSNorm, Rope, Softmax,
-    ArgOp, ArgMax, ArgMin, Embedding, ElementWise, Transpose, Slice, Cast,
+    ArgOp, ArgMax, ArgMin, Embedding, ElementWise, Transpose, Slice, Cast, Concat, Reduce, ReadKVCache,
     Model, ModelConfig, q8_0_quantize, q8_0_quantize36, q8_0_dequantize, blocks36_to_34,
     kernel_launches, library_path, load_library, matmul_run_many,
     Gguf, Sampler, TopkSampler, TopPSampler,

@@ -8,7 +8,8 @@ FP32, FP16, UINT32, INT8, Q8_0 = 0, 1, 2, 3, 4
 _NP = {FP32: np.float32, FP16: np.uint16, UINT32: np.uint32, INT8: np.int8, Q8_0: np.uint8}
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libvkllama_b200.so")
+# the in-tree build; VKLLAMA_B200_LIB names another build of the same library (A/B comparisons)
+_LIB_PATH = os.environ.get("VKLLAMA_B200_LIB") or os.path.join(_HERE, "libvkllama_b200.so")
 _lib = None
 
 vp, u32, u64, i32, f32, sz = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int, C.c_float, C.c_size_t
@@ -91,6 +92,7 @@ def load_library():
         "vkl_model_decode_profile": [vp, u32, sz, C.POINTER(f32)],
         "vkl_model_decode_trace": [vp, u32, sz, vp, sz, C.POINTER(u32), C.POINTER(u32), vp],
         "vkl_model_tp_buffer": [vp, pvp, C.POINTER(sz)], "vkl_model_tp_connect": [vp, pvp, i32],
+        "vkl_model_set_wait_limit": [vp, u32],
         "vkl_ipc_export": [vp, C.c_char_p], "vkl_ipc_open": [vp, C.c_char_p, pvp],
         "vkl_model_topk": [vp, u32, vp, vp],
         "vkl_gguf_open": [C.c_char_p, pvp], "vkl_gguf_close": [vp],
@@ -508,7 +510,50 @@ class ElementWise(Op):
 
     def __call__(self, x, y):
         out = vp()
-        _ck(self.L.vkl_elementwise_run(self.h, x.h, y.h, C.byref(out)))
+        if isinstance(y, (int, float)):  # ElementWise::operator()(Tensor, float): in place in x
+            _ck(self.L.vkl_elementwise_run_scalar(self.h, x.h, f32(float(y)), C.byref(out)))
+        else:
+            _ck(self.L.vkl_elementwise_run(self.h, x.h, y.h, C.byref(out)))
+        return self._out(out)
+
+
+class Concat(Op):
+    """Concat(dev, command, num, axis, dtype) (src/ops/concat.h:10-17)."""
+
+    def __init__(self, dev, command, num, axis, dtype=FP16):
+        super().__init__(dev, command)
+        _ck(self.L.vkl_concat_create(dev.h, command.h, num, axis, dtype, C.byref(self.h)))
+
+    def __call__(self, inputs):
+        arr = (vp * len(inputs))(*[t.h for t in inputs])
+        out = vp()
+        _ck(self.L.vkl_concat_run(self.h, arr, len(inputs), C.byref(out)))
+        return self._out(out)
+
+
+class Reduce(Op):
+    """Reduce(dev, command, op_type, dtype): 0 sum, 1 max, 2 min, 3 mean (src/ops/reduce.h:18-67)."""
+
+    def __init__(self, dev, command, op_type, dtype=FP16):
+        super().__init__(dev, command)
+        _ck(self.L.vkl_reduce_create(dev.h, command.h, op_type, dtype, C.byref(self.h)))
+
+    def __call__(self, a):
+        out = vp()
+        _ck(self.L.vkl_reduce_run(self.h, a.h, C.byref(out)))
+        return self._out(out)
+
+
+class ReadKVCache(Op):
+    """ReadKVCache(dev, command) (src/ops/read_kvcache_op.h:10-16)."""
+
+    def __init__(self, dev, command):
+        super().__init__(dev, command)
+        _ck(self.L.vkl_read_kvcache_create(dev.h, command.h, C.byref(self.h)))
+
+    def __call__(self, cache, offset, length):
+        out = vp()
+        _ck(self.L.vkl_read_kvcache_run(self.h, cache.h, offset, length, C.byref(out)))
         return self._out(out)
 
 
@@ -649,6 +694,21 @@ class Model:
         _ck(self.L.vkl_model_decode_trace(self.h, token, offset, _ptr(out), out.size, C.byref(nops), C.byref(grid), _ptr(kinds)))
         return out, kinds
 
+    def set_wait_limit(self, polls):
+        """Bound of every wait inside the decode kernel, in polls (0 = default)."""
+        _ck(self.L.vkl_model_set_wait_limit(self.h, polls))
+
+    def tp_buffer(self):
+        """(device pointer, bytes) of this rank's exchange buffer."""
+        p, n = vp(), sz()
+        _ck(self.L.vkl_model_tp_buffer(self.h, C.byref(p), C.byref(n)))
+        return p.value, n.value
+
+    def tp_connect_pointers(self, ptrs):
+        """Connect with already mapped peer pointers, indexed by rank (own entry ignored)."""
+        arr = (vp * len(ptrs))(*[vp(x) for x in ptrs])
+        _ck(self.L.vkl_model_tp_connect(self.h, arr, len(ptrs)))
+
     def tp_export(self):
         """CUDA IPC handle (64 bytes) of this rank's exchange buffer."""
         p, n = vp(), sz()
@@ -660,12 +720,15 @@ class Model:
     def tp_connect(self, handles):
         """handles[r] = IPC handle of rank r's exchange buffer (own entry ignored)."""
         ptrs = (vp * len(handles))()
+        opened = self.__dict__.setdefault("_tp_opened", {})  # a handle is mapped once; reconnecting reuses the mapping
         for r, hb in enumerate(handles):
             if r == self.cfg.tp_rank:
                 continue
-            q = vp()
-            _ck(self.L.vkl_ipc_open(self.dev.h, C.create_string_buffer(hb, 64), C.byref(q)))
-            ptrs[r] = q
+            if hb not in opened:
+                q = vp()
+                _ck(self.L.vkl_ipc_open(self.dev.h, C.create_string_buffer(hb, 64), C.byref(q)))
+                opened[hb] = q.value
+            ptrs[r] = opened[hb]
         _ck(self.L.vkl_model_tp_connect(self.h, ptrs, len(handles)))
 
     def close(self):

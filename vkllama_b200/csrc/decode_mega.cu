@@ -33,16 +33,21 @@
 namespace vkl {
 namespace {
 
-constexpr int WPG = 1;                 // consumer warps per group of a stage: each takes 4 / WPG of the group's blocks
-constexpr int NCW = 15 * WPG;          // consumer warps (+1 producer warp = 512 threads of 128 registers; two warps per group at 64 registers spill and run 1.6x slower)
+constexpr int NCW = 15;                // consumer warps (+1 producer warp = 512 threads of 128 registers)
 constexpr int CT = NCW * 32;           // consumer threads
 constexpr int THREADS = CT + 32;       // + producer warp
-constexpr int SG = (int)MEGA_SG;       // 4-block groups per ring stage: one per consumer warp
-constexpr uint32_t STAGE_CODES = SG * 2048, STAGE_SCALES = SG * 128;
+constexpr int UPW = (int)MEGA_UPW;     // units (one Q8_0 block x 32 rows) per consumer warp and ring stage
+constexpr int SU = NCW * UPW;          // units per ring stage
+static_assert(SU == (int)MEGA_SU, "host and device agree on the stage size");
+constexpr uint32_t UNIT_CODES = MEGA_UNIT_CODES, UNIT_SCALES = MEGA_UNIT_SCALES;
+constexpr uint32_t STAGE_CODES = SU * UNIT_CODES, STAGE_SCALES = SU * UNIT_SCALES;
 constexpr uint32_t STAGE_BYTES = STAGE_CODES + STAGE_SCALES;  // 32640
 static_assert(STAGE_BYTES == MEGA_STAGE_BYTES, "host and device agree on the stage size");
-constexpr int MAX_NST = 6;             // ring stages are a launch parameter (whatever fits), at most this many
-constexpr uint32_t WAIT_LIMIT = 1u << 21;
+constexpr uint32_t XB_BYTES = 64;      // the input vector in shared memory: fp16, 64 bytes per block of 32 inputs
+constexpr int MAX_NST = 12;            // ring stages are a launch parameter (whatever fits), at most this many
+// Every wait of the kernel is bounded by MegaParams::wait_limit polls (about half a microsecond each): the host
+// picks the bound, the same for all waits, so that no wait gives up while another one it depends on is still
+// legitimately waiting (for a slower tensor-parallel rank, say).
 
 __device__ __forceinline__ uint32_t s32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t a, uint32_t n) {
@@ -126,13 +131,14 @@ __device__ __forceinline__ unsigned long long gtime() {
     if (TIMED && trace) trace[k] = gtime();                            \
   } while (0)
 
-// The spin loops of the bounded waits are kept out of line: they are rarely entered (the
-// first try usually succeeds) and, inlined at every wait of every op, they made the kernel's
-// code larger than the instruction cache.
+// The spin loops of the bounded waits. They are inlined like everything else in this kernel: kept out
+// of line (to make the code smaller) they cost 10 % of the token time, the calls forcing the polled
+// words through local memory and registers to be saved around every wait.
 struct Ctx;
-__device__ __noinline__ bool slow_mbar_wait(volatile uint32_t *abort_s, uint32_t *error, uint32_t bar, uint32_t parity, uint32_t code, uint32_t sleep_ns) {
-  #pragma unroll 1
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+#define VKL_SLOW __forceinline__
+__device__ VKL_SLOW bool slow_mbar_wait(volatile uint32_t *abort_s, uint32_t *error, uint32_t limit, uint32_t bar, uint32_t parity, uint32_t code, uint32_t sleep_ns) {
+#pragma unroll 1
+  for (uint32_t i = 0; i < limit; ++i) {
     if (sleep_ns) __nanosleep(sleep_ns);  // keep a waiting warp off the shared-memory pipe the working warps need
     if (mbar_try(bar, parity)) return true;
     if ((i & 255u) == 255u && (*(volatile uint32_t *)error != 0u || *abort_s != 0)) {
@@ -144,10 +150,10 @@ __device__ __noinline__ bool slow_mbar_wait(volatile uint32_t *abort_s, uint32_t
   atomicCAS(error, 0u, code);
   return false;
 }
-__device__ __noinline__ uint32_t slow_ll_wait1(volatile uint32_t *abort_s, uint32_t *error, const uint32_t *src, uint32_t tag) {
+__device__ VKL_SLOW uint32_t slow_ll_wait1(volatile uint32_t *abort_s, uint32_t *error, uint32_t limit, const uint32_t *src, uint32_t tag) {
   uint32_t w = 0;
-  #pragma unroll 1
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+#pragma unroll 1
+  for (uint32_t i = 0; i < limit; ++i) {
     w = ld_vol_u32(src);
     if ((w >> 16) == tag) return w;
     if ((i & 255u) == 255u && (*(volatile uint32_t *)error != 0u || *abort_s != 0)) {
@@ -159,10 +165,10 @@ __device__ __noinline__ uint32_t slow_ll_wait1(volatile uint32_t *abort_s, uint3
   atomicCAS(error, 0u, 6u);
   return w;
 }
-__device__ __noinline__ uint2 slow_ll_wait2(volatile uint32_t *abort_s, uint32_t *error, const uint32_t *src, uint32_t tag) {
+__device__ VKL_SLOW uint2 slow_ll_wait2(volatile uint32_t *abort_s, uint32_t *error, uint32_t limit, const uint32_t *src, uint32_t tag) {
   uint2 w = make_uint2(0, 0);
-  #pragma unroll 1
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+#pragma unroll 1
+  for (uint32_t i = 0; i < limit; ++i) {
     w = ld_vol_v2(src);
     if (((w.x >> 16) == tag) & ((w.y >> 16) == tag)) return w;
     if ((i & 255u) == 255u && (*(volatile uint32_t *)error != 0u || *abort_s != 0)) {
@@ -179,9 +185,9 @@ __device__ __forceinline__ bool ll_ready8(const uint4 &a, const uint4 &b, uint32
          ((b.y >> 16) == tag) & ((b.z >> 16) == tag) & ((b.w >> 16) == tag);
 }
 // polls eight consecutive tagged words until all carry `tag`; the words come back through a, b
-__device__ __noinline__ void slow_ll_wait8(volatile uint32_t *abort_s, uint32_t *error, const uint32_t *src, uint32_t tag, uint4 &a, uint4 &b) {
-  #pragma unroll 1
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+__device__ VKL_SLOW void slow_ll_wait8(volatile uint32_t *abort_s, uint32_t *error, uint32_t limit, const uint32_t *src, uint32_t tag, uint4 &a, uint4 &b) {
+#pragma unroll 1
+  for (uint32_t i = 0; i < limit; ++i) {
     a = ld_vol_v4(src);
     b = ld_vol_v4(src + 4);
     if (ll_ready8(a, b, tag)) return;
@@ -198,6 +204,9 @@ struct Ctx {
   const MegaParams &p;
   volatile uint32_t *abort_s;  // shared flag: some wait of this CTA timed out or *error was seen
   __device__ __forceinline__ bool aborted() const { return *abort_s != 0; }
+  // Under tensor parallelism an input may sit behind an all-reduce that is itself waiting for a slow
+  // rank: the input's wait must outlast that one, so that the error names the wait that really failed.
+  __device__ __forceinline__ uint32_t ll_limit() const { return p.tp_size > 1 ? (p.wait_limit < 0x80000000u ? 2u * p.wait_limit : 0xffffffffu) : p.wait_limit; }
   __device__ __forceinline__ void raise(uint32_t code) const {
     *abort_s = 1;
     atomicCAS(p.error, 0u, code);
@@ -206,23 +215,23 @@ struct Ctx {
   __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, uint32_t code, uint32_t sleep_ns = 0) const {
     if (mbar_try(bar, parity)) return true;  // fast path: the phase is already complete
     if (aborted()) return false;
-    return slow_mbar_wait(abort_s, p.error, bar, parity, code, sleep_ns);
+    return slow_mbar_wait(abort_s, p.error, p.wait_limit, bar, parity, code, sleep_ns);
   }
   // One tagged word, polled (bounded) until its tag is `tag`. Returns the word; on a time-out
   // or an abort returns what it last read (the caller's results are discarded on abort).
   __device__ __forceinline__ uint32_t ll_wait1(const uint32_t *src, uint32_t tag) const {
     const uint32_t w = ld_vol_u32(src);
     if ((w >> 16) == tag) return w;
-    return slow_ll_wait1(abort_s, p.error, src, tag);
+    return slow_ll_wait1(abort_s, p.error, ll_limit(), src, tag);
   }
   // Two consecutive tagged words (8-byte aligned), already requested once.
   __device__ __forceinline__ uint2 ll_wait2(const uint32_t *src, uint2 w, uint32_t tag) const {
     if (((w.x >> 16) == tag) & ((w.y >> 16) == tag)) return w;
-    return slow_ll_wait2(abort_s, p.error, src, tag);
+    return slow_ll_wait2(abort_s, p.error, ll_limit(), src, tag);
   }
   // Eight consecutive tagged words (32-byte aligned) -> eight packed halves, polled the same way.
   __device__ __forceinline__ uint4 ll_wait8(const uint32_t *src, uint4 a, uint4 b, uint32_t tag) const {
-    if (!ll_ready8(a, b, tag)) slow_ll_wait8(abort_s, p.error, src, tag, a, b);
+    if (!ll_ready8(a, b, tag)) slow_ll_wait8(abort_s, p.error, ll_limit(), src, tag, a, b);
     return make_uint4((a.x & 0xffffu) | (a.y << 16), (a.z & 0xffffu) | (a.w << 16), (b.x & 0xffffu) | (b.y << 16), (b.z & 0xffffu) | (b.w << 16));
   }
 };
@@ -299,12 +308,12 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
         } else {
           const uint32_t n0 = e.n0, n1 = e.n1;
           const uint32_t dst = s32(ring + (size_t)slot * STAGE_BYTES);
-          mbar_expect(fb, (n0 + n1) * (2048u + 128u));
-          bulk_g2s(dst, e.codes0, n0 * 2048u, fb);
-          bulk_g2s(dst + STAGE_CODES, e.scales0, n0 * 128u, fb);
+          mbar_expect(fb, (n0 + n1) * (UNIT_CODES + UNIT_SCALES));
+          bulk_g2s(dst, e.codes0, n0 * UNIT_CODES, fb);
+          bulk_g2s(dst + STAGE_CODES, e.scales0, n0 * UNIT_SCALES, fb);
           if (n1) {
-            bulk_g2s(dst + n0 * 2048u, e.codes1, n1 * 2048u, fb);
-            bulk_g2s(dst + STAGE_CODES + n0 * 128u, e.scales1, n1 * 128u, fb);
+            bulk_g2s(dst + n0 * UNIT_CODES, e.codes1, n1 * UNIT_CODES, fb);
+            bulk_g2s(dst + STAGE_CODES + n0 * UNIT_SCALES, e.scales1, n1 * UNIT_SCALES, fb);
           }
         }
         if (++slot == NST) {
@@ -320,15 +329,16 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
     const uint32_t lo = issued > NST ? issued - NST : 0;
     for (uint32_t j = lo; j < issued; ++j) {
       const uint32_t fb = s32(&full[j % NST]), ph2 = (j / NST) & 1u;
-      #pragma unroll 1
-      for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try(fb, ph2); ++i) {
+    #pragma unroll 1
+      // (not the caller's bound, which a test may have made very short: a copy in flight lands within microseconds)
+      for (uint32_t i = 0; i < max(p.wait_limit, 1u << 20) && !mbar_try(fb, ph2); ++i) {
       }
     }
   }
 }
 
 // ------------------------------------------------------------ grid barrier
-__device__ __noinline__ bool grid_barrier(const Ctx &c, uint64_t target, uint32_t round, volatile uint32_t *seen_s) {
+__device__ VKL_SLOW bool grid_barrier(const Ctx &c, uint64_t target, uint32_t round, volatile uint32_t *seen_s) {
   cons_sync();  // every consumer store of this op is issued
   // Lane 0 of the first POLLERS warps poll the counter, each a fraction of a memory round trip
   // after the previous one, so that the last arrival is seen a fraction of a round trip after it
@@ -346,8 +356,8 @@ __device__ __noinline__ bool grid_barrier(const Ctx &c, uint64_t target, uint32_
     }
     const uint32_t tgt = round;
     bool ok = false;
-    #pragma unroll 1
-    for (uint32_t i = 0; i < WAIT_LIMIT * 8u; ++i) {
+  #pragma unroll 1
+    for (uint32_t i = 0; i < c.p.wait_limit; ++i) {
       if (*seen_s == tgt || ld_acq_u64(c.p.bar) >= target) {
         ok = true;
         break;
@@ -381,39 +391,31 @@ __device__ __forceinline__ bool better(float v, uint32_t i, const Best &b) {
 // Two stored codes (bytes 0 and 2, or 1 and 3, of a plane word) as a pair of fp16 subnormals u * 2^-24.
 __device__ __forceinline__ uint32_t codes_sub_h2(uint32_t w, bool hi) { return __byte_perm(w, 0u, hi ? 0x4341u : 0x4240u); }
 
-// One mat-vec op of the token: y[N] = W[N,K] . x[K] for up to three matrices that share x.
+// One mat-vec op of the token: y = W . x for the op's packed weight stream (MegaOp).
+//
+// Arithmetic. The stored codes u = q + 128 go into the tensor core as fp16 subnormals u * 2^-24
+// (one byte permute per pair, no arithmetic): products and their fp32 sums are exact up to the
+// accumulator's rounding, and sum_k u_k x_k = sum_k q_k x_k + 128 * sum_k x_k, so a block's
+// result is 2^24 * acc - 128 * sum(x of the block), scaled by the block's fp16 scale in fp32 as
+// the reference does (matmul_b0_fp16_x_q8_0.comp:99-133). The input is column 0 of the B operand,
+// the other columns read zeros. (An integer path, dp4a on three byte planes of the input, was
+// measured 30 % slower: dp4a issues at about 16 lanes per clock and SM on this GPU.)
 template <bool TIMED, bool DBG>
 __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global, uint32_t &it, uint32_t &slot, uint32_t &ph,
                                           unsigned char *ring, uint64_t *full, uint64_t *empty, const MegaStage *tabs, __half *xs, float *xbias,
-                                          const __half *zero16,
-                                          float *red, float *ssum, Best &best, unsigned long long *tw, uint32_t ar_seq,
+                                          const __half *zero16, float *red, float *ssum, Best &best, unsigned long long *tw, uint32_t ar_seq,
                                           uint32_t tag_in, uint32_t tag_out, unsigned long long *trace) {
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t G = gridDim.x, cta = blockIdx.x;
-  // Scalars in registers: the barriers' memory clobbers would otherwise make every use
-  // of a field a fresh global load inside the streaming loop.
-  struct {
-    uint32_t N, K, groups, nmat, tiles, epi, rot, track_argmax;
-    const float *norm_w;
-    float eps;
-    const uint32_t *in;
-    uint32_t *out_ll[3];
-    __half *out[3];
-    float *out_f32;
-  } op;
-  op.N = op_global.N; op.K = op_global.K; op.groups = op_global.groups; op.nmat = op_global.nmat;
-  op.tiles = op_global.tiles; op.epi = op_global.epi; op.rot = op_global.rot; op.track_argmax = op_global.track_argmax;
-  op.norm_w = op_global.norm_w; op.eps = op_global.eps; op.in = op_global.in;
-  op.out[0] = op_global.out[0]; op.out[1] = op_global.out[1]; op.out[2] = op_global.out[2];
-  op.out_ll[0] = op_global.out_ll[0]; op.out_ll[1] = op_global.out_ll[1]; op.out_ll[2] = op_global.out_ll[2];
-  op.out_f32 = op_global.out_f32;
-  const uint32_t K = op.K, groups = op.groups, nmat = op.nmat, tiles = op.tiles, NST = c.p.nst;
+  // The op's entry sits in shared memory: fields are read where they are used (the prologue, then again
+  // in the epilogue) instead of being carried in registers through the streaming loop, which needs them all.
+  const MegaOp &op = op_global;
+  const uint32_t K = op.K, tiles = op.tiles, NST = c.p.nst;
   const uint32_t tile0 = (cta + G - (op.rot % G)) % G;
   const uint32_t tl = tile0 < tiles ? (tiles - tile0 + G - 1) / G : 0u;  // this CTA's tiles
   // No tile here: nothing to read either. (It must not wait for the input: nobody waits for this
   // CTA's results, so by the time it looked the producers of a later op may have re-tagged the words.)
   if (tl == 0) return;
-  const uint32_t ntm = tl * nmat;                                        // (tile, matrix) row blocks of this CTA
   const uint32_t nstages = op_global.stages_per_cta[cta];  // requested here, together with the input: needed when the stream starts
   // ---- input vector -> shared memory (RMSNorm fused, rounded to fp16 where the
   // reference's RMSNorm op rounds: rms_norm_fp16.comp:70-77). Norm weights and input are
@@ -421,7 +423,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   {
     constexpr int MAXV = (2048 + CT - 1) / CT;  // 8-half vectors per thread: K <= 16384
     uint4 v[MAXV];
-    const uint32_t nv = K / 8, kpad = groups * 128;
+    const uint32_t nv = K / 8;
     const bool norm = op.norm_w != nullptr;
     constexpr int NWV = 2;  // vectors per thread whose norm weights are requested early (K <= 7680: every norm op of the model shapes)
     float4 nw[NWV][2];
@@ -459,7 +461,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
         }
       }
     }
-    for (uint32_t i = tid; i < ntm * NCW * 16; i += CT) red[i] = 0.f;  // warps that get no group of a row block leave zeros
+    for (uint32_t i = tid; i < tl * NCW * 32; i += CT) red[i] = 0.f;  // warps that get no unit of a tile leave zeros
     float alpha = 1.f;
     if (norm) {
       float s = 0.f;
@@ -511,30 +513,37 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
       bs += __shfl_xor_sync(0xffffffffu, bs, 2);
       if ((lane & 3) == 0 && i < nv) xbias[i >> 2] = 128.0f * bs;
     }
-    for (uint32_t i = K + tid; i < kpad; i += CT) xs[i] = __ushort_as_half(0);
-    for (uint32_t b = K / 32 + tid; b < kpad / 32; b += CT) xbias[b] = 0.f;
     cons_sync();
   }
   // EPI_ADD: this thread's residual value, requested now so that its memory round trip is not
-  // on the path between the end of the stream and the grid barrier
+  // on the path between the end of the stream and the publication of the results
   float resid = 0.f;
-  if (op.epi == EPI_ADD && tid < tl * 16) {
-    const uint32_t n = (tile0 + (tid >> 4) * G) * 16 + (tid & 15);
+  if (op.epi == EPI_ADD && tid < tl * 32) {
+    const uint32_t n = (tile0 + (tid >> 5) * G) * 32 + (tid & 31);
     if (n < op.N) resid = __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
   }
   if (TIMED && tw) tw[1] = clock64();
   VKL_TRACE(1);
 
-  // ---- stream this CTA's row blocks. Every stage holds one group (4 blocks x 16 rows) per
-  // consumer warp; stages run on across (tile, matrix) boundaries, so a warp's partial sums
-  // of a row block go to the warp's own slot in shared memory when its groups move on to the
-  // next row block, and nothing synchronises until the op's single reduction at the end.
-  // WPG warps share a group: warp w takes blocks (w % WPG) * BPW .. of group w / WPG.
+  // ---- stream this CTA's tiles. Every stage holds UPW units per consumer warp; a unit is one
+  // block (32 columns) of a 32-row tile: two 16-row halves, each the A operand of two m16n8k16
+  // MMAs. Stages run on across tile boundaries, so a warp's partial sums of a tile go to the
+  // warp's own slot in shared memory when its units move on to the next tile, and nothing
+  // synchronises until the op's single reduction at the end.
   {
-    constexpr int BPW = 4 / WPG;  // blocks per warp per stage
-    const uint32_t gi = warp / WPG, hb = (warp % WPG) * BPW;
     uint32_t cur = 0xffffffffu;
-    float a0 = 0.f, a1 = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};  // lanes t == 0: rows g, g + 8, 16 + g, 24 + g of the tile
+    auto flush = [&]() {
+      if (cur != 0xffffffffu && t == 0) {
+        float *slotp = red + ((size_t)cur * NCW + warp) * 32;
+        slotp[g] = acc[0];
+        slotp[g + 8] = acc[1];
+        slotp[16 + g] = acc[2];
+        slotp[24 + g] = acc[3];
+      }
+    };
+    const __half *xbase = g == 0 ? xs + t * 8 : zero16;  // column 0 of B = the input, the other columns zeros
+    const uint32_t xstep = g == 0 ? 32u : 0u;
     for (uint32_t sidx = 0; sidx < nstages; ++sidx) {
       unsigned long long w0 = 0;
       if (TIMED && tw) w0 = clock64();
@@ -550,59 +559,53 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
         }
         continue;
       }
-      // the stage's place in the op (row block, first group, run lengths) is in the producer's
+      // the stage's place in the op (tile, first block, run lengths) is in the producer's
       // table entry, which the producer wrote before it armed the stage's barrier
       const uint4 meta = *reinterpret_cast<const uint4 *>(&tabs[it & 127].n0);
       const uint32_t n0 = meta.x, n1 = meta.y, tm = meta.z, kg = meta.w;
-      const bool have = ok && gi < n0 + n1;
-      const uint32_t mt = gi < n0 ? tm : tm + 1, mk = gi < n0 ? kg + gi : gi - n0;
       const unsigned char *st = ring + (size_t)slot * STAGE_BYTES;
-      uint4 cw[BPW], sv;
-      if (have) {
+      uint4 wa[UPW], wb[UPW];
+      uint2 dsc[UPW];
+      bool have[UPW];
 #pragma unroll
-        for (int j = 0; j < BPW; ++j) cw[j] = *reinterpret_cast<const uint4 *>(st + (gi * 4 + hb + j) * 512 + lane * 16);
-        sv = *reinterpret_cast<const uint4 *>(st + STAGE_CODES + gi * 128 + g * 16);
+      for (int q = 0; q < UPW; ++q) {
+        const uint32_t u = warp * UPW + q;
+        have[q] = ok && u < n0 + n1;
+        if (have[q]) {
+          wa[q] = *reinterpret_cast<const uint4 *>(st + u * UNIT_CODES + lane * 16);        // rows g, g + 8 of the tile
+          wb[q] = *reinterpret_cast<const uint4 *>(st + u * UNIT_CODES + 512 + lane * 16);  // rows 16 + g, 24 + g
+          dsc[q] = *reinterpret_cast<const uint2 *>(st + STAGE_CODES + u * UNIT_SCALES + g * 8);  // their four block scales
+        }
       }
       __syncwarp();
       if (lane == 0 && ok) mbar_arrive(s32(&empty[slot]));  // this warp has read all it needs from the stage
-      if (have) {
+#pragma unroll
+      for (int q = 0; q < UPW; ++q) {
+        if (!have[q]) continue;
+        const uint32_t u = warp * UPW + q;
+        const uint32_t mt = u < n0 ? tm : tm + 1, b = u < n0 ? kg + u : u - n0;
         if (mt != cur) {
-          if (cur != 0xffffffffu && t == 0) {  // lanes t == 0 hold column 0 = token 0: rows g and g+8
-            float *slotp = red + ((size_t)cur * NCW + warp) * 16;
-            slotp[g] = a0;
-            slotp[g + 8] = a1;
-          }
+          flush();
           cur = mt;
-          a0 = a1 = 0.f;
+          acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
         }
         if (DBG && (c.p.timing_mode & 4u)) {  // diagnostic: ring traffic without arithmetic
-          a0 += __uint_as_float(cw[0].x ^ cw[BPW - 1].y ^ sv.x);
-        } else {
-          // The stored codes u = q + 128 go into the MMA as fp16 subnormals u * 2^-24 (one byte
-          // permute per pair, no arithmetic): products and their fp32 sums are exact up to the
-          // accumulator's rounding, and sum_k u_k x_k = sum_k q_k x_k + 128 * sum_k x_k, so the
-          // block result is 2^24 * acc - 128 * sum(x of the block). Token 0 is column 0 of B,
-          // the other columns read zeros.
-          const __half *xp = g == 0 ? xs + mk * 128 + hb * 32 + t * 8 : zero16;
-          const uint32_t xstep = g == 0 ? 32u : 0u;
-          // block scales of the group: halves 0..3 = rows g, blocks 0..3; halves 4..7 = rows g+8
-          const uint32_t dg_lo = hb < 2 ? sv.x : sv.y, dg_hi = hb < 2 ? sv.z : sv.w;
-          const uint32_t dg_lo2 = sv.y, dg_hi2 = sv.w;  // blocks 2, 3 (used when a warp takes all four)
-#pragma unroll
-          for (int j = 0; j < BPW; ++j) {
-            const uint4 X = *reinterpret_cast<const uint4 *>(xp + j * xstep);
-            const float xb = xbias[mk * 4 + hb + j];
-            const uint4 w = cw[j];
-            float cacc[4] = {0.f, 0.f, 0.f, 0.f};
-            mma16816(cacc, codes_sub_h2(w.x, false), codes_sub_h2(w.z, false), codes_sub_h2(w.x, true), codes_sub_h2(w.z, true), X.x, X.y);
-            mma16816(cacc, codes_sub_h2(w.y, false), codes_sub_h2(w.w, false), codes_sub_h2(w.y, true), codes_sub_h2(w.w, true), X.z, X.w);
-            const uint32_t lo = j < 2 ? dg_lo : dg_lo2, hi = j < 2 ? dg_hi : dg_hi2;
-            const float2 dl = __half22float2(*reinterpret_cast<const __half2 *>(&lo));
-            const float2 dh = __half22float2(*reinterpret_cast<const __half2 *>(&hi));
-            a0 = fmaf(fmaf(cacc[0], 16777216.f, -xb), (j & 1) ? dl.y : dl.x, a0);
-            a1 = fmaf(fmaf(cacc[2], 16777216.f, -xb), (j & 1) ? dh.y : dh.x, a1);
-          }
+          acc[0] += __uint_as_float(wa[q].x ^ wb[q].w ^ dsc[q].x);
+          continue;
         }
+        const uint4 X = *reinterpret_cast<const uint4 *>(xbase + b * xstep);
+        const float xb = xbias[b];
+        float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};
+        mma16816(ca, codes_sub_h2(wa[q].x, false), codes_sub_h2(wa[q].z, false), codes_sub_h2(wa[q].x, true), codes_sub_h2(wa[q].z, true), X.x, X.y);
+        mma16816(cb, codes_sub_h2(wb[q].x, false), codes_sub_h2(wb[q].z, false), codes_sub_h2(wb[q].x, true), codes_sub_h2(wb[q].z, true), X.x, X.y);
+        mma16816(ca, codes_sub_h2(wa[q].y, false), codes_sub_h2(wa[q].w, false), codes_sub_h2(wa[q].y, true), codes_sub_h2(wa[q].w, true), X.z, X.w);
+        mma16816(cb, codes_sub_h2(wb[q].y, false), codes_sub_h2(wb[q].w, false), codes_sub_h2(wb[q].y, true), codes_sub_h2(wb[q].w, true), X.z, X.w);
+        const float2 d0 = __half22float2(*reinterpret_cast<const __half2 *>(&dsc[q].x));  // rows g, g + 8
+        const float2 d1 = __half22float2(*reinterpret_cast<const __half2 *>(&dsc[q].y));  // rows 16 + g, 24 + g
+        acc[0] = fmaf(fmaf(ca[0], 16777216.f, -xb), d0.x, acc[0]);
+        acc[1] = fmaf(fmaf(ca[2], 16777216.f, -xb), d0.y, acc[1]);
+        acc[2] = fmaf(fmaf(cb[0], 16777216.f, -xb), d1.x, acc[2]);
+        acc[3] = fmaf(fmaf(cb[2], 16777216.f, -xb), d1.y, acc[3]);
       }
       ++it;
       if (++slot == NST) {
@@ -610,11 +613,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
         ph ^= 1u;
       }
     }
-    if (cur != 0xffffffffu && t == 0) {
-      float *slotp = red + ((size_t)cur * NCW + warp) * 16;
-      slotp[g] = a0;
-      slotp[g + 8] = a1;
-    }
+    flush();
   }
   // ---- one fixed-order reduction over the warps and the epilogue for all tiles
   VKL_TRACE(2);
@@ -624,39 +623,41 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   }
   cons_sync();
   VKL_TRACE(3);
-  for (uint32_t idx = tid; idx < tl * 16; idx += CT) {
-    const uint32_t lt = idx >> 4, r = idx & 15;
-    const uint32_t n = (tile0 + lt * G) * 16 + r;
-    float v[3] = {0.f, 0.f, 0.f};
-    for (uint32_t m = 0; m < nmat; ++m) {
-      const float *sp = red + ((size_t)(lt * nmat + m) * NCW) * 16 + r;
-      float sum = 0.f;
+  const uint32_t tpm = (op.N + 31) / 32;  // tiles per matrix (nmat = 3)
+  for (uint32_t idx = tid; idx < tl * 32; idx += CT) {  // tl * 32 is a multiple of the warp size: whole warps
+    const uint32_t lt = idx >> 5, r = idx & 31;
+    const uint32_t gt = tile0 + lt * G;
+    const float *sp = red + ((size_t)lt * NCW) * 32 + r;
+    float sum = 0.f;
 #pragma unroll
-      for (int w = 0; w < NCW; ++w) sum += sp[w * 16];
-      v[m] = sum;
+    for (int w = 0; w < NCW; ++w) sum += sp[w * 32];
+    if (op.epi == EPI_SWIGLU) {
+      // rows 0..15 of the tile are gate rows, rows 16..31 the up rows of the same outputs
+      const float up = __shfl_down_sync(0xffffffffu, sum, 16);
+      const uint32_t n = gt * 16 + r;
+      if (r < 16 && n < op.N && !c.aborted()) op.out_ll[0][n] = ll_pack(__float2half_rn(sum / (1.0f + expf(-sum)) * up), tag_out);
+      continue;
     }
+    const uint32_t m = op.nmat == 3 ? gt / tpm : 0u;
+    const uint32_t n = (op.nmat == 3 ? gt % tpm : gt) * 32 + r;
     if (n < op.N && !c.aborted()) {
-      if (op.epi == EPI_SWIGLU) {
-        const float gate = v[0], up = v[1];
-        op.out_ll[0][n] = ll_pack(__float2half_rn(gate / (1.0f + expf(-gate)) * up), tag_out);
-      } else if (op.epi == EPI_ADD) {
+      if (op.epi == EPI_ADD) {
         const float res = idx == tid ? resid : __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
-        op.out_ll[0][n] = ll_pack(__float2half_rn(round_h(v[0]) + res), tag_out);
+        op.out_ll[0][n] = ll_pack(__float2half_rn(round_h(sum) + res), tag_out);
       } else if (op.epi == EPI_PARTIAL) {
         // this rank's share of a row-split projection: the raw fp32 sum and the all-reduce's
         // sequence number go, as one 8-byte word, into slot [parity][my rank] of every rank's
         // exchange buffer (plain peer stores over NVLink; the word is its own arrival flag)
         const MegaParams &pp = c.p;
-        for (uint32_t r = 0; r < pp.tp_size; ++r) {
-          uint32_t *dst = static_cast<uint32_t *>(pp.tp_peer[r]) + 2 * (((size_t)(ar_seq & 1u) * pp.tp_size + pp.tp_rank) * pp.dim + n);
-          asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(v[0])), "r"(ar_seq) : "memory");
+        for (uint32_t rk = 0; rk < pp.tp_size; ++rk) {
+          uint32_t *dst = static_cast<uint32_t *>(pp.tp_peer[rk]) + 2 * (((size_t)(ar_seq & 1u) * pp.tp_size + pp.tp_rank) * pp.dim + n);
+          asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(sum)), "r"(ar_seq) : "memory");
         }
       } else {
-        const __half h0 = __float2half_rn(v[0]);
-        if (op.out_ll[0]) {
-          op.out_ll[0][n] = ll_pack(h0, tag_out);
-          if (nmat > 1) op.out_ll[1][n] = ll_pack(__float2half_rn(v[1]), tag_out);
-          if (nmat > 2) op.out_ll[2][n] = ll_pack(__float2half_rn(v[2]), tag_out);
+        const __half h0 = __float2half_rn(sum);
+        uint32_t *o = m == 0 ? op.out_ll[0] : m == 1 ? op.out_ll[1] : op.out_ll[2];
+        if (o) {
+          o[n] = ll_pack(h0, tag_out);
         } else {
           op.out[0][n] = h0;
         }
@@ -830,56 +831,6 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
     pv[grp * D + 2 * dp + 1] = acc.y;
   }
   cons_sync();
-  if (S > 1 && p.attn_merge == 2) {
-    // Every split publishes its partial row as 8-byte words {value, this op's sequence number}
-    // and then merges its own share of the head's dims from all splits' words (polling until
-    // they carry the number): no fence, no counter, no combine op. Merged in split order.
-    uint32_t *part2 = reinterpret_cast<uint32_t *>(p.attn_scratch) + 2 * ((size_t)h * p.splits + split) * (D + 4);
-    if (tid < D) {
-      float s = 0.f;
-#pragma unroll
-      for (int gq = 0; gq < CT / 64; ++gq) s += pv[gq * D + tid];
-      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(part2 + 2 * tid), "r"(__float_as_uint(s)), "r"(tag_out) : "memory");
-    }
-    if (tid == 0) {
-      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(part2 + 2 * D), "r"(__float_as_uint(mloc)), "r"(tag_out) : "memory");
-      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(part2 + 2 * (D + 1)), "r"(__float_as_uint(lloc)), "r"(tag_out) : "memory");
-    }
-    const uint32_t per = (D + S - 1) / S, d = split * per + tid;
-    if (tid < per && d < D) {
-      const uint32_t *base = reinterpret_cast<const uint32_t *>(p.attn_scratch) + 2 * ((size_t)h * p.splits) * (D + 4);
-      float ms[8], ls[8], as[8];
-      for (uint32_t sp = 0; sp < S; ++sp) {
-        const uint32_t *b = base + 2 * (size_t)sp * (D + 4);
-        uint2 wm = ld_vol_v2(b + 2 * D), wl = ld_vol_v2(b + 2 * (D + 1)), wa = ld_vol_v2(b + 2 * d);
-        #pragma unroll 1
-        for (uint32_t i = 0; (wm.y != tag_out || wl.y != tag_out || wa.y != tag_out) && i < WAIT_LIMIT; ++i) {
-          wm = ld_vol_v2(b + 2 * D);
-          wl = ld_vol_v2(b + 2 * (D + 1));
-          wa = ld_vol_v2(b + 2 * d);
-          if ((i & 255u) == 255u && (*(volatile uint32_t *)p.error != 0u || c.aborted())) break;
-        }
-        if (wm.y != tag_out || wl.y != tag_out || wa.y != tag_out) {
-          c.raise(6);
-          return;
-        }
-        ms[sp] = __uint_as_float(wm.x);
-        ls[sp] = __uint_as_float(wl.x);
-        as[sp] = __uint_as_float(wa.x);
-      }
-      float M = -INFINITY;
-      for (uint32_t sp = 0; sp < S; ++sp) M = fmaxf(M, ms[sp]);
-      float den = 0.f, num = 0.f;
-      for (uint32_t sp = 0; sp < S; ++sp)
-        if (ls[sp] > 0.f) {
-          const float w = expf(ms[sp] - M);
-          den += ls[sp] * w;
-          num += as[sp] * w;
-        }
-      p.ao[row + d] = ll_pack(__float2half_rn(num / den), tag_out);
-    }
-    return;
-  }
   float *part = p.attn_scratch + ((size_t)h * p.splits + split) * (D + 4);
   if (tid < D) {
     float s = 0.f;
@@ -927,7 +878,7 @@ __device__ __forceinline__ void attn_part_op(const Ctx &c, const MegaOp &op, flo
 }
 
 // One head per CTA: merge the split partials in split order.
-__device__ __noinline__ void attn_combine_op(const Ctx &c, uint32_t tag_out) {
+__device__ VKL_SLOW void attn_combine_op(const Ctx &c, uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t h = blockIdx.x, tid = threadIdx.x, D = p.head_dim;
   if (h >= p.heads || tid >= D) return;
@@ -947,7 +898,7 @@ __device__ __noinline__ void attn_combine_op(const Ctx &c, uint32_t tag_out) {
 }
 
 // Embedding gather + dequantisation of the current token (embedding_q8_0.comp:39-85).
-__device__ __noinline__ void embed_op(const Ctx &c, uint32_t tok, uint32_t tag_out) {
+__device__ VKL_SLOW void embed_op(const Ctx &c, uint32_t tok, uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t per = (p.dim + gridDim.x - 1) / gridDim.x;
   const uint32_t k = blockIdx.x * per + threadIdx.x;
@@ -964,7 +915,7 @@ __device__ __noinline__ void embed_op(const Ctx &c, uint32_t tok, uint32_t tag_o
 
 // CTA 0: best of the per-CTA candidates (lowest index on ties), then publish the id,
 // feed it back and advance position, step and launch epoch.
-__device__ __noinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_t pos0, uint64_t rounds_done, uint32_t ar_done,
+__device__ VKL_SLOW void argmax_final_op(const Ctx &c, float *sm, uint32_t pos0, uint64_t rounds_done, uint32_t ar_done,
                                                 uint32_t next_ebase) {
   const MegaParams &p = c.p;
   if (blockIdx.x != 0) return;
@@ -1013,8 +964,8 @@ __device__ __noinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_t p
       const uint32_t *mine = static_cast<const uint32_t *>(p.tp_peer[p.tp_rank]) + p.tp_flag_off;
       for (uint32_t r = 0; r < tp && !c.aborted(); ++r) {
         bool ok = false;
-        #pragma unroll 1
-        for (uint32_t i = 0; i < WAIT_LIMIT * 8u; ++i) {
+      #pragma unroll 1
+        for (uint32_t i = 0; i < c.p.wait_limit; ++i) {
           if ((int32_t)(ld_acq_sys_u32(mine + 16 + r) - aseq) >= 0) {
             ok = true;
             break;
@@ -1060,7 +1011,7 @@ __device__ __noinline__ void argmax_final_op(const Ctx &c, float *sm, uint32_t p
 // this all-reduce's number: x <- fp16( fp16(sum_r partial_r) + x ), the same rounding as
 // o_proj/down + residual add. No grid barrier and no separate flags: two parities of slots
 // keep a fast rank's next push from overwriting what a slow rank still reads.
-__device__ __noinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t seq, uint32_t tag_out) {
+__device__ VKL_SLOW void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t seq, uint32_t tag_out) {
   const MegaParams &p = c.p;
   const uint32_t tid = threadIdx.x, tp = p.tp_size;
   if (c.aborted()) return;
@@ -1076,8 +1027,8 @@ __device__ __noinline__ void allreduce_op(const Ctx &c, const MegaOp &op, uint32
       uint2 w = ld_vol_v2(src);
       if (w.y != seq) {
         bool ok = false;
-        #pragma unroll 1
-        for (uint32_t it = 0; it < WAIT_LIMIT * 8u; ++it) {
+      #pragma unroll 1
+        for (uint32_t it = 0; it < p.wait_limit; ++it) {
           w = ld_vol_v2(src);
           if (w.y == seq) {
             ok = true;
@@ -1105,7 +1056,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
   unsigned char *ring = smem;
   unsigned char *xq = smem + (size_t)NST * STAGE_BYTES;  // quantised input vector; attention scratch
   float *red = reinterpret_cast<float *>(xq + p.xs_bytes);
-  float *ssum = red + (size_t)p.red_slots * NCW * 16;  // [64]
+  float *ssum = red + (size_t)p.red_slots * NCW * 32;  // [64]
   const __half *zero16 = reinterpret_cast<const __half *>(ssum + 64);  // 16 zero bytes
   MegaStage *tabs = reinterpret_cast<MegaStage *>(ssum + 68);  // [128], 16-byte aligned
   uint64_t *full = reinterpret_cast<uint64_t *>(tabs + 128);
@@ -1172,7 +1123,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     VKL_TRACE(0);
     switch (op.kind) {
       case MK_EMBED: embed_op(c, tok, tag(oi)); break;
-      case MK_MATVEC: matvec_op<TIMED, DBG>(c, op, it, slot, ph, ring, full, empty, tabs, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_groups * 256), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, seq0 + ar_i + 1,
+      case MK_MATVEC: matvec_op<TIMED, DBG>(c, op, it, slot, ph, ring, full, empty, tabs, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_blocks * XB_BYTES), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, seq0 + ar_i + 1,
                          tag(op.src_op), tag(oi), trace);
         break;
       case MK_ATTN_PART:
@@ -1256,8 +1207,8 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
 
 }  // namespace
 
-size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits, uint32_t split_rows) {
-  size_t x = (size_t)max_groups * (128 * 2 + 4 * 4);  // fp16 input + one fp32 bias term per block
+size_t decode_mega_xs_bytes(uint32_t max_blocks, uint32_t head_dim, uint32_t maxlen, uint32_t splits, uint32_t split_rows) {
+  size_t x = (size_t)max_blocks * (XB_BYTES + 4);  // fp16 input + one fp32 bias term per block of 32 inputs
   // most rows a split can get: all splits at the full context, or one of fewer splits of split_rows rows
   uint32_t chunk = ((maxlen + splits - 1) / splits + 31) & ~31u;
   if (split_rows) chunk = std::max(chunk, (std::min(maxlen, split_rows) + 31) & ~31u);
@@ -1266,10 +1217,59 @@ size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t max
   return (b + 127) / 128 * 128;
 }
 size_t decode_mega_smem(size_t xs_bytes, uint32_t nst, uint32_t red_slots) {
-  return (size_t)nst * STAGE_BYTES + xs_bytes + ((size_t)red_slots * NCW * 16 + 68) * 4 + 128 * sizeof(MegaStage) + 2 * MAX_NST * 8 + 16 + 3 * sizeof(MegaOp) + 64;
+  return (size_t)nst * STAGE_BYTES + xs_bytes + ((size_t)red_slots * NCW * 32 + 68) * 4 + 128 * sizeof(MegaStage) + 2 * MAX_NST * 8 + 16 + 3 * sizeof(MegaOp) + 64;
 }
 int decode_mega_max_k() { return 16384; }
 int decode_mega_max_stages() { return MAX_NST; }
+
+// Packs the op's matrices from the library's tiled planes (common.cuh) into the stream layout of
+// MegaOp: one CTA per (block, tile), one thread per 16-byte piece. A 32-row tile's unit is the two
+// 512-byte (16 rows x 32 columns) units of the planes that hold its rows, unchanged (codes stay
+// biased by +128 in MMA fragment order), and the 32 scales in the order the consumer lanes read them.
+namespace {
+__global__ void __launch_bounds__(64) mega_pack_kernel(const uint8_t *p0, const uint8_t *p1, const uint8_t *p2, uint32_t nmat, int swiglu, uint32_t N,
+                                                       uint32_t K, uint8_t *codes, uint8_t *scales) {
+  const uint32_t b = blockIdx.x, t = blockIdx.y, blocks = K / 32;
+  const uint32_t half = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tpm = (N + 31) / 32;
+  // the 16-row plane tile behind this half of the 32-row tile
+  uint32_t m, tile16;
+  if (swiglu) {
+    m = half;  // gate rows 16 t .., then up rows 16 t ..
+    tile16 = t;
+  } else if (nmat == 3) {
+    m = t / tpm;
+    tile16 = (t % tpm) * 2 + half;
+  } else {
+    m = 0;
+    tile16 = t * 2 + half;
+  }
+  const uint8_t *src = m == 0 ? p0 : m == 1 ? p1 : p2;
+  const Q8Layout L = q8_layout(N, K);
+  const bool in = tile16 < L.tiles;
+  uint4 w = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // code 0, biased
+  if (in) w = *reinterpret_cast<const uint4 *>(src + (((size_t)tile16 * L.groups * 4 + b) * 32 + lane) * 16);
+  const size_t unit = (size_t)t * blocks + b;
+  reinterpret_cast<uint4 *>(codes + unit * MEGA_UNIT_CODES)[half * 32 + lane] = w;
+  if (lane < 16) {
+    // scales of the unit: [g][row g | g + 8 of half 0, row g | g + 8 of half 1] as fp16
+    const uint32_t g = lane & 7, up8 = lane >> 3;
+    unsigned short d = 0;
+    if (in) {
+      const unsigned short *sc = reinterpret_cast<const unsigned short *>(src + L.codes_bytes());
+      d = sc[(((size_t)tile16 * L.groups + (b >> 2)) * 8 + g) * 8 + up8 * 4 + (b & 3)];
+    }
+    reinterpret_cast<unsigned short *>(scales + unit * MEGA_UNIT_SCALES)[g * 4 + half * 2 + up8] = d;
+  }
+}
+}  // namespace
+
+cudaError_t launch_mega_pack(const uint8_t *const planes[3], uint32_t nmat, int swiglu, uint32_t N, uint32_t K, uint32_t tiles, uint8_t *codes,
+                             uint8_t *scales, cudaStream_t s) {
+  if (K % 32 || tiles == 0 || tiles > 65535u) return cudaErrorInvalidValue;
+  mega_pack_kernel<<<dim3(K / 32, tiles), 64, 0, s>>>(planes[0], planes[1], planes[2], nmat, swiglu, N, K, codes, scales);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s) {
   if (p.nst < 2 || p.nst > (uint32_t)MAX_NST) return cudaErrorInvalidValue;

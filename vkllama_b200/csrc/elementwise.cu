@@ -186,6 +186,57 @@ __global__ void elementwise_kernel(const __half *__restrict__ x, __half *y, uint
   y[i] = __float2half_rn(r);
 }
 
+// x <- fp16(x op alpha). src/shaders/element_wise_constant_fp16.comp:19-44 (fp32 arithmetic form).
+__global__ void elementwise_scalar_kernel(__half *x, uint64_t n, int op, float alpha) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float a = __half2float(x[i]);
+  float r = a + alpha;
+  if (op == 1) r = a - alpha;
+  if (op == 2) r = a * alpha;
+  if (op == 3) r = a / alpha;
+  x[i] = __float2half_rn(r);
+}
+
+// out[c, h, w + off_w ...] = in[c, h, w]: one input of a concatenation copied to its place
+// (src/shaders/concat_fp16.comp:27-49: element offset OFFSET inside the output's [c][h][w] strides).
+__global__ void concat_copy_kernel(const __half *__restrict__ in, __half *__restrict__ out, uint32_t C, uint32_t H, uint32_t W,
+                                   uint64_t ocs, uint64_t ohs, uint64_t offset) {
+  const uint64_t n = (uint64_t)C * H * W, i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t w = (uint32_t)(i % W), h = (uint32_t)((i / W) % H), c = (uint32_t)(i / ((uint64_t)W * H));
+  out[c * ocs + h * ohs + w + offset] = in[i];
+}
+
+// One warp per row: sum / max / min over the row, times mean_scale (src/shaders/reduce_fp16.comp:24-76:
+// lane-strided partial results, then a subgroup reduction; max and min start from the row's first value).
+__global__ void reduce_kernel(const __half *__restrict__ in, __half *__restrict__ out, uint32_t rows, uint32_t W, int op, float mean_scale) {
+  const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __half *x = in + (size_t)row * W;
+  float r = op == 0 ? 0.f : __half2float(x[0]);
+  for (uint32_t w = lane; w < W; w += 32) {
+    const float v = __half2float(x[w]);
+    r = op == 0 ? r + v : op == 1 ? fmaxf(r, v) : fminf(r, v);
+  }
+  // lanes combined in lane order (a subgroup reduction has no defined order; the oracle sums the same way)
+  float tot = __shfl_sync(0xffffffffu, r, 0);
+  for (int l = 1; l < 32; ++l) {
+    const float v = __shfl_sync(0xffffffffu, r, l);
+    tot = op == 0 ? tot + v : op == 1 ? fmaxf(tot, v) : fminf(tot, v);
+  }
+  if (lane == 0) out[row] = __float2half_rn(tot * mean_scale);
+}
+
+// out[c, y, :] = cache[c, (y + offset) % H, :]. src/shaders/read_kvcache_fp16.comp.
+__global__ void read_kvcache_kernel(const __half *__restrict__ cache, __half *__restrict__ out, uint32_t C, uint32_t H, uint32_t W, uint32_t offset,
+                                    uint32_t len) {
+  const uint64_t n = (uint64_t)C * len * W, i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t w = (uint32_t)(i % W), y = (uint32_t)((i / W) % len), c = (uint32_t)(i / ((uint64_t)W * len));
+  out[i] = cache[((size_t)c * H + (y + offset) % H) * W + w];
+}
+
 // ---------------------------------------------------------------- embedding
 // out[t,:] = dequant(vocab[tok_t,:]); tok >= VH -> UNK. embedding_q8_0.comp:39-85.
 __global__ void embedding_q8_kernel(const uint8_t *__restrict__ planes,
@@ -443,6 +494,30 @@ cudaError_t launch_rms_norm(const __half *x, const float *w, __half *y, uint32_t
 cudaError_t launch_add(const __half *x, __half *y, uint64_t n, int op, cudaStream_t s) {
   if (!n) return cudaSuccess;
   elementwise_kernel<<<nblk(n, 256), 256, 0, s>>>(x, y, n, op);
+  return cudaGetLastError();
+}
+cudaError_t launch_scalar_op(__half *x, uint64_t n, int op, float alpha, cudaStream_t s) {
+  if (!n) return cudaSuccess;
+  elementwise_scalar_kernel<<<nblk(n, 256), 256, 0, s>>>(x, n, op, alpha);
+  return cudaGetLastError();
+}
+cudaError_t launch_concat_copy(const __half *in, __half *out, uint32_t C, uint32_t H, uint32_t W, uint64_t ocs, uint64_t ohs, uint64_t offset,
+                               cudaStream_t s) {
+  const uint64_t n = (uint64_t)C * H * W;
+  if (!n) return cudaSuccess;
+  concat_copy_kernel<<<nblk(n, 256), 256, 0, s>>>(in, out, C, H, W, ocs, ohs, offset);
+  return cudaGetLastError();
+}
+cudaError_t launch_reduce(const __half *in, __half *out, uint32_t rows, uint32_t W, int op, float mean_scale, cudaStream_t s) {
+  if (!rows) return cudaSuccess;
+  reduce_kernel<<<(rows + 7) / 8, 256, 0, s>>>(in, out, rows, W, op, mean_scale);
+  return cudaGetLastError();
+}
+cudaError_t launch_read_kvcache(const __half *cache, __half *out, uint32_t C, uint32_t H, uint32_t W, uint32_t offset, uint32_t len,
+                                cudaStream_t s) {
+  const uint64_t n = (uint64_t)C * len * W;
+  if (!n) return cudaSuccess;
+  read_kvcache_kernel<<<nblk(n, 256), 256, 0, s>>>(cache, out, C, H, W, offset, len);
   return cudaGetLastError();
 }
 cudaError_t launch_embedding(const uint8_t *vocab, int is_q8, const uint32_t *ids, __half *out,

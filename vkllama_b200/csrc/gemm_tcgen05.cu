@@ -1,8 +1,15 @@
-// Dense FP16 GEMM for multi-token (prefill) passes on the 5th-generation tensor cores:
-// C[M,N] = A[M,K] . W[N,K]^T with fp32 accumulation in tensor memory (TMEM).
+// Dense GEMM for multi-token (prefill) passes on the 5th-generation tensor cores:
+// C[M,N] = A[M,K] . W[N,K]^T with fp32 accumulation in tensor memory (TMEM), W in FP16 or Q8_0.
 //
-// Replaces, for FP16 weights and many rows, the reference's matmul_b0_tb_fp16_v2.comp
-// (src/ops/mat_mul.cpp:71-82), which re-reads the whole weight matrix for every input row.
+// Replaces, for many rows, the reference's matmul_b0_tb_fp16_v2.comp and matmul_b0_fp16_x_q8_0.comp
+// (src/ops/mat_mul.cpp:71-103), which re-read the whole weight matrix for every input row.
+//
+// Q8_0 weights are dequantised on the way into shared memory: four extra warps read the codes and
+// scales of the stage's W tile (tiled planes, common.cuh), turn every code into the fp16 value
+// fp16(q * d) and store it where a 128-byte-swizzled tensor copy would have put it, so the MMA
+// loop is the same as for FP16 weights. q * d has up to 19 significant bits: this path rounds every
+// weight once to fp16 (relative 2^-12), where the reference multiplies in fp32; the rows-at-a-time
+// kernel (matvec.cu) keeps the exact form and is used below GEMM_Q8_MIN_ROWS rows.
 //
 // One CTA computes a 128 x BN output tile (BN = 128 or 256) with three kinds of warps:
 //   warp 0    producer: one lane issues TMA tensor copies (cp.async.bulk.tensor.2d, 128-byte
@@ -28,7 +35,8 @@ namespace {
 constexpr int BM = 128, BK = 64;
 constexpr uint32_t A_TILE_BYTES = BM * BK * 2;  // 16 KB
 constexpr uint32_t GEMM_WAIT_LIMIT = 1u << 22;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 192;          // FP16 weights: TMA producer, MMA, four epilogue warps
+constexpr int GEMM_THREADS_Q8 = 192 + 128;  // + four warps dequantising the W tile
 
 template <int BN> struct Cfg {
   static constexpr uint32_t B_TILE_BYTES = BN * BK * 2;
@@ -92,9 +100,30 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int BN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-    gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+// One Q8_0 unit (16 rows x 32 columns, 512 bytes of codes) -> fp16 values q * d in the swizzled W tile.
+// Lane (g, t) holds 8 codes of row g and 8 codes of row g + 8 at columns 8 t .. 8 t + 7 (common.cuh).
+__device__ __forceinline__ void dequant_unit(unsigned char *wtile, uint32_t row0, uint32_t chunk0, uint4 w, uint32_t d_lo, uint32_t d_hi, uint32_t lane) {
+  const uint32_t g = lane >> 2, t = lane & 3;
+  const __half2 dl = __half2half2(__ushort_as_half((unsigned short)d_lo)), dh = __half2half2(__ushort_as_half((unsigned short)d_hi));
+  uint32_t a[4], b[4];
+  // word = codes [c0, c2, c1, c3]: pair (c0, c1) is "low", (c2, c3) "high" (codes_to_h2)
+  a[0] = codes_to_h2(w.x, false); a[1] = codes_to_h2(w.x, true); a[2] = codes_to_h2(w.y, false); a[3] = codes_to_h2(w.y, true);
+  b[0] = codes_to_h2(w.z, false); b[1] = codes_to_h2(w.z, true); b[2] = codes_to_h2(w.w, false); b[3] = codes_to_h2(w.w, true);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __half2 x = __hmul2(*reinterpret_cast<__half2 *>(&a[i]), dl), y = __hmul2(*reinterpret_cast<__half2 *>(&b[i]), dh);
+    a[i] = *reinterpret_cast<uint32_t *>(&x);
+    b[i] = *reinterpret_cast<uint32_t *>(&y);
+  }
+  // 128-byte swizzle of a K-major tile with 128-byte rows: 16-byte chunk c of row r sits at chunk c ^ (r % 8)
+  const uint32_t ra = row0 + g, rb = row0 + g + 8, c = chunk0 + t;
+  *reinterpret_cast<uint4 *>(wtile + ra * 128 + ((c ^ (ra & 7)) << 4)) = make_uint4(a[0], a[1], a[2], a[3]);
+  *reinterpret_cast<uint4 *>(wtile + rb * 128 + ((c ^ (rb & 7)) << 4)) = make_uint4(b[0], b[1], b[2], b[3]);
+}
+
+template <int BN, bool Q8>
+__global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ unsigned char smem_raw[];
   // swizzle atoms are 1024 bytes: align the stage ring
@@ -110,7 +139,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   const uint32_t nkb = p.K / BK;
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&full[s])) : "memory");
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sa(&full[s])), "r"(Q8 ? 5u : 1u) : "memory");  // the TMA lane (+ one lane per dequantising warp)
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&empty[s])) : "memory");
     }
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&acc_ready)) : "memory");
@@ -134,11 +163,47 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         if (failed_s) break;
         const uint32_t bar = sa(&full[s]);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(C::STAGE_BYTES) : "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(Q8 ? A_TILE_BYTES : C::STAGE_BYTES) : "memory");
         unsigned char *st = stages + (size_t)s * C::STAGE_BYTES;
         tma_load_2d(sa(st), &map_a, kb * BK, m0, bar);
-        tma_load_2d(sa(st + A_TILE_BYTES), &map_w, kb * BK, n0, bar);
+        if (!Q8) tma_load_2d(sa(st + A_TILE_BYTES), &map_w, kb * BK, n0, bar);
       }
+    }
+  } else if (Q8 && warp >= 6) {
+    // ------------------------------------------- W tile: Q8_0 -> fp16 in shared memory
+    // BN rows x 64 columns = (BN / 16) row tiles x 2 blocks: units of 512 bytes of codes, dealt round robin to
+    // the four warps. The scales of a row tile and 4-block group are 8 x 16 bytes: row g's four blocks, then row g + 8's.
+    const uint32_t dw = warp - 6, g = lane >> 2;
+    const uint32_t tiles16 = (p.N + 15) / 16, groups = ((p.K + 31) / 32 + 3) / 4;
+    constexpr uint32_t UNITS = (BN / 16) * 2;
+    for (uint32_t kb = 0; kb < nkb; ++kb) {
+      const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
+      uint32_t ok = 1;
+      if (lane == 0 && use > 0) ok = mbar_wait_bounded(sa(&empty[s]), (use - 1) & 1u) ? 1u : 0u;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) {
+        if (lane == 0) failed_s = 4;
+        break;
+      }
+      if (failed_s) break;
+      unsigned char *wt = stages + (size_t)s * C::STAGE_BYTES + A_TILE_BYTES;
+      for (uint32_t u = dw; u < UNITS; u += 4) {
+        const uint32_t tl = u >> 1, bl = u & 1;  // row tile inside the W tile, block inside the K step
+        const uint32_t tile = n0 / 16 + tl, b = kb * 2 + bl;
+        uint4 w = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // code 0 (stored biased by 128)
+        uint32_t d_lo = 0, d_hi = 0;
+        if (tile < tiles16) {
+          w = ldg_stream(p.w_codes + (((size_t)tile * groups * 4 + b) * 32 + lane) * 16);
+          const unsigned short *sc = reinterpret_cast<const unsigned short *>(p.w_scales) + (((size_t)tile * groups + (b >> 2)) * 8 + g) * 8 + (b & 3);
+          d_lo = sc[0];
+          d_hi = sc[4];
+        }
+        dequant_unit(wt, tl * 16, bl * 4, w, d_lo, d_hi, lane);
+      }
+      // the tensor core reads shared memory through the async proxy: order this warp's stores before its arrival
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sa(&full[s])) : "memory");
     }
   } else if (warp == 1) {
     // --------------------------------------------------------------------- MMA
@@ -168,7 +233,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sa(&acc_ready)) : "memory");
       }
     }
-  } else {
+  } else if (warp >= 2 && warp < 6) {
     // ---------------------------------------------------------------- epilogue
     // a warp may only touch TMEM lanes 32*(warp % 4) .. +31
     const uint32_t quad = warp & 3u;
@@ -264,17 +329,29 @@ bool make_map(CUtensorMap *map, const __half *base, uint32_t rows, uint32_t K, u
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN> cudaError_t launch_bn(const GemmParams &p, cudaStream_t s) {
+template <int BN, bool Q8> cudaError_t launch_bn(const GemmParams &p, cudaStream_t s) {
   CUtensorMap ma, mw;
-  if (!make_map(&ma, p.a, p.M, p.K, BM) || !make_map(&mw, p.w, p.N, p.K, BN)) return cudaErrorInvalidValue;
-  cudaError_t e = cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::SMEM);
+  if (!make_map(&ma, p.a, p.M, p.K, BM)) return cudaErrorInvalidValue;
+  if (Q8) {
+    mw = ma;  // unused: the W tile is written by the dequantising warps
+  } else if (!make_map(&mw, p.w, p.N, p.K, BN)) {
+    return cudaErrorInvalidValue;
+  }
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::SMEM);
   if (e != cudaSuccess) return e;
   // x = row tile, so that the CTAs sharing one tile of W run together and W crosses HBM once
-  gemm_f16_tcgen05_kernel<BN><<<dim3((p.M + BM - 1) / BM, (p.N + BN - 1) / BN), GEMM_THREADS, Cfg<BN>::SMEM, s>>>(ma, mw, p);
+  gemm_tcgen05_kernel<BN, Q8><<<dim3((p.M + BM - 1) / BM, (p.N + BN - 1) / BN), Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, Cfg<BN>::SMEM, s>>>(ma, mw, p);
   return cudaGetLastError();
 }
 
 }  // namespace
+
+// SMs of the current device (the tile shape is chosen so that the grid still fills them).
+static size_t sm_count() {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+  return (size_t)n;
+}
 
 bool gemm_tcgen05_supported(uint32_t M, uint32_t N, uint32_t K) { return M >= 1 && K % BK == 0 && K >= BK && (N % 8) == 0; }
 
@@ -283,8 +360,16 @@ cudaError_t launch_gemm_f16_tcgen05(const GemmParams &p, cudaStream_t s) {
   if ((reinterpret_cast<uintptr_t>(p.a) | reinterpret_cast<uintptr_t>(p.w)) & 15) return cudaErrorMisalignedAddress;
   // 128 x 256 tiles halve the shared-memory reads per flop; use them once they still fill the GPU
   const size_t tiles256 = (size_t)((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
-  if (tiles256 >= 148) return launch_bn<256>(p, s);
-  return launch_bn<128>(p, s);
+  if (tiles256 >= sm_count()) return launch_bn<256, false>(p, s);
+  return launch_bn<128, false>(p, s);
+}
+
+cudaError_t launch_gemm_q8_tcgen05(const GemmParams &p, cudaStream_t s) {
+  if (!gemm_tcgen05_supported(p.M, p.N, p.K) || !p.w_codes || !p.w_scales) return cudaErrorInvalidValue;
+  if (reinterpret_cast<uintptr_t>(p.a) & 15) return cudaErrorMisalignedAddress;
+  const size_t tiles256 = (size_t)((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
+  if (tiles256 >= sm_count()) return launch_bn<256, true>(p, s);
+  return launch_bn<128, true>(p, s);
 }
 
 cudaError_t launch_swiglu_f32(const float *gate, const float *up, __half *out, size_t n, cudaStream_t s) {

@@ -56,6 +56,16 @@ cudaError_t launch_synth_q8(uint8_t *blocks34, uint64_t seed, uint64_t tensor, u
 cudaError_t launch_rms_norm(const __half *x, const float *w, __half *y, uint32_t rows,
                             uint32_t W, float eps, cudaStream_t s);
 cudaError_t launch_add(const __half *x, __half *y, uint64_t n, int op, cudaStream_t s);
+// x <- fp16(x op alpha), op 0 add, 1 sub, 2 mul, 3 div.
+cudaError_t launch_scalar_op(__half *x, uint64_t n, int op, float alpha, cudaStream_t s);
+// Copies a dense [C,H,W] input to out[c * ocs + h * ohs + w + offset] (element strides).
+cudaError_t launch_concat_copy(const __half *in, __half *out, uint32_t C, uint32_t H, uint32_t W, uint64_t ocs, uint64_t ohs, uint64_t offset,
+                               cudaStream_t s);
+// Row reduction over W: op 0 sum, 1 max, 2 min; the result is scaled by mean_scale.
+cudaError_t launch_reduce(const __half *in, __half *out, uint32_t rows, uint32_t W, int op, float mean_scale, cudaStream_t s);
+// out[c, y, :] = cache[c, (y + offset) % H, :] for y < len.
+cudaError_t launch_read_kvcache(const __half *cache, __half *out, uint32_t C, uint32_t H, uint32_t W, uint32_t offset, uint32_t len,
+                                cudaStream_t s);
 cudaError_t launch_embedding(const uint8_t *vocab, int vocab_is_q8, const uint32_t *ids,
                              __half *out, uint32_t T, uint32_t VH, uint32_t VW, uint32_t unk,
                              cudaStream_t s);
@@ -116,9 +126,17 @@ enum MegaKind { MK_EMBED = 0, MK_MATVEC = 1, MK_ATTN_PART = 2, MK_ATTN_COMBINE =
 // is a multiple of 16 bytes.
 struct alignas(16) MegaOp {
   uint32_t kind, epi, nmat, rot;
-  uint32_t N, K, tiles, groups;
-  const uint8_t *codes[3];
-  const uint8_t *scales[3];
+  uint32_t N, K;          // rows of one matrix, columns
+  uint32_t tiles, blocks; // 32-row tiles of the op's packed weight stream, Q8_0 blocks per row (K / 32)
+  // The op's weights, packed for the kernel (mega_pack): per 32-row tile and block one unit of
+  // MEGA_UNIT_CODES + MEGA_UNIT_SCALES bytes. Codes: the two 512-byte (16 rows x 32 columns) units of the
+  // library's tiled planes (common.cuh) that hold the tile's rows, as they are: MMA A-fragment order, biased
+  // by +128. Scales: [g 0..7][rows g, g + 8, 16 + g, 24 + g] fp16. Which matrix row a tile row is:
+  //   one matrix         tile t, row r = matrix row 32 t + r
+  //   nmat = 3 (K, Q, V) tile t = matrix t / tpm, rows 32 (t % tpm) + r, tpm = ceil(N / 32)
+  //   SwiGLU (gate, up)  tile t: rows 0..15 = gate rows 16 t + r, rows 16..31 = up rows 16 t + r - 16
+  const uint8_t *codes;
+  const uint8_t *scales;
   const float *norm_w;  // fused RMSNorm of the input, or null
   float eps;
   uint32_t track_argmax;  // lm head: keep a per-CTA (max, index) candidate
@@ -136,9 +154,9 @@ struct alignas(16) MegaOp {
   float *out_f32;
   __half *kcache, *vcache;  // MK_ATTN_PART
 };
-// One ring stage of the persistent kernel: up to MEGA_SG consecutive groups (4 Q8_0 blocks x
-// 16 rows each) of a CTA's weight stream, as at most two contiguous runs: the tail of one
-// (tile, matrix) and the head of the next.
+// One ring stage of the persistent kernel: up to MEGA_SU consecutive units (one Q8_0 block x
+// 32 rows each) of a CTA's weight stream, as at most two contiguous runs: the tail of one
+// tile and the head of the next.
 //
 // An entry with n0 == MEGA_KV_MARK stands for the K and V rows of an attention op instead:
 // codes0 / scales0 are the layer's K / V cache. How many ring stages it becomes depends on the
@@ -147,12 +165,17 @@ struct alignas(16) MegaOp {
 struct MegaStage {
   const uint8_t *codes0, *scales0;
   const uint8_t *codes1, *scales1;
-  uint32_t n0, n1;  // groups of the first and of the second run
-  uint32_t tm, kg;  // consumers' view: row block (local tile x matrix) and first group of run 0; run 1 starts row block tm + 1
+  uint32_t n0, n1;  // units of the first and of the second run
+  uint32_t tm, kg;  // consumers' view: local tile and first block of run 0; run 1 starts at block 0 of local tile tm + 1
 };
 constexpr uint32_t MEGA_KV_MARK = 0xffffffffu;
-constexpr uint32_t MEGA_SG = 15;  // groups per stage = consumer warps: one group per warp per stage
-constexpr uint32_t MEGA_STAGE_BYTES = MEGA_SG * (2048 + 128);
+constexpr uint32_t MEGA_UNIT_CODES = 1024, MEGA_UNIT_SCALES = 64;  // 32 rows x 32 codes, 32 fp16 scales
+#ifndef VKL_MEGA_UPW
+#define VKL_MEGA_UPW 2
+#endif
+constexpr uint32_t MEGA_UPW = VKL_MEGA_UPW;       // units per consumer warp and stage
+constexpr uint32_t MEGA_SU = 15 * MEGA_UPW;       // units per stage
+constexpr uint32_t MEGA_STAGE_BYTES = MEGA_SU * (MEGA_UNIT_CODES + MEGA_UNIT_SCALES);
 // Cache rows (head_dim fp16 values each) of one KV ring stage: whole rows, a multiple of 8.
 __host__ __device__ inline uint32_t mega_kv_rows_per_stage(uint32_t head_dim) { return (MEGA_STAGE_BYTES / (head_dim * 2u)) & ~7u; }
 // Splits per head at KV length L: as few as keep a split within `split_rows` cache rows. With one
@@ -170,27 +193,27 @@ __host__ __device__ inline void mega_kv_range(uint32_t L, uint32_t S, uint32_t s
   c0 = split * chunk < L ? split * chunk : L;
   c1 = c0 + chunk < L ? c0 + chunk : L;
 }
-// How a stage that starts at group `kg` of a (tile, matrix) of `groups` groups is cut: n0 groups
-// of this (tile, matrix), then n1 of the next one (if the op has one for this CTA). Host and
-// device walk the stream with the same rule.
+// How a stage that starts at block `kg` of a tile of `blocks` blocks is cut: n0 units of this
+// tile, then n1 of the next one (if the op has one for this CTA). Host and device walk the
+// stream with the same rule.
 struct MegaCut {
   uint32_t n0, n1;
 };
-__host__ __device__ inline MegaCut mega_stage_cut(uint32_t kg, uint32_t groups, bool has_next) {
+__host__ __device__ inline MegaCut mega_stage_cut(uint32_t kg, uint32_t blocks, bool has_next) {
   MegaCut c;
-  c.n0 = groups - kg < MEGA_SG ? groups - kg : MEGA_SG;
-  const uint32_t rem = MEGA_SG - c.n0;
-  c.n1 = has_next ? (rem < groups ? rem : groups) : 0u;
+  c.n0 = blocks - kg < MEGA_SU ? blocks - kg : MEGA_SU;
+  const uint32_t rem = MEGA_SU - c.n0;
+  c.n1 = has_next ? (rem < blocks ? rem : blocks) : 0u;
   return c;
 }
-__host__ __device__ inline void mega_stage_advance(const MegaCut &c, uint32_t groups, uint32_t &tm, uint32_t &kg) {
+__host__ __device__ inline void mega_stage_advance(const MegaCut &c, uint32_t blocks, uint32_t &tm, uint32_t &kg) {
   if (c.n1) {
     tm += 1;
     kg = c.n1;
   } else {
     kg += c.n0;
   }
-  if (kg >= groups) {
+  if (kg >= blocks) {
     kg = 0;
     tm += 1;
   }
@@ -212,14 +235,14 @@ struct MegaParams {
   uint32_t *x, *q, *k, *v, *ao;  // tagged words (see MegaOp)
   const float *freqc, *freqs;
   float *attn_scratch;      // heads*splits*(head_dim+4): per (head, split) the un-normalised P.V row, its max and its sum
-  uint32_t attn_merge;      // how a head's split partials are merged: 0 combine op, 1 last-arriving split, 2 tagged words, every split merges its share
+  uint32_t attn_merge;      // how a head's split partials are merged: 0 combine op, 1 last-arriving split
   uint32_t *attn_counters;  // [heads] arrivals of a head's splits (the last one merges them), or null: separate combine op
   float *arg_scratch;       // grid*2
   unsigned long long *bar;  // [0] arrivals, [1] completed launches
   uint32_t *error;          // 0, or the code of the wait that timed out
   uint32_t dim, heads, head_dim, maxlen, splits, vocab;
   uint32_t xs_bytes;
-  uint32_t xmax_groups;  // largest K of any op, in groups of 128 inputs: the input area holds that many fp16 values
+  uint32_t xmax_blocks;  // largest K of any op, in blocks of 32 inputs: the input area holds that many blocks of digits
   // Tensor parallelism: every rank's exchange buffer (peer pointers, own included).
   // Layout of one buffer, in 4-byte words: partial sums [2 parities][tp][dim] x {fp32 sum, sequence number}, then
   // at word tp_flag_off: flags[16] (all-reduce sequence per source rank), arg flags[16],
@@ -227,15 +250,20 @@ struct MegaParams {
   uint32_t tp_rank, tp_size, tp_flag_off;
   void *tp_peer[8];
   uint32_t nst;               // ring stages (as many as fit beside the input and reduction areas)
-  uint32_t red_slots;         // reduction slots: the largest (tiles of one CTA) x (matrices) of any op
+  uint32_t red_slots;         // reduction slots: the most tiles one CTA gets of any op
   uint32_t split_rows;        // cache rows one attention split should hold: a token at KV length L uses min(splits, ceil(L / split_rows)) splits per head (0: always `splits`)
   uint32_t barrier_pollers;   // warps whose lane 0 polls the grid barrier counter, staggered in time
   // Optional timeline of CTA 0: per op, nanoseconds of work and of barrier wait.
   unsigned long long *timing;
   uint32_t timing_mode;  // third column of the timeline: 0 = ring wait, 1 = op prologue
   uint32_t sm_mhz;       // SM clock for the timeline's cycle counts (measured by the host before a profiled launch)
+  uint32_t wait_limit;   // polls after which any wait of the kernel gives up and raises *error
 };
-size_t decode_mega_xs_bytes(uint32_t max_groups, uint32_t head_dim, uint32_t maxlen, uint32_t splits, uint32_t split_rows);
+size_t decode_mega_xs_bytes(uint32_t max_blocks, uint32_t head_dim, uint32_t maxlen, uint32_t splits, uint32_t split_rows);
+// Packs up to three Q8_0 matrices (tiled planes) that share an input into one op's weight stream
+// (layout and row rules at MegaOp). tiles = the stream's 32-row tiles.
+cudaError_t launch_mega_pack(const uint8_t *const planes[3], uint32_t nmat, int swiglu, uint32_t N, uint32_t K, uint32_t tiles,
+                             uint8_t *codes, uint8_t *scales, cudaStream_t s);
 size_t decode_mega_smem(size_t xs_bytes, uint32_t nst, uint32_t red_slots);
 int decode_mega_max_k();
 int decode_mega_max_stages();
@@ -245,7 +273,9 @@ cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s);
 // ---- dense FP16 GEMM on tcgen05 tensor cores: C[M,N] = A[M,K] . W[N,K]^T (gemm_tcgen05.cu) ----
 struct GemmParams {
   const __half *a;         // [M,K] row-major
-  const __half *w;         // [N,K] row-major (a transposed-weight matrix of the reference)
+  const __half *w;         // [N,K] row-major (a transposed-weight matrix of the reference); FP16 weights
+  const uint8_t *w_codes;  // Q8_0 weights [N,K] as tiled planes (common.cuh): codes ...
+  const uint8_t *w_scales; // ... and scales
   __half *c;               // [M,N] fp16 output, or nullptr when c_f32 is set
   float *c_f32;            // raw fp32 output (for the fused SwiGLU step)
   const __half *residual;  // optional [M,N]: c = fp16(fp16(acc) + residual)
@@ -257,6 +287,13 @@ struct GemmParams {
 constexpr uint32_t GEMM_MIN_ROWS = 32;  // below this the weight-streaming mat-vec kernel is used
 bool gemm_tcgen05_supported(uint32_t M, uint32_t N, uint32_t K);
 cudaError_t launch_gemm_f16_tcgen05(const GemmParams &p, cudaStream_t s);
+// The same GEMM with Q8_0 weights (w_codes / w_scales), dequantised into the shared-memory tiles.
+constexpr uint32_t GEMM_Q8_MIN_ROWS = 64;  // below this the rows-at-a-time kernel keeps the exact fp32 scaling
+cudaError_t launch_gemm_q8_tcgen05(const GemmParams &p, cudaStream_t s);
+// Rows from which a weight of this kind goes to the tensor-core GEMM.
+inline uint32_t gemm_min_rows(bool q8) { return q8 ? GEMM_Q8_MIN_ROWS : GEMM_MIN_ROWS; }
+// Dispatch on the weight kind: w set = FP16 weights, else w_codes / w_scales = Q8_0.
+inline cudaError_t launch_gemm_tcgen05(const GemmParams &p, cudaStream_t s) { return p.w ? launch_gemm_f16_tcgen05(p, s) : launch_gemm_q8_tcgen05(p, s); }
 cudaError_t launch_swiglu_f32(const float *gate, const float *up, __half *out, size_t n, cudaStream_t s);
 
 }  // namespace vkl

@@ -79,9 +79,12 @@ struct vkl_model {
   bool mega_ready = false, mega_tried = false;
   int mega_grid = 0;
   vkl_tensor *mega_ops = nullptr, *mega_sync = nullptr, *mega_arg = nullptr, *mega_attn = nullptr, *mega_stages = nullptr, *mega_counts = nullptr, *mega_ll = nullptr;
+  std::vector<vkl_tensor *> mega_packed;  // the ops' weight streams in the persistent kernel's layout
   MegaParams mp;
   uint32_t mega_launches_per_token = 1;
   uint32_t sm_mhz = 0;  // measured SM clock, for the profiled launches' cycle counts
+  uint32_t wait_limit = 0;  // polls a wait of the decode kernel may spin (0: the default of build_mega)
+  bool tp_failed = false;   // a wait on another rank ran out: the ranks' sequence counters are out of step until they reconnect
   cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
   uint32_t *pos_dev() { return (uint32_t *)state->data(); }
   uint32_t *step_dev() { return (uint32_t *)state->data() + 1; }
@@ -91,6 +94,7 @@ struct vkl_model {
     if (tp_buf) cudaFree(tp_buf);
     for (auto &l : L)
       for (vkl_tensor *p : {l.attn_norm, l.ffn_norm, l.wq, l.wk, l.wv, l.wo, l.gate, l.up, l.down, l.kcache, l.vcache}) vkl_tensor_release(p);
+    for (vkl_tensor *p : mega_packed) vkl_tensor_release(p);
     for (vkl_tensor *p : {tok_embd, output_norm, output, fc, fs, x, xn, q, k, v, ao, t, gu32, logits16, logits32, toks, state, out_ids, forced, argpart, attn_scratch, attn_counters, mega_ops, mega_sync, mega_arg, mega_attn, mega_stages, mega_counts, mega_ll})
       vkl_tensor_release(p);
     if (ev0) cudaEventDestroy(ev0);
@@ -119,7 +123,7 @@ int ensure_rows(vkl_model *m, uint32_t T) {
       vkl_tensor_release(*t);
       *t = nullptr;
     }
-    m->mega_ready = m->mega_tried = false;
+    m->mega_ready = m->mega_tried = false;  // the packed weight streams (mega_packed) do not depend on the row count: kept
   }
   const size_t D = m->cfg.dim;
   VKL_OKAY(ensure_tensor(m->dev, &m->x, 1, T, D, VKL_FP16));
@@ -129,7 +133,7 @@ int ensure_rows(vkl_model *m, uint32_t T) {
   VKL_OKAY(ensure_tensor(m->dev, &m->v, 1, T, m->dim_l, VKL_FP16));
   VKL_OKAY(ensure_tensor(m->dev, &m->ao, 1, T, m->dim_l, VKL_FP16));
   VKL_OKAY(ensure_tensor(m->dev, &m->t, 1, T, m->ffn_l, VKL_FP16));
-  if (!q8(m) && T >= GEMM_MIN_ROWS) VKL_OKAY(ensure_tensor(m->dev, &m->gu32, 2, T, m->ffn_l, VKL_FP32));
+  if (T >= gemm_min_rows(q8(m))) VKL_OKAY(ensure_tensor(m->dev, &m->gu32, 2, T, m->ffn_l, VKL_FP32));
   VKL_OKAY(ensure_tensor(m->dev, &m->toks, 1, 1, T, VKL_UINT32));
   const size_t sc = attention_scratch_bytes(1, m->heads_l, m->head_dim, m->splits);
   VKL_OKAY(ensure_tensor(m->dev, &m->attn_scratch, 1, 1, sc / 4, VKL_FP32));
@@ -155,11 +159,16 @@ MvParams mv(const vkl_model *m, const vkl_tensor *w, const __half *x, __half *ou
   return p;
 }
 
-// Many-row projection with FP16 weights on the tcgen05 tensor cores.
+// Many-row projection on the tcgen05 tensor cores (Q8_0 weights are dequantised into the shared-memory tiles).
 GemmParams gemm(vkl_model *m, const vkl_tensor *w, const __half *a, __half *out, uint32_t M) {
   GemmParams g = {};
   g.a = a;
-  g.w = (const __half *)w->data();
+  if (q8(m)) {
+    g.w_codes = w->codes();
+    g.w_scales = w->scales();
+  } else {
+    g.w = (const __half *)w->data();
+  }
   g.c = out;
   g.M = M;
   g.N = (uint32_t)w->h;
@@ -171,7 +180,7 @@ GemmParams gemm(vkl_model *m, const vkl_tensor *w, const __half *a, __half *out,
 }
 bool use_gemm(const vkl_model *m, uint32_t rows) {
   static const bool off = [] { const char *e = getenv("VKLLAMA_PREFILL_GEMM"); return e && !strcmp(e, "0"); }();
-  return !off && !q8(m) && rows >= GEMM_MIN_ROWS && gemm_tcgen05_supported(rows, m->dim_l, m->cfg.dim) &&
+  return !off && rows >= gemm_min_rows(q8(m)) && gemm_tcgen05_supported(rows, m->dim_l, m->cfg.dim) &&
          gemm_tcgen05_supported(rows, m->cfg.dim, m->dim_l) && gemm_tcgen05_supported(rows, m->ffn_l, m->cfg.dim) &&
          gemm_tcgen05_supported(rows, m->cfg.dim, m->ffn_l);
 }
@@ -224,9 +233,9 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
       VKL_LAUNCH(1, launch_matvec(p, EPI_PLAIN, true, s));
     } else if (use_gemm(m, T)) {
       VKL_LAUNCH(1, launch_rms_norm(x, (const float *)y.attn_norm->data(), xn, T, D, m->cfg.eps, s));
-      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(gemm(m, y.wk, xn, kb, T), s));
-      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(gemm(m, y.wq, xn, qb, T), s));
-      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(gemm(m, y.wv, xn, vb, T), s));
+      VKL_LAUNCH(1, launch_gemm_tcgen05(gemm(m, y.wk, xn, kb, T), s));
+      VKL_LAUNCH(1, launch_gemm_tcgen05(gemm(m, y.wq, xn, qb, T), s));
+      VKL_LAUNCH(1, launch_gemm_tcgen05(gemm(m, y.wv, xn, vb, T), s));
     } else {
       VKL_LAUNCH(1, launch_rms_norm(x, (const float *)y.attn_norm->data(), xn, T, D, m->cfg.eps, s));
       VKL_LAUNCH((T + 63) / 64, launch_matvec(p, EPI_PLAIN, false, s));
@@ -253,7 +262,7 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
     if (use_gemm(m, rows)) {
       GemmParams g = gemm(m, y.wo, ao, xr, rows);
       g.residual = xr;
-      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, s));
+      VKL_LAUNCH(1, launch_gemm_tcgen05(g, s));
     } else {
       MvParams o = mv(m, y.wo, ao, xr, rows);
       o.residual = xr;
@@ -275,10 +284,15 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
       float *g32 = (float *)m->gu32->data(), *u32 = g32 + (size_t)rows * m->ffn_l;
       GemmParams g = gemm(m, y.gate, xn, nullptr, rows);
       g.c_f32 = g32;
-      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, s));
-      g.w = (const __half *)y.up->data();
+      VKL_LAUNCH(1, launch_gemm_tcgen05(g, s));
+      if (q8(m)) {
+        g.w_codes = y.up->codes();
+        g.w_scales = y.up->scales();
+      } else {
+        g.w = (const __half *)y.up->data();
+      }
       g.c_f32 = u32;
-      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, s));
+      VKL_LAUNCH(1, launch_gemm_tcgen05(g, s));
       VKL_LAUNCH(1, launch_swiglu_f32(g32, u32, tb, (size_t)rows * m->ffn_l, s));
     } else {
       VKL_LAUNCH(1, launch_rms_norm(xr, (const float *)y.ffn_norm->data(), xn, rows, D, m->cfg.eps, s));
@@ -288,7 +302,7 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
     if (use_gemm(m, rows)) {
       GemmParams g = gemm(m, y.down, tb, xr, rows);
       g.residual = xr;
-      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, s));
+      VKL_LAUNCH(1, launch_gemm_tcgen05(g, s));
     } else {
       MvParams d = mv(m, y.down, tb, xr, rows);
       d.residual = xr;
@@ -344,15 +358,16 @@ int build_mega(vkl_model *m) {
     const uint32_t cap = se ? std::max(1u, (uint32_t)atoi(se)) : (tp > 1 ? 32u : 8u);
     if (splits > cap) splits = cap;
   }
-  const uint32_t max_groups = (std::max(c.dim, m->ffn_l) / 32 + 3) / 4;
+  const uint32_t max_blocks = std::max({c.dim, m->dim_l, m->ffn_l}) / 32;
   // Rows per attention split (VKLLAMA_SPLIT_ROWS; 0 = always all splits). Short contexts run one CTA
   // per head and skip the merge between CTAs; the default keeps a split's K rows within three ring stages.
   const char *sr_env = getenv("VKLLAMA_SPLIT_ROWS");
   const uint32_t split_rows = sr_env ? (uint32_t)atoi(sr_env) : 384u;
-  const size_t xs_bytes = decode_mega_xs_bytes(max_groups, m->head_dim, c.maxlen, splits, split_rows);
-  // every op's (tiles per CTA) x (matrices) needs a reduction slot
-  auto slots = [&](uint32_t rows, uint32_t nmat) { return (((rows + 15) / 16 + G - 1) / G) * nmat; };
-  const uint32_t red_slots = std::max({slots(m->dim_l, 3), slots(c.dim, 1), slots(m->ffn_l, 2), slots(m->vocab_l, 1)});
+  const size_t xs_bytes = decode_mega_xs_bytes(max_blocks, m->head_dim, c.maxlen, splits, split_rows);
+  // every tile a CTA gets of an op needs a reduction slot: QKV = 3 matrices of 32-row tiles, gate/up = one
+  // tile per 16 outputs, the others one tile per 32 rows
+  auto slots = [&](uint32_t tiles) { return (tiles + G - 1) / G; };
+  const uint32_t red_slots = std::max({slots(3 * ((m->dim_l + 31) / 32)), slots((c.dim + 31) / 32), slots((m->ffn_l + 15) / 16), slots((m->vocab_l + 31) / 32)});
   uint32_t nst = (uint32_t)decode_mega_max_stages();  // as many ring stages as fit
   while (nst >= 2 && decode_mega_smem(xs_bytes, nst, red_slots) > (size_t)m->dev->prop.sharedMemPerBlockOptin) --nst;
   if (nst < 2) return VKL_OK;
@@ -374,6 +389,8 @@ int build_mega(vkl_model *m) {
   }
   uint32_t *x = (uint32_t *)m->mega_ll->data(), *kb = x + c.dim, *qb = kb + m->dim_l, *vb = qb + m->dim_l, *ao = vb + m->dim_l, *tb = ao + m->dim_l;
   uint32_t x_writer = 0;  // index of the op that last wrote the residual stream x
+  int pack_status = VKL_OK;
+  size_t pack_index = 0;
   auto matvec = [&](std::initializer_list<const vkl_tensor *> ws, const float *norm, float eps, const uint32_t *in, uint32_t src_op,
                     std::initializer_list<uint32_t *> outs, int epi) {
     MegaOp o = {};
@@ -382,16 +399,37 @@ int build_mega(vkl_model *m) {
     const vkl_tensor *w0 = *ws.begin();
     o.N = (uint32_t)w0->h;
     o.K = (uint32_t)w0->w;
-    o.tiles = (o.N + 15) / 16;
-    o.groups = ((o.K + 31) / 32 + 3) / 4;
+    o.blocks = o.K / 32;
     o.nmat = (uint32_t)ws.size();
-    int i = 0;
-    for (const vkl_tensor *w : ws) {
-      o.codes[i] = w->codes();
-      o.scales[i] = w->scales();
-      ++i;
+    const bool swiglu = epi == EPI_SWIGLU;
+    o.tiles = swiglu ? (o.N + 15) / 16 : o.nmat * ((o.N + 31) / 32);
+    // the op's weights in the kernel's stream layout (a second copy: the tiled planes stay for the
+    // multi-token passes and the per-op API)
+    {
+      const uint8_t *planes[3] = {nullptr, nullptr, nullptr};
+      int j = 0;
+      for (const vkl_tensor *w : ws) planes[j++] = w->data();
+      const size_t units = (size_t)o.tiles * o.blocks;
+      const bool packed = pack_index < m->mega_packed.size();  // an earlier build of the tables packed it already
+      vkl_tensor *pk = packed ? m->mega_packed[pack_index] : nullptr;
+      if (!packed) {
+        if (int st = tensor_new(m->dev, 1, 1, units * (MEGA_UNIT_CODES + MEGA_UNIT_SCALES) / 4, VKL_UINT32, &pk)) {
+          pack_status = st;
+          return 0u;
+        }
+        m->mega_packed.push_back(pk);
+      }
+      ++pack_index;
+      uint8_t *codes = pk->data(), *scales = codes + units * MEGA_UNIT_CODES;
+      if (!packed) {
+        cudaError_t pe = launch_mega_pack(planes, o.nmat, swiglu ? 1 : 0, o.N, o.K, o.tiles, codes, scales, m->stream);
+        count_launches(1);
+        if (pe != cudaSuccess && pack_status == VKL_OK) pack_status = fail(VKL_INTERNAL, "decode kernel: packing the weights failed: %s", cudaGetErrorString(pe));
+      }
+      o.codes = codes;
+      o.scales = scales;
     }
-    i = 0;
+    int i = 0;
     for (uint32_t *p : outs) o.out_ll[i++] = p;
     o.norm_w = norm;
     o.eps = eps;
@@ -455,6 +493,7 @@ int build_mega(vkl_model *m) {
   am.kind = MK_ARGMAX;
   ops.push_back(am);
 
+  if (pack_status != VKL_OK) return pack_status;
   // Stage tables: every CTA's ring stages for one token, in the order its consumers walk them
   // (the same cutting rule as the kernel: mega_stage_cut / mega_stage_advance).
   std::vector<std::vector<MegaStage>> per_cta(G);
@@ -480,15 +519,14 @@ int build_mega(vkl_model *m) {
       const size_t before = per_cta[cta].size();
       const uint32_t tile0 = ((uint32_t)cta + G - (o.rot % G)) % G;
       const uint32_t tl = tile0 < o.tiles ? (o.tiles - tile0 + G - 1) / G : 0u;
-      const uint32_t ntm = tl * o.nmat;
-      auto run = [&](uint32_t tm, uint32_t kg, const uint8_t *&codes, const uint8_t *&scales) {
-        const size_t g0 = (size_t)(tile0 + (tm / o.nmat) * G) * o.groups + kg;
-        codes = o.codes[tm % o.nmat] + g0 * 2048;
-        scales = o.scales[tm % o.nmat] + g0 * 128;
+      auto run = [&](uint32_t lt, uint32_t kg, const uint8_t *&codes, const uint8_t *&scales) {
+        const size_t unit = (size_t)(tile0 + lt * G) * o.blocks + kg;
+        codes = o.codes + unit * MEGA_UNIT_CODES;
+        scales = o.scales + unit * MEGA_UNIT_SCALES;
       };
       uint32_t tm = 0, kg = 0;
-      while (tm < ntm) {
-        const MegaCut cut = mega_stage_cut(kg, o.groups, tm + 1 < ntm);
+      while (tm < tl) {
+        const MegaCut cut = mega_stage_cut(kg, o.blocks, tm + 1 < tl);
         MegaStage e = {};
         e.n0 = cut.n0;
         e.n1 = cut.n1;
@@ -497,7 +535,7 @@ int build_mega(vkl_model *m) {
         run(tm, kg, e.codes0, e.scales0);
         if (cut.n1) run(tm + 1, 0, e.codes1, e.scales1);
         per_cta[cta].push_back(e);
-        mega_stage_advance(cut, o.groups, tm, kg);
+        mega_stage_advance(cut, o.blocks, tm, kg);
       }
       op_stages.push_back((uint32_t)(per_cta[cta].size() - before));
     }
@@ -551,8 +589,7 @@ int build_mega(vkl_model *m) {
   p.attn_scratch = (float *)m->mega_attn->data();
   {
     const char *cenv = getenv("VKLLAMA_DECODE_COMBINE");
-    p.attn_merge = cenv && !strcmp(cenv, "separate") ? 0u : cenv && !strcmp(cenv, "tagged") ? 2u : 1u;  // "tagged" measured equal to "last"
-    if (splits > 8) p.attn_merge = 1u;
+    p.attn_merge = cenv && !strcmp(cenv, "separate") ? 0u : 1u;
     uint32_t *counters = (uint32_t *)(p.attn_scratch + 2 * (size_t)m->heads_l * splits * (m->head_dim + 4));
     p.attn_counters = p.attn_merge == 1 ? counters : nullptr;
     VKL_CUDA(cudaMemsetAsync(m->mega_attn->data(), 0, (2 * (size_t)m->heads_l * splits * (m->head_dim + 4) + m->heads_l) * 4, m->stream));
@@ -562,7 +599,7 @@ int build_mega(vkl_model *m) {
   p.error = (uint32_t *)m->mega_sync->data() + 4;
   p.dim = c.dim; p.heads = m->heads_l; p.head_dim = m->head_dim; p.maxlen = c.maxlen; p.splits = splits; p.vocab = m->vocab_l;
   p.xs_bytes = (uint32_t)xs_bytes;
-  p.xmax_groups = max_groups;
+  p.xmax_blocks = max_blocks;
   {
     p.nst = nst;
     p.red_slots = red_slots;
@@ -572,6 +609,9 @@ int build_mega(vkl_model *m) {
     p.barrier_pollers = bp ? std::min(std::max((uint32_t)atoi(bp), 1u), 8u) : 1u;
     p.split_rows = split_rows;
   }
+  // One bound for every wait of the kernel (about half a microsecond per poll: 2^21 polls are a second or
+  // two; tensor-parallel ranks get eight times that, for a rank that starts its launch late).
+  p.wait_limit = m->wait_limit ? m->wait_limit : (tp > 1 ? (1u << 24) : (1u << 21));
   m->mega_grid = G;
   m->mega_ready = true;
   return VKL_OK;
@@ -604,6 +644,10 @@ int check_mega(vkl_model *m) {
     // the aborted launch did not advance the ops' sequence base: words it tagged must not look current
     bump_sequence_kernel<<<1, 1, 0, m->stream>>>((uint32_t *)m->state->data() + 7, m->mp.nops);
     cudaStreamSynchronize(m->stream);
+    // Under tensor parallelism the aborted launch leaves the ranks out of step (all-reduce and arg-max
+    // sequence numbers, words already pushed under the number a retry would expect): the model refuses
+    // further steps until every rank has called vkl_model_tp_connect again, between two host barriers.
+    if (m->cfg.tp_size > 1) m->tp_failed = true;
     return fail(VKL_INTERNAL, "decode kernel: a bounded wait ran out (code %u: 1 weight stage, 2 ring slot, 3 grid barrier, 4 all-reduce, 5 arg-max exchange, 6 tagged input)", err);
   }
   return VKL_OK;
@@ -626,6 +670,8 @@ int build_decode_graph(vkl_model *m);
 
 // Enqueue one decode step: the persistent kernel when available, else the graph.
 int decode_step(vkl_model *m) {
+  if (m->tp_failed)
+    return fail(VKL_FAILED_PRECONDITION, "model: a wait on another tensor-parallel rank ran out earlier; reconnect the ranks (vkl_model_tp_connect on every rank, between host barriers) before the next step");
   if (m->mega_ready) {
     VKL_LAUNCH(1, launch_decode_mega(m->mp, m->mega_grid, m->stream));
     return VKL_OK;
@@ -795,9 +841,23 @@ int vkl_model_destroy(vkl_model *m) {
   return VKL_OK;
 }
 
+// New weights: the decode kernel's packed copies and tables, if already built, are stale.
+static void drop_packed(vkl_model *m) {
+  if (m->mega_packed.empty() && !m->mega_tried) return;
+  cudaStreamSynchronize(m->stream);
+  for (vkl_tensor *t : m->mega_packed) vkl_tensor_release(t);
+  m->mega_packed.clear();
+  for (vkl_tensor **t : {&m->mega_ops, &m->mega_sync, &m->mega_arg, &m->mega_attn, &m->mega_stages, &m->mega_counts, &m->mega_ll}) {
+    vkl_tensor_release(*t);
+    *t = nullptr;
+  }
+  m->mega_ready = m->mega_tried = false;
+}
+
 int vkl_model_set_weight(vkl_model *m, const char *name, int dtype, const void *data, size_t bytes) {
   if (!m || !name || !data) return fail(VKL_INVALID_ARGUMENT, "model_set_weight: null argument");
   VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  drop_packed(m);
   Slot s;
   VKL_OKAY(find_slot(m, name, &s));
   if (s.norm) {
@@ -844,6 +904,7 @@ int vkl_model_set_weight(vkl_model *m, const char *name, int dtype, const void *
 int vkl_model_synth_weights(vkl_model *m, uint64_t seed, float wstd, float nstd) {
   if (!m) return fail(VKL_INVALID_ARGUMENT, "model_synth_weights: null model");
   VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  drop_packed(m);
   std::vector<std::string> names = {"token_embd.weight", "output_norm.weight", "output.weight"};
   for (uint32_t l = 0; l < m->cfg.layers; ++l)
     for (const char *k : kLayerNames) names.push_back("blk." + std::to_string(l) + "." + k + ".weight");
@@ -1205,6 +1266,23 @@ int vkl_model_tp_connect(vkl_model *m, void *const *peer_ptrs, int n) {
     m->tp_peer[i] = peer_ptrs[i];
   }
   m->tp_connected = true;
+  // (Re)connection: every rank calls this while no rank has a kernel in flight (host barrier before and
+  // after), so the exchange buffer and the sequence counters restart from zero on all ranks together.
+  VKL_CUDA(cudaSetDevice(m->dev->ordinal));
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  VKL_CUDA(cudaMemsetAsync(m->tp_buf, 0, m->tp_bytes, m->stream));
+  VKL_CUDA(cudaMemsetAsync((uint32_t *)m->state->data() + 3, 0, 8, m->stream));  // all-reduces done, arg-max exchanges done
+  VKL_CUDA(cudaStreamSynchronize(m->stream));
+  m->tp_failed = false;
+  if (m->mega_ready)
+    for (int i = 0; i < 8; ++i) m->mp.tp_peer[i] = m->tp_peer[i];
+  return VKL_OK;
+}
+int vkl_model_set_wait_limit(vkl_model *m, uint32_t polls) {
+  if (!m) return fail(VKL_INVALID_ARGUMENT, "model_set_wait_limit: null model");
+  if (polls && polls < 256) return fail(VKL_INVALID_ARGUMENT, "model_set_wait_limit: at least 256 polls (0 restores the default)");
+  m->wait_limit = polls;
+  if (m->mega_ready) m->mp.wait_limit = polls ? polls : (m->cfg.tp_size > 1 ? (1u << 24) : (1u << 21));
   return VKL_OK;
 }
 int vkl_ipc_export(void *device_ptr, unsigned char handle[64]) {

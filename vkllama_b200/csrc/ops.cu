@@ -5,6 +5,7 @@
 // dispatches.
 #include <math.h>
 
+#include <algorithm>
 #include <cmath>
 
 #include "runtime.h"
@@ -71,8 +72,6 @@ struct MatMulOp : vkl_op {
       return fail(VKL_INVALID_ARGUMENT, "matmul operator defined as %d b_dtype but dtype of weight tensor is %d", b_dtype, weight->dtype);
     if (broadcast_type < 0 || broadcast_type > 2)
       return fail(VKL_INVALID_ARGUMENT, "broadcast_type %d is unsupported.", broadcast_type);
-    if (broadcast_type != 0)
-      return fail(VKL_UNIMPLEMENTED, "matmul broadcast_type %d has no caller on the Llama-2 path and is not built", broadcast_type);
     const bool ok = (a_dtype == VKL_FP16 && b_dtype == VKL_FP16) || (a_dtype == VKL_FP16 && b_dtype == VKL_Q8_0 && transpose_b);
     if (!ok) return fail(VKL_INVALID_ARGUMENT, "%d a_dtype and %d b_dtype is unsupported", a_dtype, b_dtype);
     return base_init();
@@ -81,9 +80,23 @@ struct MatMulOp : vkl_op {
   int run_weight(vkl_tensor *a, vkl_tensor **o) {
     if (!weight || weight->size() == 0 || !a || a->dtype != a_dtype)
       return fail(VKL_INVALID_ARGUMENT, "matmul op defined with %d a dtype but %d given.", a_dtype, a ? a->dtype : -1);
-    if (weight->c != a->c)
+    // src/ops/mat_mul.cpp:117-124, 246-254: 0 = operands pair up channel by channel, 1 = one B for every channel of A,
+    // 2 = one A for every channel of B
+    if ((broadcast_type == 0 && weight->c != a->c) || (broadcast_type == 1 && weight->c != 1) || (broadcast_type == 2 && a->c != 1))
       return fail(VKL_INVALID_ARGUMENT, "matmul op defined with broadcast_type = %d but weight channels = %zu != a.channels = %zu", broadcast_type, weight->c, a->c);
     VKL_OKAY(need_dense(a, "matmul"));
+    if (broadcast_type != 0 && (weight->c != 1 || a->c != 1)) {
+      if (b_dtype != VKL_FP16) return fail(VKL_UNIMPLEMENTED, "matmul: batched Q8_0 weights are not supported");
+      const size_t Kb = transpose_b ? weight->w : weight->h, Nb = transpose_b ? weight->h : weight->w, Cb = std::max(a->c, weight->c);
+      if (a->w != Kb) return fail(VKL_INVALID_ARGUMENT, "matmul: a.width = %zu but the weight expects %zu", a->w, Kb);
+      VKL_OKAY(enter("matmul"));
+      VKL_OKAY(ensure_tensor(dev, &out, Cb, a->h, Nb, VKL_FP16));
+      VKL_LAUNCH(1, launch_bmm_f16((const __half *)a->data(), (const __half *)weight->data(), (__half *)out->data(), (uint32_t)Cb, (uint32_t)a->h,
+                                   (uint32_t)Nb, (uint32_t)Kb, a->c == 1 ? 0 : a->cs / 2, a->hs / 2, weight->c == 1 ? 0 : weight->cs / 2,
+                                   weight->hs / 2, out->cs / 2, out->hs / 2, transpose_b, scale, bias, act, cmd->stream));
+      *o = out;
+      return leave();
+    }
     const size_t K = transpose_b ? weight->w : weight->h, N = transpose_b ? weight->h : weight->w;
     if (a->w != K) return fail(VKL_INVALID_ARGUMENT, "matmul: a.width = %zu but the weight expects %zu", a->w, K);
     VKL_OKAY(enter("matmul"));
@@ -99,14 +112,20 @@ struct MatMulOp : vkl_op {
       p.x_ld = (uint32_t)K; p.out_ld = (uint32_t)N;
       p.scale = scale; p.bias = bias; p.act = act;
       p.fp16_weights = b_dtype == VKL_FP16;
-      if (p.fp16_weights && a->h >= GEMM_MIN_ROWS && gemm_tcgen05_supported((uint32_t)a->h, (uint32_t)N, (uint32_t)K)) {
-        // many rows: one pass over the weights on the tcgen05 tensor cores
+      if (a->h >= gemm_min_rows(!p.fp16_weights) && gemm_tcgen05_supported((uint32_t)a->h, (uint32_t)N, (uint32_t)K)) {
+        // many rows: one pass over the weights on the tcgen05 tensor cores (Q8_0 dequantised on the way in)
         GemmParams g = {};
-        g.a = (const __half *)a->data(); g.w = (const __half *)weight->data(); g.c = (__half *)out->data();
+        g.a = (const __half *)a->data(); g.c = (__half *)out->data();
+        if (p.fp16_weights) {
+          g.w = (const __half *)weight->data();
+        } else {
+          g.w_codes = weight->codes();
+          g.w_scales = weight->scales();
+        }
         g.M = (uint32_t)a->h; g.N = (uint32_t)N; g.K = (uint32_t)K;
         g.scale = scale; g.bias = bias; g.act = act;
         VKL_OKAY(command_error_word(cmd, &g.error));
-        VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, cmd->stream));
+        VKL_LAUNCH(1, launch_gemm_tcgen05(g, cmd->stream));
       } else if (p.fp16_weights && (K & 7)) {
         VKL_LAUNCH(1, launch_bmm_f16((const __half *)a->data(), (const __half *)weight->data(), (__half *)out->data(), 1,
                                      (uint32_t)a->h, (uint32_t)N, (uint32_t)K, 0, K, 0, K, 0, N, 1, scale, bias, act, cmd->stream));
@@ -127,16 +146,17 @@ struct MatMulOp : vkl_op {
     if (!a || !b || b->size() == 0 || a->dtype != a_dtype || b->dtype != b_dtype)
       return fail(VKL_INVALID_ARGUMENT, "matmul op defined with %d a_dtype and %d b_dtype but inputs a.dtype() = %d, b.dtype() = %d", a_dtype,
                   b_dtype, a ? a->dtype : -1, b ? b->dtype : -1);
-    if (b->c != a->c)
+    if ((broadcast_type == 0 && b->c != a->c) || (broadcast_type == 1 && b->c != 1) || (broadcast_type == 2 && a->c != 1))
       return fail(VKL_INVALID_ARGUMENT, "matmul defined with %d broadcast_type but a.channels() = %zu, b.channels() = %zu", broadcast_type, a->c, b->c);
     if (b_dtype != VKL_FP16) return fail(VKL_UNIMPLEMENTED, "matmul: the two-operand form takes FP16 operands");
-    const size_t K = a->w, N = transpose_b ? b->h : b->w;
+    const size_t K = a->w, N = transpose_b ? b->h : b->w, C = std::max(a->c, b->c);
     if ((transpose_b ? b->w : b->h) != K) return fail(VKL_INVALID_ARGUMENT, "matmul: inner extents differ (%zu vs %zu)", K, transpose_b ? b->w : b->h);
     VKL_OKAY(enter("matmul"));
-    VKL_OKAY(ensure_tensor(dev, &out, a->c, a->h, N, VKL_FP16));
-    VKL_LAUNCH(1, launch_bmm_f16((const __half *)a->data(), (const __half *)b->data(), (__half *)out->data(), (uint32_t)a->c, (uint32_t)a->h,
-                                 (uint32_t)N, (uint32_t)K, a->cs / 2, a->hs / 2, b->cs / 2, b->hs / 2, out->cs / 2, out->hs / 2, transpose_b,
-                                 scale, bias, act, cmd->stream));
+    VKL_OKAY(ensure_tensor(dev, &out, C, a->h, N, VKL_FP16));
+    // a broadcast operand (src/shaders/matmul_broadcast1_fp16_v2.comp, matmul_broadcast2_fp16_v2.comp) is a channel stride of 0
+    VKL_LAUNCH(1, launch_bmm_f16((const __half *)a->data(), (const __half *)b->data(), (__half *)out->data(), (uint32_t)C, (uint32_t)a->h,
+                                 (uint32_t)N, (uint32_t)K, broadcast_type == 2 ? 0 : a->cs / 2, a->hs / 2, broadcast_type == 1 ? 0 : b->cs / 2,
+                                 b->hs / 2, out->cs / 2, out->hs / 2, transpose_b, scale, bias, act, cmd->stream));
     *o = out;
     return leave();
   }
@@ -179,26 +199,34 @@ struct FeedForwardOp : vkl_op {
     VKL_OKAY(ensure_tensor(dev, &t0, x->c, x->h, w1->h, VKL_FP16));
     VKL_OKAY(ensure_tensor(dev, &out, x->c, x->h, w2->h, VKL_FP16));
     const bool q8 = dtype == VKL_Q8_0;
-    if (!q8 && x->h >= GEMM_MIN_ROWS && gemm_tcgen05_supported((uint32_t)x->h, (uint32_t)w1->h, (uint32_t)w1->w) &&
+    if (x->h >= gemm_min_rows(q8) && gemm_tcgen05_supported((uint32_t)x->h, (uint32_t)w1->h, (uint32_t)w1->w) &&
         gemm_tcgen05_supported((uint32_t)x->h, (uint32_t)w2->h, (uint32_t)w2->w)) {
       // many rows: gate and up as tensor-core GEMMs with raw fp32 results, SwiGLU on those
       // (the rounding points of ffn_up_and_gate_fp16.comp), then the down GEMM
       VKL_OKAY(ensure_tensor(dev, &gu32, 2, x->h, w1->h, VKL_FP32));
+      auto weight_of = [q8](GemmParams &gp, const vkl_tensor *w) {
+        gp.w = q8 ? nullptr : (const __half *)w->data();
+        gp.w_codes = q8 ? w->codes() : nullptr;
+        gp.w_scales = q8 ? w->scales() : nullptr;
+      };
       GemmParams g = {};
-      g.a = (const __half *)x->data(); g.w = (const __half *)w1->data(); g.c_f32 = (float *)gu32->data();
+      g.a = (const __half *)x->data(); g.c_f32 = (float *)gu32->data();
+      weight_of(g, w1);
       g.M = (uint32_t)x->h; g.N = (uint32_t)w1->h; g.K = (uint32_t)w1->w;
       g.scale = 1.f;
       VKL_OKAY(command_error_word(cmd, &g.error));
-      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, cmd->stream));
-      g.w = (const __half *)w3->data(); g.c_f32 += (size_t)x->h * w1->h;
-      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(g, cmd->stream));
+      VKL_LAUNCH(1, launch_gemm_tcgen05(g, cmd->stream));
+      weight_of(g, w3);
+      g.c_f32 += (size_t)x->h * w1->h;
+      VKL_LAUNCH(1, launch_gemm_tcgen05(g, cmd->stream));
       VKL_LAUNCH(1, launch_swiglu_f32((const float *)gu32->data(), (const float *)gu32->data() + (size_t)x->h * w1->h, (__half *)t0->data(),
                                       (size_t)x->h * w1->h, cmd->stream));
       GemmParams d = {};
-      d.a = (const __half *)t0->data(); d.w = (const __half *)w2->data(); d.c = (__half *)out->data();
+      d.a = (const __half *)t0->data(); d.c = (__half *)out->data();
+      weight_of(d, w2);
       d.M = (uint32_t)x->h; d.N = (uint32_t)w2->h; d.K = (uint32_t)w2->w;
       d.scale = 1.f; d.error = g.error;
-      VKL_LAUNCH(1, launch_gemm_f16_tcgen05(d, cmd->stream));
+      VKL_LAUNCH(1, launch_gemm_tcgen05(d, cmd->stream));
       *o = out;
       return leave();
     }
@@ -540,6 +568,107 @@ struct ElementWiseOp : vkl_op {
     *o = y;
     return leave();
   }
+  // src/ops/elementwise.cpp:104-133: x <- x op y for a scalar y, in place. The reference hands the scalar over as
+  // fp32 or, on devices with fp16 arithmetic, truncated to fp16; this is the fp32 form.
+  int run_scalar(vkl_tensor *x, float y, vkl_tensor **o) {
+    if (!x) return fail(VKL_INVALID_ARGUMENT, "elementwise: null tensor");
+    if (x->dtype != dtype) return fail(VKL_INVALID_ARGUMENT, "elementwise op defined with %d dtype but the input has %d", dtype, x->dtype);
+    VKL_OKAY(need_dense(x, "elementwise"));
+    VKL_OKAY(enter("elementwise"));
+    VKL_LAUNCH(1, launch_scalar_op((__half *)x->data(), x->size(), type, y, cmd->stream));
+    *o = x;
+    return leave();
+  }
+};
+
+// ------------------------------------------------------------------- Concat
+struct ConcatOp : vkl_op {
+  int num, axis, dtype;
+  vkl_tensor *out = nullptr;
+  ConcatOp(vkl_device *d, vkl_command *c, int n, int ax, int dt) : vkl_op(d, c), num(n), axis(ax), dtype(dt) {}
+  ~ConcatOp() override { vkl_tensor_release(out); }
+  // src/ops/concat.cpp:20-65
+  int init() override {
+    if (dtype != VKL_FP16) return fail(VKL_INVALID_ARGUMENT, "Concat op: only fp16 dtype is supported.");
+    if (num < 1) return fail(VKL_INVALID_ARGUMENT, "Concat op: %d inputs", num);
+    return base_init();
+  }
+  // src/ops/concat.cpp:67-184
+  int run(vkl_tensor *const *in, size_t n, vkl_tensor **o) {
+    if (!in || n != (size_t)num) return fail(VKL_INVALID_ARGUMENT, "operator has %zu inputs but %zu are given", (size_t)num, n);
+    for (size_t i = 0; i < n; ++i) {
+      if (!in[i] || in[i]->dtype != dtype) return fail(VKL_INVALID_ARGUMENT, "dtype of inputs are unsupported.");
+      VKL_OKAY(need_dense(in[i], "concat"));
+    }
+    if (axis < 0 || axis > 2) return fail(VKL_INVALID_ARGUMENT, "axis %d is unsupported.", axis);
+    const vkl_tensor *r = in[0];
+    size_t c = r->c, h = r->h, w = r->w;
+    for (size_t i = 1; i < n; ++i) {
+      const vkl_tensor *t = in[i];
+      if (axis == 0 && (t->h != r->h || t->w != r->w)) return fail(VKL_INVALID_ARGUMENT, "inputs shape error on axis 0");
+      if (axis == 1 && (t->c != r->c || t->w != r->w)) return fail(VKL_INVALID_ARGUMENT, "inputs shape error on axis 1");
+      if (axis == 2 && (t->c != r->c || t->h != r->h)) return fail(VKL_INVALID_ARGUMENT, "inputs shape error on axis 2");
+      if (axis == 0) c += t->c;
+      if (axis == 1) h += t->h;
+      if (axis == 2) w += t->w;
+    }
+    VKL_OKAY(enter("concat"));
+    VKL_OKAY(ensure_tensor(dev, &out, c, h, w, dtype));
+    size_t offset = 0;  // in elements of the output: whole inputs (axis 0), rows (axis 1) or columns (axis 2)
+    for (size_t i = 0; i < n; ++i) {
+      const vkl_tensor *t = in[i];
+      VKL_LAUNCH(1, launch_concat_copy((const __half *)t->data(), (__half *)out->data(), (uint32_t)t->c, (uint32_t)t->h, (uint32_t)t->w, out->cs / 2,
+                                       out->hs / 2, offset, cmd->stream));
+      offset += axis == 0 ? t->size() : axis == 1 ? t->w * t->h : t->w;
+    }
+    *o = out;
+    return leave();
+  }
+};
+
+// ------------------------------------------------------------------- Reduce
+struct ReduceOp : vkl_op {
+  int op_type, dtype;  // 0 sum, 1 max, 2 min, 3 mean (src/ops/reduce.h:18)
+  vkl_tensor *out = nullptr;
+  ReduceOp(vkl_device *d, vkl_command *c, int t, int dt) : vkl_op(d, c), op_type(t), dtype(dt) {}
+  ~ReduceOp() override { vkl_tensor_release(out); }
+  int init() override {
+    if (dtype != VKL_FP16) return fail(VKL_INVALID_ARGUMENT, "Reduce op: only fp16 dtype is supported");
+    if (op_type < 0 || op_type > 3) return fail(VKL_INVALID_ARGUMENT, "Reduce op: type %d is unknown", op_type);
+    return base_init();
+  }
+  // src/ops/reduce.h:67-112: [c, h, w] -> [c, h, 1]
+  int run(vkl_tensor *a, vkl_tensor **o) {
+    if (!a || a->dtype != dtype) return fail(VKL_INTERNAL, "reduce op defined with %d dtype but the dtype of input0 is %d", dtype, a ? a->dtype : -1);
+    if (a->w == 0) return fail(VKL_INVALID_ARGUMENT, "reduce: empty rows");
+    VKL_OKAY(need_dense(a, "reduce"));
+    VKL_OKAY(enter("reduce"));
+    VKL_OKAY(ensure_tensor(dev, &out, a->c, a->h, 1, dtype));
+    VKL_LAUNCH(1, launch_reduce((const __half *)a->data(), (__half *)out->data(), (uint32_t)a->rows(), (uint32_t)a->w, op_type == 3 ? 0 : op_type,
+                                op_type == 3 ? 1.0f / (float)a->w : 1.0f, cmd->stream));
+    *o = out;
+    return leave();
+  }
+};
+
+// -------------------------------------------------------------- ReadKVCache
+struct ReadKVCacheOp : vkl_op {
+  vkl_tensor *out = nullptr;
+  ReadKVCacheOp(vkl_device *d, vkl_command *c) : vkl_op(d, c) {}
+  ~ReadKVCacheOp() override { vkl_tensor_release(out); }
+  int init() override { return base_init(); }
+  // src/ops/read_kvcache_op.cpp:31-71: rows (offset + y) % maxlen of every head, y < len
+  int run(vkl_tensor *cache, uint32_t offset, uint32_t len, vkl_tensor **o) {
+    if (!cache || cache->dtype != VKL_FP16) return fail(VKL_INVALID_ARGUMENT, "read_kvcache: the cache must be an fp16 tensor");
+    if (len > cache->h) return fail(VKL_OUT_OF_RANGE, "read %d len but size of cache is %zu", (int)len, cache->h);
+    VKL_OKAY(need_dense(cache, "read_kvcache"));
+    VKL_OKAY(enter("read_kvcache"));
+    VKL_OKAY(ensure_tensor(dev, &out, cache->c, len, cache->w, VKL_FP16));
+    VKL_LAUNCH(1, launch_read_kvcache((const __half *)cache->data(), (__half *)out->data(), (uint32_t)cache->c, (uint32_t)cache->h, (uint32_t)cache->w,
+                                      offset, len, cmd->stream));
+    *o = out;
+    return leave();
+  }
 };
 
 // ---------------------------------------------------------------- Transpose
@@ -807,6 +936,38 @@ int vkl_elementwise_run(vkl_op *op, vkl_tensor *x, vkl_tensor *y, vkl_tensor **o
   VKL_OKAY(as(op, &m, "elementwise_run"));
   if (!out) return fail(VKL_INVALID_ARGUMENT, "elementwise_run: null output");
   return m->run(x, y, out);
+}
+int vkl_elementwise_run_scalar(vkl_op *op, vkl_tensor *x, float y, vkl_tensor **out) {
+  ElementWiseOp *m;
+  VKL_OKAY(as(op, &m, "elementwise_run_scalar"));
+  if (!out) return fail(VKL_INVALID_ARGUMENT, "elementwise_run_scalar: null output");
+  return m->run_scalar(x, y, out);
+}
+int vkl_concat_create(vkl_device *dev, vkl_command *cmd, int num, int axis, int dtype, vkl_op **out) { MAKE(ConcatOp, num, axis, dtype) }
+int vkl_concat_run(vkl_op *op, vkl_tensor *const *inputs, size_t n, vkl_tensor **out) {
+  ConcatOp *m;
+  VKL_OKAY(as(op, &m, "concat_run"));
+  if (!out) return fail(VKL_INVALID_ARGUMENT, "concat_run: null output");
+  return m->run(inputs, n, out);
+}
+int vkl_reduce_create(vkl_device *dev, vkl_command *cmd, int op_type, int dtype, vkl_op **out) { MAKE(ReduceOp, op_type, dtype) }
+int vkl_reduce_run(vkl_op *op, vkl_tensor *a, vkl_tensor **out) {
+  ReduceOp *m;
+  VKL_OKAY(as(op, &m, "reduce_run"));
+  if (!out) return fail(VKL_INVALID_ARGUMENT, "reduce_run: null output");
+  return m->run(a, out);
+}
+int vkl_read_kvcache_create(vkl_device *dev, vkl_command *cmd, vkl_op **out) {
+  if (!out) return fail(VKL_INVALID_ARGUMENT, "op create: null output");
+  if (!dev || !cmd) return fail(VKL_INVALID_ARGUMENT, "op create: null device or command");
+  *out = new ReadKVCacheOp(dev, cmd);
+  return VKL_OK;
+}
+int vkl_read_kvcache_run(vkl_op *op, vkl_tensor *cache, uint32_t offset, uint32_t len, vkl_tensor **out) {
+  ReadKVCacheOp *m;
+  VKL_OKAY(as(op, &m, "read_kvcache_run"));
+  if (!out) return fail(VKL_INVALID_ARGUMENT, "read_kvcache_run: null output");
+  return m->run(cache, offset, len, out);
 }
 int vkl_transpose_create(vkl_device *dev, vkl_command *cmd, int type, int dtype, vkl_op **out) { MAKE(TransposeOp, type, dtype) }
 int vkl_transpose_run(vkl_op *op, vkl_tensor *in, vkl_tensor **out) {

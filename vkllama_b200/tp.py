@@ -5,6 +5,7 @@ kernel's own peer stores over NVLink (no collective library call per token)."""
 
 def connect(model, dist, rank, world):
     """Exchange IPC handles over the process group and connect `model`'s ranks."""
+    dist.barrier()  # no rank may still run a step when the buffers are (re)connected and cleared
     mine = model.tp_export()
     handles = [None] * world
     dist.all_gather_object(handles, mine)
