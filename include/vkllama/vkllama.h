@@ -370,6 +370,50 @@ class ElementWise : public Op {
     const int st = vkl_elementwise_run(op_, x.handle(), y.handle(), &o);  // sequenced before `o` is read
     return out(st, o);
   }
+  absl::StatusOr<Tensor> operator()(Tensor x, float y) noexcept {  // elementwise.cpp:104-133: in place in x
+    vkl_tensor *o = nullptr;
+    const int st = vkl_elementwise_run_scalar(op_, x.handle(), y, &o);
+    return out(st, o);
+  }
+};
+
+// src/ops/concat.h:10-17
+class Concat : public Op {
+ public:
+  Concat(GPUDevice *dev, Command *command, const int num, const int axis, Tensor::DType dtype = FP16) : Op(dev, command) {
+    vkl_concat_create(dev->handle(), command->handle(), num, axis, dtype, &op_);
+  }
+  absl::StatusOr<Tensor> operator()(const std::vector<Tensor> &inputs) noexcept {
+    std::vector<vkl_tensor *> hs;
+    for (const Tensor &t : inputs) hs.push_back(t.handle());
+    vkl_tensor *o = nullptr;
+    const int st = vkl_concat_run(op_, hs.data(), hs.size(), &o);
+    return out(st, o);
+  }
+};
+
+// src/ops/reduce.h:18-67: 0 sum, 1 max, 2 min, 3 mean
+class Reduce : public Op {
+ public:
+  Reduce(GPUDevice *dev, Command *command, int op_type, Tensor::DType dtype = FP16) : Op(dev, command) {
+    vkl_reduce_create(dev->handle(), command->handle(), op_type, dtype, &op_);
+  }
+  absl::StatusOr<Tensor> operator()(Tensor a) noexcept {
+    vkl_tensor *o = nullptr;
+    const int st = vkl_reduce_run(op_, a.handle(), &o);
+    return out(st, o);
+  }
+};
+
+// src/ops/read_kvcache_op.h:10-16
+class ReadKVCache : public Op {
+ public:
+  ReadKVCache(GPUDevice *dev, Command *command) : Op(dev, command) { vkl_read_kvcache_create(dev->handle(), command->handle(), &op_); }
+  absl::StatusOr<Tensor> operator()(Tensor cache, uint32_t offset, uint32_t len) noexcept {
+    vkl_tensor *o = nullptr;
+    const int st = vkl_read_kvcache_run(op_, cache.handle(), offset, len, &o);
+    return out(st, o);
+  }
 };
 
 // src/ops/transpose.h:14-19

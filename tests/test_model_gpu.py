@@ -386,3 +386,33 @@ def test_short_wait_bound_on_a_healthy_model_is_reported_not_hung(dev):
             codes.add(e.message)
     dm.set_wait_limit(0)
     assert dm.generate(prompt, 6)[0].tolist() == want.tolist()  # the sequence base was reset: stale tags do not match
+
+
+def test_tagged_words_survive_the_16_bit_tag_wrap(dev, monkeypatch):
+    """The activation words carry the low 16 bits of a sequence number that advances by the op count
+    per token (8 ops for a one-block model): after 8192 tokens the tags come round again. A prompt of
+    8300 tokens is fed token by token through the persistent kernel (66400 op numbers), then the
+    logits and the following greedy steps are compared with the oracle: a word misread as current
+    anywhere on the way would derail the residual stream for good."""
+    monkeypatch.setenv("VKLLAMA_PREFILL", "sequential")
+    cfg = dict(dim=128, heads=2, ffn=256, vocab=500, layers=1, maxlen=8448)
+    om = O.Model(seed=17, **cfg)
+    dm = vk.Model(dev, cfg["dim"], cfg["heads"], cfg["ffn"], cfg["vocab"], cfg["layers"], cfg["maxlen"])
+    load_from_oracle(dm, om)
+    P = 8300
+    prompt = O.synth_tokens(17, 1000, P, cfg["vocab"])
+    ids, _, _ = dm.generate(prompt, 6)
+    ids2, _, _ = dm.generate(prompt, 6)  # a second job continues the sequence numbers where the first ended
+    assert ids.tolist() == ids2.tolist()
+    # The oracle takes the prompt in one call. (Its logits for that call are not comparable: in a multi-token
+    # call the reference rotates the clipped query of the last block at the call's first position,
+    # multiheadattention_v2.cpp:223-253, which a token-by-token prefill never does. The caches are.)
+    om.forward(prompt, 0)
+    gk, gv = dm.read_kv(0)
+    assert_close(gk[:, :P], om.kcache(0)[:, :P], tol=5e-3, what="kcache after the wrap")
+    assert_close(gv[:, :P], om.vcache(0)[:, :P], tol=5e-3, what="vcache after the wrap")
+    tok = np.array([int(ids[0])], np.uint32)
+    for i in range(3):
+        w, g = om.forward(tok, P + i), dm(tok, P + i)
+        assert np.abs(g - w).max() <= LOGITS_MAX_ABS, "step %d after the wrap" % i
+        tok = np.array([int(np.argmax(w))], np.uint32)

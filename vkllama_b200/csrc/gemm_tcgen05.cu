@@ -41,7 +41,7 @@ constexpr int GEMM_THREADS_Q8 = 192 + 128;  // + four warps dequantising the W t
 template <int BN> struct Cfg {
   static constexpr uint32_t B_TILE_BYTES = BN * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-  static constexpr int STAGES = BN == 128 ? 6 : 4;  // 192 KB of stages either way
+  static constexpr int STAGES = (192 * 1024 / (int)STAGE_BYTES) < 8 ? (192 * 1024 / (int)STAGE_BYTES) : 8;  // up to 192 KB of stages
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
 };
 
@@ -175,35 +175,60 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
     // the four warps. The scales of a row tile and 4-block group are 8 x 16 bytes: row g's four blocks, then row g + 8's.
     const uint32_t dw = warp - 6, g = lane >> 2;
     const uint32_t tiles16 = (p.N + 15) / 16, groups = ((p.K + 31) / 32 + 3) / 4;
-    constexpr uint32_t UNITS = (BN / 16) * 2;
-    for (uint32_t kb = 0; kb < nkb; ++kb) {
-      const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
-      uint32_t ok = 1;
-      if (lane == 0 && use > 0) ok = mbar_wait_bounded(sa(&empty[s]), (use - 1) & 1u) ? 1u : 0u;
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) {
-        if (lane == 0) failed_s = 4;
-        break;
-      }
-      if (failed_s) break;
-      unsigned char *wt = stages + (size_t)s * C::STAGE_BYTES + A_TILE_BYTES;
-      for (uint32_t u = dw; u < UNITS; u += 4) {
-        const uint32_t tl = u >> 1, bl = u & 1;  // row tile inside the W tile, block inside the K step
+    constexpr uint32_t UNITS = (BN / 16) * 2, UPQ = UNITS / 4;  // units per stage, and of those this warp's
+    constexpr uint32_t PF = UPQ >= 8 ? 1 : 8 / UPQ;              // stages whose units are requested ahead
+    // The codes of a stage come from DRAM (a microsecond away) and a stage is converted in a fraction of that:
+    // the loads of the next PF stages are kept in flight in registers while one stage is converted and stored.
+    uint4 wq[PF][UPQ];
+    uint32_t dq[PF][UPQ];  // the two scales of the lane's rows g and g + 8, packed
+    auto request = [&](uint32_t kb, uint32_t slot) {
+#pragma unroll
+      for (uint32_t j = 0; j < UPQ; ++j) {
+        const uint32_t u = dw + 4 * j, tl = u >> 1, bl = u & 1;  // row tile inside the W tile, block inside the K step
         const uint32_t tile = n0 / 16 + tl, b = kb * 2 + bl;
-        uint4 w = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // code 0 (stored biased by 128)
-        uint32_t d_lo = 0, d_hi = 0;
-        if (tile < tiles16) {
-          w = ldg_stream(p.w_codes + (((size_t)tile * groups * 4 + b) * 32 + lane) * 16);
+        wq[slot][j] = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // code 0 (stored biased by 128)
+        dq[slot][j] = 0;
+        if (kb < nkb && tile < tiles16) {
+          wq[slot][j] = ldg_stream(p.w_codes + (((size_t)tile * groups * 4 + b) * 32 + lane) * 16);
           const unsigned short *sc = reinterpret_cast<const unsigned short *>(p.w_scales) + (((size_t)tile * groups + (b >> 2)) * 8 + g) * 8 + (b & 3);
-          d_lo = sc[0];
-          d_hi = sc[4];
+          dq[slot][j] = (uint32_t)__ldg(sc) | ((uint32_t)__ldg(sc + 4) << 16);
         }
-        dequant_unit(wt, tl * 16, bl * 4, w, d_lo, d_hi, lane);
       }
-      // the tensor core reads shared memory through the async proxy: order this warp's stores before its arrival
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sa(&full[s])) : "memory");
+    };
+#pragma unroll
+    for (uint32_t i = 0; i < PF; ++i) request(i, i);
+    for (uint32_t kb0 = 0; kb0 < nkb; kb0 += PF) {
+      bool stop = false;
+#pragma unroll
+      for (uint32_t i = 0; i < PF; ++i) {  // register slots are indexed by compile-time constants
+        const uint32_t kb = kb0 + i;
+        if (kb >= nkb || stop) continue;
+        const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
+        uint32_t ok = 1;
+        if (lane == 0 && use > 0) ok = mbar_wait_bounded(sa(&empty[s]), (use - 1) & 1u) ? 1u : 0u;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+          if (lane == 0) failed_s = 4;
+          stop = true;
+          continue;
+        }
+        if (failed_s) {
+          stop = true;
+          continue;
+        }
+        unsigned char *wt = stages + (size_t)s * C::STAGE_BYTES + A_TILE_BYTES;
+#pragma unroll
+        for (uint32_t j = 0; j < UPQ; ++j) {
+          const uint32_t u = dw + 4 * j;
+          dequant_unit(wt, (u >> 1) * 16, (u & 1) * 4, wq[i][j], dq[i][j] & 0xffffu, dq[i][j] >> 16, lane);
+        }
+        request(kb + PF, i);  // refill this slot for the stage PF steps ahead
+        // the tensor core reads shared memory through the async proxy: order this warp's stores before its arrival
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sa(&full[s])) : "memory");
+      }
+      if (stop) break;
     }
   } else if (warp == 1) {
     // --------------------------------------------------------------------- MMA
@@ -364,12 +389,23 @@ cudaError_t launch_gemm_f16_tcgen05(const GemmParams &p, cudaStream_t s) {
   return launch_bn<128, false>(p, s);
 }
 
+// The widest W tile whose grid still gives every SM a CTA (narrow tiles re-read A from L2 more often,
+// but with few rows of A an idle SM costs more than that).
+static int pick_bn(const GemmParams &p) {
+  const size_t mt = (p.M + BM - 1) / BM, sms = sm_count();
+  for (int bn : {256, 128, 64}) if (mt * ((p.N + bn - 1) / bn) >= sms) return bn;
+  return 32;
+}
+
 cudaError_t launch_gemm_q8_tcgen05(const GemmParams &p, cudaStream_t s) {
   if (!gemm_tcgen05_supported(p.M, p.N, p.K) || !p.w_codes || !p.w_scales) return cudaErrorInvalidValue;
   if (reinterpret_cast<uintptr_t>(p.a) & 15) return cudaErrorMisalignedAddress;
-  const size_t tiles256 = (size_t)((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
-  if (tiles256 >= sm_count()) return launch_bn<256, true>(p, s);
-  return launch_bn<128, true>(p, s);
+  switch (pick_bn(p)) {
+    case 256: return launch_bn<256, true>(p, s);
+    case 128: return launch_bn<128, true>(p, s);
+    case 64: return launch_bn<64, true>(p, s);
+    default: return launch_bn<32, true>(p, s);
+  }
 }
 
 cudaError_t launch_swiglu_f32(const float *gate, const float *up, __half *out, size_t n, cudaStream_t s) {
