@@ -36,9 +36,9 @@ sys.path.insert(0, ROOT)
 # first PARITY_IDS greedy steps are each decided by several fp16 ulps: implementations that differ
 # only in fp32 summation order (decode plans, tensor-parallel degrees) then produce the same ids,
 # and `parity.ids_sha` can be compared across lines.
-PROMPT_ID_7B = 1000
-PROMPT_ID_13B = 1000
-PARITY_IDS = 32
+PROMPT_ID_7B = 3144    # smallest top-2 gap over 64 steps: 14 fp16 ulps (32-token prompt, one multi-token call)
+PROMPT_ID_13B = 2037   # 7 fp16 ulps over 64 steps (128-token prompt fed token by token)
+PARITY_IDS = 64
 
 WORKLOADS = {
     # name: dims, prompt, decode tokens
@@ -431,11 +431,19 @@ def main():
         ap = synth_tokens(aw["seed"], aw["prompt_id"], aw["prompt"], aw["vocab"])
         one.generate(ap, aw["decode"] + 1)
         a_ids, a_pre, a_dec = one.generate(ap, aw["decode"] + 1)
+        # the ids the sharded runs are compared with: prompt fed token by token, as sharded models prefill (a
+        # multi-token call rotates the last block's clipped query at the call's first position, as the reference
+        # does, so its first ids are not comparable with a token-by-token prefill)
+        os.environ["VKLLAMA_PREFILL"] = "sequential"
+        s_ids, _, _ = one.generate(ap, aw["decode"] + 1)
+        os.environ.pop("VKLLAMA_PREFILL", None)
         one.close()
         anchor = {"workload": "llama2-13b-q8_0", "tp": 1, "value": aw["decode"] / (a_dec / 1000.0), "unit": "tokens/s",
-                  "ms_per_token": a_dec / aw["decode"], "prefill_ms": a_pre, "ids_sha": ids_sha(a_ids), "n_ids": PARITY_IDS}
+                  "ms_per_token": a_dec / aw["decode"], "prefill_ms": a_pre, "ids_sha": ids_sha(s_ids), "n_ids": PARITY_IDS,
+                  "ids_sha_what": "token-by-token prefill, comparable with the ids_sha of the 2/4/8-GPU lines",
+                  "ids_sha_batched_prefill": ids_sha(a_ids)}
         if tp > 1:
-            same = np.asarray(a_ids) == np.asarray(ids)
+            same = np.asarray(s_ids) == np.asarray(ids)
             parity["tp1"] = {"ids_sha": anchor["ids_sha"], "matches_tp1": anchor["ids_sha"] == parity["ids_sha"],
                              "ids_equal_until": int(np.argmin(same)) if not same.all() else int(same.size),
                              "of": int(same.size)}

@@ -47,6 +47,9 @@ def main():
     ap.add_argument("--first", type=int, default=2000, help="first candidate tensor id")
     ap.add_argument("--max-found", type=int, default=6)
     ap.add_argument("--out", default=None)
+    ap.add_argument("--token-by-token", action="store_true",
+                    help="feed the prompt one token per call, as tensor-parallel models prefill (a multi-token call "
+                         "rotates the last block's clipped query at the call's first position, so its first ids differ)")
     a = ap.parse_args()
     import vkllama_b200 as vk
     from vkllama_b200.synth import synth_tokens
@@ -59,7 +62,11 @@ def main():
     pid = a.first
     while time.time() - t0 < a.budget_s and len(found) < a.max_found:
         prompt = synth_tokens(w["seed"], pid, w["prompt"], w["vocab"])
-        logits = m(prompt, 0)
+        if a.token_by_token:
+            for i in range(w["prompt"]):
+                logits = m(prompt[i:i + 1], i)
+        else:
+            logits = m(prompt, 0)
         ids, gaps = [], []
         for i in range(a.steps):
             if i:
@@ -76,7 +83,7 @@ def main():
         tried += 1
         pid += 1
     res = {"model": a.model, "seed": w["seed"], "prompt_tokens": w["prompt"], "steps": a.steps, "min_ulps": a.min_ulps,
-           "tried": tried, "steps_walked": steps_walked, "seconds": time.time() - t0, "found": found}
+           "token_by_token": bool(a.token_by_token), "tried": tried, "steps_walked": steps_walked, "seconds": time.time() - t0, "found": found}
     print(json.dumps({k: v for k, v in res.items() if k != "found"}), flush=True)
     if a.out:
         os.makedirs(os.path.dirname(os.path.abspath(a.out)), exist_ok=True)
