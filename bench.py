@@ -431,9 +431,9 @@ def main():
         ap = synth_tokens(aw["seed"], aw["prompt_id"], aw["prompt"], aw["vocab"])
         one.generate(ap, aw["decode"] + 1)
         a_ids, a_pre, a_dec = one.generate(ap, aw["decode"] + 1)
-        # the ids the sharded runs are compared with: prompt fed token by token, as sharded models prefill (a
-        # multi-token call rotates the last block's clipped query at the call's first position, as the reference
-        # does, so its first ids are not comparable with a token-by-token prefill)
+        # the ids the sharded runs are compared with: prompt fed token by token. Sharded models take the last
+        # prompt token through the decode kernel; a single-GPU multi-token call instead rotates the last block's
+        # clipped query at the call's first position, as the reference does, and its first ids differ for that
         os.environ["VKLLAMA_PREFILL"] = "sequential"
         s_ids, _, _ = one.generate(ap, aw["decode"] + 1)
         os.environ.pop("VKLLAMA_PREFILL", None)

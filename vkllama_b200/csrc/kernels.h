@@ -66,6 +66,19 @@ cudaError_t launch_reduce(const __half *in, __half *out, uint32_t rows, uint32_t
 // out[c, y, :] = cache[c, (y + offset) % H, :] for y < len.
 cudaError_t launch_read_kvcache(const __half *cache, __half *out, uint32_t C, uint32_t H, uint32_t W, uint32_t offset, uint32_t len,
                                 cudaStream_t s);
+// All-reduce of fp32 partial sums [n] over tensor-parallel ranks with the residual add of the K-split
+// projections: x = fp16(fp16(sum over ranks, in rank order) + x). part[r] / flags[r] are rank r's partial
+// sums and flag words [tp] (peer mappings; [rank] is this GPU's). A wait that runs out of `wait_limit`
+// polls stores 16 into *error and leaves x as it was.
+struct TpRowsParams {
+  const float *part[8];
+  uint32_t *flags[8];
+  __half *x;
+  size_t n;
+  uint32_t rank, tp, seq, wait_limit;
+  uint32_t *error;
+};
+cudaError_t launch_tp_reduce_rows(const TpRowsParams &p, int sms, cudaStream_t s);
 cudaError_t launch_embedding(const uint8_t *vocab, int vocab_is_q8, const uint32_t *ids,
                              __half *out, uint32_t T, uint32_t VH, uint32_t VW, uint32_t unk,
                              cudaStream_t s);

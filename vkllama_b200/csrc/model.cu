@@ -70,6 +70,10 @@ struct vkl_model {
   uint32_t tp_flag_off = 0;
   void *tp_peer[8] = {};
   bool tp_connected = false;
+  // many-token passes of a sharded model: two alternating regions of fp32 partial sums [tp_pf_rows, dim]
+  // and the ranks' flag words behind the one-token exchange area, and the count of all-reduces so far
+  size_t tp_pf_off = 0, tp_pf_flag_off = 0;
+  uint32_t tp_pf_rows = 0, tp_pf_seq = 0;
   vkl_tensor *out_ids = nullptr;
   vkl_tensor *argpart = nullptr, *attn_scratch = nullptr, *attn_counters = nullptr;
   uint32_t splits = 8, out_cap = 0;
@@ -204,7 +208,10 @@ struct Marker {
 
 // One pass over T tokens already in m->toks, first position in state[0].
 // Leaves the last token's fp16/fp32 logits and its arg-max in state[2].
-int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
+// `fill_only`: the pass only has to leave the T tokens' keys and values in the caches (it stops after the
+// last block's attention and clips nothing); the one form tensor-parallel models run with T > 1, their
+// K-split projections summed over the ranks by launch_tp_reduce_rows. `tok_off`: first token in m->toks.
+int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr, bool fill_only = false, uint32_t tok_off = 0) {
   cudaStream_t s = m->stream;
   MARK(-1);
   const uint32_t D = m->cfg.dim, nl = m->cfg.layers;
@@ -212,14 +219,39 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
   __half *x = (__half *)m->x->data(), *xn = (__half *)m->xn->data();
   __half *qb = (__half *)m->q->data(), *kb = (__half *)m->k->data(), *vb = (__half *)m->v->data();
   __half *ao = (__half *)m->ao->data(), *tb = (__half *)m->t->data();
-  VKL_LAUNCH(1, launch_embedding(m->tok_embd->data(), m->tok_embd->dtype == VKL_Q8_0, (const uint32_t *)m->toks->data(), x, T,
+  const bool sharded = m->cfg.tp_size > 1;
+  if (sharded && !(fill_only && T > 1 && T <= m->tp_pf_rows && use_gemm(m, T))) return fail(VKL_INTERNAL, "run_tokens: no sharded form of this pass");
+  // K-split projection of a sharded model: fp32 partial sums into this rank's exchange region, then the sum over ranks
+  auto reduce_rows = [&](GemmParams g, __half *xio, uint32_t nrows) -> int {
+    const uint32_t seq = ++m->tp_pf_seq;
+    const size_t region = m->tp_pf_off + (size_t)(seq & 1u) * m->tp_pf_rows * D * 4;
+    g.c = nullptr;
+    g.residual = nullptr;
+    g.c_f32 = (float *)((char *)m->tp_buf + region);
+    VKL_LAUNCH(1, launch_gemm_tcgen05(g, s));
+    TpRowsParams r = {};
+    for (uint32_t i = 0; i < m->cfg.tp_size; ++i) {
+      r.part[i] = (const float *)((const char *)m->tp_peer[i] + region);
+      r.flags[i] = (uint32_t *)((char *)m->tp_peer[i] + m->tp_pf_flag_off);
+    }
+    r.x = xio;
+    r.n = (size_t)nrows * D;
+    r.rank = m->cfg.tp_rank;
+    r.tp = m->cfg.tp_size;
+    r.seq = seq;
+    r.wait_limit = m->wait_limit ? m->wait_limit : (1u << 24);
+    r.error = (uint32_t *)m->state->data() + 6;
+    VKL_LAUNCH(2, launch_tp_reduce_rows(r, m->dev->prop.multiProcessorCount, s));
+    return VKL_OK;
+  };
+  VKL_LAUNCH(1, launch_embedding(m->tok_embd->data(), m->tok_embd->dtype == VKL_Q8_0, (const uint32_t *)m->toks->data() + tok_off, x, T,
                                  (uint32_t)m->tok_embd->h, D, 0, s));
   MARK(0);
   uint32_t rows = T;      // rows still alive (the last block keeps one: llama2.h:181-191)
   __half *xr = x;         // first live row of the residual stream
   for (uint32_t l = 0; l < nl; ++l) {
     Layer &y = m->L[l];
-    const bool clip = (l == nl - 1) && T > 1;
+    const bool clip = (l == nl - 1) && T > 1 && !fill_only;
     // --- attention ---------------------------------------------------------
     MvParams p = mv(m, y.wk, dec ? x : xn, kb, T);
     p.codes[1] = y.wq->data(); p.codes[2] = y.wv->data();
@@ -254,12 +286,15 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
     a.use_pdl = dec && pdl;
     VKL_LAUNCH(dec ? 1 : 2, launch_attention(a, s));
     MARK(2);
+    if (fill_only && l == nl - 1) break;  // the caches are complete
     if (clip) {
       xr = x + (size_t)(T - 1) * D;
       rows = 1;
     }
     // --- o_proj + residual (add_op_(attn, in): llama2.h:193-196) -------------
-    if (use_gemm(m, rows)) {
+    if (sharded) {
+      VKL_OKAY(reduce_rows(gemm(m, y.wo, ao, xr, rows), xr, rows));
+    } else if (use_gemm(m, rows)) {
       GemmParams g = gemm(m, y.wo, ao, xr, rows);
       g.residual = xr;
       VKL_LAUNCH(1, launch_gemm_tcgen05(g, s));
@@ -299,7 +334,9 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
       VKL_LAUNCH((rows + 63) / 64, launch_matvec(f, EPI_SWIGLU, false, s));
     }
     MARK(4);
-    if (use_gemm(m, rows)) {
+    if (sharded) {
+      VKL_OKAY(reduce_rows(gemm(m, y.down, tb, xr, rows), xr, rows));
+    } else if (use_gemm(m, rows)) {
       GemmParams g = gemm(m, y.down, tb, xr, rows);
       g.residual = xr;
       VKL_LAUNCH(1, launch_gemm_tcgen05(g, s));
@@ -311,6 +348,7 @@ int run_tokens(vkl_model *m, uint32_t T, bool pdl, Marker *mk = nullptr) {
     }
     MARK(5);
   }
+  if (fill_only) return VKL_OK;
   // --- output layer: RMSNorm(1e-6) -> lm head -> fp32 cast (llama2.h:283-298) --
   if (T > 1 && nl == 0) xr = x + (size_t)(T - 1) * D;
   MvParams h = mv(m, m->output, xr, (__half *)m->logits16->data(), 1);
@@ -661,6 +699,10 @@ int check_gemm(vkl_model *m) {
   VKL_CUDA(cudaMemcpy(&err, (uint32_t *)m->state->data() + 6, 4, cudaMemcpyDeviceToHost));
   if (err) {
     cudaMemset((uint32_t *)m->state->data() + 6, 0, 4);
+    if (err == 16u) {  // the ranks' all-reduce counters are out of step from here on
+      m->tp_failed = true;
+      return fail(VKL_INTERNAL, "prefill: the wait for another tensor-parallel rank's partial sums ran out");
+    }
     return fail(VKL_INTERNAL, "prefill GEMM: a bounded mbarrier wait ran out");
   }
   return VKL_OK;
@@ -821,6 +863,10 @@ int vkl_model_create(vkl_device *dev, const vkl_model_config *cfg, vkl_model **o
   if (tp > 1) {
     m->tp_flag_off = 4 * tp * c.dim;  // partial sums: [2 parities][tp][dim] words of {fp32 sum, sequence number}
     m->tp_bytes = ((size_t)m->tp_flag_off + 64) * 4;
+    m->tp_pf_rows = std::min(c.maxlen, 1024u);
+    m->tp_pf_off = (m->tp_bytes + 255) / 256 * 256;
+    m->tp_pf_flag_off = m->tp_pf_off + 2 * (size_t)m->tp_pf_rows * c.dim * 4;
+    m->tp_bytes = m->tp_pf_flag_off + 64;
     if (cudaMalloc(&m->tp_buf, m->tp_bytes) != cudaSuccess) return bail(fail(VKL_RESOURCE_EXHAUSTED, "model_create: exchange buffer allocation failed"));
     cudaMemsetAsync(m->tp_buf, 0, m->tp_bytes, m->stream);
     m->tp_peer[c.tp_rank] = m->tp_buf;
@@ -985,14 +1031,35 @@ int vkl_model_generate(vkl_model *m, const uint32_t *prompt, size_t n_prompt, si
   // the persistent decode kernel: while the position is inside the prompt the kernel feeds
   // itself the next prompt id instead of its arg-max.
   const char *pf = getenv("VKLLAMA_PREFILL");
-  const bool sequential = m->mega_ready && n_prompt > 1 && (m->cfg.tp_size > 1 || (pf && !strcmp(pf, "sequential")));
+  const bool by_token = pf && !strcmp(pf, "sequential");
+  const bool sequential = m->mega_ready && n_prompt > 1 && (m->cfg.tp_size > 1 || by_token);
   if (m->cfg.tp_size > 1 && !m->mega_ready) return fail(VKL_UNIMPLEMENTED, "model_generate: tensor-parallel models need the persistent decode kernel");
+  if (m->tp_failed) return decode_step(m);  // reports the state
   const uint32_t nf = sequential ? (uint32_t)n_prompt : 0u;
   VKL_CUDA(cudaMemcpyAsync((uint32_t *)m->state->data() + 5, &nf, 4, cudaMemcpyHostToDevice, m->stream));
   if (sequential) VKL_CUDA(cudaMemcpyAsync(m->forced->data(), prompt, n_prompt * 4, cudaMemcpyHostToDevice, m->stream));
   VKL_CUDA(cudaEventRecord(m->ev0, m->stream));
   if (sequential) {
-    for (size_t i = 0; i < n_prompt; ++i) VKL_OKAY(decode_step(m));
+    // A sharded model first fills the caches for all but the last prompt tokens in many-token passes on the
+    // tensor-core GEMMs (chunks of at most tp_pf_rows tokens, each with enough rows for that path); what is
+    // left, the last prompt token at least, goes through the decode kernel, which also yields the first id.
+    size_t done = 0;
+    if (m->cfg.tp_size > 1 && !by_token) {
+      while (n_prompt - 1 - done >= gemm_min_rows(q8(m))) {
+        const uint32_t T = (uint32_t)std::min<size_t>(n_prompt - 1 - done, m->tp_pf_rows);
+        if (!use_gemm(m, T)) break;
+        const uint32_t at = (uint32_t)done;
+        VKL_CUDA(cudaMemcpyAsync(m->state->data(), &at, 4, cudaMemcpyHostToDevice, m->stream));
+        VKL_OKAY(run_tokens(m, T, false, nullptr, true, at));
+        done += T;
+      }
+      if (done) {
+        const uint32_t at = (uint32_t)done;
+        VKL_CUDA(cudaMemcpyAsync(m->state->data(), &at, 4, cudaMemcpyHostToDevice, m->stream));
+        VKL_CUDA(cudaMemcpyAsync(m->toks->data(), (const uint32_t *)m->toks->data() + done, 4, cudaMemcpyDeviceToDevice, m->stream));
+      }
+    }
+    for (size_t i = done; i < n_prompt; ++i) VKL_OKAY(decode_step(m));
   } else if (n_prompt == 1) {
     VKL_OKAY(decode_step(m));
   } else {
@@ -1274,6 +1341,7 @@ int vkl_model_tp_connect(vkl_model *m, void *const *peer_ptrs, int n) {
   VKL_CUDA(cudaMemsetAsync((uint32_t *)m->state->data() + 3, 0, 8, m->stream));  // all-reduces done, arg-max exchanges done
   VKL_CUDA(cudaStreamSynchronize(m->stream));
   m->tp_failed = false;
+  m->tp_pf_seq = 0;
   if (m->mega_ready)
     for (int i = 0; i < 8; ++i) m->mp.tp_peer[i] = m->tp_peer[i];
   return VKL_OK;
