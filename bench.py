@@ -276,36 +276,54 @@ def run_gemm(args):
     tpeak, tkind = peak_tensor()
     dev = vk.Device(0)
     cmd = vk.Command(dev)
-    a, wt = vk.Tensor(1, M, K, dev, vk.FP16), vk.Tensor(1, N, K, dev, vk.FP16)
-    op = vk.MatMul(dev, cmd, wt, 1.0, 0.0, 0, 0, True, vk.FP16, vk.FP16).init()
+    q8 = args.gemm_weights == "q8_0"
+    wdt = vk.Q8_0 if q8 else vk.FP16
+    wbytes = q8_bytes(N, K) if q8 else 2 * N * K
+    # weight copies are rotated so that every launch streams a matrix that is not in L2
+    copies = max(2, -(-400_000_000 // wbytes))
+    a = vk.Tensor(1, M, K, dev, vk.FP16)
     cmd.begin()
     cmd.fill_synthetic(a, 20240606, 1, 0.0, 1.0)
-    cmd.fill_synthetic(wt, 20240606, 2, 0.0, 0.02)
-    for _ in range(max(args.warmup, 3)):
-        op(a)
+    ws = []
+    for i in range(copies):
+        wt = vk.Tensor(1, N, K, dev, wdt)
+        cmd.fill_synthetic(wt, 20240606, 2 + i, 0.0, 0.02)
+        ws.append(wt)
+    ops = [vk.MatMul(dev, cmd, wt, 1.0, 0.0, 0, 0, True, vk.FP16, wdt).init() for wt in ws]
+    cmd.end()
+    cmd.submit_and_wait()
+    cmd.begin()
+    vk.matmul_run_many(ops, a, max(args.warmup, 3) * len(ops))
     cmd.end()
     cmd.submit_and_wait()
     launches0 = vk.kernel_launches()
     cmd.begin()
-    for _ in range(args.steps):
-        op(a)
+    us = vk.matmul_run_many(ops, a, args.steps * len(ops), timed=True)
     cmd.end()
     cmd.submit_and_wait()
-    us = cmd.elapsed_us() / args.steps
     tf = 2.0 * M * N * K / (us * 1e-6) / 1e12
+    hpeak, hkind = peak_hbm()
+    algo = wbytes + 2 * M * K + 2 * M * N
+    gbs = algo / (us * 1e-6) / 1e9
+    # which roof is lower for this shape: streaming the weights once, or the dense fp16 tensor rate
+    t_hbm, t_tensor = algo / (hpeak * 1e9), 2.0 * M * N * K / (tpeak * 1e12)
+    roof = ({"bound": "hbm", "achieved": gbs, "peak": hpeak, "unit": "GB/s", "frac": gbs / hpeak, "peak_kind": hkind}
+            if t_hbm > t_tensor else
+            {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak, "peak_kind": tkind})
+    roof["kernel"] = "gemm_tcgen05_kernel"
     print(json.dumps({"metric": "prefill_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
-                      "warmup": max(args.warmup, 3), "us_per_launch": us, "dtype": "fp16 x fp16 -> fp32 accumulate -> fp16",
-                      "config": {"workload": "gemm %dx%dx%d (rows x weight rows x K)" % (M, N, K)},
-                      "roofline": {"bound": "tensor", "kernel": "gemm_f16_tcgen05_kernel", "achieved": tf, "peak": tpeak,
-                                   "unit": "TFLOP/s", "frac": tf / tpeak, "peak_kind": tkind},
-                      "gpu_launches": int(vk.kernel_launches() - launches0)}))
+                      "warmup": max(args.warmup, 3), "us_per_launch": us, "GBps": gbs,
+                      "dtype": ("q8_0 (dequantised to fp16 in shared memory)" if q8 else "fp16") + " x fp16 -> fp32 accumulate -> fp16",
+                      "config": {"workload": "gemm %dx%dx%d (rows x weight rows x K), %s weights, %d rotated copies" % (M, N, K, args.gemm_weights, copies)},
+                      "roofline": roof, "gpu_launches": int(vk.kernel_launches() - launches0)}))
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--micro", default=None, help="'all' or ROWSxK: Q8_0 mat-vec microbenchmark instead of the token loop")
     ap.add_argument("--micro-tokens", default="1,2,4,8,16,64")
-    ap.add_argument("--gemm", default=None, help="MxNxK: FP16 tensor-core prefill GEMM microbenchmark instead of the token loop")
+    ap.add_argument("--gemm", default=None, help="MxNxK: tensor-core prefill GEMM microbenchmark instead of the token loop")
+    ap.add_argument("--gemm-weights", default="f16", choices=["f16", "q8_0"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
