@@ -7,17 +7,21 @@
 //
 //   * a producer warp walks the static schedule of this CTA's weight tiles for
 //     ALL mat-vec ops of the token and streams them with bulk-copy TMA
-//     (cp.async.bulk + mbarrier) into a shared-memory ring. Weights never depend
-//     on activations, so the producer runs ahead across op boundaries and HBM
-//     stays busy while the consumers sit in a grid barrier, a norm or attention;
-//   * fifteen consumer warps take one group (4 Q8_0 blocks x 16 rows) of every ring
-//     stage each, convert codes to fp16 exactly, multiply on the tensor cores
-//     (m16n8k16, fp32 accumulate), apply block scales in fp32, reduce across warps
-//     in fixed order and run the fused epilogue (RMSNorm prologue, residual add,
-//     SwiGLU, fp32 logits, running arg-max). An int8 tensor-core variant (m16n8k32
-//     on three exact byte slices of the input) was measured 30 % slower: the legacy
-//     int8 mma.sync path is slow on this GPU;
-//   * ops are separated by a grid barrier (one atomic counter, bounded spin).
+//     (cp.async.bulk + mbarrier) into a shared-memory ring, one copy per stage: what a
+//     CTA reads of an op is one consecutive range of the op's packed stream. Weights never
+//     depend on activations, so the producer runs ahead across op boundaries and HBM
+//     stays busy while the consumers sit in a norm, an attention op or a wait;
+//   * fifteen consumer warps take their units (one Q8_0 block x 32 rows) of every ring
+//     stage, put the codes into the tensor cores as fp16 subnormals (exact, one byte permute
+//     per pair), multiply (m16n8k16, fp32 accumulate), apply block scales in fp32, reduce
+//     across warps in fixed order and run the fused epilogue (RMSNorm prologue, residual add,
+//     SwiGLU, fp32 logits, running arg-max). The arithmetic is off the critical path: with
+//     it switched off (diagnostic mode) a token takes the same time, and eleven warps do as
+//     well as fifteen. mma.sync m16n8k16 (f16) and m16n8k32 (s8) both issue every 8 cycles
+//     per SM sub-partition on this GPU; an int8 variant on three exact byte slices of the
+//     input was 30 % slower for its integer-to-float conversions;
+//   * activations cross CTAs as tagged words (value + sequence tag in one 32-bit word) that
+//     the readers poll; only the output layer's arg-max needs a grid barrier.
 //
 // Tiles of op i go to CTA (tile + rot_i) mod grid; rot_i advances by the op's
 // tile count so the uneven remainder rotates over the SMs.
@@ -33,15 +37,15 @@
 namespace vkl {
 namespace {
 
-constexpr int NCW = 15;                // consumer warps (+1 producer warp = 512 threads of 128 registers)
+constexpr int NCW = (int)MEGA_NCW;     // consumer warps (15 + 1 producer warp = 512 threads of 128 registers)
 constexpr int CT = NCW * 32;           // consumer threads
 constexpr int THREADS = CT + 32;       // + producer warp
 constexpr int UPW = (int)MEGA_UPW;     // units (one Q8_0 block x 32 rows) per consumer warp and ring stage
 constexpr int SU = NCW * UPW;          // units per ring stage
 static_assert(SU == (int)MEGA_SU, "host and device agree on the stage size");
 constexpr uint32_t UNIT_CODES = MEGA_UNIT_CODES, UNIT_SCALES = MEGA_UNIT_SCALES;
-constexpr uint32_t STAGE_CODES = SU * UNIT_CODES, STAGE_SCALES = SU * UNIT_SCALES;
-constexpr uint32_t STAGE_BYTES = STAGE_CODES + STAGE_SCALES;  // 32640
+constexpr uint32_t UNIT_BYTES = UNIT_CODES + UNIT_SCALES;  // a unit's codes, then its 32 scales
+constexpr uint32_t STAGE_BYTES = SU * UNIT_BYTES;          // 32640
 static_assert(STAGE_BYTES == MEGA_STAGE_BYTES, "host and device agree on the stage size");
 constexpr uint32_t XB_BYTES = 64;      // the input vector in shared memory: fp16, 64 bytes per block of 32 inputs
 constexpr int MAX_NST = 12;            // ring stages are a launch parameter (whatever fits), at most this many
@@ -274,7 +278,7 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
           // contiguous in [heads, maxlen, head_dim], up to kv_rps rows per stage
           const uint32_t rowb = p.head_dim * 2u;
           for (uint32_t kv = 0; kv < 2 && !stop; ++kv) {
-            const uint8_t *src = (kv ? e.scales0 : e.codes0) + ((size_t)kv_head * p.maxlen + kv_c0) * rowb;
+            const uint8_t *src = (kv ? e.src2 : e.src) + ((size_t)kv_head * p.maxlen + kv_c0) * rowb;
             for (uint32_t r0 = kv_c0; r0 < kv_c1; r0 += kv_rps) {
               if (issued >= NST && !(p.timing_mode & 128u) && !c.wait(s32(&empty[slot]), ph ^ 1u, 2, 0)) {
                 stop = true;
@@ -306,15 +310,10 @@ __device__ __forceinline__ void producer(const Ctx &c, unsigned char *ring, uint
         if (p.timing_mode & 2u) {  // diagnostic: consumer speed without the weight stream
           mbar_arrive(fb);
         } else {
-          const uint32_t n0 = e.n0, n1 = e.n1;
-          const uint32_t dst = s32(ring + (size_t)slot * STAGE_BYTES);
-          mbar_expect(fb, (n0 + n1) * (UNIT_CODES + UNIT_SCALES));
-          bulk_g2s(dst, e.codes0, n0 * UNIT_CODES, fb);
-          bulk_g2s(dst + STAGE_CODES, e.scales0, n0 * UNIT_SCALES, fb);
-          if (n1) {
-            bulk_g2s(dst + n0 * UNIT_CODES, e.codes1, n1 * UNIT_CODES, fb);
-            bulk_g2s(dst + STAGE_CODES + n0 * UNIT_SCALES, e.scales1, n1 * UNIT_SCALES, fb);
-          }
+          // a CTA's units of an op are consecutive in memory, across its tiles: one copy per stage
+          const uint32_t bytes = (e.n0 + e.n1) * UNIT_BYTES;
+          mbar_expect(fb, bytes);
+          bulk_g2s(s32(ring + (size_t)slot * STAGE_BYTES), e.src, bytes, fb);
         }
         if (++slot == NST) {
           slot = 0;
@@ -439,7 +438,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     }
     {
       // the first loads together (one memory round trip when the producers are done), then the tag checks
-      constexpr int LFIRST = 3;  // K <= 11520 in one round trip
+      constexpr int LFIRST = (11008 / 8 + CT - 1) / CT;  // K <= 11008 (the largest input of the model shapes) in one round trip
       uint4 la[LFIRST], lb[LFIRST];
 #pragma unroll
       for (int j = 0; j < LFIRST; ++j) {
@@ -572,9 +571,9 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
         const uint32_t u = warp * UPW + q;
         have[q] = ok && u < n0 + n1;
         if (have[q]) {
-          wa[q] = *reinterpret_cast<const uint4 *>(st + u * UNIT_CODES + lane * 16);        // rows g, g + 8 of the tile
-          wb[q] = *reinterpret_cast<const uint4 *>(st + u * UNIT_CODES + 512 + lane * 16);  // rows 16 + g, 24 + g
-          dsc[q] = *reinterpret_cast<const uint2 *>(st + STAGE_CODES + u * UNIT_SCALES + g * 8);  // their four block scales
+          wa[q] = *reinterpret_cast<const uint4 *>(st + u * UNIT_BYTES + lane * 16);        // rows g, g + 8 of the tile
+          wb[q] = *reinterpret_cast<const uint4 *>(st + u * UNIT_BYTES + 512 + lane * 16);  // rows 16 + g, 24 + g
+          dsc[q] = *reinterpret_cast<const uint2 *>(st + u * UNIT_BYTES + UNIT_CODES + g * 8);  // their four block scales
         }
       }
       __syncwarp();
@@ -1228,10 +1227,12 @@ int decode_mega_max_stages() { return MAX_NST; }
 // Packs the op's matrices from the library's tiled planes (common.cuh) into the stream layout of
 // MegaOp: one CTA per (block, tile), one thread per 16-byte piece. A 32-row tile's unit is the two
 // 512-byte (16 rows x 32 columns) units of the planes that hold its rows, unchanged (codes stay
-// biased by +128 in MMA fragment order), and the 32 scales in the order the consumer lanes read them.
+// biased by +128 in MMA fragment order), followed by the 32 scales in the order the consumer lanes
+// read them. Tiles are stored in the order the decode kernel's CTAs take them (mega_stream_tile), so
+// that every CTA reads one consecutive range of the op.
 namespace {
 __global__ void __launch_bounds__(64) mega_pack_kernel(const uint8_t *p0, const uint8_t *p1, const uint8_t *p2, uint32_t nmat, int swiglu, uint32_t N,
-                                                       uint32_t K, uint8_t *codes, uint8_t *scales) {
+                                                       uint32_t K, uint32_t tiles, uint32_t grid, uint8_t *stream) {
   const uint32_t b = blockIdx.x, t = blockIdx.y, blocks = K / 32;
   const uint32_t half = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tpm = (N + 31) / 32;
@@ -1252,8 +1253,9 @@ __global__ void __launch_bounds__(64) mega_pack_kernel(const uint8_t *p0, const 
   const bool in = tile16 < L.tiles;
   uint4 w = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // code 0, biased
   if (in) w = *reinterpret_cast<const uint4 *>(src + (((size_t)tile16 * L.groups * 4 + b) * 32 + lane) * 16);
-  const size_t unit = (size_t)t * blocks + b;
-  reinterpret_cast<uint4 *>(codes + unit * MEGA_UNIT_CODES)[half * 32 + lane] = w;
+  const size_t unit = (size_t)mega_stream_tile(t, tiles, grid) * blocks + b;
+  uint8_t *dst = stream + unit * (MEGA_UNIT_CODES + MEGA_UNIT_SCALES);
+  reinterpret_cast<uint4 *>(dst)[half * 32 + lane] = w;
   if (lane < 16) {
     // scales of the unit: [g][row g | g + 8 of half 0, row g | g + 8 of half 1] as fp16
     const uint32_t g = lane & 7, up8 = lane >> 3;
@@ -1262,15 +1264,15 @@ __global__ void __launch_bounds__(64) mega_pack_kernel(const uint8_t *p0, const 
       const unsigned short *sc = reinterpret_cast<const unsigned short *>(src + L.codes_bytes());
       d = sc[(((size_t)tile16 * L.groups + (b >> 2)) * 8 + g) * 8 + up8 * 4 + (b & 3)];
     }
-    reinterpret_cast<unsigned short *>(scales + unit * MEGA_UNIT_SCALES)[g * 4 + half * 2 + up8] = d;
+    reinterpret_cast<unsigned short *>(dst + MEGA_UNIT_CODES)[g * 4 + half * 2 + up8] = d;
   }
 }
 }  // namespace
 
-cudaError_t launch_mega_pack(const uint8_t *const planes[3], uint32_t nmat, int swiglu, uint32_t N, uint32_t K, uint32_t tiles, uint8_t *codes,
-                             uint8_t *scales, cudaStream_t s) {
-  if (K % 32 || tiles == 0 || tiles > 65535u) return cudaErrorInvalidValue;
-  mega_pack_kernel<<<dim3(K / 32, tiles), 64, 0, s>>>(planes[0], planes[1], planes[2], nmat, swiglu, N, K, codes, scales);
+cudaError_t launch_mega_pack(const uint8_t *const planes[3], uint32_t nmat, int swiglu, uint32_t N, uint32_t K, uint32_t tiles, uint32_t grid,
+                             uint8_t *stream, cudaStream_t s) {
+  if (K % 32 || tiles == 0 || tiles > 65535u || grid == 0) return cudaErrorInvalidValue;
+  mega_pack_kernel<<<dim3(K / 32, tiles), 64, 0, s>>>(planes[0], planes[1], planes[2], nmat, swiglu, N, K, tiles, grid, stream);
   return cudaGetLastError();
 }
 

@@ -144,12 +144,13 @@ struct alignas(16) MegaOp {
   // The op's weights, packed for the kernel (mega_pack): per 32-row tile and block one unit of
   // MEGA_UNIT_CODES + MEGA_UNIT_SCALES bytes. Codes: the two 512-byte (16 rows x 32 columns) units of the
   // library's tiled planes (common.cuh) that hold the tile's rows, as they are: MMA A-fragment order, biased
-  // by +128. Scales: [g 0..7][rows g, g + 8, 16 + g, 24 + g] fp16. Which matrix row a tile row is:
+  // by +128. Then the unit's scales: [g 0..7][rows g, g + 8, 16 + g, 24 + g] fp16. Units of a tile follow each
+  // other block by block, tiles in the order of mega_stream_tile: everything one CTA reads of the op is one
+  // consecutive range. Which matrix row a tile row is:
   //   one matrix         tile t, row r = matrix row 32 t + r
   //   nmat = 3 (K, Q, V) tile t = matrix t / tpm, rows 32 (t % tpm) + r, tpm = ceil(N / 32)
   //   SwiGLU (gate, up)  tile t: rows 0..15 = gate rows 16 t + r, rows 16..31 = up rows 16 t + r - 16
   const uint8_t *codes;
-  const uint8_t *scales;
   const float *norm_w;  // fused RMSNorm of the input, or null
   float eps;
   uint32_t track_argmax;  // lm head: keep a per-CTA (max, index) candidate
@@ -168,26 +169,35 @@ struct alignas(16) MegaOp {
   __half *kcache, *vcache;  // MK_ATTN_PART
 };
 // One ring stage of the persistent kernel: up to MEGA_SU consecutive units (one Q8_0 block x
-// 32 rows each) of a CTA's weight stream, as at most two contiguous runs: the tail of one
-// tile and the head of the next.
+// 32 rows each) of a CTA's weight stream, one range of memory: the tail of one tile (n0 units)
+// and, when that ends inside the stage, the head of the CTA's next tile (n1 units).
 //
 // An entry with n0 == MEGA_KV_MARK stands for the K and V rows of an attention op instead:
-// codes0 / scales0 are the layer's K / V cache. How many ring stages it becomes depends on the
+// src / src2 are the layer's K / V cache. How many ring stages it becomes depends on the
 // token's KV length: producer and consumers both derive this CTA's (head, split) row range from
 // the position and cut it into stages of mega_kv_rows_per_stage() rows, all K stages first.
 struct MegaStage {
-  const uint8_t *codes0, *scales0;
-  const uint8_t *codes1, *scales1;
-  uint32_t n0, n1;  // units of the first and of the second run
-  uint32_t tm, kg;  // consumers' view: local tile and first block of run 0; run 1 starts at block 0 of local tile tm + 1
+  const uint8_t *src, *src2;
+  uint32_t n0, n1;  // units of the first and of the second tile
+  uint32_t tm, kg;  // consumers' view: local tile and first block of the n0 units; the n1 units start at block 0 of local tile tm + 1
 };
 constexpr uint32_t MEGA_KV_MARK = 0xffffffffu;
+// Where tile t of an op (of `tiles` tiles, dealt to a grid of `grid` CTAs as tile0 + lt * grid) sits in the
+// op's weight stream: the tiles of one CTA are consecutive, CTAs in the order of their first tile.
+__host__ __device__ inline uint32_t mega_stream_tile(uint32_t t, uint32_t tiles, uint32_t grid) {
+  const uint32_t tile0 = t % grid, lt = t / grid, q = tiles / grid, r = tiles % grid;
+  return tile0 * q + (tile0 < r ? tile0 : r) + lt;
+}
 constexpr uint32_t MEGA_UNIT_CODES = 1024, MEGA_UNIT_SCALES = 64;  // 32 rows x 32 codes, 32 fp16 scales
 #ifndef VKL_MEGA_UPW
 #define VKL_MEGA_UPW 2
 #endif
 constexpr uint32_t MEGA_UPW = VKL_MEGA_UPW;       // units per consumer warp and stage
-constexpr uint32_t MEGA_SU = 15 * MEGA_UPW;       // units per stage
+#ifndef VKL_MEGA_NCW
+#define VKL_MEGA_NCW 15
+#endif
+constexpr uint32_t MEGA_NCW = VKL_MEGA_NCW;       // consumer warps of the kernel
+constexpr uint32_t MEGA_SU = MEGA_NCW * MEGA_UPW; // units per stage
 constexpr uint32_t MEGA_STAGE_BYTES = MEGA_SU * (MEGA_UNIT_CODES + MEGA_UNIT_SCALES);
 // Cache rows (head_dim fp16 values each) of one KV ring stage: whole rows, a multiple of 8.
 __host__ __device__ inline uint32_t mega_kv_rows_per_stage(uint32_t head_dim) { return (MEGA_STAGE_BYTES / (head_dim * 2u)) & ~7u; }
@@ -276,7 +286,7 @@ size_t decode_mega_xs_bytes(uint32_t max_blocks, uint32_t head_dim, uint32_t max
 // Packs up to three Q8_0 matrices (tiled planes) that share an input into one op's weight stream
 // (layout and row rules at MegaOp). tiles = the stream's 32-row tiles.
 cudaError_t launch_mega_pack(const uint8_t *const planes[3], uint32_t nmat, int swiglu, uint32_t N, uint32_t K, uint32_t tiles,
-                             uint8_t *codes, uint8_t *scales, cudaStream_t s);
+                             uint32_t grid, uint8_t *stream, cudaStream_t s);
 size_t decode_mega_smem(size_t xs_bytes, uint32_t nst, uint32_t red_slots);
 int decode_mega_max_k();
 int decode_mega_max_stages();

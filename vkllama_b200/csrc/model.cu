@@ -407,6 +407,7 @@ int build_mega(vkl_model *m) {
   auto slots = [&](uint32_t tiles) { return (tiles + G - 1) / G; };
   const uint32_t red_slots = std::max({slots(3 * ((m->dim_l + 31) / 32)), slots((c.dim + 31) / 32), slots((m->ffn_l + 15) / 16), slots((m->vocab_l + 31) / 32)});
   uint32_t nst = (uint32_t)decode_mega_max_stages();  // as many ring stages as fit
+  if (const char *rs = getenv("VKLLAMA_RING_STAGES")) nst = std::min(nst, std::max(2u, (uint32_t)atoi(rs)));  // experiments: a shallower ring
   while (nst >= 2 && decode_mega_smem(xs_bytes, nst, red_slots) > (size_t)m->dev->prop.sharedMemPerBlockOptin) --nst;
   if (nst < 2) return VKL_OK;
   int occ = 0;
@@ -458,14 +459,13 @@ int build_mega(vkl_model *m) {
         m->mega_packed.push_back(pk);
       }
       ++pack_index;
-      uint8_t *codes = pk->data(), *scales = codes + units * MEGA_UNIT_CODES;
+      uint8_t *codes = pk->data();
       if (!packed) {
-        cudaError_t pe = launch_mega_pack(planes, o.nmat, swiglu ? 1 : 0, o.N, o.K, o.tiles, codes, scales, m->stream);
+        cudaError_t pe = launch_mega_pack(planes, o.nmat, swiglu ? 1 : 0, o.N, o.K, o.tiles, (uint32_t)G, codes, m->stream);
         count_launches(1);
         if (pe != cudaSuccess && pack_status == VKL_OK) pack_status = fail(VKL_INTERNAL, "decode kernel: packing the weights failed: %s", cudaGetErrorString(pe));
       }
       o.codes = codes;
-      o.scales = scales;
     }
     int i = 0;
     for (uint32_t *p : outs) o.out_ll[i++] = p;
@@ -545,8 +545,8 @@ int build_mega(vkl_model *m) {
       for (uint32_t cta = 0; cta < m->heads_l * splits; ++cta) {
         MegaStage e = {};
         e.n0 = MEGA_KV_MARK;
-        e.codes0 = (const uint8_t *)o.kcache;
-        e.scales0 = (const uint8_t *)o.vcache;
+        e.src = (const uint8_t *)o.kcache;
+        e.src2 = (const uint8_t *)o.vcache;
         per_cta[cta].push_back(e);
       }
       continue;
@@ -557,10 +557,10 @@ int build_mega(vkl_model *m) {
       const size_t before = per_cta[cta].size();
       const uint32_t tile0 = ((uint32_t)cta + G - (o.rot % G)) % G;
       const uint32_t tl = tile0 < o.tiles ? (o.tiles - tile0 + G - 1) / G : 0u;
-      auto run = [&](uint32_t lt, uint32_t kg, const uint8_t *&codes, const uint8_t *&scales) {
-        const size_t unit = (size_t)(tile0 + lt * G) * o.blocks + kg;
-        codes = o.codes + unit * MEGA_UNIT_CODES;
-        scales = o.scales + unit * MEGA_UNIT_SCALES;
+      // the CTA's units of the op are consecutive in the packed stream (mega_stream_tile): a stage is one range
+      auto run = [&](uint32_t lt, uint32_t kg) {
+        const size_t unit = (size_t)mega_stream_tile(tile0 + lt * (uint32_t)G, o.tiles, (uint32_t)G) * o.blocks + kg;
+        return o.codes + unit * (MEGA_UNIT_CODES + MEGA_UNIT_SCALES);
       };
       uint32_t tm = 0, kg = 0;
       while (tm < tl) {
@@ -570,8 +570,9 @@ int build_mega(vkl_model *m) {
         e.n1 = cut.n1;
         e.tm = tm;
         e.kg = kg;
-        run(tm, kg, e.codes0, e.scales0);
-        if (cut.n1) run(tm + 1, 0, e.codes1, e.scales1);
+        e.src = run(tm, kg);
+        if (cut.n1 && run(tm + 1, 0) != e.src + (size_t)cut.n0 * (MEGA_UNIT_CODES + MEGA_UNIT_SCALES))
+          return fail(VKL_INTERNAL, "decode kernel: a stage's two runs are not consecutive");
         per_cta[cta].push_back(e);
         mega_stage_advance(cut, o.blocks, tm, kg);
       }
