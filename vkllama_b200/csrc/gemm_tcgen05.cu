@@ -36,18 +36,32 @@ constexpr int BM = 128, BK = 64;
 constexpr uint32_t A_TILE_BYTES = BM * BK * 2;  // 16 KB
 constexpr uint32_t GEMM_WAIT_LIMIT = 1u << 22;
 constexpr int GEMM_THREADS = 192;          // FP16 weights: TMA producer, MMA, four epilogue warps
-constexpr int GEMM_THREADS_Q8 = 192 + 128;  // + four warps dequantising the W tile
+#ifndef VKL_GEMM_NDW
+#define VKL_GEMM_NDW 16
+#endif
+constexpr int NDW = VKL_GEMM_NDW;               // warps dequantising the W tile: one warp issues an instruction every five cycles or so
+                                                // (a dependent chain of permutes, multiplies and stores), so it takes several per SM
+                                                // sub-partition to keep up with the weight stream
+constexpr int GEMM_THREADS_Q8 = 192 + 32 * NDW;
 
-template <int BN> struct Cfg {
+// Q8_0 weights: what a dequantising warp keeps in flight from DRAM, in shared memory (asynchronous 16-byte
+// copies, waited for in order): Q8_UNITS_AHEAD units of 512 bytes of codes + 128 bytes of scales per warp.
+constexpr uint32_t Q8_UNIT_STAGING = 512 + 128, Q8_UNITS_AHEAD = 4;
+constexpr uint32_t Q8_STAGING_BYTES = NDW * Q8_UNITS_AHEAD * Q8_UNIT_STAGING;  // 40 KB
+
+template <int BN, bool Q8 = false> struct Cfg {
   static constexpr uint32_t B_TILE_BYTES = BN * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
-  static constexpr int STAGES = (192 * 1024 / (int)STAGE_BYTES) < 8 ? (192 * 1024 / (int)STAGE_BYTES) : 8;  // up to 192 KB of stages
-  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
+  static constexpr int RING_BYTES = 192 * 1024 - (Q8 ? (int)Q8_STAGING_BYTES : 0);  // up to 192 KB of stages (and staging)
+  static constexpr int STAGES = (RING_BYTES / (int)STAGE_BYTES) < 8 ? (RING_BYTES / (int)STAGE_BYTES) : 8;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + (Q8 ? Q8_STAGING_BYTES : 0) + 1024;
 };
 
 __device__ __forceinline__ uint32_t sa(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+// Bounded wait. `sleep_ns`: pause between polls, for the waits that are long by design (the epilogue warps wait
+// for the whole K loop): a warp that spins takes issue slots from the warps that work on the same sub-partition.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t sleep_ns = 0) {
   for (uint32_t i = 0; i < GEMM_WAIT_LIMIT; ++i) {
     uint32_t ok;
     asm volatile(
@@ -56,6 +70,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
         : "r"(bar), "r"(parity)
         : "memory");
     if (ok) return true;
+    if (sleep_ns) __nanosleep(sleep_ns);
   }
   return false;
 }
@@ -124,7 +139,7 @@ __device__ __forceinline__ void dequant_unit(unsigned char *wtile, uint32_t row0
 template <int BN, bool Q8>
 __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, Q8>;
   extern __shared__ unsigned char smem_raw[];
   // swizzle atoms are 1024 bytes: align the stage ring
   unsigned char *stages = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -139,7 +154,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
   const uint32_t nkb = p.K / BK;
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sa(&full[s])), "r"(Q8 ? 5u : 1u) : "memory");  // the TMA lane (+ one lane per dequantising warp)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sa(&full[s])), "r"(Q8 ? 1u + NDW : 1u) : "memory");  // the TMA lane (+ one lane per dequantising warp)
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&empty[s])) : "memory");
     }
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&acc_ready)) : "memory");
@@ -172,40 +187,50 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
   } else if (Q8 && warp >= 6) {
     // ------------------------------------------- W tile: Q8_0 -> fp16 in shared memory
     // BN rows x 64 columns = (BN / 16) row tiles x 2 blocks: units of 512 bytes of codes, dealt round robin to
-    // the four warps. The scales of a row tile and 4-block group are 8 x 16 bytes: row g's four blocks, then row g + 8's.
-    const uint32_t dw = warp - 6, g = lane >> 2;
+    // the dequantising warps. The scales of a row tile and 4-block group are 8 x 16 bytes: row g's four blocks, then row g + 8's.
+    const uint32_t dw = warp - 6, g = lane >> 2, t = lane & 3;
     const uint32_t tiles16 = (p.N + 15) / 16, groups = ((p.K + 31) / 32 + 3) / 4;
-    constexpr uint32_t UNITS = (BN / 16) * 2, UPQ = UNITS / 4;  // units per stage, and of those this warp's
-    constexpr uint32_t PF = UPQ >= 8 ? 1 : 8 / UPQ;              // stages whose units are requested ahead
-    // The codes of a stage come from DRAM (a microsecond away) and a stage is converted in a fraction of that:
-    // the loads of the next PF stages are kept in flight in registers while one stage is converted and stored.
-    uint4 wq[PF][UPQ];
-    uint32_t dq[PF][UPQ];  // the two scales of the lane's rows g and g + 8, packed
+    constexpr uint32_t UNITS = (BN / 16) * 2, UPQ = (UNITS + NDW - 1) / NDW;  // units per stage, and of those at most this warp's
+    constexpr uint32_t PF = Q8_UNITS_AHEAD / UPQ;                            // stages whose units are requested ahead
+    static_assert(UPQ <= Q8_UNITS_AHEAD && PF >= 1, "staging holds at least one stage of a warp's units");
+    // The codes of a stage come from DRAM (a microsecond away) and a stage is converted in a fraction of that, so the
+    // next PF stages' units are kept in flight. They travel as asynchronous copies into this warp's own staging
+    // area, which complete in order (cp.async groups): loads into registers would share the warp's few scoreboards,
+    // and the wait for the oldest would also wait for the youngest, one DRAM round trip per stage.
+    unsigned char *stg = stages + (size_t)C::STAGES * C::STAGE_BYTES + (size_t)dw * Q8_UNITS_AHEAD * Q8_UNIT_STAGING;
+    auto unit_of = [&](uint32_t kb, uint32_t j, uint32_t &tile, uint32_t &b) {
+      const uint32_t u = dw + NDW * j;
+      tile = n0 / 16 + (u >> 1);  // row tile of the matrix
+      b = kb * 2 + (u & 1);       // block of the row
+      return u < UNITS && kb < nkb && tile < tiles16;
+    };
     auto request = [&](uint32_t kb, uint32_t slot) {
 #pragma unroll
       for (uint32_t j = 0; j < UPQ; ++j) {
-        const uint32_t u = dw + 4 * j, tl = u >> 1, bl = u & 1;  // row tile inside the W tile, block inside the K step
-        const uint32_t tile = n0 / 16 + tl, b = kb * 2 + bl;
-        wq[slot][j] = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // code 0 (stored biased by 128)
-        dq[slot][j] = 0;
-        if (kb < nkb && tile < tiles16) {
-          wq[slot][j] = ldg_stream(p.w_codes + (((size_t)tile * groups * 4 + b) * 32 + lane) * 16);
-          const unsigned short *sc = reinterpret_cast<const unsigned short *>(p.w_scales) + (((size_t)tile * groups + (b >> 2)) * 8 + g) * 8 + (b & 3);
-          dq[slot][j] = (uint32_t)__ldg(sc) | ((uint32_t)__ldg(sc + 4) << 16);
+        uint32_t tile, b;
+        if (unit_of(kb, j, tile, b)) {
+          const uint32_t dst = sa(stg + (slot * UPQ + j) * Q8_UNIT_STAGING);
+          const unsigned char *src = p.w_codes + (((size_t)tile * groups * 4 + b) * 32 + lane) * 16;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + lane * 16), "l"(src) : "memory");
+          if (t == 0) {  // the 4-block group's scales of rows g and g + 8: 16 bytes
+            const unsigned char *sc = p.w_scales + (((size_t)tile * groups + (b >> 2)) * 8 + g) * 16;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512 + g * 16), "l"(sc) : "memory");
+          }
         }
       }
+      asm volatile("cp.async.commit_group;" ::: "memory");  // one group per stage, also when it is empty
     };
 #pragma unroll
     for (uint32_t i = 0; i < PF; ++i) request(i, i);
     for (uint32_t kb0 = 0; kb0 < nkb; kb0 += PF) {
       bool stop = false;
 #pragma unroll
-      for (uint32_t i = 0; i < PF; ++i) {  // register slots are indexed by compile-time constants
+      for (uint32_t i = 0; i < PF; ++i) {  // staging slots are indexed by compile-time constants
         const uint32_t kb = kb0 + i;
         if (kb >= nkb || stop) continue;
         const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
         uint32_t ok = 1;
-        if (lane == 0 && use > 0) ok = mbar_wait_bounded(sa(&empty[s]), (use - 1) & 1u) ? 1u : 0u;
+        if (lane == 0 && use > 0) ok = mbar_wait_bounded(sa(&empty[s]), (use - 1) & 1u, 100) ? 1u : 0u;
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) {
           if (lane == 0) failed_s = 4;
@@ -216,20 +241,37 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
           stop = true;
           continue;
         }
+        asm volatile("cp.async.wait_group %0;" ::"n"(PF - 1) : "memory");  // this stage's copies (the oldest group) have landed
+        __syncwarp();
         unsigned char *wt = stages + (size_t)s * C::STAGE_BYTES + A_TILE_BYTES;
 #pragma unroll
         for (uint32_t j = 0; j < UPQ; ++j) {
-          const uint32_t u = dw + 4 * j;
-          dequant_unit(wt, (u >> 1) * 16, (u & 1) * 4, wq[i][j], dq[i][j] & 0xffffu, dq[i][j] >> 16, lane);
+          const uint32_t u = dw + NDW * j;
+          if (u >= UNITS) continue;
+          uint32_t tile, b;
+          uint4 w = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // code 0 (stored biased by 128): rows beyond the matrix
+          uint32_t lo = 0, hi = 0;
+          if (unit_of(kb, j, tile, b)) {
+            const unsigned char *src = stg + (i * UPQ + j) * Q8_UNIT_STAGING;
+            w = *reinterpret_cast<const uint4 *>(src + lane * 16);
+            const uint4 d = *reinterpret_cast<const uint4 *>(src + 512 + g * 16);  // x, y: row g's four blocks; z, w: row g + 8's
+            const uint32_t sh = (b & 1) * 16;
+            lo = ((b & 2 ? d.y : d.x) >> sh) & 0xffffu;
+            hi = ((b & 2 ? d.w : d.z) >> sh) & 0xffffu;
+          }
+          dequant_unit(wt, (u >> 1) * 16, (u & 1) * 4, w, lo, hi, lane);
         }
-        request(kb + PF, i);  // refill this slot for the stage PF steps ahead
-        // the tensor core reads shared memory through the async proxy: order this warp's stores before its arrival
+        // the tensor core reads shared memory through the async proxy: order this warp's stores before its arrival.
+        // (The fence waits for the thread's memory operations in flight: the refill below comes after it, or every
+        // stage would cost a DRAM round trip.)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
+        __syncwarp();          // every lane has fenced, and has read the staging slot
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sa(&full[s])) : "memory");
+        request(kb + PF, i);   // refill the slot for the stage PF steps ahead
       }
       if (stop) break;
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");  // nothing of this warp may still be landing when the CTA exits
   } else if (warp == 1) {
     // --------------------------------------------------------------------- MMA
     if (lane == 0) {
@@ -264,7 +306,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
     const uint32_t quad = warp & 3u;
     const uint32_t row = m0 + quad * 32 + lane;
     uint32_t ok = 1;
-    if (lane == 0) ok = mbar_wait_bounded(sa(&acc_ready), 0) ? 1u : 0u;
+    if (lane == 0) ok = mbar_wait_bounded(sa(&acc_ready), 0, 1000) ? 1u : 0u;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     if (!ok) {
       if (lane == 0) failed_s = 3;
@@ -362,10 +404,10 @@ template <int BN, bool Q8> cudaError_t launch_bn(const GemmParams &p, cudaStream
   } else if (!make_map(&mw, p.w, p.N, p.K, BN)) {
     return cudaErrorInvalidValue;
   }
-  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN>::SMEM);
+  cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN, Q8>::SMEM);
   if (e != cudaSuccess) return e;
   // x = row tile, so that the CTAs sharing one tile of W run together and W crosses HBM once
-  gemm_tcgen05_kernel<BN, Q8><<<dim3((p.M + BM - 1) / BM, (p.N + BN - 1) / BN), Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, Cfg<BN>::SMEM, s>>>(ma, mw, p);
+  gemm_tcgen05_kernel<BN, Q8><<<dim3((p.M + BM - 1) / BM, (p.N + BN - 1) / BN), Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, Cfg<BN, Q8>::SMEM, s>>>(ma, mw, p);
   return cudaGetLastError();
 }
 
@@ -380,27 +422,41 @@ static size_t sm_count() {
 
 bool gemm_tcgen05_supported(uint32_t M, uint32_t N, uint32_t K) { return M >= 1 && K % BK == 0 && K >= BK && (N % 8) == 0; }
 
+// W-tile width. A grid runs in waves of one CTA per SM, and a last wave that fills a fraction of the SMs takes
+// as long as a full one: pick the width with the smallest waves x (time of one tile). A tile's time is a fixed
+// part (the K loop's pipeline latencies, the A tile's copies, the epilogue) plus a part that grows with the
+// width; the fixed part dominates, most of all for FP16 weights.
+static int forced_bn() {
+  static const int forced = [] { const char *e = getenv("VKLLAMA_GEMM_BN"); return e ? atoi(e) : 0; }();  // experiments
+  return forced == 256 || forced == 128 || forced == 64 || forced == 32 ? forced : 0;
+}
+static int pick_bn(const GemmParams &p, bool q8) {
+  if (int f = forced_bn()) return (q8 || f >= 128) ? f : 128;
+  const size_t mt = (p.M + BM - 1) / BM, sms = sm_count();
+  int best = 0;
+  double best_cost = 0.0;
+  for (int bn : {256, 128, 64, 32}) {
+    if (!q8 && bn < 128) break;
+    const size_t ctas = mt * ((p.N + bn - 1) / bn), waves = (ctas + sms - 1) / sms;
+    const double cost = (double)waves * (bn + (q8 ? 240.0 : 1200.0));  // fitted to measured wave times (K = 4096): 32 + 0.135 bn us, 27 + 0.022 bn us
+    if (!best || cost < best_cost) {
+      best = bn;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
 cudaError_t launch_gemm_f16_tcgen05(const GemmParams &p, cudaStream_t s) {
   if (!gemm_tcgen05_supported(p.M, p.N, p.K)) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(p.a) | reinterpret_cast<uintptr_t>(p.w)) & 15) return cudaErrorMisalignedAddress;
-  // 128 x 256 tiles halve the shared-memory reads per flop; use them once they still fill the GPU
-  const size_t tiles256 = (size_t)((p.M + BM - 1) / BM) * ((p.N + 255) / 256);
-  if (tiles256 >= sm_count()) return launch_bn<256, false>(p, s);
-  return launch_bn<128, false>(p, s);
-}
-
-// The widest W tile whose grid still gives every SM a CTA (narrow tiles re-read A from L2 more often,
-// but with few rows of A an idle SM costs more than that).
-static int pick_bn(const GemmParams &p) {
-  const size_t mt = (p.M + BM - 1) / BM, sms = sm_count();
-  for (int bn : {256, 128, 64}) if (mt * ((p.N + bn - 1) / bn) >= sms) return bn;
-  return 32;
+  return pick_bn(p, false) == 256 ? launch_bn<256, false>(p, s) : launch_bn<128, false>(p, s);
 }
 
 cudaError_t launch_gemm_q8_tcgen05(const GemmParams &p, cudaStream_t s) {
   if (!gemm_tcgen05_supported(p.M, p.N, p.K) || !p.w_codes || !p.w_scales) return cudaErrorInvalidValue;
   if (reinterpret_cast<uintptr_t>(p.a) & 15) return cudaErrorMisalignedAddress;
-  switch (pick_bn(p)) {
+  switch (pick_bn(p, true)) {
     case 256: return launch_bn<256, true>(p, s);
     case 128: return launch_bn<128, true>(p, s);
     case 64: return launch_bn<64, true>(p, s);
