@@ -69,7 +69,10 @@ def test_device_synthetic_generator_matches_host_generator(dev):
 @pytest.mark.parametrize("M,N,K,act", [
     (1, 4096, 4096, 0), (1, 11008, 4096, 0), (1, 4096, 11008, 0), (1, 32000, 4096, 0),
     (2, 4096, 4096, 0), (8, 4096, 4096, 1), (9, 17, 256, 0), (16, 4096, 4096, 0), (33, 1000, 4096, 0),
-    (64, 4096, 4096, 0), (100, 256, 11008, 0), (5, 16, 32, 0), (3, 50, 96, 1)])
+    (64, 4096, 4096, 0), (100, 256, 11008, 0), (5, 16, 32, 0), (3, 50, 96, 1),
+    # from 64 rows on: the tcgen05 GEMM with the dequantising warps, every tile width (32 / 64 / 128 / 256 columns by
+    # rows and matrix size), several row tiles, a ragged last column tile, one and two K steps
+    (512, 1024, 4096, 0), (512, 11008, 256, 0), (200, 352, 1024, 1), (128, 11008, 128, 0), (64, 40, 64, 0), (130, 2048, 2048, 0)])
 def test_matmul_q8_0(dev, M, N, K, act):
     w = O.synth_q8_0(31, 1, N, K)
     x = O.synth_f16(31, 2, M * K).reshape(M, K)
@@ -185,7 +188,7 @@ def test_feed_forward_fp16(dev, M, dim, hidden):
 
 
 # ---- FeedForward (tests/test_feedforward.cpp:143-148 Q8_0: dims 16,8,256,17; 7B) --
-@pytest.mark.parametrize("M,dim,hidden", [(64, 32, 256), (1, 4096, 11008), (4, 4096, 11008), (17, 64, 96)])
+@pytest.mark.parametrize("M,dim,hidden", [(64, 32, 256), (1, 4096, 11008), (4, 4096, 11008), (17, 64, 96), (128, 1024, 2752)])
 def test_feed_forward_q8_0(dev, M, dim, hidden):
     gate = O.synth_q8_0(51, 1, hidden, dim)
     down = O.synth_q8_0(51, 2, dim, hidden)

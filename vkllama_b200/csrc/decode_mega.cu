@@ -209,8 +209,8 @@ struct Ctx {
   volatile uint32_t *abort_s;  // shared flag: some wait of this CTA timed out or *error was seen
   __device__ __forceinline__ bool aborted() const { return *abort_s != 0; }
   // Under tensor parallelism an input may sit behind an all-reduce that is itself waiting for a slow
-  // rank: the input's wait must outlast that one, so that the error names the wait that really failed.
-  __device__ __forceinline__ uint32_t ll_limit() const { return p.tp_size > 1 ? (p.wait_limit < 0x80000000u ? 2u * p.wait_limit : 0xffffffffu) : p.wait_limit; }
+  // rank: the input's wait must outlast that one (four times its polls), so that the error names the wait that really failed.
+  __device__ __forceinline__ uint32_t ll_limit() const { return p.tp_size > 1 ? (p.wait_limit < 0x40000000u ? 4u * p.wait_limit : 0xffffffffu) : p.wait_limit; }
   __device__ __forceinline__ void raise(uint32_t code) const {
     *abort_s = 1;
     atomicCAS(p.error, 0u, code);
@@ -356,7 +356,10 @@ __device__ VKL_SLOW bool grid_barrier(const Ctx &c, uint64_t target, uint32_t ro
     const uint32_t tgt = round;
     bool ok = false;
   #pragma unroll 1
-    for (uint32_t i = 0; i < c.p.wait_limit; ++i) {
+    // (under tensor parallelism a CTA without a tile of the projections runs ahead to this barrier while others
+    // wait for another rank's partial sums: the barrier's wait outlasts theirs, so that the error names theirs)
+    const uint32_t limit = c.p.tp_size > 1 ? (c.p.wait_limit < 0x10000000u ? 16u * c.p.wait_limit : 0xffffffffu) : c.p.wait_limit;
+    for (uint32_t i = 0; i < limit; ++i) {
       if (*seen_s == tgt || ld_acq_u64(c.p.bar) >= target) {
         ok = true;
         break;
@@ -517,7 +520,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   // EPI_ADD: this thread's residual value, requested now so that its memory round trip is not
   // on the path between the end of the stream and the publication of the results
   float resid = 0.f;
-  if (op.epi == EPI_ADD && tid < tl * 32) {
+  if ((op.epi == EPI_ADD || op.epi == EPI_REDUCE) && tid < tl * 32) {
     const uint32_t n = (tile0 + (tid >> 5) * G) * 32 + (tid & 31);
     if (n < op.N) resid = __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
   }
@@ -643,6 +646,50 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
       if (op.epi == EPI_ADD) {
         const float res = idx == tid ? resid : __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
         op.out_ll[0][n] = ll_pack(__float2half_rn(round_h(sum) + res), tag_out);
+      } else if (op.epi == EPI_REDUCE) {
+        // this rank's share of a row-split projection, reduced in place: the row's raw fp32 sum and the all-reduce's
+        // sequence number go as one 8-byte word into slot [parity][my rank] of every OTHER rank's exchange buffer
+        // (plain peer stores over NVLink; the word is its own arrival flag); then this thread polls (bounded, all
+        // missing words per round) the same row's words of the other ranks in its own buffer, adds in rank order (the
+        // same order on every rank: bit-identical residual streams) and publishes x = fp16(fp16(sum) + x).
+        const MegaParams &pp = c.p;
+        const uint32_t tp = pp.tp_size, me = pp.tp_rank;
+        const size_t par = (size_t)(ar_seq & 1u) * tp;
+        for (uint32_t rk = 0; rk < tp; ++rk) {
+          if (rk == me) continue;
+          uint32_t *dst = static_cast<uint32_t *>(pp.tp_peer[rk]) + 2 * ((par + me) * pp.dim + n);
+          asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(sum)), "r"(ar_seq) : "memory");
+        }
+        const float res = idx == tid ? resid : __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
+        const uint32_t *mine = static_cast<const uint32_t *>(pp.tp_peer[me]) + 2 * (par * pp.dim + n);
+        float part[8];
+        uint32_t missing = ((1u << tp) - 1u) & ~(1u << me);
+        part[me & 7u] = sum;
+        const uint32_t limit = pp.wait_limit;
+      #pragma unroll 1
+        for (uint32_t itw = 0; missing && itw < limit; ++itw) {
+#pragma unroll
+          for (uint32_t r = 0; r < 8; ++r) {
+            if (missing & (1u << r)) {
+              const uint2 w = ld_vol_v2(mine + 2 * (size_t)r * pp.dim);
+              if (w.y == ar_seq) {
+                part[r] = __uint_as_float(w.x);
+                missing &= ~(1u << r);
+              }
+            }
+          }
+          if (itw > 100000u) __nanosleep(64);
+          if ((itw & 1023u) == 1023u && (*(volatile uint32_t *)pp.error != 0u || c.aborted())) break;
+        }
+        if (missing) {
+          c.raise(4);
+        } else {
+          float s = 0.f;
+#pragma unroll
+          for (uint32_t r = 0; r < 8; ++r)
+            if (r < tp) s += part[r];
+          op.out_ll[0][n] = ll_pack(__float2half_rn(round_h(s) + res), tag_out);
+        }
       } else if (op.epi == EPI_PARTIAL) {
         // this rank's share of a row-split projection: the raw fp32 sum and the all-reduce's
         // sequence number go, as one 8-byte word, into slot [parity][my rank] of every rank's
@@ -1124,6 +1171,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
       case MK_EMBED: embed_op(c, tok, tag(oi)); break;
       case MK_MATVEC: matvec_op<TIMED, DBG>(c, op, it, slot, ph, ring, full, empty, tabs, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_blocks * XB_BYTES), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, seq0 + ar_i + 1,
                          tag(op.src_op), tag(oi), trace);
+        if (op.epi == EPI_REDUCE) ++ar_i;  // (every CTA counts it, with or without a tile of the op)
         break;
       case MK_ATTN_PART:
         attn_part_op(c, op, reinterpret_cast<float *>(xq), pos0, S_eff, tag(op.src_op), tag(op.tag_op), slot, ph, ring, full, empty);

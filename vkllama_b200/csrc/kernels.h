@@ -10,7 +10,10 @@ namespace vkl {
 
 // EPI_PARTIAL (persistent decode kernel only): raw fp32 partial sums of a row-split
 // projection, pushed into every tensor-parallel rank's exchange buffer.
-enum MvEpilogue { EPI_PLAIN = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
+// EPI_REDUCE (persistent decode kernel only): the same, and the thread that pushed a row's partial sum also
+// waits for the other ranks' sums of that row, adds them in rank order with the residual and publishes the row:
+// the all-reduce needs no op of its own.
+enum MvEpilogue { EPI_PLAIN = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3, EPI_REDUCE = 4 };
 
 // Y = epilogue(X . W^T) for up to three Q8_0 (tiled planes) or FP16 (row-major)
 // weight matrices [N,K] sharing one input X [M,K].

@@ -484,6 +484,10 @@ int build_mega(vkl_model *m) {
   // split CTA that finishes last, inside the attention op; "separate" = a combine op after a grid barrier.
   const char *cenv = getenv("VKLLAMA_DECODE_COMBINE");
   const bool last_combine = !(cenv && !strcmp(cenv, "separate"));
+  // Tensor parallelism: the all-reduce after o_proj and down runs inside their epilogues (EPI_REDUCE);
+  // VKLLAMA_TP_ALLREDUCE=separate keeps it as an op of its own behind them (MK_ALLREDUCE).
+  const char *arenv = getenv("VKLLAMA_TP_ALLREDUCE");
+  const bool reduce_in_place = !(arenv && !strcmp(arenv, "separate"));
   MegaOp e = {};
   e.kind = MK_EMBED;
   ops.push_back(e);  // op 0 writes x
@@ -516,11 +520,11 @@ int build_mega(vkl_model *m) {
       ops.push_back(r);
       return (uint32_t)ops.size() - 1;
     };
-    x_writer = matvec({y.wo}, nullptr, 0.f, ao, ao_writer, {x}, tp > 1 ? EPI_PARTIAL : EPI_ADD);
-    if (tp > 1) x_writer = allreduce();
+    x_writer = matvec({y.wo}, nullptr, 0.f, ao, ao_writer, {x}, tp > 1 ? (reduce_in_place ? EPI_REDUCE : EPI_PARTIAL) : EPI_ADD);
+    if (tp > 1 && !reduce_in_place) x_writer = allreduce();
     const uint32_t gu = matvec({y.gate, y.up}, (const float *)y.ffn_norm->data(), c.eps, x, x_writer, {tb}, EPI_SWIGLU);
-    x_writer = matvec({y.down}, nullptr, 0.f, tb, gu, {x}, tp > 1 ? EPI_PARTIAL : EPI_ADD);
-    if (tp > 1) x_writer = allreduce();
+    x_writer = matvec({y.down}, nullptr, 0.f, tb, gu, {x}, tp > 1 ? (reduce_in_place ? EPI_REDUCE : EPI_PARTIAL) : EPI_ADD);
+    if (tp > 1 && !reduce_in_place) x_writer = allreduce();
   }
   matvec({m->output}, (const float *)m->output_norm->data(), c.final_eps, x, x_writer, {}, EPI_PLAIN);
   ops.back().out[0] = (__half *)m->logits16->data();  // plain fp16 + fp32 logits and arg-max candidates: a grid barrier follows
