@@ -4,13 +4,17 @@
 // Replaces the reference's four weight shaders
 //   src/shaders/matmul_b0_fp16_x_q8_0.comp, kqv_fp16_x_q8_0.comp,
 //   ffn_up_and_gate_q8_0.comp, matmul_b0_tb_fp16_v2.comp / ffn_up_and_gate_fp16.comp
-// with one HBM-bound kernel: one CTA per 16-row tile, eight warps splitting K,
+// with one HBM-bound kernel: 16-row tiles dealt evenly to a grid that fits the GPU in one
+// wave (a CTA takes every gridDim.x-th tile and requests its next tile's first weights
+// before it reduces the current one), eight warps splitting K,
 // every lane streaming 128-bit weight loads that are already MMA A-fragments
 // (see Q8Layout), exact int8->fp16 conversion, m16n8k16 tensor-core products
 // with fp32 accumulation, the block scale applied in fp32 per 32-column block
 // (as the shaders do: `sums += sum_b * d`), a fixed-order cross-warp reduction
 // and the fused epilogue (scale/bias/SiLU, residual add, or SwiGLU).
 // The optional prologue fuses RMSNorm of the input row (decode path).
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -34,24 +38,29 @@ __global__ void __launch_bounds__(kThreads) mv_kernel(const MvParams p) {
   extern __shared__ __align__(16) unsigned char smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const uint32_t tile = blockIdx.x, mat = blockIdx.y;
+  const uint32_t mat = blockIdx.y, ntiles = (p.N + 15) / 16;
+  uint32_t tile = blockIdx.x;
   const uint32_t blocks = (p.K + 31) / 32, groups = (blocks + 3) / 4;
   const uint32_t g0 = (warp * groups) / kWarps, g1 = ((warp + 1) * groups) / kWarps;
 
   const uint8_t *cb[NW];
   const uint8_t *sb[NW];
+  uint32_t row_g = 0;
+  auto set_tile = [&](uint32_t tl) {  // where the loads of tile `tl` read
 #pragma unroll
-  for (int w = 0; w < NW; ++w) {
-    const uint32_t mi = (EPI == EPI_SWIGLU) ? w : mat;
-    if (Q8) {
-      cb[w] = p.codes[mi] + (size_t)tile * groups * 2048 + lane * 16;
-      sb[w] = p.scales[mi] + (size_t)tile * groups * 128 + g * 16;
-    } else {
-      cb[w] = p.codes[mi];
-      sb[w] = nullptr;
+    for (int w = 0; w < NW; ++w) {
+      const uint32_t mi = (EPI == EPI_SWIGLU) ? w : mat;
+      if (Q8) {
+        cb[w] = p.codes[mi] + (size_t)tl * groups * 2048 + lane * 16;
+        sb[w] = p.scales[mi] + (size_t)tl * groups * 128 + g * 16;
+      } else {
+        cb[w] = p.codes[mi];
+        sb[w] = nullptr;
+      }
     }
-  }
-  const uint32_t row_g = tile * 16 + g;
+    row_g = tl * 16 + g;
+  };
+  set_tile(tile);
 
   auto load = [&](Stage<Q8, NW> &st, uint32_t grp) {
 #pragma unroll
@@ -138,6 +147,7 @@ __global__ void __launch_bounds__(kThreads) mv_kernel(const MvParams p) {
     return *reinterpret_cast<uint4 *>(h);
   };
 
+  for (;; tile += gridDim.x) {  // this CTA's tiles
   float acc[NW][MT][4];
 #pragma unroll
   for (int w = 0; w < NW; ++w)
@@ -205,7 +215,16 @@ __global__ void __launch_bounds__(kThreads) mv_kernel(const MvParams p) {
       }
     }
   }
-  if (p.use_pdl) asm volatile("griddepcontrol.launch_dependents;");
+  // the next tile's first groups are requested now: the weight stream keeps going through the reduction below
+  const bool more = tile + gridDim.x < ntiles;
+  if (more) {
+    set_tile(tile + gridDim.x);
+#pragma unroll
+    for (int d = 0; d < KD; ++d)
+      if (g0 + d < g1) load(st[d], g0 + d);
+  } else if (p.use_pdl) {
+    asm volatile("griddepcontrol.launch_dependents;");
+  }
 
   // ---- fixed-order cross-warp reduction + epilogue ------------------------
 #pragma unroll
@@ -245,6 +264,9 @@ __global__ void __launch_bounds__(kThreads) mv_kernel(const MvParams p) {
       if (p.out_f32) p.out_f32[o] = __half2float(hy);
     }
   }
+  if (!more) break;
+  __syncthreads();  // `red` is free for the next tile
+  }
 }
 
 template <int MT, int EPI, bool XS, bool Q8>
@@ -257,8 +279,21 @@ cudaError_t launch_t(const MvParams &p, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
+  // One wave: the CTAs that fit the GPU at once, each with the same number of tiles (or one less).
+  static int sms = 0, dev_cached = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != dev_cached) {
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    dev_cached = dev;
+  }
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem) != cudaSuccess || per_sm < 1) per_sm = 1;
+  const uint32_t ntiles = (p.N + 15) / 16, nmat = EPI == EPI_SWIGLU ? 1u : p.nmat;
+  const uint32_t slots = std::max(1u, (uint32_t)(sms * per_sm) / nmat);
+  const uint32_t per_cta = (ntiles + slots - 1) / slots;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((p.N + 15) / 16, EPI == EPI_SWIGLU ? 1 : p.nmat, 1);
+  cfg.gridDim = dim3((ntiles + per_cta - 1) / per_cta, nmat, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
