@@ -406,7 +406,7 @@ template <bool TIMED, bool DBG>
 __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global, uint32_t &it, uint32_t &slot, uint32_t &ph,
                                           unsigned char *ring, uint64_t *full, uint64_t *empty, const MegaStage *tabs, __half *xs, float *xbias,
                                           const __half *zero16, float *red, float *ssum, Best &best, unsigned long long *tw, uint32_t ar_seq,
-                                          uint32_t tag_in, uint32_t tag_out, unsigned long long *trace) {
+                                          uint32_t tag_in, uint32_t tag_out, uint32_t tag_res, unsigned long long *trace) {
   const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const uint32_t G = gridDim.x, cta = blockIdx.x;
   // The op's entry sits in shared memory: fields are read where they are used (the prologue, then again
@@ -522,7 +522,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
   float resid = 0.f;
   if ((op.epi == EPI_ADD || op.epi == EPI_REDUCE) && tid < tl * 32) {
     const uint32_t n = (tile0 + (tid >> 5) * G) * 32 + (tid & 31);
-    if (n < op.N) resid = __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
+    if (n < op.N) resid = __half2float(ll_half(c.ll_wait1(op.out_ll[0] + n, tag_res)));  // (its tag is checked: the word may come from another CTA)
   }
   if (TIMED && tw) tw[1] = clock64();
   VKL_TRACE(1);
@@ -644,7 +644,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     const uint32_t n = (op.nmat == 3 ? gt % tpm : gt) * 32 + r;
     if (n < op.N && !c.aborted()) {
       if (op.epi == EPI_ADD) {
-        const float res = idx == tid ? resid : __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
+        const float res = idx == tid ? resid : __half2float(ll_half(c.ll_wait1(op.out_ll[0] + n, tag_res)));
         op.out_ll[0][n] = ll_pack(__float2half_rn(round_h(sum) + res), tag_out);
       } else if (op.epi == EPI_REDUCE) {
         // this rank's share of a row-split projection, reduced in place: the row's raw fp32 sum and the all-reduce's
@@ -660,7 +660,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
           uint32_t *dst = static_cast<uint32_t *>(pp.tp_peer[rk]) + 2 * ((par + me) * pp.dim + n);
           asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(__float_as_uint(sum)), "r"(ar_seq) : "memory");
         }
-        const float res = idx == tid ? resid : __half2float(ll_half(ld_vol_u32(op.out_ll[0] + n)));
+        const float res = idx == tid ? resid : __half2float(ll_half(c.ll_wait1(op.out_ll[0] + n, tag_res)));
         const uint32_t *mine = static_cast<const uint32_t *>(pp.tp_peer[me]) + 2 * (par * pp.dim + n);
         float part[8];
         uint32_t missing = ((1u << tp) - 1u) & ~(1u << me);
@@ -1057,7 +1057,7 @@ __device__ VKL_SLOW void argmax_final_op(const Ctx &c, float *sm, uint32_t pos0,
 // this all-reduce's number: x <- fp16( fp16(sum_r partial_r) + x ), the same rounding as
 // o_proj/down + residual add. No grid barrier and no separate flags: two parities of slots
 // keep a fast rank's next push from overwriting what a slow rank still reads.
-__device__ VKL_SLOW void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t seq, uint32_t tag_out) {
+__device__ VKL_SLOW void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t seq, uint32_t tag_out, uint32_t tag_res) {
   const MegaParams &p = c.p;
   const uint32_t tid = threadIdx.x, tp = p.tp_size;
   if (c.aborted()) return;
@@ -1090,7 +1090,7 @@ __device__ VKL_SLOW void allreduce_op(const Ctx &c, const MegaOp &op, uint32_t s
       }
       s += __uint_as_float(w.x);
     }
-    const float res = __half2float(ll_half(ld_vol_u32(op.out_ll[0] + i)));  // the residual, whatever op tagged it
+    const float res = __half2float(ll_half(c.ll_wait1(op.out_ll[0] + i, tag_res)));  // the residual, under the tag of the op that wrote it
     op.out_ll[0][i] = ll_pack(__float2half_rn(round_h(s) + res), tag_out);
   }
 }
@@ -1170,7 +1170,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
     switch (op.kind) {
       case MK_EMBED: embed_op(c, tok, tag(oi)); break;
       case MK_MATVEC: matvec_op<TIMED, DBG>(c, op, it, slot, ph, ring, full, empty, tabs, reinterpret_cast<__half *>(xq), reinterpret_cast<float *>(xq + (size_t)p.xmax_blocks * XB_BYTES), zero16, red, ssum, best, (TIMED && timed) ? twait : nullptr, seq0 + ar_i + 1,
-                         tag(op.src_op), tag(oi), trace);
+                         tag(op.src_op), tag(oi), tag(op.res_op), trace);
         if (op.epi == EPI_REDUCE) ++ar_i;  // (every CTA counts it, with or without a tile of the op)
         break;
       case MK_ATTN_PART:
@@ -1180,7 +1180,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_mega_kernel(const __grid_co
       case MK_ATTN_COMBINE: attn_combine_op(c, tag(oi)); break;
       case MK_ALLREDUCE:
         ++ar_i;
-        allreduce_op(c, op, seq0 + ar_i, tag(oi));
+        allreduce_op(c, op, seq0 + ar_i, tag(oi), tag(op.res_op));
         break;
       case MK_ARGMAX:
         argmax_final_op(c, reinterpret_cast<float *>(xq), pos0, base_rounds + rounds, seq0 + ar_i, ebase + p.nops);

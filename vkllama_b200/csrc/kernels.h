@@ -165,6 +165,7 @@ struct alignas(16) MegaOp {
   const uint32_t *in;     // input vector [K], tagged words
   uint32_t src_op;        // index of the op that produced `in` (MK_ATTN_PART: of the op that produced q, k, v)
   uint32_t tag_op;        // index of the op whose tag this op's tagged results carry (its own, unless a skipped op is expected)
+  uint32_t res_op;        // residual add (and all-reduce): index of the op that last wrote out_ll[0], whose tag the residual words carry
   uint32_t barrier_after; // a grid barrier follows this op (its results are not tagged, or the next op needs one)
   uint32_t *out_ll[3];    // tagged outputs; EPI_ADD: out_ll[0] is also the residual
   __half *out[3];         // plain fp16 outputs (lm head)

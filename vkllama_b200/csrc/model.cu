@@ -473,6 +473,7 @@ int build_mega(vkl_model *m) {
     o.eps = eps;
     o.in = in;
     o.src_op = src_op;
+    o.res_op = x_writer;  // (read by the residual epilogues only: x is what they add to)
     o.tag_op = (uint32_t)ops.size();
     o.barrier_after = 0;
     o.rot = rot;
@@ -511,20 +512,23 @@ int build_mega(vkl_model *m) {
       ops.push_back(cb);
       ao_writer = (uint32_t)ops.size() - 1;
     }
-    auto allreduce = [&]() {
+    auto allreduce = [&](uint32_t res_writer) {
       MegaOp r = {};
       r.kind = MK_ALLREDUCE;
       r.N = c.dim;
       r.out_ll[0] = x;
+      r.res_op = res_writer;
       r.tag_op = (uint32_t)ops.size();
       ops.push_back(r);
       return (uint32_t)ops.size() - 1;
     };
+    uint32_t before = x_writer;
     x_writer = matvec({y.wo}, nullptr, 0.f, ao, ao_writer, {x}, tp > 1 ? (reduce_in_place ? EPI_REDUCE : EPI_PARTIAL) : EPI_ADD);
-    if (tp > 1 && !reduce_in_place) x_writer = allreduce();
+    if (tp > 1 && !reduce_in_place) x_writer = allreduce(before);
     const uint32_t gu = matvec({y.gate, y.up}, (const float *)y.ffn_norm->data(), c.eps, x, x_writer, {tb}, EPI_SWIGLU);
+    before = x_writer;
     x_writer = matvec({y.down}, nullptr, 0.f, tb, gu, {x}, tp > 1 ? (reduce_in_place ? EPI_REDUCE : EPI_PARTIAL) : EPI_ADD);
-    if (tp > 1 && !reduce_in_place) x_writer = allreduce();
+    if (tp > 1 && !reduce_in_place) x_writer = allreduce(before);
   }
   matvec({m->output}, (const float *)m->output_norm->data(), c.final_eps, x, x_writer, {}, EPI_PLAIN);
   ops.back().out[0] = (__half *)m->logits16->data();  // plain fp16 + fp32 logits and arg-max candidates: a grid barrier follows
