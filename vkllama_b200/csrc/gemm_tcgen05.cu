@@ -4,14 +4,15 @@
 // Replaces, for many rows, the reference's matmul_b0_tb_fp16_v2.comp and matmul_b0_fp16_x_q8_0.comp
 // (src/ops/mat_mul.cpp:71-103), which re-read the whole weight matrix for every input row.
 //
-// Q8_0 weights are dequantised on the way into shared memory: four extra warps read the codes and
-// scales of the stage's W tile (tiled planes, common.cuh), turn every code into the fp16 value
-// fp16(q * d) and store it where a 128-byte-swizzled tensor copy would have put it, so the MMA
-// loop is the same as for FP16 weights. q * d has up to 19 significant bits: this path rounds every
-// weight once to fp16 (relative 2^-12), where the reference multiplies in fp32; the rows-at-a-time
-// kernel (matvec.cu) keeps the exact form and is used below GEMM_Q8_MIN_ROWS rows.
+// Q8_0 weights are dequantised on the way into shared memory: sixteen extra warps, in two groups that take
+// alternating K steps, fetch the codes and scales of their stage's W tile (tiled planes, common.cuh) with
+// ordered asynchronous copies, turn every code into the fp16 value fp16(q * d) and store it where a
+// 128-byte-swizzled tensor copy would have put it, so the MMA loop is the same as for FP16 weights.
+// q * d has up to 19 significant bits: this path rounds every weight once to fp16 (relative 2^-12), where
+// the reference multiplies in fp32; the rows-at-a-time kernel (matvec.cu) keeps the exact form and is used
+// below GEMM_Q8_MIN_ROWS rows.
 //
-// One CTA computes a 128 x BN output tile (BN = 128 or 256) with three kinds of warps:
+// One CTA computes a 128 x BN output tile (BN = 32 ... 256, picked per launch) with these kinds of warps:
 //   warp 0    producer: one lane issues TMA tensor copies (cp.async.bulk.tensor.2d, 128-byte
 //             swizzle) of the A and W tiles of each 64-wide K block into a ring of shared-
 //             memory stages; the copies complete on the stage's "full" mbarrier.
@@ -42,6 +43,14 @@ constexpr int GEMM_THREADS = 192;          // FP16 weights: TMA producer, MMA, f
 constexpr int NDW = VKL_GEMM_NDW;               // warps dequantising the W tile: one warp issues an instruction every five cycles or so
                                                 // (a dependent chain of permutes, multiplies and stores), so it takes several per SM
                                                 // sub-partition to keep up with the weight stream
+#ifndef VKL_GEMM_NG
+#define VKL_GEMM_NG 2
+#endif
+constexpr int NG = VKL_GEMM_NG;                 // the dequantising warps work in NG groups on alternating K steps: a warp's pass over
+                                                // one K step is a serial chain of waits, loads, conversion, stores and a proxy fence
+                                                // (about half a microsecond), so several K steps have to be in work at a time
+constexpr int NDWG = NDW / NG;                  // warps per group = arrivals per stage
+static_assert(NDW % NG == 0, "whole groups");
 constexpr int GEMM_THREADS_Q8 = 192 + 32 * NDW;
 
 // Q8_0 weights: what a dequantising warp keeps in flight from DRAM, in shared memory (asynchronous 16-byte
@@ -154,7 +163,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
   const uint32_t nkb = p.K / BK;
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sa(&full[s])), "r"(Q8 ? 1u + NDW : 1u) : "memory");  // the TMA lane (+ one lane per dequantising warp)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sa(&full[s])), "r"(Q8 ? 1u + NDWG : 1u) : "memory");  // the TMA lane (+ one lane per dequantising warp)
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&empty[s])) : "memory");
     }
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&acc_ready)) : "memory");
@@ -189,17 +198,18 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
     // BN rows x 64 columns = (BN / 16) row tiles x 2 blocks: units of 512 bytes of codes, dealt round robin to
     // the dequantising warps. The scales of a row tile and 4-block group are 8 x 16 bytes: row g's four blocks, then row g + 8's.
     const uint32_t dw = warp - 6, g = lane >> 2, t = lane & 3;
+    const uint32_t grp = dw % NG, wi = dw / NG;  // this warp's group (its K steps: grp, grp + NG, ...) and place in it
     const uint32_t tiles16 = (p.N + 15) / 16, groups = ((p.K + 31) / 32 + 3) / 4;
-    constexpr uint32_t UNITS = (BN / 16) * 2, UPQ = (UNITS + NDW - 1) / NDW;  // units per stage, and of those at most this warp's
-    constexpr uint32_t PF = Q8_UNITS_AHEAD / UPQ;                            // stages whose units are requested ahead
+    constexpr uint32_t UNITS = (BN / 16) * 2, UPQ = (UNITS + NDWG - 1) / NDWG;  // units per stage, and of those at most this warp's
+    constexpr uint32_t PF = Q8_UNITS_AHEAD / UPQ;                              // of its own K steps, how many are requested ahead
     static_assert(UPQ <= Q8_UNITS_AHEAD && PF >= 1, "staging holds at least one stage of a warp's units");
-    // The codes of a stage come from DRAM (a microsecond away) and a stage is converted in a fraction of that, so the
-    // next PF stages' units are kept in flight. They travel as asynchronous copies into this warp's own staging
-    // area, which complete in order (cp.async groups): loads into registers would share the warp's few scoreboards,
-    // and the wait for the oldest would also wait for the youngest, one DRAM round trip per stage.
+    // The codes of a stage come from DRAM (a microsecond away), so the warp's next PF stages' units are kept in
+    // flight. They travel as asynchronous copies into this warp's own staging area, which complete in order
+    // (cp.async groups): loads into registers would share the warp's few scoreboards, and the wait for the oldest
+    // would also wait for the youngest.
     unsigned char *stg = stages + (size_t)C::STAGES * C::STAGE_BYTES + (size_t)dw * Q8_UNITS_AHEAD * Q8_UNIT_STAGING;
     auto unit_of = [&](uint32_t kb, uint32_t j, uint32_t &tile, uint32_t &b) {
-      const uint32_t u = dw + NDW * j;
+      const uint32_t u = wi + NDWG * j;
       tile = n0 / 16 + (u >> 1);  // row tile of the matrix
       b = kb * 2 + (u & 1);       // block of the row
       return u < UNITS && kb < nkb && tile < tiles16;
@@ -221,12 +231,12 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
       asm volatile("cp.async.commit_group;" ::: "memory");  // one group per stage, also when it is empty
     };
 #pragma unroll
-    for (uint32_t i = 0; i < PF; ++i) request(i, i);
-    for (uint32_t kb0 = 0; kb0 < nkb; kb0 += PF) {
+    for (uint32_t i = 0; i < PF; ++i) request(grp + NG * i, i);
+    for (uint32_t kb0 = grp; kb0 < nkb; kb0 += NG * PF) {
       bool stop = false;
 #pragma unroll
       for (uint32_t i = 0; i < PF; ++i) {  // staging slots are indexed by compile-time constants
-        const uint32_t kb = kb0 + i;
+        const uint32_t kb = kb0 + NG * i;
         if (kb >= nkb || stop) continue;
         const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
         uint32_t ok = 1;
@@ -246,7 +256,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
         unsigned char *wt = stages + (size_t)s * C::STAGE_BYTES + A_TILE_BYTES;
 #pragma unroll
         for (uint32_t j = 0; j < UPQ; ++j) {
-          const uint32_t u = dw + NDW * j;
+          const uint32_t u = wi + NDWG * j;
           if (u >= UNITS) continue;
           uint32_t tile, b;
           uint4 w = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // code 0 (stored biased by 128): rows beyond the matrix
@@ -262,12 +272,11 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
           dequant_unit(wt, (u >> 1) * 16, (u & 1) * 4, w, lo, hi, lane);
         }
         // the tensor core reads shared memory through the async proxy: order this warp's stores before its arrival.
-        // (The fence waits for the thread's memory operations in flight: the refill below comes after it, or every
-        // stage would cost a DRAM round trip.)
+        // (The fence waits for the thread's memory operations in flight: the refill below comes after it.)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();          // every lane has fenced, and has read the staging slot
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sa(&full[s])) : "memory");
-        request(kb + PF, i);   // refill the slot for the stage PF steps ahead
+        request(kb + NG * PF, i);   // refill the slot for this warp's stage PF steps ahead
       }
       if (stop) break;
     }
