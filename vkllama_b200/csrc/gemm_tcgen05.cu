@@ -33,6 +33,12 @@
 namespace vkl {
 namespace {
 
+#ifndef VKL_GEMM_NACC2
+#define VKL_GEMM_NACC2 1
+#endif
+#ifndef VKL_GEMM_MMAONLY
+#define VKL_GEMM_MMAONLY 0  // diagnostic build: the MMA lane runs alone on whatever the shared memory holds
+#endif
 constexpr int BM = 128, BK = 64;
 constexpr uint32_t A_TILE_BYTES = BM * BK * 2;  // 16 KB
 constexpr uint32_t GEMM_WAIT_LIMIT = 1u << 22;
@@ -170,7 +176,11 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     failed_s = 0;
   }
-  if (warp == 1) tmem_alloc<BN>(sa(&tmem_base_s));
+  // Tiles of up to 128 columns accumulate the even and the odd 16-wide K slices in two TMEM accumulators, added in
+  // the epilogue: a tcgen05.mma of so few columns takes about 110 cycles however narrow it is when it has to
+  // follow the one before it on the same accumulator; two independent chains hide half of that.
+  constexpr uint32_t NACC = VKL_GEMM_NACC2 && BN <= 128 ? 2 : 1;
+  if (warp == 1) tmem_alloc<NACC * BN>(sa(&tmem_base_s));
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -178,7 +188,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
-    if (lane == 0) {
+    if (lane == 0 && !VKL_GEMM_MMAONLY) {
       for (uint32_t kb = 0; kb < nkb; ++kb) {
         const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
         if (use > 0 && !mbar_wait_bounded(sa(&empty[s]), (use - 1) & 1u)) {
@@ -193,7 +203,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
         if (!Q8) tma_load_2d(sa(st + A_TILE_BYTES), &map_w, kb * BK, n0, bar);
       }
     }
-  } else if (Q8 && warp >= 6) {
+  } else if (Q8 && warp >= 6 && !VKL_GEMM_MMAONLY) {
     // ------------------------------------------- W tile: Q8_0 -> fp16 in shared memory
     // BN rows x 64 columns = (BN / 16) row tiles x 2 blocks: units of 512 bytes of codes, dealt round robin to
     // the dequantising warps. The scales of a row tile and 4-block group are 8 x 16 bytes: row g's four blocks, then row g + 8's.
@@ -287,7 +297,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
       constexpr uint32_t idesc = instr_desc(BM, BN);
       for (uint32_t kb = 0; kb < nkb; ++kb) {
         const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
-        if (!mbar_wait_bounded(sa(&full[s]), use & 1u)) {
+        if (!VKL_GEMM_MMAONLY && !mbar_wait_bounded(sa(&full[s]), use & 1u)) {
           failed_s = 2;
           break;
         }
@@ -297,9 +307,9 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
 #pragma unroll
         for (uint32_t k = 0; k < BK / 16; ++k) {
           const uint64_t da = smem_desc(a_addr + k * 32), db = smem_desc(b_addr + k * 32);
-          const uint32_t accumulate = (kb | k) ? 1u : 0u;
+          const uint32_t accumulate = NACC == 2 ? ((kb | (k >> 1)) ? 1u : 0u) : ((kb | k) ? 1u : 0u);
           asm volatile(
-              "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_acc),
+              "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_acc + (NACC == 2 ? (k & 1u) * BN : 0u)),
               "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
               : "memory");
         }
@@ -326,6 +336,12 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
         if (n0 + cc >= p.N) break;  // uniform over the warp
         uint32_t r[32];
         tmem_ld32(tmem_acc + ((quad * 32u) << 16) + cc, r);
+        if (NACC == 2) {
+          uint32_t r2[32];
+          tmem_ld32(tmem_acc + ((quad * 32u) << 16) + BN + cc, r2);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+        }
         if (row < p.M) {
           const size_t o = (size_t)row * p.N + n0 + cc;
 #pragma unroll
@@ -368,7 +384,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
     for (int i = 0; i < 2000; ++i) __nanosleep(100);
     __syncthreads();
   }
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)(NACC * BN)) : "memory");
 }
 
 // y <- fp16( silu(gate) * up ) on fp32 inputs: the epilogue of ffn_up_and_gate_fp16.comp.
