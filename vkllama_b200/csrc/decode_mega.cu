@@ -48,9 +48,6 @@ constexpr uint32_t UNIT_BYTES = UNIT_CODES + UNIT_SCALES;  // a unit's codes, th
 constexpr uint32_t STAGE_BYTES = SU * UNIT_BYTES;          // 32640
 static_assert(STAGE_BYTES == MEGA_STAGE_BYTES, "host and device agree on the stage size");
 constexpr uint32_t XB_BYTES = 64;      // the input vector in shared memory: fp16, 64 bytes per block of 32 inputs
-#ifndef VKL_PREFETCH
-#define VKL_PREFETCH 0
-#endif
 constexpr int MAX_NST = 12;            // ring stages are a launch parameter (whatever fits), at most this many
 // Every wait of the kernel is bounded by MegaParams::wait_limit polls (about half a microsecond each): the host
 // picks the bound, the same for all waits, so that no wait gives up while another one it depends on is still
@@ -549,86 +546,7 @@ __device__ __forceinline__ void matvec_op(const Ctx &c, const MegaOp &op_global,
     };
     const __half *xbase = g == 0 ? xs + t * 8 : zero16;  // column 0 of B = the input, the other columns zeros
     const uint32_t xstep = g == 0 ? 32u : 0u;
-#if VKL_PREFETCH
-    // Variant: a warp that finds its NEXT stage already landed copies its units into registers (and gives the
-    // stage back) before the arithmetic of the current one, so that a full ring drains sooner after the consumers
-    // were held up; a stage that has not landed is waited for only after the arithmetic.
-    struct StageRegs {
-      uint4 wa[UPW], wb[UPW];
-      uint2 dsc[UPW];
-      uint4 meta;
-      bool ok;
-    };
-    auto read_stage = [&](StageRegs &r, bool ok) {
-      r.ok = ok;
-      r.meta = *reinterpret_cast<const uint4 *>(&tabs[it & 127].n0);
-      const unsigned char *st = ring + (size_t)slot * STAGE_BYTES;
-      const uint32_t nu = r.meta.x + r.meta.y;
-#pragma unroll
-      for (int q = 0; q < UPW; ++q) {
-        const uint32_t u = warp * UPW + q;
-        if (ok && u < nu) {
-          r.wa[q] = *reinterpret_cast<const uint4 *>(st + u * UNIT_BYTES + lane * 16);
-          r.wb[q] = *reinterpret_cast<const uint4 *>(st + u * UNIT_BYTES + 512 + lane * 16);
-          r.dsc[q] = *reinterpret_cast<const uint2 *>(st + u * UNIT_BYTES + UNIT_CODES + g * 8);
-        }
-      }
-      __syncwarp();
-      if (lane == 0 && ok) mbar_arrive(s32(&empty[slot]));
-      ++it;
-      if (++slot == NST) {
-        slot = 0;
-        ph ^= 1u;
-      }
-    };
-    auto math_stage = [&](const StageRegs &r) {
-      const uint32_t n0 = r.meta.x, n1 = r.meta.y, tm = r.meta.z, kg = r.meta.w;
-#pragma unroll
-      for (int q = 0; q < UPW; ++q) {
-        const uint32_t u = warp * UPW + q;
-        if (!(r.ok && u < n0 + n1)) continue;
-        const uint32_t mt = u < n0 ? tm : tm + 1, b = u < n0 ? kg + u : u - n0;
-        if (mt != cur) {
-          flush();
-          cur = mt;
-          acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-        }
-        const uint4 X = *reinterpret_cast<const uint4 *>(xbase + b * xstep);
-        const float xb = xbias[b];
-        float ca[4] = {0.f, 0.f, 0.f, 0.f}, cb[4] = {0.f, 0.f, 0.f, 0.f};
-        mma16816(ca, codes_sub_h2(r.wa[q].x, false), codes_sub_h2(r.wa[q].z, false), codes_sub_h2(r.wa[q].x, true), codes_sub_h2(r.wa[q].z, true), X.x, X.y);
-        mma16816(cb, codes_sub_h2(r.wb[q].x, false), codes_sub_h2(r.wb[q].z, false), codes_sub_h2(r.wb[q].x, true), codes_sub_h2(r.wb[q].z, true), X.x, X.y);
-        mma16816(ca, codes_sub_h2(r.wa[q].y, false), codes_sub_h2(r.wa[q].w, false), codes_sub_h2(r.wa[q].y, true), codes_sub_h2(r.wa[q].w, true), X.z, X.w);
-        mma16816(cb, codes_sub_h2(r.wb[q].y, false), codes_sub_h2(r.wb[q].w, false), codes_sub_h2(r.wb[q].y, true), codes_sub_h2(r.wb[q].w, true), X.z, X.w);
-        const float2 d0 = __half22float2(*reinterpret_cast<const __half2 *>(&r.dsc[q].x));
-        const float2 d1 = __half22float2(*reinterpret_cast<const __half2 *>(&r.dsc[q].y));
-        acc[0] = fmaf(fmaf(ca[0], 16777216.f, -xb), d0.x, acc[0]);
-        acc[1] = fmaf(fmaf(ca[2], 16777216.f, -xb), d0.y, acc[1]);
-        acc[2] = fmaf(fmaf(cb[0], 16777216.f, -xb), d1.x, acc[2]);
-        acc[3] = fmaf(fmaf(cb[2], 16777216.f, -xb), d1.y, acc[3]);
-      }
-    };
-    if (!DBG && nstages) {
-      StageRegs ra, rb;
-      read_stage(ra, c.wait(s32(&full[slot]), ph, 1));
-      for (uint32_t sidx = 0; sidx < nstages; ++sidx) {
-        const bool more = sidx + 1 < nstages;
-        bool have_b = false;
-        if (more && __all_sync(0xffffffffu, mbar_try(s32(&full[slot]), ph) != 0u)) {
-          read_stage(rb, true);
-          have_b = true;
-        }
-        math_stage(ra);
-        if (more) {
-          if (!have_b) read_stage(rb, c.wait(s32(&full[slot]), ph, 1));
-          ra = rb;
-        }
-      }
-    }
-    for (uint32_t sidx = 0; DBG && sidx < nstages; ++sidx) {
-#else
     for (uint32_t sidx = 0; sidx < nstages; ++sidx) {
-#endif
       unsigned long long w0 = 0;
       if (TIMED && tw) w0 = clock64();
       const bool ok = (DBG && (c.p.timing_mode & 128u)) ? true : c.wait(s32(&full[slot]), ph, 1);
