@@ -89,6 +89,7 @@ struct vkl_model {
   uint32_t sm_mhz = 0;  // measured SM clock, for the profiled launches' cycle counts
   uint32_t wait_limit = 0;  // polls a wait of the decode kernel may spin (0: the default of build_mega)
   bool tp_failed = false;   // a wait on another rank ran out: the ranks' sequence counters are out of step until they reconnect
+  unsigned char *pin = nullptr;  // pinned host staging of the one-token call: this rank's fp32 logits, then the decode kernel's error word
   cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev2 = nullptr;
   uint32_t *pos_dev() { return (uint32_t *)state->data(); }
   uint32_t *step_dev() { return (uint32_t *)state->data() + 1; }
@@ -96,6 +97,7 @@ struct vkl_model {
   ~vkl_model() {
     if (decode_graph) cudaGraphExecDestroy(decode_graph);
     if (tp_buf) cudaFree(tp_buf);
+    if (pin) cudaFreeHost(pin);
     for (auto &l : L)
       for (vkl_tensor *p : {l.attn_norm, l.ffn_norm, l.wq, l.wk, l.wv, l.wo, l.gate, l.up, l.down, l.kcache, l.vcache}) vkl_tensor_release(p);
     for (vkl_tensor *p : mega_packed) vkl_tensor_release(p);
@@ -666,6 +668,15 @@ int build_mega(vkl_model *m) {
 
 __global__ void bump_sequence_kernel(uint32_t *seq, uint32_t by) { *seq += by; }
 
+// Start of a one-token call: position, step counter, no forced tokens, the token itself (one launch instead of
+// three small copies).
+__global__ void begin_token_kernel(uint32_t *state, uint32_t *tok, uint32_t pos, uint32_t id) {
+  state[0] = pos;
+  state[1] = 0;
+  state[5] = 0;
+  tok[0] = id;
+}
+
 // SM cycles and nanoseconds of one thread spinning for about 50 us: the SM clock a profiled
 // launch converts its cycle counts with.
 __global__ void clock_probe_kernel(unsigned long long *out) {
@@ -1006,6 +1017,24 @@ int vkl_model_forward(vkl_model *m, const uint32_t *toks, size_t n, size_t offse
   VKL_CUDA(cudaSetDevice(m->dev->ordinal));
   VKL_OKAY(ensure_rows(m, (uint32_t)n));
   if (n == 1) VKL_OKAY(prepare_decode(m));
+  if (n == 1) {
+    // The per-token call of a host-driven loop: one small launch sets the step up, the logits and the decode
+    // kernel's error word come back through pinned memory behind one synchronisation.
+    const size_t lb = (size_t)m->vocab_l * 4;
+    if (!m->pin) VKL_CUDA(cudaHostAlloc((void **)&m->pin, lb + 16, cudaHostAllocDefault));
+    begin_token_kernel<<<1, 1, 0, m->stream>>>((uint32_t *)m->state->data(), (uint32_t *)m->toks->data(), (uint32_t)offset, toks[0]);
+    VKL_LAUNCH(1, cudaGetLastError());
+    VKL_OKAY(decode_step(m));
+    VKL_CUDA(cudaMemcpyAsync(m->pin, m->logits32->data(), lb, cudaMemcpyDeviceToHost, m->stream));
+    uint32_t *errw = (uint32_t *)(m->pin + lb);
+    *errw = 0;
+    if (m->mega_ready) VKL_CUDA(cudaMemcpyAsync(errw, m->mp.error, 4, cudaMemcpyDeviceToHost, m->stream));
+    VKL_CUDA(cudaStreamSynchronize(m->stream));
+    memcpy(logits_out, m->pin, lb);
+    if (*errw) VKL_OKAY(check_mega(m));  // (reads the word again, resets the kernel's state, reports)
+    VKL_OKAY(check_gemm(m));
+    return VKL_OK;
+  }
   VKL_CUDA(cudaMemsetAsync((uint32_t *)m->state->data() + 5, 0, 4, m->stream));
   const uint32_t st[2] = {(uint32_t)offset, 0};
   VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
