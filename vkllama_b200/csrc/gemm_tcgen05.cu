@@ -30,11 +30,40 @@
 #include "common.cuh"
 #include "kernels.h"
 
+#ifndef VKL_GEMM_TRACE
+#define VKL_GEMM_TRACE 0  // diagnostic build: CTA (0,0) stamps the global timer at fixed points of every K step
+#endif
+#if VKL_GEMM_TRACE
+__device__ unsigned long long g_gemm_trace[8 * 512];
+extern "C" int vkl_debug_gemm_trace_clear() {
+  static unsigned long long zeros[8 * 512];
+  return (int)cudaMemcpyToSymbol(g_gemm_trace, zeros, sizeof(zeros));
+}
+extern "C" int vkl_debug_gemm_trace(unsigned long long *out, size_t n) {
+  return (int)cudaMemcpyFromSymbol(out, g_gemm_trace, (n < 8 * 512 ? n : 8 * 512) * sizeof(unsigned long long));
+}
+#define GEMM_STAMP(kb, k)                                                                       \
+  do {                                                                                          \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (kb) < 512) {                                     \
+      unsigned long long t_;                                                                    \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                    \
+      g_gemm_trace[(kb) * 8 + (k)] = t_;                                                        \
+    }                                                                                           \
+  } while (0)
+#else
+#define GEMM_STAMP(kb, k) \
+  do {                    \
+  } while (0)
+#endif
+
 namespace vkl {
 namespace {
 
 #ifndef VKL_GEMM_NACC2
 #define VKL_GEMM_NACC2 1
+#endif
+#ifndef VKL_GEMM_TESTWAIT
+#define VKL_GEMM_TESTWAIT 0
 #endif
 #ifndef VKL_GEMM_MMAONLY
 #define VKL_GEMM_MMAONLY 0  // diagnostic build: the MMA lane runs alone on whatever the shared memory holds
@@ -55,14 +84,18 @@ constexpr int NDW = VKL_GEMM_NDW;               // warps dequantising the W tile
 constexpr int NG = VKL_GEMM_NG;                 // the dequantising warps work in NG groups on alternating K steps: a warp's pass over
                                                 // one K step is a serial chain of waits, loads, conversion, stores and a proxy fence
                                                 // (about half a microsecond), so several K steps have to be in work at a time
-constexpr int NDWG = NDW / NG;                  // warps per group = arrivals per stage
-static_assert(NDW % NG == 0, "whole groups");
+// The MMA lane (warp 1) issues some sixty instructions per K step and the whole CTA waits on it. A warp's scheduler
+// is warp % 4: the dequantising warps that would share warp 1's scheduler (every fourth) are left idle, or that
+// lane gets an issue slot every twenty-odd cycles and a K step takes 0.58 us instead of 0.3.
+constexpr int NDW_ACTIVE = NDW - NDW / 4;       // 12 of 16
+constexpr int NDWG = NDW_ACTIVE / NG;           // warps per group = arrivals per stage
+static_assert(NDW % 4 == 0 && NDW_ACTIVE % NG == 0, "whole groups");
 constexpr int GEMM_THREADS_Q8 = 192 + 32 * NDW;
 
 // Q8_0 weights: what a dequantising warp keeps in flight from DRAM, in shared memory (asynchronous 16-byte
 // copies, waited for in order): Q8_UNITS_AHEAD units of 512 bytes of codes + 128 bytes of scales per warp.
-constexpr uint32_t Q8_UNIT_STAGING = 512 + 128, Q8_UNITS_AHEAD = 4;
-constexpr uint32_t Q8_STAGING_BYTES = NDW * Q8_UNITS_AHEAD * Q8_UNIT_STAGING;  // 40 KB
+constexpr uint32_t Q8_UNIT_STAGING = 512 + 128, Q8_UNITS_AHEAD = 6;
+constexpr uint32_t Q8_STAGING_BYTES = NDW_ACTIVE * Q8_UNITS_AHEAD * Q8_UNIT_STAGING;  // 45 KB
 
 template <int BN, bool Q8 = false> struct Cfg {
   static constexpr uint32_t B_TILE_BYTES = BN * BK * 2;
@@ -86,6 +119,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         : "memory");
     if (ok) return true;
     if (sleep_ns) __nanosleep(sleep_ns);
+  }
+  return false;
+}
+
+// The same with the non-blocking test (mbarrier.test_wait), for the MMA lane: try_wait may suspend the thread.
+__device__ __forceinline__ bool mbar_spin_bounded(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (GEMM_WAIT_LIMIT << 4); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
   }
   return false;
 }
@@ -161,6 +208,9 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
   __shared__ __align__(8) uint64_t full[C::STAGES];   // TMA bytes of the stage have landed
   __shared__ __align__(8) uint64_t empty[C::STAGES];  // the MMAs have read the stage
   __shared__ __align__(8) uint64_t acc_ready;
+#if VKL_GEMM_TRACE
+  __shared__ __align__(8) uint64_t full_a[C::STAGES];  // diagnostic build, Q8_0: the A tile's copy completes on a barrier of its own
+#endif
   __shared__ uint32_t tmem_base_s;
   __shared__ volatile uint32_t failed_s;
 
@@ -171,6 +221,9 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
     for (int s = 0; s < C::STAGES; ++s) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sa(&full[s])), "r"(Q8 ? 1u + NDWG : 1u) : "memory");  // the TMA lane (+ one lane per dequantising warp)
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&empty[s])) : "memory");
+#if VKL_GEMM_TRACE
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&full_a[s])) : "memory");
+#endif
     }
     asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(sa(&acc_ready)) : "memory");
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -196,18 +249,24 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
           break;
         }
         if (failed_s) break;
+        GEMM_STAMP(kb, 0);  // the stage is free: its A tile is requested now
+#if VKL_GEMM_TRACE
+        const uint32_t bar = Q8 ? sa(&full_a[s]) : sa(&full[s]);
+        if (Q8) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sa(&full[s])) : "memory");  // the producer's share of the count
+#else
         const uint32_t bar = sa(&full[s]);
+#endif
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(Q8 ? A_TILE_BYTES : C::STAGE_BYTES) : "memory");
         unsigned char *st = stages + (size_t)s * C::STAGE_BYTES;
         tma_load_2d(sa(st), &map_a, kb * BK, m0, bar);
         if (!Q8) tma_load_2d(sa(st + A_TILE_BYTES), &map_w, kb * BK, n0, bar);
       }
     }
-  } else if (Q8 && warp >= 6 && !VKL_GEMM_MMAONLY) {
+  } else if (Q8 && warp >= 6 && (warp & 3u) != 1u && !VKL_GEMM_MMAONLY) {
     // ------------------------------------------- W tile: Q8_0 -> fp16 in shared memory
     // BN rows x 64 columns = (BN / 16) row tiles x 2 blocks: units of 512 bytes of codes, dealt round robin to
     // the dequantising warps. The scales of a row tile and 4-block group are 8 x 16 bytes: row g's four blocks, then row g + 8's.
-    const uint32_t dw = warp - 6, g = lane >> 2, t = lane & 3;
+    const uint32_t dw = (warp - 6) - (warp - 5) / 4, g = lane >> 2, t = lane & 3;  // index among the active dequantising warps
     const uint32_t grp = dw % NG, wi = dw / NG;  // this warp's group (its K steps: grp, grp + NG, ...) and place in it
     const uint32_t tiles16 = (p.N + 15) / 16, groups = ((p.K + 31) / 32 + 3) / 4;
     constexpr uint32_t UNITS = (BN / 16) * 2, UPQ = (UNITS + NDWG - 1) / NDWG;  // units per stage, and of those at most this warp's
@@ -250,8 +309,12 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
         if (kb >= nkb || stop) continue;
         const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
         uint32_t ok = 1;
+        if (wi == 0 && lane == 0) GEMM_STAMP(kb, 1);  // a dequantising warp turns to the stage
         if (lane == 0 && use > 0) ok = mbar_wait_bounded(sa(&empty[s]), (use - 1) & 1u, 100) ? 1u : 0u;
         ok = __shfl_sync(0xffffffffu, ok, 0);
+#if !VKL_GEMM_TRACE
+        if (wi == 0 && lane == 0) GEMM_STAMP(kb, 2);  // ... has the stage
+#endif
         if (!ok) {
           if (lane == 0) failed_s = 4;
           stop = true;
@@ -263,6 +326,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
         }
         asm volatile("cp.async.wait_group %0;" ::"n"(PF - 1) : "memory");  // this stage's copies (the oldest group) have landed
         __syncwarp();
+        if (wi == 0 && lane == 0) GEMM_STAMP(kb, 3);  // ... has its codes
         unsigned char *wt = stages + (size_t)s * C::STAGE_BYTES + A_TILE_BYTES;
 #pragma unroll
         for (uint32_t j = 0; j < UPQ; ++j) {
@@ -286,6 +350,14 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();          // every lane has fenced, and has read the staging slot
         if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(sa(&full[s])) : "memory");
+        if (wi == 0 && lane == 0) GEMM_STAMP(kb, 4);  // ... has written and published its part of the W tile
+#if VKL_GEMM_TRACE
+        if (lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && kb < 512) {  // [7]: the last warp of the group to publish
+          unsigned long long t_;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
+          atomicMax(&g_gemm_trace[kb * 8 + 7], t_);
+        }
+#endif
         request(kb + NG * PF, i);   // refill the slot for this warp's stage PF steps ahead
       }
       if (stop) break;
@@ -297,11 +369,19 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
       constexpr uint32_t idesc = instr_desc(BM, BN);
       for (uint32_t kb = 0; kb < nkb; ++kb) {
         const uint32_t s = kb % C::STAGES, use = kb / C::STAGES;
-        if (!VKL_GEMM_MMAONLY && !mbar_wait_bounded(sa(&full[s]), use & 1u)) {
+        if (!VKL_GEMM_MMAONLY && !(VKL_GEMM_TESTWAIT ? mbar_spin_bounded(sa(&full[s]), use & 1u) : mbar_wait_bounded(sa(&full[s]), use & 1u))) {
           failed_s = 2;
           break;
         }
         if (failed_s) break;
+#if VKL_GEMM_TRACE
+        GEMM_STAMP(kb, 2);  // (diagnostic build: reuses slot 2) the MMA lane has the W tile
+        if (Q8 && !mbar_wait_bounded(sa(&full_a[s]), use & 1u)) {
+          failed_s = 2;
+          break;
+        }
+#endif
+        GEMM_STAMP(kb, 5);  // the MMA lane has the full stage
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = sa(stages + (size_t)s * C::STAGE_BYTES), b_addr = a_addr + A_TILE_BYTES;
 #pragma unroll
@@ -315,6 +395,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
         }
         // arrives once every MMA issued so far has completed (implies fence::before_thread_sync)
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sa(&empty[s])) : "memory");
+        GEMM_STAMP(kb, 6);  // ... has issued the stage's MMAs and the commit
         if (kb + 1 == nkb)
           asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sa(&acc_ready)) : "memory");
       }
@@ -463,7 +544,9 @@ static int pick_bn(const GemmParams &p, bool q8) {
   for (int bn : {256, 128, 64, 32}) {
     if (!q8 && bn < 128) break;
     const size_t ctas = mt * ((p.N + bn - 1) / bn), waves = (ctas + sms - 1) / sms;
-    const double cost = (double)waves * (bn + (q8 ? 240.0 : 1200.0));  // fitted to measured wave times (K = 4096): 32 + 0.135 bn us, 27 + 0.022 bn us
+    // measured time of one wave at K = 4096, us: Q8_0 30.9 / 31.2 / 43.0 / 73.4 for 32 / 64 / 128 / 256 columns, FP16 27 + 0.022 bn
+    const double wave = q8 ? (bn == 32 ? 30.9 : bn == 64 ? 31.2 : bn == 128 ? 43.0 : 73.4) : 27.0 + 0.022 * bn;
+    const double cost = (double)waves * wave;
     if (!best || cost < best_cost) {
       best = bn;
       best_cost = cost;
