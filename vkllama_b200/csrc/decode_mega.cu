@@ -1328,7 +1328,7 @@ cudaError_t launch_decode_mega(const MegaParams &p, int grid, cudaStream_t s) {
   if (p.nst < 2 || p.nst > (uint32_t)MAX_NST) return cudaErrorInvalidValue;
   const size_t smem = decode_mega_smem(p.xs_bytes, p.nst, p.red_slots);
   // the diagnostic switches (no weight copies, no arithmetic) are compiled into separate instances
-  const bool dbg = (p.timing_mode & (2u | 4u | 64u | 128u)) != 0;
+  const bool dbg = (p.timing_mode & (2u | 4u | 16u | 64u | 128u)) != 0;  // (16: the diagnostic instance with nothing switched off, its own baseline)
   auto kern = p.timing ? decode_mega_kernel<true, true> : dbg ? decode_mega_kernel<false, true> : decode_mega_kernel<false, false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;

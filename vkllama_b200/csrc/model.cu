@@ -652,7 +652,7 @@ int build_mega(vkl_model *m) {
   {
     p.nst = nst;
     p.red_slots = red_slots;
-    p.timing_mode = (getenv("VKLLAMA_DEBUG_NOCOPY") ? 2 : 0) | (getenv("VKLLAMA_DEBUG_NOMATH") ? 4 : 0) |
+    p.timing_mode = (getenv("VKLLAMA_DEBUG_NOCOPY") ? 2 : 0) | (getenv("VKLLAMA_DEBUG_NOMATH") ? 4 : 0) | (getenv("VKLLAMA_DEBUG_INSTANCE") ? 16 : 0) |
                     (getenv("VKLLAMA_DEBUG_NOBODY") ? 64 : 0) | (getenv("VKLLAMA_DEBUG_NOHANDSHAKE") ? 128 : 0);  // diagnostics
     const char *bp = getenv("VKLLAMA_BARRIER_POLLERS");
     p.barrier_pollers = bp ? std::min(std::max((uint32_t)atoi(bp), 1u), 8u) : 1u;
