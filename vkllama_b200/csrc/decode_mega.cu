@@ -11,15 +11,17 @@
 //     CTA reads of an op is one consecutive range of the op's packed stream. Weights never
 //     depend on activations, so the producer runs ahead across op boundaries and HBM
 //     stays busy while the consumers sit in a norm, an attention op or a wait;
-//   * fifteen consumer warps take their units (one Q8_0 block x 32 rows) of every ring
+//   * eleven consumer warps take their units (one Q8_0 block x 32 rows) of every ring
 //     stage, put the codes into the tensor cores as fp16 subnormals (exact, one byte permute
 //     per pair), multiply (m16n8k16, fp32 accumulate), apply block scales in fp32, reduce
 //     across warps in fixed order and run the fused epilogue (RMSNorm prologue, residual add,
-//     SwiGLU, fp32 logits, running arg-max). The arithmetic is off the critical path: with
-//     it switched off (diagnostic mode) a token takes the same time, and eleven warps do as
-//     well as fifteen. mma.sync m16n8k16 (f16) and m16n8k32 (s8) both issue every 8 cycles
-//     per SM sub-partition on this GPU; an int8 variant on three exact byte slices of the
-//     input was 30 % slower for its integer-to-float conversions;
+//     SwiGLU, fp32 logits, running arg-max). What they cost is instruction issue, not the
+//     tensor pipe (12 % busy; mma.sync m16n8k16 (f16) and m16n8k32 (s8) both issue every 8
+//     cycles per scheduler on this GPU). A warp's scheduler is warp % 4: eleven or fifteen
+//     consumer warps (+ the producer) load the four schedulers evenly, every other count is
+//     15-25 % slower; eleven (24 KB stages, seven of them, 168 registers) measured 1.5 %
+//     faster than fifteen (32 KB stages, five, 128 registers). An int8 variant on three exact
+//     byte slices of the input was 30 % slower for its integer-to-float conversions;
 //   * activations cross CTAs as tagged words (value + sequence tag in one 32-bit word) that
 //     the readers poll; only the output layer's arg-max needs a grid barrier.
 //
@@ -37,7 +39,7 @@
 namespace vkl {
 namespace {
 
-constexpr int NCW = (int)MEGA_NCW;     // consumer warps (15 + 1 producer warp = 512 threads of 128 registers)
+constexpr int NCW = (int)MEGA_NCW;     // consumer warps (11 + 1 producer warp = 384 threads of 168 registers)
 constexpr int CT = NCW * 32;           // consumer threads
 constexpr int THREADS = CT + 32;       // + producer warp
 constexpr int UPW = (int)MEGA_UPW;     // units (one Q8_0 block x 32 rows) per consumer warp and ring stage

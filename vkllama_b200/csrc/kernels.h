@@ -198,7 +198,7 @@ constexpr uint32_t MEGA_UNIT_CODES = 1024, MEGA_UNIT_SCALES = 64;  // 32 rows x 
 #endif
 constexpr uint32_t MEGA_UPW = VKL_MEGA_UPW;       // units per consumer warp and stage
 #ifndef VKL_MEGA_NCW
-#define VKL_MEGA_NCW 15
+#define VKL_MEGA_NCW 11
 #endif
 constexpr uint32_t MEGA_NCW = VKL_MEGA_NCW;       // consumer warps of the kernel
 constexpr uint32_t MEGA_SU = MEGA_NCW * MEGA_UPW; // units per stage
