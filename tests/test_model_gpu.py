@@ -341,7 +341,7 @@ def test_wait_that_runs_out_returns_an_error_and_leaves_the_device_usable(dev):
     leaves through its normal path, the call reports which wait ran out, the shard refuses further
     steps until it is reconnected, and other models on the device keep working. Nothing faults and
     nothing waits for ever."""
-    cfg = dict(dim=256, heads=4, ffn=512, vocab=1000, layers=2, maxlen=64)
+    cfg = dict(dim=256, heads=4, ffn=512, vocab=1000, layers=2, maxlen=128)
     lone = vk.Model(dev, cfg["dim"], cfg["heads"], cfg["ffn"], cfg["vocab"], cfg["layers"], cfg["maxlen"], tp_rank=0, tp_size=2)
     lone.synth_weights(41)
     ptr, nbytes = lone.tp_buffer()
@@ -358,6 +358,15 @@ def test_wait_that_runs_out_returns_an_error_and_leaves_the_device_usable(dev):
     with pytest.raises(vk.VklError) as e:
         lone.generate(np.array([1, 2, 3], np.uint32), 4)
     assert e.value.code == 13 and "code 4" in e.value.message
+    # the many-token prefill of a sharded model waits for the other ranks' partial sums in its row all-reduce:
+    # the same bound, its own message, the same refusal afterwards
+    lone.tp_connect_pointers([ptr, ptr])
+    with pytest.raises(vk.VklError) as e:
+        lone.generate(O.synth_tokens(41, 1000, 70, cfg["vocab"]), 2)
+    assert e.value.code == 13 and "another tensor-parallel rank" in e.value.message, e.value.message
+    with pytest.raises(vk.VklError) as e:
+        lone(tok, 0)
+    assert e.value.code == 9
     # the device and other models are unaffected
     om, dm, cfg2 = small_pair(dev, seed=42)
     prompt = O.synth_tokens(42, 1000, 6, cfg2["vocab"])
