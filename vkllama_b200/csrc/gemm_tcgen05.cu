@@ -87,14 +87,15 @@ constexpr int NG = VKL_GEMM_NG;                 // the dequantising warps work i
 // The MMA lane (warp 1) issues some sixty instructions per K step and the whole CTA waits on it. A warp's scheduler
 // is warp % 4: the dequantising warps that would share warp 1's scheduler (every fourth) are left idle, or that
 // lane gets an issue slot every twenty-odd cycles and a K step takes 0.58 us instead of 0.3.
-constexpr int NDW_ACTIVE = NDW - NDW / 4;       // 12 of 16
+__host__ __device__ constexpr int skipped_below(int w) { return w < 9 ? 0 : (w - 9) / 4 + 1; }  // warps 9, 13, 17, ... below warp w
+constexpr int NDW_ACTIVE = NDW - skipped_below(6 + NDW);                      // the launched warps 6 .. 5 + NDW, less those
 constexpr int NDWG = NDW_ACTIVE / NG;           // warps per group = arrivals per stage
-static_assert(NDW % 4 == 0 && NDW_ACTIVE % NG == 0, "whole groups");
+static_assert(NDW_ACTIVE % NG == 0, "whole groups");
 constexpr int GEMM_THREADS_Q8 = 192 + 32 * NDW;
 
 // Q8_0 weights: what a dequantising warp keeps in flight from DRAM, in shared memory (asynchronous 16-byte
 // copies, waited for in order): Q8_UNITS_AHEAD units of 512 bytes of codes + 128 bytes of scales per warp.
-constexpr uint32_t Q8_UNIT_STAGING = 512 + 128, Q8_UNITS_AHEAD = 6;
+constexpr uint32_t Q8_UNIT_STAGING = 512 + 128, Q8_UNITS_AHEAD = NDW_ACTIVE >= 16 ? 4 : 6;
 constexpr uint32_t Q8_STAGING_BYTES = NDW_ACTIVE * Q8_UNITS_AHEAD * Q8_UNIT_STAGING;  // 45 KB
 
 template <int BN, bool Q8 = false> struct Cfg {
@@ -266,7 +267,7 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
     // ------------------------------------------- W tile: Q8_0 -> fp16 in shared memory
     // BN rows x 64 columns = (BN / 16) row tiles x 2 blocks: units of 512 bytes of codes, dealt round robin to
     // the dequantising warps. The scales of a row tile and 4-block group are 8 x 16 bytes: row g's four blocks, then row g + 8's.
-    const uint32_t dw = (warp - 6) - (warp - 5) / 4, g = lane >> 2, t = lane & 3;  // index among the active dequantising warps
+    const uint32_t dw = (warp - 6) - (uint32_t)skipped_below((int)warp), g = lane >> 2, t = lane & 3;  // index among the active dequantising warps
     const uint32_t grp = dw % NG, wi = dw / NG;  // this warp's group (its K steps: grp, grp + NG, ...) and place in it
     const uint32_t tiles16 = (p.N + 15) / 16, groups = ((p.K + 31) / 32 + 3) / 4;
     constexpr uint32_t UNITS = (BN / 16) * 2, UPQ = (UNITS + NDWG - 1) / NDWG;  // units per stage, and of those at most this warp's
