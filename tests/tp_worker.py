@@ -44,8 +44,14 @@ def run_case(cfg, dist, rank, world, vk, vtp, synth_tokens):
     ids2, _, dec_ms = m.generate(prompt, n_gen)  # a second job reuses the exchange buffers
     # one more decode step through the per-token call: every rank returns its logits slice
     logits = m(np.array([ids[-1]], np.uint32), P + n_gen - 1)
+    # a several-token call on the sharded model (the reference's Model::operator() with a prompt): every rank's
+    # slice of the last token's logits, against the twin fed the same tokens with its last one in a call of its own
+    multi = None
+    if many:
+        k = P - 7
+        multi = m(prompt[:k], 0)
     gathered = [None] * world
-    dist.all_gather_object(gathered, (ids.tolist(), ids2.tolist(), logits))
+    dist.all_gather_object(gathered, (ids.tolist(), ids2.tolist(), logits, multi))
     res = None
     if rank == 0:
         one = vk.Model(dev, cfg["dim"], cfg["heads"], cfg["ffn"], cfg["vocab"], cfg["layers"], cfg["maxlen"])
@@ -68,6 +74,12 @@ def run_case(cfg, dist, rank, world, vk, vtp, synth_tokens):
         one2_logits = None
         if ids.tolist() == want:
             one2_logits = one(np.array([want[-1]], np.uint32), P + n_gen - 1)
+        multi_err = None
+        if many:
+            k = P - 7
+            one(prompt[:k - 1], 0)
+            want_multi = one(prompt[k - 1:k], k - 1)
+            multi_err = float(np.abs(np.concatenate([g[3] for g in gathered]) - want_multi).max())
         full = np.concatenate([g[2] for g in gathered])
         same_ranks = all(g[0] == gathered[0][0] and g[1] == gathered[0][0] for g in gathered)
         bad = [i for i in range(n_gen) if ids[i] != want[i]]
@@ -79,7 +91,8 @@ def run_case(cfg, dist, rank, world, vk, vtp, synth_tokens):
         res["ok"] = bool(same_ranks and follows and (bad or err <= 5e-2) and (not bad or bad[0] >= 2))
         if many:  # the pass really ran: a few kernels per block instead of one launch per prompt token
             res["launches"] = launches
-            res["ok"] = bool(res["ok"] and launches < P)
+            res["multi_token_call_logits_max_abs"] = multi_err
+            res["ok"] = bool(res["ok"] and launches < P and multi_err <= 5e-2)
         one.close()
     dist.barrier()
     m.close()

@@ -1013,10 +1013,44 @@ int vkl_model_forward(vkl_model *m, const uint32_t *toks, size_t n, size_t offse
   if (n == 0) return fail(VKL_INVALID_ARGUMENT, "model_forward: no tokens");
   if (n > m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_forward: %zu tokens exceed the context length %u", n, m->cfg.maxlen);
   if (offset + n > (size_t)2 * m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_forward: position %zu is beyond the RoPE table (2*maxlen)", offset + n);
-  if (n > 1 && m->cfg.tp_size > 1) return fail(VKL_UNIMPLEMENTED, "model_forward: multi-token calls are not built for tensor-parallel models (vkl_model_generate prefills token by token)");
   VKL_CUDA(cudaSetDevice(m->dev->ordinal));
   VKL_OKAY(ensure_rows(m, (uint32_t)n));
-  if (n == 1) VKL_OKAY(prepare_decode(m));
+  if (n == 1 || m->cfg.tp_size > 1) VKL_OKAY(prepare_decode(m));
+  if (n > 1 && m->cfg.tp_size > 1) {
+    // Sharded model, several tokens: all but the last fill the caches (many-token passes where they are long
+    // enough for the tensor-core path, else token by token through the decode kernel, which feeds itself the
+    // next id), the last goes through the decode kernel and leaves this rank's slice of its logits. The last
+    // block's query is rotated at its own position here, not at the call's first (the single-GPU form keeps the
+    // reference's quirk, this one does not).
+    if (!m->mega_ready) return fail(VKL_UNIMPLEMENTED, "model_forward: tensor-parallel models need the persistent decode kernel");
+    if (offset + n > m->cfg.maxlen) return fail(VKL_OUT_OF_RANGE, "model_forward: multi-token calls of a tensor-parallel model must end inside the context length");
+    if (m->tp_failed) return decode_step(m);  // reports the state
+    const uint32_t st[2] = {(uint32_t)offset, 0};
+    const uint32_t nf = (uint32_t)(offset + n);
+    VKL_CUDA(cudaMemcpyAsync(m->state->data(), st, 8, cudaMemcpyHostToDevice, m->stream));
+    VKL_CUDA(cudaMemcpyAsync((uint32_t *)m->state->data() + 5, &nf, 4, cudaMemcpyHostToDevice, m->stream));
+    VKL_CUDA(cudaMemcpyAsync(m->toks->data(), toks, n * 4, cudaMemcpyHostToDevice, m->stream));
+    VKL_CUDA(cudaMemcpyAsync((uint32_t *)m->forced->data() + offset, toks, n * 4, cudaMemcpyHostToDevice, m->stream));
+    size_t done = 0;
+    while (n - 1 - done >= gemm_min_rows(q8(m))) {
+      const uint32_t T = (uint32_t)std::min<size_t>(n - 1 - done, m->tp_pf_rows);
+      if (!use_gemm(m, T)) break;
+      const uint32_t at = (uint32_t)(offset + done);
+      VKL_CUDA(cudaMemcpyAsync(m->state->data(), &at, 4, cudaMemcpyHostToDevice, m->stream));
+      VKL_OKAY(run_tokens(m, T, false, nullptr, true, (uint32_t)done));
+      done += T;
+    }
+    if (done) {
+      const uint32_t at = (uint32_t)(offset + done);
+      VKL_CUDA(cudaMemcpyAsync(m->state->data(), &at, 4, cudaMemcpyHostToDevice, m->stream));
+      VKL_CUDA(cudaMemcpyAsync(m->toks->data(), (const uint32_t *)m->toks->data() + done, 4, cudaMemcpyDeviceToDevice, m->stream));
+    }
+    for (size_t i = done; i < n; ++i) VKL_OKAY(decode_step(m));
+    VKL_CUDA(cudaMemcpyAsync(logits_out, m->logits32->data(), (size_t)m->vocab_l * 4, cudaMemcpyDeviceToHost, m->stream));
+    VKL_CUDA(cudaStreamSynchronize(m->stream));
+    VKL_OKAY(check_gemm(m));
+    return check_mega(m);
+  }
   if (n == 1) {
     // The per-token call of a host-driven loop: one small launch sets the step up, the logits and the decode
     // kernel's error word come back through pinned memory behind one synchronisation.
