@@ -423,9 +423,10 @@ def main():
             first, _, _ = model.generate(prompt, 1)
             tok = np.array([int(first[0])], np.uint32)
         barrier()
+        buf = np.empty(w["vocab"] // tp, np.float32)  # the loop's logits buffer, reused every token
         a = time.time()
         for i in range(w["decode"]):
-            logits = model(tok, w["prompt"] + i)  # this rank's slice of the fp32 logits comes back to the host
+            logits = model(tok, w["prompt"] + i, out=buf)  # this rank's slice of the fp32 logits comes back to the host
             tok[0] = int(np.argmax(logits)) if tp == 1 else model.last_token()
         barrier()
         e2e_t += time.time() - a

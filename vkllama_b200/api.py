@@ -636,10 +636,15 @@ class Model:
     def synth_weights(self, seed, wstd=0.02, nstd=0.01):
         _ck(self.L.vkl_model_synth_weights(self.h, seed, wstd, nstd))
 
-    def __call__(self, toks, offset):
-        """Model::operator()(toks, offset) -> fp32 logits of the last token."""
+    def __call__(self, toks, offset, out=None):
+        """Model::operator()(toks, offset) -> fp32 logits of the last token (into `out` when given: a loop that
+        reuses its buffer spares the allocator a 128 KB mapping per token)."""
         t = np.ascontiguousarray(toks, np.uint32)
-        out = np.empty(self.cfg.vocab // max(1, self.cfg.tp_size), np.float32)
+        n = self.cfg.vocab // max(1, self.cfg.tp_size)
+        if out is None:
+            out = np.empty(n, np.float32)
+        elif out.dtype != np.float32 or out.size != n or not out.flags.c_contiguous:
+            raise ValueError("out must be a contiguous float32 array of %d elements" % n)
         _ck(self.L.vkl_model_forward(self.h, _ptr(t), t.size, offset, _ptr(out)))
         return out
 
