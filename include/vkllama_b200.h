@@ -256,7 +256,12 @@ int vkl_model_set_weight(vkl_model *m, const char *name, int dtype, const void *
  * 1+N(0,nstd) norm weights) without touching the host. */
 int vkl_model_synth_weights(vkl_model *m, uint64_t seed, float wstd, float nstd);
 /* Model::operator()(toks, offset) (llama2.h:683-843): host token ids in, fp32
- * logits of the last token out (vocab floats), synchronous. */
+ * logits of the last token out (vocab floats; a tensor-parallel rank gets its slice),
+ * synchronous. A call with several tokens on a tensor-parallel model fills the caches
+ * in many-token passes and takes the last token through the decode kernel: it must
+ * end inside the context length, and the last block's query is rotated at the
+ * token's own position (the single-device form rotates it at the call's first, as
+ * the reference does after clipping Q). */
 int vkl_model_forward(vkl_model *m, const uint32_t *toks, size_t n, size_t offset,
                       float *logits_out);
 /* llama2_infer's loop (app/llama2_infer.cpp:141-210) with the greedy pick kept
