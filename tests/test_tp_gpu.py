@@ -34,11 +34,15 @@ MANY_13B = dict(GEOM_13B, maxlen=256, seed=11, prompt=97, n_gen=16, many_token_p
 MANY_TOY = dict(dim=512, heads=8, ffn=1024, vocab=2000, layers=3, maxlen=256, seed=12, prompt=150, n_gen=12, many_token_prefill=True)
 
 
+# a prompt longer than one many-token pass takes (1024 rows): two passes at different offsets, then the decode kernel
+MANY_LONG = dict(dim=512, heads=8, ffn=1024, vocab=2000, layers=2, maxlen=2048, seed=13, prompt=1100, n_gen=8, many_token_prefill=True)
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_tp_matches_single_gpu(world):
     if NGPU < world:
         pytest.skip("needs %d GPUs" % world)
-    cases = [c for c in (TOY_4, TOY_8, GEOM_13B, MANY_13B, MANY_TOY) if c["heads"] % world == 0]
+    cases = [c for c in (TOY_4, TOY_8, GEOM_13B, MANY_13B, MANY_TOY, MANY_LONG) if c["heads"] % world == 0]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % world, "--master-addr", "127.0.0.1",
            "--master-port", str(29610 + world), os.path.join(ROOT, "tests", "tp_worker.py"), json.dumps(cases)]
