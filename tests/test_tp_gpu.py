@@ -34,6 +34,8 @@ MANY_13B = dict(GEOM_13B, maxlen=256, seed=11, prompt=97, n_gen=16, many_token_p
 MANY_TOY = dict(dim=512, heads=8, ffn=1024, vocab=2000, layers=3, maxlen=256, seed=12, prompt=150, n_gen=12, many_token_prefill=True)
 
 
+# the all-reduce as an op of its own (the switch VKLLAMA_TP_ALLREDUCE=separate) must keep giving the same ids
+TOY_4_SEPARATE = dict(TOY_4, seed=14, allreduce="separate")
 # a prompt longer than one many-token pass takes (1024 rows): two passes at different offsets, then the decode kernel
 MANY_LONG = dict(dim=512, heads=8, ffn=1024, vocab=2000, layers=2, maxlen=2048, seed=13, prompt=1100, n_gen=8, many_token_prefill=True)
 
@@ -42,7 +44,7 @@ MANY_LONG = dict(dim=512, heads=8, ffn=1024, vocab=2000, layers=2, maxlen=2048, 
 def test_tp_matches_single_gpu(world):
     if NGPU < world:
         pytest.skip("needs %d GPUs" % world)
-    cases = [c for c in (TOY_4, TOY_8, GEOM_13B, MANY_13B, MANY_TOY, MANY_LONG) if c["heads"] % world == 0]
+    cases = [c for c in (TOY_4, TOY_4_SEPARATE, TOY_8, GEOM_13B, MANY_13B, MANY_TOY, MANY_LONG) if c["heads"] % world == 0]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=%d" % world, "--master-addr", "127.0.0.1",
            "--master-port", str(29610 + world), os.path.join(ROOT, "tests", "tp_worker.py"), json.dumps(cases)]

@@ -34,6 +34,12 @@ def run_case(cfg, dist, rank, world, vk, vtp, synth_tokens):
     # "many_token_prefill": all but the last prompt token go through the sharded many-token pass (tensor-core
     # GEMMs, partial sums of the K-split projections summed over the ranks); the twin then prefills the same way
     many = cfg.pop("many_token_prefill", False)
+    # "allreduce": "separate" keeps the all-reduce as an op of its own behind the K-split projections (the decode
+    # plan reads the switch when it is built, at the first one-token step)
+    if cfg.pop("allreduce", "in place") == "separate":
+        os.environ["VKLLAMA_TP_ALLREDUCE"] = "separate"
+    else:
+        os.environ.pop("VKLLAMA_TP_ALLREDUCE", None)
     if many:
         os.environ.pop("VKLLAMA_PREFILL", None)
     else:
