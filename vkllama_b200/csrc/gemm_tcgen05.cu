@@ -179,12 +179,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 // One Q8_0 unit (16 rows x 32 columns, 512 bytes of codes) -> fp16 values q * d in the swizzled W tile.
-// Lane (g, t) holds 8 codes of row g and 8 codes of row g + 8 at columns 8 t .. 8 t + 7 (common.cuh).
-__device__ __forceinline__ void dequant_unit(unsigned char *wtile, uint32_t row0, uint32_t chunk0, uint4 w, uint32_t d_lo, uint32_t d_hi, uint32_t lane) {
-  const uint32_t g = lane >> 2, t = lane & 3;
+// Lane (g, t) holds 8 codes of row g and 8 codes of row g + 8 at columns 8 t .. 8 t + 7 (common.cuh). 128-byte
+// swizzle of a K-major tile with 128-byte rows: 16-byte chunk c of row r sits at chunk c ^ (r % 8); the two store
+// offsets depend on the warp's unit, not on the K step, and are worked out beforehand.
+__device__ __forceinline__ void dequant_unit_at(unsigned char *wtile, uint32_t off_a, uint32_t off_b, uint4 w, uint32_t d_lo, uint32_t d_hi) {
   const __half2 dl = __half2half2(__ushort_as_half((unsigned short)d_lo)), dh = __half2half2(__ushort_as_half((unsigned short)d_hi));
   uint32_t a[4], b[4];
-  // word = codes [c0, c2, c1, c3]: pair (c0, c1) is "low", (c2, c3) "high" (codes_to_h2)
   a[0] = codes_to_h2(w.x, false); a[1] = codes_to_h2(w.x, true); a[2] = codes_to_h2(w.y, false); a[3] = codes_to_h2(w.y, true);
   b[0] = codes_to_h2(w.z, false); b[1] = codes_to_h2(w.z, true); b[2] = codes_to_h2(w.w, false); b[3] = codes_to_h2(w.w, true);
 #pragma unroll
@@ -193,10 +193,8 @@ __device__ __forceinline__ void dequant_unit(unsigned char *wtile, uint32_t row0
     a[i] = *reinterpret_cast<uint32_t *>(&x);
     b[i] = *reinterpret_cast<uint32_t *>(&y);
   }
-  // 128-byte swizzle of a K-major tile with 128-byte rows: 16-byte chunk c of row r sits at chunk c ^ (r % 8)
-  const uint32_t ra = row0 + g, rb = row0 + g + 8, c = chunk0 + t;
-  *reinterpret_cast<uint4 *>(wtile + ra * 128 + ((c ^ (ra & 7)) << 4)) = make_uint4(a[0], a[1], a[2], a[3]);
-  *reinterpret_cast<uint4 *>(wtile + rb * 128 + ((c ^ (rb & 7)) << 4)) = make_uint4(b[0], b[1], b[2], b[3]);
+  *reinterpret_cast<uint4 *>(wtile + off_a) = make_uint4(a[0], a[1], a[2], a[3]);
+  *reinterpret_cast<uint4 *>(wtile + off_b) = make_uint4(b[0], b[1], b[2], b[3]);
 }
 
 template <int BN, bool Q8>
@@ -278,24 +276,31 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
     // (cp.async groups): loads into registers would share the warp's few scoreboards, and the wait for the oldest
     // would also wait for the youngest.
     unsigned char *stg = stages + (size_t)C::STAGES * C::STAGE_BYTES + (size_t)dw * Q8_UNITS_AHEAD * Q8_UNIT_STAGING;
-    auto unit_of = [&](uint32_t kb, uint32_t j, uint32_t &tile, uint32_t &b) {
-      const uint32_t u = wi + NDWG * j;
-      tile = n0 / 16 + (u >> 1);  // row tile of the matrix
-      b = kb * 2 + (u & 1);       // block of the row
-      return u < UNITS && kb < nkb && tile < tiles16;
-    };
+    // What does not change from K step to K step is worked out once per unit of this warp: where its codes and its
+    // scales start in the planes (they advance by 1024 bytes per K step and by 128 bytes per two K steps), where
+    // its two stores go in the W tile (128-byte swizzle), which half of the block pair it is.
+    const unsigned char *cbase[UPQ], *sbase[UPQ];
+    uint32_t off_a[UPQ], off_b[UPQ], bl[UPQ];
+    bool valid[UPQ];
+#pragma unroll
+    for (uint32_t j = 0; j < UPQ; ++j) {
+      const uint32_t u = wi + NDWG * j, tile = n0 / 16 + (u >> 1);
+      bl[j] = u & 1u;
+      valid[j] = u < UNITS && tile < tiles16;
+      cbase[j] = p.w_codes + (((size_t)tile * groups * 4 + bl[j]) * 32 + lane) * 16;
+      sbase[j] = p.w_scales + ((size_t)tile * groups * 8 + g) * 16;
+      const uint32_t ra = (u >> 1) * 16 + g, rb = ra + 8, c = bl[j] * 4 + t;
+      off_a[j] = ra * 128 + ((c ^ (ra & 7)) << 4);
+      off_b[j] = rb * 128 + ((c ^ (rb & 7)) << 4);
+    }
     auto request = [&](uint32_t kb, uint32_t slot) {
 #pragma unroll
       for (uint32_t j = 0; j < UPQ; ++j) {
-        uint32_t tile, b;
-        if (unit_of(kb, j, tile, b)) {
+        if (valid[j] && kb < nkb) {
           const uint32_t dst = sa(stg + (slot * UPQ + j) * Q8_UNIT_STAGING);
-          const unsigned char *src = p.w_codes + (((size_t)tile * groups * 4 + b) * 32 + lane) * 16;
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + lane * 16), "l"(src) : "memory");
-          if (t == 0) {  // the 4-block group's scales of rows g and g + 8: 16 bytes
-            const unsigned char *sc = p.w_scales + (((size_t)tile * groups + (b >> 2)) * 8 + g) * 16;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512 + g * 16), "l"(sc) : "memory");
-          }
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + lane * 16), "l"(cbase[j] + (size_t)kb * 1024) : "memory");
+          if (t == 0)  // the 4-block group's scales of rows g and g + 8: 16 bytes
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512 + g * 16), "l"(sbase[j] + (size_t)(kb >> 1) * 128) : "memory");
         }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");  // one group per stage, also when it is empty
@@ -331,20 +336,18 @@ __global__ void __launch_bounds__(Q8 ? GEMM_THREADS_Q8 : GEMM_THREADS, 1)
         unsigned char *wt = stages + (size_t)s * C::STAGE_BYTES + A_TILE_BYTES;
 #pragma unroll
         for (uint32_t j = 0; j < UPQ; ++j) {
-          const uint32_t u = wi + NDWG * j;
-          if (u >= UNITS) continue;
-          uint32_t tile, b;
+          if (wi + NDWG * j >= UNITS) continue;
           uint4 w = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);  // code 0 (stored biased by 128): rows beyond the matrix
           uint32_t lo = 0, hi = 0;
-          if (unit_of(kb, j, tile, b)) {
+          if (valid[j]) {
             const unsigned char *src = stg + (i * UPQ + j) * Q8_UNIT_STAGING;
             w = *reinterpret_cast<const uint4 *>(src + lane * 16);
-            const uint4 d = *reinterpret_cast<const uint4 *>(src + 512 + g * 16);  // x, y: row g's four blocks; z, w: row g + 8's
-            const uint32_t sh = (b & 1) * 16;
-            lo = ((b & 2 ? d.y : d.x) >> sh) & 0xffffu;
-            hi = ((b & 2 ? d.w : d.z) >> sh) & 0xffffu;
+            // row g's four block scales, then row g + 8's: this unit's block of the four is ((kb & 1) << 1) | bl
+            const unsigned short *d = reinterpret_cast<const unsigned short *>(src + 512 + g * 16) + (((kb & 1u) << 1) | bl[j]);
+            lo = d[0];
+            hi = d[4];
           }
-          dequant_unit(wt, (u >> 1) * 16, (u & 1) * 4, w, lo, hi, lane);
+          dequant_unit_at(wt, off_a[j], off_b[j], w, lo, hi);
         }
         // the tensor core reads shared memory through the async proxy: order this warp's stores before its arrival.
         // (The fence waits for the thread's memory operations in flight: the refill below comes after it.)
