@@ -24,7 +24,10 @@ namespace {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kDepth = 2;  // 4-block groups kept in flight per warp
+#ifndef VKL_MV_DEPTH
+#define VKL_MV_DEPTH 2
+#endif
+constexpr int kDepth = VKL_MV_DEPTH;  // 4-block groups kept in flight per warp
 
 template <bool Q8, int NW>
 struct Stage {
